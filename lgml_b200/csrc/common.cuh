@@ -1,0 +1,69 @@
+// Shared helpers of the sm_100a kernels.  Every launcher is an extern "C" function that
+// takes raw device pointers and a stream, launches, and returns 0 or an error code whose
+// text lgml_last_error() of the same library gives.  Nothing here allocates.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define LGML_API extern "C" __attribute__((visibility("default")))
+
+// One error string per library (each .cu file is built into its own shared object).
+static thread_local char lgml_err_buf[512];
+
+#define LGML_DEFINE_LAST_ERROR(prefix) \
+    LGML_API const char *prefix##_last_error(void) { return lgml_err_buf; }
+
+#define LGML_FAIL(...)                                           \
+    do {                                                         \
+        snprintf(lgml_err_buf, sizeof(lgml_err_buf), __VA_ARGS__); \
+        return -1;                                               \
+    } while (0)
+
+#define LGML_REQUIRE(cond, ...) \
+    do {                        \
+        if (!(cond)) LGML_FAIL(__VA_ARGS__); \
+    } while (0)
+
+static inline int lgml_launch_status(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(lgml_err_buf, sizeof(lgml_err_buf), "%s: %s", what, cudaGetErrorString(e));
+        return (int)e;
+    }
+    return 0;
+}
+
+// Element types: 0 = float32, 1 = bfloat16.
+enum { LGML_F32 = 0, LGML_BF16 = 1 };
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads in a fixed order (warp trees, then the warps'
+// partial sums by index), so that a row's result does not depend on what else is launched.
+__device__ __forceinline__ float block_sum(float v, float *smem /* >= 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += smem[w];
+    return total;
+}

@@ -1,0 +1,192 @@
+// Embedding gather, RMSNorm (with the residual add and a row gather fused in), SwiGLU
+// activation, bias add and the seeded normal fill.  The residual stream is float32 in
+// every mode; norms and the activation compute in float32.
+#include "common.cuh"
+
+LGML_DEFINE_LAST_ERROR(lgml_elementwise)
+
+// ---------------------------------------------------------------------------------------
+// x[t, :] = table[ids[t], :]            (lua/lgml/transformer.lua:2303: get_rows, no scale)
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_rows_kernel(const TW *__restrict__ table, const int *__restrict__ ids,
+                                  float *__restrict__ out, int width, int vocab, int *__restrict__ status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    if (id < 0 || id >= vocab) {  // the host checks ids first; never read out of the table
+        if (threadIdx.x == 0) atomicExch(status, 1);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = 0.f;
+        return;
+    }
+    const TW *row = table + (size_t)id * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = to_f32(row[i]);
+}
+
+LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids, float *out, int n_tokens,
+                             int width, int vocab, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes");
+    if (n_tokens == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == LGML_F32)
+        embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>((const float *)table, ids, out, width, vocab, status);
+    else if (table_dtype == LGML_BF16)
+        embed_rows_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16 *)table, ids, out, width, vocab, status);
+    else
+        LGML_FAIL("embed_rows: unknown table type %d", table_dtype);
+    return lgml_launch_status("embed_rows");
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm: y = x / sqrt(mean(x^2) + eps) * w   (src/lgml.c:1626-1633 + the multiply at
+// lua/lgml/transformer.lua:1760).  Options, all in one pass over the row:
+//   delta != null : x[row] += delta[row] first, and the sum is written back (the residual add)
+//   rows  != null : output row r reads x[rows[r]] (the logits' row selection, :2349-2350);
+//                   delta is then added for the gathered rows only and x is not written.
+// One block per output row; the mean square is summed in a fixed order.
+// ---------------------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta, const float *__restrict__ weight,
+                               const int *__restrict__ rows, TO *__restrict__ out, int width, float eps) {
+    __shared__ float red[32];
+    extern __shared__ float cache[];  // the row, so that x is read once
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float *xr = x + src * width;
+    const TD *dr = delta ? delta + src * width : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = xr[i];
+        if (dr) {
+            v += to_f32(dr[i]);
+            if (!rows) xr[i] = v;
+        }
+        cache[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        out[(size_t)r * width + i] = from_f32<TO>(cache[i] * inv * weight[i]);
+}
+
+template <typename TD>
+static int rmsnorm_dispatch(float *x, const TD *delta, const float *weight, const int *rows, void *out, int out_dtype,
+                            int n_rows, int width, float eps, cudaStream_t stream) {
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    const size_t smem = (size_t)width * sizeof(float);
+    if (out_dtype == LGML_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<TD, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        rmsnorm_kernel<TD, float><<<n_rows, threads, smem, stream>>>(x, delta, weight, rows, (float *)out, width, eps);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<TD, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        rmsnorm_kernel<TD, __nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, delta, weight, rows, (__nv_bfloat16 *)out, width, eps);
+    }
+    return lgml_launch_status("rmsnorm");
+}
+
+LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, const float *weight, const int *rows, void *out,
+                          int out_dtype, int n_rows, int width, float eps, cudaStream_t stream) {
+    LGML_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes");
+    LGML_REQUIRE((size_t)width * sizeof(float) <= 200 * 1024, "rmsnorm: width %d is over the %d a row buffer holds", width, 200 * 1024 / 4);
+    LGML_REQUIRE(out_dtype == LGML_F32 || out_dtype == LGML_BF16, "rmsnorm: unknown output type %d", out_dtype);
+    if (n_rows == 0) return 0;
+    if (delta == nullptr || delta_dtype == LGML_F32)
+        return rmsnorm_dispatch<float>(x, (const float *)delta, weight, rows, out, out_dtype, n_rows, width, eps, stream);
+    if (delta_dtype == LGML_BF16)
+        return rmsnorm_dispatch<__nv_bfloat16>(x, (const __nv_bfloat16 *)delta, weight, rows, out, out_dtype, n_rows, width, eps, stream);
+    LGML_FAIL("rmsnorm: unknown delta type %d", delta_dtype);
+}
+
+// ---------------------------------------------------------------------------------------
+// act[t, f] = silu(gate[t, f]) * up[t, f], with gate = gu[t, 0:F] and up = gu[t, F:2F]
+// (lua/lgml/transformer.lua:2047-2048; silu(a) = a * sigmoid(a), src/lgml.c:1476-1482)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ act, int n_tokens, int width) {
+    const size_t total = (size_t)n_tokens * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width, f = i - t * width;
+        const float g = to_f32(gu[t * 2 * width + f]);
+        const float u = to_f32(gu[t * 2 * width + width + f]);
+        const float s = g / (1.0f + expf(-g));
+        act[i] = from_f32<T>(s * u);
+    }
+}
+
+LGML_API int lgml_silu_mul(const void *gu, void *act, int dtype, int n_tokens, int width, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && width > 0, "silu_mul: bad sizes");
+    if (n_tokens == 0) return 0;
+    const size_t total = (size_t)n_tokens * width;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == LGML_F32)
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float *)gu, (float *)act, n_tokens, width);
+    else if (dtype == LGML_BF16)
+        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)act, n_tokens, width);
+    else
+        LGML_FAIL("silu_mul: unknown type %d", dtype);
+    return lgml_launch_status("silu_mul");
+}
+
+// ---------------------------------------------------------------------------------------
+// x[t, :] += delta[t, :]   (the residual sum in float32 when no norm follows)
+// ---------------------------------------------------------------------------------------
+template <typename TD>
+__global__ void residual_add_kernel(float *__restrict__ x, const TD *__restrict__ delta, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] += to_f32(delta[i]);
+}
+
+LGML_API int lgml_residual_add(float *x, const void *delta, int delta_dtype, long long total, cudaStream_t stream) {
+    LGML_REQUIRE(total >= 0, "residual_add: bad size");
+    if (total == 0) return 0;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (delta_dtype == LGML_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float *)delta, (size_t)total);
+    else if (delta_dtype == LGML_BF16)
+        residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16 *)delta, (size_t)total);
+    else
+        LGML_FAIL("residual_add: unknown type %d", delta_dtype);
+    return lgml_launch_status("residual_add");
+}
+
+// ---------------------------------------------------------------------------------------
+// Seeded normal fill: value i of a tensor = mean + sd * N(0,1) from a counter-based stream
+// (splitmix64 of seed and index, then Box-Muller; mischief/lgml fills its test tensors the
+// same way, src/lgml.c:3064-3079, :3133-3137).  Used to make full-size random models on
+// the device without a host copy.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
+    z += 0x9e3779b97f4a7c15ULL;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+    return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T *__restrict__ out, size_t n, float mean, float sd, uint64_t seed) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const uint64_t h = splitmix64(seed ^ splitmix64(i));
+        const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
+        const float u2 = (float)(uint32_t)((h >> 8) & 0xffffff) * (1.0f / 16777216.0f);
+        const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+        out[i] = from_f32<T>(mean + sd * z);
+    }
+}
+
+LGML_API int lgml_fill_normal(void *out, int dtype, long long n, float mean, float sd, unsigned long long seed, cudaStream_t stream) {
+    LGML_REQUIRE(n >= 0, "fill_normal: bad size");
+    if (n == 0) return 0;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
+    if (dtype == LGML_F32)
+        fill_normal_kernel<float><<<blocks, threads, 0, stream>>>((float *)out, (size_t)n, mean, sd, seed);
+    else if (dtype == LGML_BF16)
+        fill_normal_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16 *)out, (size_t)n, mean, sd, seed);
+    else
+        LGML_FAIL("fill_normal: unknown type %d", dtype);
+    return lgml_launch_status("fill_normal");
+}

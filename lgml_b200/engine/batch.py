@@ -1,0 +1,119 @@
+"""The description of one step's batch, as the kernels read it.
+
+A step holds, for each request in it, that request's next tokens: a prompt, a
+portion of one, or a single decoded token.  All tokens of the step form one
+ragged batch (mischief/lgml: ``M:batch_inputs``, ``lua/lgml/transformer.lua:2502-2551``):
+
+* ``token_ids[N]``, ``positions[N]`` (= tokens already cached + index in the portion,
+  ``:2441-2447``), ``seq_of_token[N]`` (the row of the request in this batch),
+* ``seq_start[S+1]`` (first token of each request), ``seq_pos0[S]``, ``slots[S]``,
+* one block table ``[S, width]`` per cache group, -1 where a request has no page,
+* ``logit_rows[R]``: the token rows whose logits are wanted (``:2540-2545``).
+
+Everything goes to the device in one copy from pinned memory; no dense mask is
+built (the reference fills an (n, window) mask on the host each pass,
+``src/lgml.c:2993-3010``; here the attention kernel walks the block table).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class CacheView:
+    """What one layer call sees of the cache."""
+
+    k: Optional[torch.Tensor] = None            # [pages, Hkv, page, D]
+    v: Optional[torch.Tensor] = None
+    block_table: Optional[torch.Tensor] = None  # int32 [S, width]
+    writable: bool = True
+    state: Optional[torch.Tensor] = None        # [max_slots, ...] for a fixed-state layer
+    page_size: int = 0
+
+
+class StepBatch:
+    def __init__(self, cache_manager, requests: Sequence, tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
+                 device, pinned: Optional[torch.Tensor] = None):
+        cm = cache_manager
+        self.cache_manager = cm
+        self.requests = list(requests)
+        S = len(self.requests)
+        lens = [len(t) for t in tokens]
+        N = sum(lens)
+        self.n_tokens, self.n_seqs = N, S
+        self.seq_lens = lens
+        self.pos0 = [r.n_tokens for r in self.requests]
+        self.kv_lens = [p + n for p, n in zip(self.pos0, lens)]
+        self.max_q_len = max(lens) if lens else 0
+        self.max_kv_len = max(self.kv_lens) if lens else 0
+
+        flat: List[int] = []
+        for t in tokens:
+            flat.extend(int(v) for v in t)
+        positions: List[int] = []
+        seq_of: List[int] = []
+        starts = [0]
+        for s, (p0, n) in enumerate(zip(self.pos0, lens)):
+            positions.extend(range(p0, p0 + n))
+            seq_of.extend([s] * n)
+            starts.append(starts[-1] + n)
+        rows: List[int] = []
+        self.rows_of_seq: List[List[int]] = []
+        for s, w in enumerate(want):
+            mine = []
+            for i in w:
+                if not 0 <= i < lens[s]:
+                    raise IndexError(f"wanted place {i} is outside the {lens[s]} tokens request {self.requests[s].id!r} brings")
+                mine.append(len(rows))
+                rows.append(starts[s] + int(i))
+            self.rows_of_seq.append(mine)
+        self.n_rows = len(rows)
+
+        tables = [cm.block_table_rows(self.requests, g) for g in range(len(cm.groups))]
+        self.table_width = [len(t[0]) if t else 1 for t in tables]
+        parts = [flat, positions, seq_of, starts, self.pos0, [r.slot for r in self.requests], self.kv_lens, rows or [0]]
+        for t in tables:
+            parts.append([p for row in t for p in row])
+        total = sum(len(p) for p in parts)
+        host = torch.tensor([v for p in parts for v in p], dtype=torch.int32)
+        if pinned is not None and pinned.numel() >= total:
+            pinned[:total].copy_(host)
+            host = pinned[:total]
+        dev = torch.empty(total, dtype=torch.int32, device=device)
+        dev.copy_(host, non_blocking=True)
+        self.h2d_bytes = total * 4
+        self._dev = dev
+        off = 0
+
+        def take(n):
+            nonlocal off
+            v = dev[off:off + n]
+            off += n
+            return v
+
+        self.token_ids = take(N)
+        self.positions = take(N)
+        self.seq_of_token = take(N)
+        self.seq_start = take(S + 1)
+        self.seq_pos0 = take(S)
+        self.slots = take(S)
+        self.seq_kv_len = take(S)
+        r = take(max(len(rows), 1))
+        self.logit_rows = r[: len(rows)]
+        self.block_tables = [take(S * w).view(S, w) for w in self.table_width]
+
+    def cache_view(self, owner: int, writable: bool = True) -> CacheView:
+        """The cache of schedule entry ``owner`` as this batch's requests see it."""
+        cm = self.cache_manager
+        g = cm.group_of_layer.get(owner)
+        if g is not None:
+            grp = cm.groups[g]
+            return CacheView(k=grp.k[owner], v=grp.v[owner], block_table=self.block_tables[g], writable=writable,
+                             page_size=cm.page_size)
+        sg = cm.state_group_of_layer.get(owner)
+        if sg is not None:
+            return CacheView(state=cm.state_groups[sg].state[owner], writable=writable)
+        return CacheView(writable=False)

@@ -1,0 +1,157 @@
+"""The Python entry point: load a model, generate.
+
+Option names and meanings follow mischief/lgml's ``engine.new``
+(``lua/lgml/engine.lua:376-467``): ``model`` (a folder with config.json and
+safetensors here), ``n_ctx`` (the size of the cache pool all slots share, and the
+most tokens of one request), ``slots`` (the most requests kept at once, default 4:
+``lua/lgml/kvpool.lua:28``), ``ubatch`` (prompt tokens per request per step,
+default 512), ``max_tokens`` (default reply length: the free context),
+``sampling`` (sampler defaults, a request's values replace them),
+``repeat_stop_tokens``.  ``generate.greedy`` of the reference
+(``lua/lgml/generate.lua:19-34``) is ``Engine.greedy``.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..sampling import Sampler, SamplingParams
+from .runner import ModelRunner
+from .scheduler import REPEAT_STOP, UBATCH, GenRequest, Scheduler
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    try:
+        return _DTYPES[str(name)]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, not '{name}'") from None
+
+
+class Engine:
+    def __init__(self, model=None, *, config=None, random_weights: Optional[int] = None, dtype="bfloat16", n_ctx: Optional[int] = None,
+                 slots: int = 4, ubatch: int = UBATCH, max_batch_tokens: Optional[int] = None, max_tokens: Optional[int] = None,
+                 sampling: Optional[dict] = None, repeat_stop_tokens: int = REPEAT_STOP, device="cuda:0"):
+        dt = parse_dtype(dtype)
+        if model is None and config is None:
+            raise ValueError("give a model folder, or a config with random_weights=seed")
+        if model is not None:
+            from ..config import load_config
+            cfg = load_config(model)
+        else:
+            cfg = config
+        self.config = cfg
+        max_pos = cfg.max_position_embeddings
+        n_ctx = min(n_ctx or max_pos, max_pos)
+        self.n_ctx = n_ctx
+        n_pages = -(-n_ctx // 64)
+        max_batch_tokens = max_batch_tokens or max(ubatch, 2048)
+        kw = dict(n_pages=n_pages, max_slots=slots, max_step_tokens=max_batch_tokens)
+        if model is not None:
+            self.runner = ModelRunner.from_folder(model, dt, device, **kw)
+        else:
+            self.runner = ModelRunner.from_config(cfg, int(random_weights or 0), dt, device, **kw)
+        self.rt = self.runner.rt
+        self.default_max_tokens = max_tokens
+        self.sampling_defaults = dict(sampling or {})
+        self.scheduler = Scheduler(self.runner.cache, max_position=min(max_pos, n_ctx), ubatch=ubatch,
+                                   max_batch_tokens=max_batch_tokens, repeat_stop_tokens=repeat_stop_tokens)
+        self.eos_ids = list(getattr(cfg, "eos_token_ids", []) or [])
+        self._next_id = 0
+        self.timings: Dict[str, float] = {}
+
+    # ---- one scheduler turn -------------------------------------------------------------
+    def _turn(self) -> List[GenRequest]:
+        sch = self.scheduler
+        plan = sch.plan()
+        if not plan:
+            return []
+        entries = [(e.request.cache_req, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan]
+        logits = self.runner.step(entries)
+        sampled: Dict[Hashable, int] = {}
+        rows = [e for e in plan if e.sample]
+        if rows:
+            neutral = all(e.request.params.is_neutral for e in rows)
+            if neutral:
+                temps = torch.tensor([e.request.params.temperature for e in rows], dtype=torch.float32).pin_memory()
+                us = torch.tensor([0.0 if e.request.params.greedy else e.request.sampler.uniform() for e in rows],
+                                  dtype=torch.float64).pin_memory()
+                out = torch.empty(len(rows), dtype=torch.int32, device=logits.device)
+                ops.sample_rows(logits, temps.to(logits.device, non_blocking=True), us.to(logits.device, non_blocking=True), out)
+                toks = out.cpu().tolist()
+            else:
+                host = logits.cpu().numpy()
+                toks = [e.request.sampler.sample(host[i]) for i, e in enumerate(rows)]
+            for e, t in zip(rows, toks):
+                sampled[e.request.id] = int(t)
+        self.rt.check_status()
+        return sch.complete(plan, sampled)
+
+    # ---- public --------------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None, stop: Optional[Sequence[int]] = None,
+                 seed: Optional[int] = None, return_details: bool = False, **sampling):
+        """Token ids in, token ids out.  ``prompts``: lists of token ids.  Sampler options
+        (``temperature``, ``top_k``, ``top_p``, ``min_p``, ``repeat_penalty``,
+        ``frequency_penalty``, ``presence_penalty``, ``repeat_last_n``, ``logit_bias``) and
+        ``seed`` as in the sampler; request i draws from the stream of ``seed + i``.
+        Returns one list of new ids per prompt (with the stop id when one ends it)."""
+        opts = {**self.sampling_defaults, **sampling}
+        stop_ids = list(stop) if stop is not None else self.eos_ids
+        reqs = []
+        t0 = time.perf_counter()
+        for i, p in enumerate(prompts):
+            p = [int(t) for t in p]
+            room = self.scheduler.max_position - len(p)
+            limit = max_tokens if max_tokens is not None else (self.default_max_tokens or room)
+            params = SamplingParams(seed=None if seed is None else seed + i, **opts)
+            req = GenRequest(id=("gen", self._next_id), prompt=p, max_new_tokens=max(min(limit, room), 0), params=params,
+                             stop_ids=stop_ids)
+            self._next_id += 1
+            if req.max_new_tokens == 0:
+                req.finish_reason = "length"
+            else:
+                self.scheduler.add(req)
+            reqs.append(req)
+        while not self.scheduler.idle:
+            self._turn()
+        torch.cuda.synchronize(self.rt.device)
+        self.timings = {"total": time.perf_counter() - t0}
+        if return_details:
+            return reqs
+        return [r.generated for r in reqs]
+
+    def greedy(self, prompt: Sequence[int], n_predict: int, stop: Optional[Sequence[int]] = None):
+        """Greedy decode of one prompt: (new ids, timings {prefill, decode, n_decode}), as
+        ``generate.greedy`` (``lua/lgml/generate.lua:19-34``)."""
+        runner = self.runner
+        req = runner.open(("greedy", self._next_id))
+        self._next_id += 1
+        out: List[int] = []
+        tok = torch.empty(1, dtype=torch.int32, device=self.rt.device)
+        stop = set(stop or ())
+        try:
+            t0 = time.perf_counter()
+            ids = [int(t) for t in prompt]
+            pos = 0
+            while pos < len(ids):          # the prompt in portions of ubatch
+                part = ids[pos:pos + self.scheduler.ubatch]
+                pos += len(part)
+                logits = runner.step([(req, part, [len(part) - 1] if pos == len(ids) else [])])
+            cur = int(ops.argmax_rows(logits, tok).item())
+            t1 = time.perf_counter()
+            out.append(cur)
+            while len(out) < n_predict and cur not in stop:
+                logits = runner.step([(req, [cur], [0])])
+                cur = int(ops.argmax_rows(logits, tok).item())
+                out.append(cur)
+            t2 = time.perf_counter()
+            self.rt.check_status()
+        finally:
+            runner.close(req)
+        return out, {"prefill": t1 - t0, "decode": t2 - t1, "n_decode": len(out) - 1}

@@ -1,0 +1,125 @@
+"""The step function: run one batch of (request, its next tokens) from the cache.
+
+``ModelRunner.step`` is the only way tokens go through the model; generation, the
+scheduler and trace replay all call it.  It runs exactly the tokens it is given, as
+one batch, on the cache that earlier steps left, writes their keys and values,
+advances the requests, and returns float32 logits at the wanted places
+(mischief/lgml: ``M:run_batch``, ``lua/lgml/transformer.lua:2585-2624``: several
+sequences, "one id for a decode step, or a chunk of a prompt", ``:2493-2494``;
+positions advance after the pass, ``:2620-2622``).
+"""
+from __future__ import annotations
+
+from typing import Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheManager, PoolFull, Request
+from ..models import build_model
+from ..weights import load_tensors, random_tensors
+from .batch import StepBatch
+from .runtime import Runtime
+
+
+class StepError(ValueError):
+    """A step the runner refuses before anything is launched."""
+
+
+class ModelRunner:
+    def __init__(self, model, rt: Runtime, n_pages: int, max_slots: int = 4, max_step_tokens: int = 0):
+        self.model = model
+        self.rt = rt
+        self.cache = CacheManager(model.cache_layout(), n_pages=n_pages, max_slots=max_slots, dtype=rt.dtype,
+                                  device=rt.device, max_step_tokens=max_step_tokens)
+        # a ring of pinned staging buffers: a buffer is reused only after its copy has run
+        self._pinned = [[torch.empty(1 << 16, dtype=torch.int32).pin_memory(), None] for _ in range(4)]
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ---- construction ------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder, dtype: torch.dtype, device="cuda:0", **kw) -> "ModelRunner":
+        from ..config import load_config
+
+        cfg = load_config(folder)
+        rt = Runtime(device, dtype)
+        model = build_model(cfg)
+        tensors = load_tensors(folder, model.tensor_specs(), dtype, rt.device)
+        model.bind(tensors, rt)
+        return cls(model, rt, **kw)
+
+    @classmethod
+    def from_config(cls, cfg, seed: int, dtype: torch.dtype, device="cuda:0", std: float = 0.02, on_device: bool = True,
+                    **kw) -> "ModelRunner":
+        """Random weights without a folder: drawn on the device (full-size models) or on
+        the host with the same streams as ``write_random_model``."""
+        from .. import ops
+        from ..weights import MATRIX
+        from ..weights.loader import target_dtype
+        import zlib
+
+        rt = Runtime(device, dtype)
+        model = build_model(cfg)
+        specs = [s for s in model.tensor_specs() if not s.optional]
+        if on_device:
+            tensors = {}
+            for s in specs:
+                t = torch.empty(s.shape, dtype=target_dtype(s.kind, dtype), device=rt.device)
+                ops.fill_normal(t, s.init[0], s.init[1] * std, (seed << 32) ^ zlib.crc32(s.name.encode()))
+                tensors[s.name] = t
+        else:
+            host = random_tensors(specs, seed, std)
+            tensors = {s.name: host[s.name].to(device=rt.device, dtype=target_dtype(s.kind, dtype)) for s in specs}
+        model.bind(tensors, rt)
+        return cls(model, rt, **kw)
+
+    # ---- requests ----------------------------------------------------------------------
+    def open(self, rid: Hashable) -> Request:
+        return self.cache.open(rid)
+
+    def close(self, req: Request) -> None:
+        self.cache.close(req)
+
+    # ---- the step ----------------------------------------------------------------------
+    def validate(self, entries: Sequence[Tuple[Request, Sequence[int], Sequence[int]]]) -> None:
+        seen = set()
+        vocab = self.model.vocab_size
+        max_pos = self.model.max_position
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        for req, tokens, want in entries:
+            if req.closed:
+                raise StepError(f"request {req.id!r} is closed")
+            if id(req) in seen:
+                raise StepError(f"request {req.id!r} appears twice in one step")
+            seen.add(id(req))
+            if len(tokens) == 0:
+                raise StepError(f"request {req.id!r} brings no tokens")
+            for t in tokens:
+                if not 0 <= int(t) < vocab:
+                    raise StepError(f"request {req.id!r}: token id {t} is outside the vocabulary of {vocab}")
+            if max_pos is not None and req.n_tokens + len(tokens) > max_pos:
+                raise StepError(f"request {req.id!r}: context full ({req.n_tokens} + {len(tokens)} tokens > {max_pos} positions)")
+
+    def step(self, entries: Sequence[Tuple[Request, Sequence[int], Sequence[int]]]) -> torch.Tensor:
+        """entries: (request, its next tokens, the places among them whose logits are
+        wanted).  Returns float32 [wanted, vocab] in the order of entries and places."""
+        self.validate(entries)
+        for req, tokens, _ in entries:
+            if not self.cache.reserve(req, len(tokens)):
+                raise PoolFull(f"kv pool full: request {req.id!r} needs pages for {len(tokens)} more tokens, "
+                               f"{self.cache.n_free_pages} of {self.cache.n_pages} pages are free")
+        stage = self._pinned[self.steps % len(self._pinned)]
+        if stage[1] is not None:
+            stage[1].synchronize()
+        batch = StepBatch(self.cache, [e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries],
+                          self.rt.device, stage[0])
+        stage[1] = torch.cuda.Event()
+        stage[1].record()
+        self.last_batch = batch
+        logits = self.model.forward(self.rt, batch)
+        for req, tokens, _ in entries:
+            self.cache.commit(req, len(tokens))
+        self.steps += 1
+        self.tokens_run += batch.n_tokens
+        return logits

@@ -1,0 +1,65 @@
+"""The runtime a model runs on: device, compute type, and the choice of kernel per operation.
+
+Two modes.  ``float32``: every tensor and every sum is 32-bit, matrix products by
+the fixed-order FMA kernel, attention by the general kernel; nothing uses tensor cores
+or a reduced-precision matrix mode.  ``bfloat16``: weights, activations between
+kernels and the cache are bfloat16; the residual stream, norms, softmax, rotation
+angles and logits stay float32.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+
+_STATUS_TEXT = {
+    1: "a token id was outside the vocabulary",
+    2: "a key/value write had no page in the block table",
+    3: "attention met a position without a page in the block table",
+}
+
+
+class DeviceFault(RuntimeError):
+    """A kernel flagged an input it refused to use (it skipped the access)."""
+
+
+class Runtime:
+    def __init__(self, device="cuda:0", dtype: torch.dtype = torch.bfloat16, gemm: str = "auto"):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError(f"the engine runs on a CUDA device only, not on '{device}'")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available; the engine has no CPU path")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute type must be bfloat16 or float32, not {dtype}")
+        self.dtype = dtype
+        torch.cuda.set_device(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.gemm_backend = gemm
+        self.attention_backend = "auto"
+
+    # ---- matrix products ---------------------------------------------------------------
+    def linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """y = x . w^T (+ bias); x [M,K], w [N,K] in the compute type, y in ``out_dtype``."""
+        out_dtype = out_dtype or self.dtype
+        if self.dtype == torch.float32:
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+            return ops.gemm_f32(x, w, out, bias)
+        return ops.gemm_bf16(x, w, out_dtype, bias, backend=self.gemm_backend)
+
+    # ---- attention ---------------------------------------------------------------------
+    def attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int) -> torch.Tensor:
+        if self.dtype == torch.float32 or self.attention_backend == "ref":
+            return ops.paged_attention_ref(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v,
+                                           out, n_heads, scale, window, self.status)
+        return ops.paged_attention(q, batch, cache, out, n_heads, scale, window, self.status)
+
+    # ---- faults ------------------------------------------------------------------------
+    def check_status(self) -> None:
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise DeviceFault(f"kernel status {code}: {_STATUS_TEXT.get(code, 'unknown')}")

@@ -1,0 +1,306 @@
+"""Python face of the sm_100a kernels: argument checks, then the launch.
+
+Every function takes torch tensors that live on the CUDA device, checks types,
+shapes and contiguity on the host, and launches on torch's current stream, so
+the launches can be captured into a CUDA graph with everything else.  There is
+no CPU implementation and no library fallback behind these calls; a tensor on
+another device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import csrc
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or the launch failed."""
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dt}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, what: str, dtype=None, ndim=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} must be on the CUDA device (it is on {t.device}); there is no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, not {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{what} must have {ndim} dimensions, not {t.dim()}")
+
+
+def _rows_contiguous(t: torch.Tensor, what: str) -> int:
+    """Row stride of a 2-D tensor whose rows are dense."""
+    if t.dim() != 2 or t.stride(1) != 1 or t.stride(0) < t.shape[1]:
+        raise KernelError(f"{what} must be 2-D with dense rows (shape {tuple(t.shape)}, strides {t.stride()})")
+    return t.stride(0)
+
+
+_prototyped = set()
+
+
+def _fn(lib_name: str, fn_name: str, argtypes):
+    lib = csrc.load(lib_name)
+    fn = getattr(lib, fn_name)
+    key = (lib_name, fn_name)
+    if key not in _prototyped:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        err = getattr(lib, f"lgml_{lib_name}_last_error")
+        err.restype = ctypes.c_char_p
+        _prototyped.add(key)
+    return fn
+
+
+def _check(lib_name: str, rc: int, what: str) -> None:
+    if rc != 0:
+        err = getattr(csrc.load(lib_name), f"lgml_{lib_name}_last_error")
+        err.restype = ctypes.c_char_p
+        raise KernelError(f"{what}: {err().decode('utf-8', 'replace')} (code {rc})")
+
+
+# ----------------------------------------------------------------------------------------
+# elementwise
+# ----------------------------------------------------------------------------------------
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]] as float32."""
+    _need(table, "embedding table", ndim=2)
+    _need(ids, "token ids", torch.int32, 1)
+    _need(out, "embedding output", torch.float32, 2)
+    if not table.is_contiguous() or not out.is_contiguous():
+        raise KernelError("embedding table and output must be contiguous")
+    n, width = out.shape
+    if ids.numel() != n or table.shape[1] != width:
+        raise KernelError(f"embed_rows: shapes disagree: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
+    fn = _fn("elementwise", "lgml_embed_rows", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("elementwise", fn(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), n, width, table.shape[0], _ptr(status), _stream()), "embed_rows")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = rmsnorm(x [+ delta]) * weight.  With ``delta`` and no ``rows`` the sum is
+    written back to x (the residual add); with ``rows`` output row r reads x[rows[r]]."""
+    _need(x, "norm input", torch.float32, 2)
+    _need(weight, "norm weight", torch.float32, 1)
+    _need(out, "norm output", ndim=2)
+    width = x.shape[1]
+    n_rows = out.shape[0]
+    if not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != width or weight.numel() != width:
+        raise KernelError(f"rmsnorm: shapes disagree: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is None and n_rows != x.shape[0]:
+        raise KernelError("rmsnorm: without a row list the output has the input's rows")
+    if rows is not None:
+        _need(rows, "row list", torch.int32, 1)
+        if rows.numel() != n_rows:
+            raise KernelError("rmsnorm: one output row per listed row")
+    ddt = F32
+    if delta is not None:
+        _need(delta, "residual delta", ndim=2)
+        if delta.shape != x.shape or not delta.is_contiguous():
+            raise KernelError("rmsnorm: delta must have the input's shape and be contiguous")
+        ddt = dtype_code(delta.dtype)
+    fn = _fn("elementwise", "lgml_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check("elementwise", fn(_ptr(x), _ptr(delta), ddt, _ptr(weight), _ptr(rows), _ptr(out), dtype_code(out.dtype), n_rows, width, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    _need(gate_up, "gate|up", ndim=2)
+    _need(out, "activation", gate_up.dtype, 2)
+    n, two_f = gate_up.shape
+    if two_f != 2 * out.shape[1] or out.shape[0] != n or not gate_up.is_contiguous() or not out.is_contiguous():
+        raise KernelError(f"silu_mul: shapes disagree: gate|up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+    fn = _fn("elementwise", "lgml_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check("elementwise", fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, out.shape[1], _stream()), "silu_mul")
+    return out
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += delta, the sum in float32."""
+    _need(x, "residual stream", torch.float32)
+    _need(delta, "residual delta")
+    if x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous():
+        raise KernelError("residual_add: shapes disagree or not contiguous")
+    fn = _fn("elementwise", "lgml_residual_add", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check("elementwise", fn(_ptr(x), _ptr(delta), dtype_code(delta.dtype), x.numel(), _stream()), "residual_add")
+    return x
+
+
+def fill_normal(out: torch.Tensor, mean: float, sd: float, seed: int) -> torch.Tensor:
+    """Seeded N(mean, sd^2) fill on the device."""
+    _need(out, "tensor to fill")
+    if not out.is_contiguous():
+        raise KernelError("fill_normal: tensor must be contiguous")
+    fn = _fn("elementwise", "lgml_fill_normal", [c_void_p, c_int, c_longlong, c_float, c_float, c_ulonglong, c_void_p])
+    _check("elementwise", fn(_ptr(out), dtype_code(out.dtype), out.numel(), float(mean), float(sd), seed & 0xFFFFFFFFFFFFFFFF, _stream()), "fill_normal")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# matrix products
+# ----------------------------------------------------------------------------------------
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = a[M,K] . w[N,K]^T (+ bias), true float32 with a fixed summation order."""
+    _need(a, "gemm input", torch.float32, 2)
+    _need(w, "gemm weight", torch.float32, 2)
+    _need(out, "gemm output", ndim=2)
+    lda, ldw, ldc = _rows_contiguous(a, "gemm input"), _rows_contiguous(w, "gemm weight"), _rows_contiguous(out, "gemm output")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise KernelError("gemm_f32: bias length is not N")
+    fn = _fn("gemm_f32", "lgml_gemm_f32", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check("gemm_f32", fn(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), dtype_code(out.dtype), M, N, K, lda, ldw, ldc, _stream()), "gemm_f32")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# position encoding + cache write, attention
+# ----------------------------------------------------------------------------------------
+
+PAIRING = {"half": 0, "adjacent": 1}
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                  inv_freq: torch.Tensor, n_rot: int, pairing: str, k_pages: torch.Tensor, v_pages: torch.Tensor, n_heads: int,
+                  n_kv_heads: int, head_dim: int, status: torch.Tensor, write_kv: bool = True) -> None:
+    """Rotate the first ``n_rot`` dimensions of q (in place) and k by the positions, and
+    store k and v in their cells (``write_kv`` False: rotate q only, for a layer that
+    reads another layer's cache).  ``n_rot`` 0 means no rotation."""
+    _need(qkv, "qkv", ndim=2)
+    ldq = _rows_contiguous(qkv, "qkv")
+    n = qkv.shape[0]
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    _need(inv_freq, "rotary frequencies", torch.float32, 1)
+    _need(k_pages, "key pages", qkv.dtype, 4)
+    _need(v_pages, "value pages", qkv.dtype, 4)
+    if positions.numel() != n or seq_of_token.numel() != n:
+        raise KernelError("rope_kv_write: one position and one request index per token")
+    n_pages, hkv, page, d = k_pages.shape
+    if (hkv, d) != (n_kv_heads, head_dim) or v_pages.shape != k_pages.shape or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise KernelError(f"rope_kv_write: pages {tuple(k_pages.shape)} do not fit {n_kv_heads} KV heads of {head_dim}")
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim or not block_table.is_contiguous():
+        raise KernelError("rope_kv_write: qkv width is not (H + 2 Hkv) D, or the block table is not contiguous")
+    if n_rot % 2 or n_rot > head_dim or inv_freq.numel() < n_rot // 2:
+        raise KernelError(f"rope_kv_write: n_rot {n_rot} must be even, at most head_dim, and have n_rot / 2 frequencies")
+    fn = _fn("rope_cache", "lgml_rope_kv_write", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("rope_cache", fn(_ptr(qkv), dtype_code(qkv.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
+                            _ptr(inv_freq), n_rot, PAIRING[pairing], _ptr(k_pages), _ptr(v_pages), n_pages, page, n,
+                            n_heads, n_kv_heads, head_dim, 1 if write_kv else 0, _ptr(status), _stream()), "rope_kv_write")
+
+
+def paged_attention_ref(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                        k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                        status: torch.Tensor) -> torch.Tensor:
+    """out[t, h] = attention of query (t, h) over its request's cached keys at positions
+    <= its own (the last ``window`` of them if window > 0).  ``q`` may be a column slice
+    of a wider buffer."""
+    _need(q, "queries", ndim=2)
+    _need(out, "attention output", q.dtype, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    n_pages, hkv, page, d = k_pages.shape
+    _need(k_pages, "key pages", q.dtype, 4)
+    _need(v_pages, "value pages", q.dtype, 4)
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d):
+        raise KernelError(f"paged_attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads of {d}")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("paged_attention: pages and block table must be contiguous")
+    fn = _fn("attention_ref", "lgml_paged_attention_ref", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                           c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check("attention_ref", fn(_ptr(q), dtype_code(q.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
+                               _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n, n_heads, hkv, d, float(scale), int(window or 0),
+                               _ptr(status), _stream()), "paged_attention_ref")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# sampling
+# ----------------------------------------------------------------------------------------
+
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits, "logits", torch.float32, 2)
+    _need(out, "token output", torch.int32, 1)
+    ld = _rows_contiguous(logits, "logits")
+    fn = _fn("sampling", "lgml_argmax_rows", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("sampling", fn(_ptr(logits), ld, logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax_rows")
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Row r: argmax if temperature[r] <= 0, else the inverse-CDF draw of
+    softmax(logits[r] / temperature[r]) at uniform[r]."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(temperature, "temperatures", torch.float32, 1)
+    _need(uniform, "uniform numbers", torch.float64, 1)
+    _need(out, "token output", torch.int32, 1)
+    ld = _rows_contiguous(logits, "logits")
+    r = logits.shape[0]
+    if temperature.numel() != r or uniform.numel() != r or out.numel() != r:
+        raise KernelError("sample_rows: one temperature, uniform number and output per row")
+    fn = _fn("sampling", "lgml_sample_rows", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check("sampling", fn(_ptr(logits), ld, r, logits.shape[1], _ptr(temperature), _ptr(uniform), _ptr(out), _stream()), "sample_rows")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# bfloat16 matrix products and the fast attention paths
+# ----------------------------------------------------------------------------------------
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
+              backend: str = "auto") -> torch.Tensor:
+    """y[M,N] = x[M,K] . w[N,K]^T (+ bias) with bfloat16 operands and float32 accumulation;
+    y is bfloat16 or float32.  ``backend``: "cublas" calls the library product (the reference
+    engine's matrix products are a library's too); "auto" is the same until a hand-written
+    tensor-core kernel takes the shape."""
+    _need(x, "gemm input", torch.bfloat16, 2)
+    _need(w, "gemm weight", torch.bfloat16, 2)
+    if x.shape[1] != w.shape[1]:
+        raise KernelError(f"gemm_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if x.shape[0] == 0:
+        return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
+    if bias is None and out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    y = torch.mm(x, w.t(), out_dtype=torch.float32)
+    if bias is not None:
+        y += bias
+    return y if out_dtype == torch.float32 else y.to(out_dtype)
+
+
+def paged_attention(q, batch, cache, out, n_heads: int, scale: float, window: int, status: torch.Tensor) -> torch.Tensor:
+    """bfloat16 attention over the paged cache; picks the kernel by the batch's shape."""
+    return paged_attention_ref(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads,
+                               scale, window, status)

@@ -1,0 +1,77 @@
+"""The attention mixer: q/k/v projections, position encoding, cache write, attention over
+the cache, output projection.
+
+Formulas in mischief/lgml's order (``lua/lgml/transformer.lua``): q, k, v = W h
+(``:1770``, ``:1779-1781``), rotate q and k (``:1775``, ``:1788``), write k and v to
+the cache before attention reads it (``:1838-1839``, ``:2405-2406``), softmax of
+(q.k) * scale + causal mask over the request's own cells and the weighted sum of v
+(``:1805-1816``), scale 1/sqrt(D) unless given (``:1845``), then W_o (``:1864``).  The
+reference loads no bias (``:304-319``); with ``bias`` the four projections add one.
+
+q, k and v are one fused product: the three matrices are concatenated row-wise when
+they are bound.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..cache import PagedKV
+from ..weights import MATRIX, VECTOR, TensorSpec
+from .base import Part, register_part
+
+
+class Attention(Part):
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position, bias: bool = False,
+                 out_bias: Optional[bool] = None, window: Optional[int] = None, scale: Optional[float] = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads are no multiple of {n_kv_heads} KV heads")
+        self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
+        self.position = position
+        self.bias = bool(bias)
+        self.out_bias = self.bias if out_bias is None else bool(out_bias)
+        self.window = window
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.wqkv = self.bqkv = self.wo = self.bo = None
+
+    def cache_spec(self):
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+
+    def tensor_specs(self, prefix):
+        H, G, D, E = self.n_heads, self.n_kv_heads, self.head_dim, self.width
+        specs = [TensorSpec(prefix + ".q_proj.weight", (H * D, E)), TensorSpec(prefix + ".k_proj.weight", (G * D, E)),
+                 TensorSpec(prefix + ".v_proj.weight", (G * D, E)), TensorSpec(prefix + ".o_proj.weight", (E, H * D))]
+        if self.bias:
+            specs += [TensorSpec(prefix + ".q_proj.bias", (H * D,), VECTOR), TensorSpec(prefix + ".k_proj.bias", (G * D,), VECTOR),
+                      TensorSpec(prefix + ".v_proj.bias", (G * D,), VECTOR)]
+        if self.out_bias:
+            specs.append(TensorSpec(prefix + ".o_proj.bias", (E,), VECTOR))
+        return specs + self.position.tensor_specs(prefix)
+
+    def bind(self, prefix, tensors, rt):
+        self.wqkv = torch.cat([tensors[prefix + f".{n}_proj.weight"] for n in "qkv"], dim=0).contiguous()
+        self.wo = tensors[prefix + ".o_proj.weight"]
+        if self.bias:
+            self.bqkv = torch.cat([tensors[prefix + f".{n}_proj.bias"] for n in "qkv"], dim=0).contiguous()
+        if self.out_bias:
+            self.bo = tensors[prefix + ".o_proj.bias"]
+        self.position.bind(prefix, tensors, rt)
+
+    def forward(self, rt, h, batch, cache):
+        """h [tokens, width] in the compute type -> delta [tokens, width].  ``cache`` has
+        ``k``, ``v`` (pages), ``block_table`` and ``writable`` (False when the cache
+        belongs to another layer, which has already written this step's cells)."""
+        H, D = self.n_heads, self.head_dim
+        qkv = rt.linear(h, self.wqkv, bias=self.bqkv)
+        ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, cache.block_table, self.position.inv_freq,
+                          self.position.n_rot, self.position.pairing, cache.k, cache.v, H, self.n_kv_heads, D,
+                          rt.status, write_kv=cache.writable)
+        o = torch.empty((h.shape[0], H * D), dtype=h.dtype, device=h.device)
+        rt.attention(qkv[:, : H * D], batch, cache, o, H, self.scale, self.window or 0)
+        return rt.linear(o, self.wo, bias=self.bo)
+
+
+register_part("mixer", "attention", Attention)

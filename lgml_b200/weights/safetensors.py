@@ -1,0 +1,179 @@
+"""safetensors files: index, read, write.
+
+The format and every check follow mischief/lgml's reader (``src/safetensors.c``):
+an 8-byte little-endian header length, a JSON header, raw little-endian data
+(``st_read`` ``:278-332``); the header length is bounded and must lie inside the
+file (``:101``); a tensor has at most four dimensions, each at least one
+(``:173-188``); ``begin <= end <= data size`` and ``end - begin`` equals the
+element count times the element size (``check_entry`` ``:229-244``); names are
+1..63 bytes (``:313-315``); a name that two files hold is an error (``:486-487``)
+and so is a folder without tensors (``:545``).
+"""
+from __future__ import annotations
+
+import json
+import struct
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Dict, Iterable, Tuple
+
+import numpy as np
+import torch
+
+MAX_HEADER = 100 << 20
+MAX_TENSORS = 65536
+MAX_NAME = 63
+
+# dtype -> (bytes per element, numpy type used to view the bytes, torch type of the view)
+_DTYPES = {
+    "F64": (8, "<f8", torch.float64),
+    "F32": (4, "<f4", torch.float32),
+    "F16": (2, "<f2", torch.float16),
+    "BF16": (2, "<u2", torch.bfloat16),
+    "I64": (8, "<i8", torch.int64),
+    "I32": (4, "<i4", torch.int32),
+    "I16": (2, "<i2", torch.int16),
+    "I8": (1, "i1", torch.int8),
+}
+_TORCH_TO_ST = {torch.float64: "F64", torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16",
+                torch.int64: "I64", torch.int32: "I32", torch.int16: "I16", torch.int8: "I8"}
+
+
+class SafetensorsError(ValueError):
+    """A file that is not a well-formed safetensors file; the message names the file."""
+
+
+@dataclass(frozen=True)
+class TensorEntry:
+    name: str
+    dtype: str
+    shape: Tuple[int, ...]
+    path: Path
+    begin: int  # absolute offsets in the file
+    end: int
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+
+def read_index(path) -> Dict[str, TensorEntry]:
+    """The tensors of one file, every size and offset checked; reads no data."""
+    path = Path(path)
+    size = path.stat().st_size
+    with open(path, "rb") as f:
+        head = f.read(8)
+        if len(head) != 8:
+            raise SafetensorsError(f"{path}: shorter than its 8-byte header length")
+        (hlen,) = struct.unpack("<Q", head)
+        if hlen < 2 or hlen > MAX_HEADER or 8 + hlen > size:
+            raise SafetensorsError(f"{path}: bad header length {hlen} (file has {size} bytes)")
+        raw = f.read(hlen)
+    if len(raw) != hlen:
+        raise SafetensorsError(f"{path}: short read of the header")
+    try:
+        header = json.loads(raw.decode("utf-8"))
+    except (UnicodeDecodeError, json.JSONDecodeError) as e:
+        raise SafetensorsError(f"{path}: header is not JSON: {e}") from None
+    if not isinstance(header, dict):
+        raise SafetensorsError(f"{path}: header must be an object")
+    data_start = 8 + hlen
+    data_size = size - data_start
+    out: Dict[str, TensorEntry] = {}
+    for name, ent in header.items():
+        if name == "__metadata__":
+            continue
+        nbytes = len(name.encode("utf-8"))
+        if nbytes < 1 or nbytes > MAX_NAME or "\0" in name:
+            raise SafetensorsError(f"{path}: bad tensor name {name!r} (1..{MAX_NAME} bytes, no NUL)")
+        if not isinstance(ent, dict):
+            raise SafetensorsError(f"{path}: entry of '{name}' must be an object")
+        dtype = ent.get("dtype")
+        if dtype not in _DTYPES:
+            raise SafetensorsError(f"{path}: tensor '{name}' has unsupported dtype {dtype!r}")
+        shape = ent.get("shape")
+        if not isinstance(shape, list) or len(shape) > 4 or not all(isinstance(d, int) and d >= 1 for d in shape):
+            raise SafetensorsError(f"{path}: tensor '{name}' has bad shape {shape!r} (at most 4 dimensions, each >= 1)")
+        offs = ent.get("data_offsets")
+        if not (isinstance(offs, list) and len(offs) == 2 and all(isinstance(o, int) for o in offs)):
+            raise SafetensorsError(f"{path}: tensor '{name}' has bad data_offsets {offs!r}")
+        begin, end = offs
+        numel = 1
+        for d in shape:
+            numel *= d
+        if not (0 <= begin <= end <= data_size) or end - begin != numel * _DTYPES[dtype][0]:
+            raise SafetensorsError(
+                f"{path}: tensor '{name}' offsets [{begin}, {end}) do not fit {numel} x {dtype} in {data_size} data bytes")
+        out[name] = TensorEntry(name, dtype, tuple(shape), path, data_start + begin, data_start + end)
+        if len(out) > MAX_TENSORS:
+            raise SafetensorsError(f"{path}: more than {MAX_TENSORS} tensors")
+    return out
+
+
+def index_folder(folder) -> Dict[str, TensorEntry]:
+    """All tensors of a model folder.  With ``model.safetensors.index.json`` the
+    files it names are read; else every ``*.safetensors`` in the folder."""
+    folder = Path(folder)
+    idx_file = folder / "model.safetensors.index.json"
+    if idx_file.exists():
+        try:
+            wm = json.loads(idx_file.read_text())["weight_map"]
+            files = sorted({folder / v for v in wm.values()})
+        except (KeyError, TypeError, AttributeError, json.JSONDecodeError) as e:
+            raise SafetensorsError(f"{idx_file}: no usable weight_map: {e}") from None
+    else:
+        files = sorted(folder.glob("*.safetensors"))
+    if not files:
+        raise SafetensorsError(f"{folder}: no safetensors files")
+    out: Dict[str, TensorEntry] = {}
+    for f in files:
+        if not f.exists():
+            raise SafetensorsError(f"{f}: named by the index but missing")
+        for name, ent in read_index(f).items():
+            if name in out:
+                raise SafetensorsError(f"tensor '{name}' is in both {out[name].path.name} and {f.name}")
+            out[name] = ent
+    if not out:
+        raise SafetensorsError(f"{folder}: no tensors")
+    return out
+
+
+def read_tensor(entry: TensorEntry) -> torch.Tensor:
+    """The tensor on the host in its stored type (a copy, so the file can close)."""
+    _, np_dtype, torch_dtype = _DTYPES[entry.dtype]
+    count = entry.numel
+    arr = np.fromfile(entry.path, dtype=np.dtype(np_dtype), count=count, offset=entry.begin)
+    if arr.size != count:
+        raise SafetensorsError(f"{entry.path}: short read of tensor '{entry.name}'")
+    t = torch.from_numpy(arr)
+    if entry.dtype == "BF16":
+        t = t.view(torch.bfloat16)
+    return t.reshape(entry.shape)
+
+
+def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata=None) -> None:
+    """Write host tensors under their names, in the order given."""
+    header = {}
+    if metadata:
+        header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
+    off = 0
+    blobs = []
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        if t.dtype not in _TORCH_TO_ST:
+            raise SafetensorsError(f"tensor '{name}' has a type safetensors cannot hold: {t.dtype}")
+        st = _TORCH_TO_ST[t.dtype]
+        raw = (t.view(torch.int16) if t.dtype == torch.bfloat16 else t).numpy().tobytes()
+        header[name] = {"dtype": st, "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        off += len(raw)
+        blobs.append(raw)
+    hjson = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    hjson += b" " * ((8 - len(hjson) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hjson)))
+        f.write(hjson)
+        for raw in blobs:
+            f.write(raw)
