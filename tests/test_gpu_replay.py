@@ -1,0 +1,109 @@
+"""The engine against the plain implementation, under every way of cutting the work.
+
+Each request alone and whole; most of it in one step and the last 32 tokens one by
+one; in portions of changing size down to two tokens; and mixed, up to four live
+requests, portions of some beside decoded tokens of others, with so few pages that
+they are used again.  In float32 and in bfloat16, on tiny configurations that differ
+in every size and option, with attention sharpened so that a wrong key shows.  In
+float32 the four ways must agree bit for bit (the kernels sum in an order that does
+not depend on the batch), as mischief/lgml demands of its own passes
+(``test/replay_check.lua:63-76``, ``test/test_qwen_moe.lua:466-509``).
+"""
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+# tolerances: float32 kernels against a float64 oracle; bfloat16 has 8 bits of mantissa
+# and the error grows with depth, so it is bounded relative to the size of the logits.
+TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=3e-2, rtol=3e-2)}
+
+
+def sequences(cfg, which):
+    V = cfg["vocab_size"]
+    lens = {"A": [21, 33, 47, 70, 100, 128], "B": [25, 64, 101, 154, 200, 65, 130], "C": [40, 129, 257, 64, 310]}[which]
+    return {f"r{i}": H.random_ids(n, V, 100 + i) for i, n in enumerate(lens)}
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def tiny(request, tmp_path_factory):
+    cfg, seed = H.TINY[request.param]
+    out = {}
+    for dtype in ("float32", "bfloat16"):
+        out[dtype] = H.make_folder(tmp_path_factory.mktemp(f"tiny{request.param}_{dtype}"), cfg, seed, dtype=dtype, sharpen=40.0)
+    return request.param, cfg, out
+
+
+def make_runner(folder, dtype, n_pages, slots=4):
+    from lgml_b200.engine.engine import parse_dtype
+    from lgml_b200.engine.runner import ModelRunner
+
+    return ModelRunner.from_folder(folder, parse_dtype(dtype), "cuda:0", n_pages=n_pages, max_slots=slots)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_all_cuttings_match_oracle(tiny, dtype):
+    which, cfg, folders = tiny
+    folder = folders[dtype]
+    seqs = sequences(cfg, which)
+    longest = max(len(s) for s in seqs.values())
+    pages_one = -(-longest // 64)
+    results = {}
+    # alone and whole; tail one by one; portions
+    for name, trace in (("whole", H.trace_whole(seqs)), ("tail", H.trace_tail(seqs)), ("portions", H.trace_portions(seqs))):
+        runner = make_runner(folder, dtype, n_pages=pages_one)
+        results[name] = H.run_trace(runner, trace)
+        assert runner.cache.groups[0].pool.n_held == 0
+    # mixed, with a pool that cannot hold all requests at once: pages are used again
+    max_tokens = 64 * (pages_one + 3)
+    trace = H.trace_mixed(seqs, max_tokens=max_tokens, seed=7)
+    assert max(len(st["entries"]) for st in trace) >= 3
+    runner = make_runner(folder, dtype, n_pages=max_tokens // 64)
+    results["mixed"] = H.run_trace(runner, trace)
+    pool = runner.cache.groups[0].pool
+    assert pool.taken_total > pool.n_pages, "the trace never used a page twice"
+    for name, got in results.items():
+        worst = H.compare_with_oracle(got, folder, seqs, **TOL[dtype])
+        print(f"tiny-{which} {dtype} {name}: max |diff| {worst:.3g}")
+    if dtype == "float32":
+        for name in ("tail", "portions", "mixed"):
+            for key, row in results["whole"].items():
+                assert torch.equal(row, results[name][key]), f"float32 {name} differs from whole at {key}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_and_single_token_prompt(tiny, dtype):
+    """The first tokens of a sequence, a one-token prompt, and a two-token portion at a page's edge."""
+    which, cfg, folders = tiny
+    folder = folders[dtype]
+    V = cfg["vocab_size"]
+    seqs = {"one": H.random_ids(1, V, 5), "two": H.random_ids(2, V, 6), "edge": H.random_ids(66, V, 8)}
+    steps = [
+        {"step": 0, "entries": [{"id": "one", "tokens": seqs["one"], "want": [0]}, {"id": "two", "tokens": seqs["two"], "want": [0, 1]}], "end": ["one", "two"]},
+        {"step": 1, "entries": [{"id": "edge", "tokens": seqs["edge"][:63], "want": list(range(63))}], "end": []},
+        {"step": 2, "entries": [{"id": "edge", "tokens": seqs["edge"][63:65], "want": [0, 1]}], "end": []},
+        {"step": 3, "entries": [{"id": "edge", "tokens": seqs["edge"][65:], "want": [0]}], "end": ["edge"]},
+    ]
+    runner = make_runner(folder, dtype, n_pages=4)
+    got = H.run_trace(runner, steps)
+    H.compare_with_oracle(got, folder, seqs, **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(tiny, dtype):
+    """A short prompt, then token by token to the end of the context, on pages another request used."""
+    which, cfg, folders = tiny
+    folder = folders[dtype]
+    n = cfg["max_position_embeddings"]
+    ids = H.random_ids(n, cfg["vocab_size"], 77)
+    junk = H.random_ids(n, cfg["vocab_size"], 78)
+    runner = make_runner(folder, dtype, n_pages=-(-n // 64))
+    # dirty every page first
+    H.run_trace(runner, [{"step": 0, "entries": [{"id": "junk", "tokens": junk, "want": []}], "end": ["junk"]}])
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": ids[:3], "want": [0, 1, 2]}], "end": []}]
+    for p in range(3, n):
+        steps.append({"step": p, "entries": [{"id": "x", "tokens": [ids[p]], "want": [0]}], "end": ["x"] if p == n - 1 else []})
+    got = H.run_trace(runner, steps)
+    H.compare_with_oracle(got, folder, {"x": ids}, **TOL[dtype])
