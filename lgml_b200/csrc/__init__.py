@@ -61,7 +61,7 @@ def find_nvcc() -> str:
 def _writable(d: Path) -> bool:
     try:
         d.mkdir(parents=True, exist_ok=True)
-        probe = d / f".probe-{os.getpid()}"
+        probe = d / f".probe-{os.getpid()}-{threading.get_ident()}"
         probe.write_bytes(b"")
         probe.unlink()
         return True
@@ -69,7 +69,17 @@ def _writable(d: Path) -> bool:
         return False
 
 
+_build_dir: Optional[Path] = None
+
+
 def build_dir() -> Path:
+    global _build_dir
+    if _build_dir is None:
+        _build_dir = _find_build_dir()
+    return _build_dir
+
+
+def _find_build_dir() -> Path:
     env = os.environ.get("LGML_BUILD_DIR")
     if env and _writable(Path(env)):
         return Path(env)

@@ -1,0 +1,104 @@
+"""Configuration and registry (no GPU)."""
+import json
+
+import pytest
+
+from lgml_b200.config import (ConfigError, LlamaConfig, ModelConfig, architectures, config_from_dict, load_config,
+                              lookup_architecture, register_architecture)
+from tests import helpers as H
+
+
+def test_llama_defaults_follow_the_reference():
+    d = {"architectures": ["LlamaForCausalLM"], "vocab_size": 100, "hidden_size": 96, "intermediate_size": 50,
+         "num_hidden_layers": 1, "num_attention_heads": 6, "rms_norm_eps": 1e-5, "max_position_embeddings": 64}
+    c = config_from_dict(d)
+    assert c.num_key_value_heads == 6            # defaults to the heads
+    assert c.head_dim == 16                      # hidden // heads
+    assert c.rope_theta == 10000.0
+    assert c.rope_scaling is None and not c.tie_word_embeddings and not c.attention_bias and not c.mlp_bias
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_round_trip(which):
+    cfg, _ = H.TINY[which]
+    c = config_from_dict(cfg)
+    again = config_from_dict(json.loads(json.dumps(c.to_dict())))
+    assert again == c
+    assert c.head_dim == cfg["head_dim"] and c.vocab_size == cfg["vocab_size"]
+
+
+def test_head_width_may_differ_from_hidden():
+    c = config_from_dict(H.TINY_B)
+    assert c.num_attention_heads * c.head_dim == 192 != c.hidden_size
+
+
+def test_rope_parameters_style():
+    d = dict(H.TINY_B)
+    rs = d.pop("rope_scaling")
+    theta = d.pop("rope_theta")
+    d["rope_parameters"] = dict(rs, rope_theta=theta)
+    assert config_from_dict(d) == config_from_dict(H.TINY_B)
+    d["rope_parameters"] = {"rope_type": "default", "rope_theta": 1234.0}
+    c = config_from_dict(d)
+    assert c.rope_theta == 1234.0 and c.rope_scaling is None
+
+
+@pytest.mark.parametrize("key", ["vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                                 "rms_norm_eps", "max_position_embeddings"])
+def test_missing_key_is_named(key):
+    d = dict(H.TINY_A)
+    del d[key]
+    with pytest.raises(ConfigError, match=key):
+        config_from_dict(d)
+
+
+@pytest.mark.parametrize("change,match", [
+    ({"num_key_value_heads": 3}, "multiple"),
+    ({"head_dim": 15}, "even"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "rope_type"),
+    ({"rope_scaling": {"rope_type": "llama3", "factor": 8.0}}, "low_freq_factor"),
+    ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
+    ({"vocab_size": 0}, "vocab_size"),
+])
+def test_bad_values_are_refused(change, match):
+    with pytest.raises(ConfigError, match=match):
+        config_from_dict({**H.TINY_A, **change})
+
+
+def test_unknown_architecture_is_named():
+    with pytest.raises(ConfigError, match="MambaForCausalLM"):
+        config_from_dict({**H.TINY_A, "architectures": ["MambaForCausalLM"]})
+    with pytest.raises(ConfigError, match="architectures"):
+        config_from_dict({k: v for k, v in H.TINY_A.items() if k != "architectures"})
+    assert "LlamaForCausalLM" in architectures()
+
+
+def test_load_config_errors(tmp_path):
+    with pytest.raises(ConfigError, match="config.json"):
+        load_config(tmp_path)
+    (tmp_path / "config.json").write_text("{not json")
+    with pytest.raises(ConfigError, match="JSON"):
+        load_config(tmp_path)
+    (tmp_path / "config.json").write_text(json.dumps(H.TINY_B))
+    assert isinstance(load_config(tmp_path), LlamaConfig)
+
+
+def test_eos_forms():
+    assert config_from_dict({**H.TINY_A, "eos_token_id": 7}).eos_token_ids == [7]
+    assert config_from_dict({**H.TINY_A, "eos_token_id": [7, 9]}).eos_token_ids == [7, 9]
+
+
+def test_registry_takes_a_new_architecture():
+    class Toy(ModelConfig):
+        @classmethod
+        def from_dict(cls, d):
+            return cls(architecture="ToyForTest")
+
+        def validate(self):
+            pass
+
+    register_architecture("ToyForTest", Toy, lambda cfg: "model")
+    cls, builder = lookup_architecture("ToyForTest")
+    assert cls is Toy and builder(None) == "model"
+    assert config_from_dict({"architectures": ["ToyForTest"]}).architecture == "ToyForTest"
