@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, tuple] = {
     "rope_cache": ("rope_cache.cu", []),
     "attention_ref": ("attention_ref.cu", []),
     "sampling": ("sampling.cu", []),
+    "attention_decode": ("attention_decode.cu", []),
 }
 
 _HEADERS = ["common.cuh"]

@@ -35,8 +35,15 @@ class CacheView:
 
 
 class StepBatch:
+    """Host lists -> one int32 buffer -> one copy -> device views.
+
+    ``table_widths`` forces the width of each group's block table and ``device_buffer``
+    makes the views live in a buffer the caller keeps: both are what a captured CUDA graph
+    needs, since its kernels were recorded with fixed addresses and strides."""
+
     def __init__(self, cache_manager, requests: Sequence, tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
-                 device, pinned: Optional[torch.Tensor] = None):
+                 device, pinned: Optional[torch.Tensor] = None, table_widths: Optional[Sequence[int]] = None,
+                 device_buffer: Optional[torch.Tensor] = None):
         cm = cache_manager
         self.cache_manager = cm
         self.requests = list(requests)
@@ -49,6 +56,7 @@ class StepBatch:
         self.kv_lens = [p + n for p, n in zip(self.pos0, lens)]
         self.max_q_len = max(lens) if lens else 0
         self.max_kv_len = max(self.kv_lens) if lens else 0
+        self.decode_splits = None       # a fixed split count (set by a captured graph)
 
         flat: List[int] = []
         for t in tokens:
@@ -72,7 +80,9 @@ class StepBatch:
             self.rows_of_seq.append(mine)
         self.n_rows = len(rows)
 
-        tables = [cm.block_table_rows(self.requests, g) for g in range(len(cm.groups))]
+        tables = []
+        for g in range(len(cm.groups)):
+            tables.append(cm.block_table_rows(self.requests, g, table_widths[g] if table_widths else None))
         self.table_width = [len(t[0]) if t else 1 for t in tables]
         parts = [flat, positions, seq_of, starts, self.pos0, [r.slot for r in self.requests], self.kv_lens, rows or [0]]
         for t in tables:
@@ -82,7 +92,12 @@ class StepBatch:
         if pinned is not None and pinned.numel() >= total:
             pinned[:total].copy_(host)
             host = pinned[:total]
-        dev = torch.empty(total, dtype=torch.int32, device=device)
+        if device_buffer is not None:
+            if device_buffer.numel() < total:
+                raise ValueError("the step's description does not fit the buffer kept for it")
+            dev = device_buffer[:total]
+        else:
+            dev = torch.empty(total, dtype=torch.int32, device=device)
         dev.copy_(host, non_blocking=True)
         self.h2d_bytes = total * 4
         self._dev = dev
@@ -104,6 +119,10 @@ class StepBatch:
         r = take(max(len(rows), 1))
         self.logit_rows = r[: len(rows)]
         self.block_tables = [take(S * w).view(S, w) for w in self.table_width]
+
+    @staticmethod
+    def buffer_ints(n_tokens: int, n_seqs: int, n_rows: int, table_widths: Sequence[int]) -> int:
+        return 3 * n_tokens + (n_seqs + 1) + 3 * n_seqs + max(n_rows, 1) + n_seqs * sum(table_widths)
 
     def cache_view(self, owner: int, writable: bool = True) -> CacheView:
         """The cache of schedule entry ``owner`` as this batch's requests see it."""

@@ -21,12 +21,15 @@ from .batch import StepBatch
 from .runtime import Runtime
 
 
+MAX_GRAPH_BATCH = 256
+
+
 class StepError(ValueError):
     """A step the runner refuses before anything is launched."""
 
 
 class ModelRunner:
-    def __init__(self, model, rt: Runtime, n_pages: int, max_slots: int = 4, max_step_tokens: int = 0):
+    def __init__(self, model, rt: Runtime, n_pages: int, max_slots: int = 4, max_step_tokens: int = 0, use_graphs: bool = True):
         self.model = model
         self.rt = rt
         self.cache = CacheManager(model.cache_layout(), n_pages=n_pages, max_slots=max_slots, dtype=rt.dtype,
@@ -35,6 +38,13 @@ class ModelRunner:
         self._pinned = [[torch.empty(1 << 16, dtype=torch.int32).pin_memory(), None] for _ in range(4)]
         self.steps = 0
         self.tokens_run = 0
+        # decode steps (one token per request) replay a CUDA graph captured per batch size
+        self.use_graphs = use_graphs
+        self._graphs = {}
+        self._graph_seen = set()
+        max_pos = model.max_position or (n_pages * self.cache.page_size)
+        self._graph_widths = [min(g.pool.n_pages, -(-max_pos // self.cache.page_size)) for g in self.cache.groups]
+        self.graph_replays = 0
 
     # ---- construction ------------------------------------------------------------------
     @classmethod
@@ -112,14 +122,63 @@ class ModelRunner:
         stage = self._pinned[self.steps % len(self._pinned)]
         if stage[1] is not None:
             stage[1].synchronize()
-        batch = StepBatch(self.cache, [e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries],
-                          self.rt.device, stage[0])
-        stage[1] = torch.cuda.Event()
-        stage[1].record()
-        self.last_batch = batch
-        logits = self.model.forward(self.rt, batch)
+        S = len(entries)
+        if self.use_graphs and all(len(e[1]) == 1 for e in entries) and S <= MAX_GRAPH_BATCH:
+            logits = self._graph_step(entries, stage)
+        else:
+            batch = StepBatch(self.cache, [e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries],
+                              self.rt.device, stage[0])
+            stage[1] = torch.cuda.Event()
+            stage[1].record()
+            self.last_batch = batch
+            logits = self.model.forward(self.rt, batch)
         for req, tokens, _ in entries:
             self.cache.commit(req, len(tokens))
         self.steps += 1
-        self.tokens_run += batch.n_tokens
+        self.tokens_run += sum(len(e[1]) for e in entries)
+        return logits
+
+    def _graph_step(self, entries, stage) -> torch.Tensor:
+        """A decode step through a captured graph.  The first step of a batch size runs
+        eagerly (it also loads the kernels); the second captures; later ones replay.  The
+        graph computes the logits of every token; the wanted rows are picked after it."""
+        S = len(entries)
+        reqs, toks = [e[0] for e in entries], [e[1] for e in entries]
+        all_rows = [[0]] * S
+        if S not in self._graph_seen:
+            self._graph_seen.add(S)
+            batch = StepBatch(self.cache, reqs, toks, [e[2] for e in entries], self.rt.device, stage[0])
+            stage[1] = torch.cuda.Event()
+            stage[1].record()
+            self.last_batch = batch
+            return self.model.forward(self.rt, batch)
+        slot = self._graphs.get(S)
+        if slot is None:
+            buf = torch.zeros(StepBatch.buffer_ints(S, S, S, self._graph_widths), dtype=torch.int32, device=self.rt.device)
+            slot = {"buffer": buf, "graph": None, "logits": None}
+            self._graphs[S] = slot
+        batch = StepBatch(self.cache, reqs, toks, all_rows, self.rt.device, stage[0], table_widths=self._graph_widths,
+                          device_buffer=slot["buffer"])
+        stage[1] = torch.cuda.Event()
+        stage[1].record()
+        self.last_batch = batch
+        if slot["graph"] is None:
+            # sized for the longest context the tables can describe, so the capture fits every later step
+            hkv = max((g.spec.n_kv_heads for g in self.cache.groups), default=1)
+            batch.max_kv_len = max(self._graph_widths, default=1) * self.cache.page_size
+            from .. import ops
+            batch.decode_splits = ops.decode_splits(S, hkv, 1, batch.max_kv_len)
+            slot["splits"] = batch.decode_splits
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                slot["logits"] = self.model.forward(self.rt, batch)
+            slot["graph"] = g
+        slot["graph"].replay()
+        self.graph_replays += 1
+        logits = slot["logits"]
+        want_rows = [i for i, e in enumerate(entries) for _ in e[2]]
+        if want_rows != list(range(S)) or any(len(e[2]) != 1 for e in entries):
+            if not want_rows:
+                return logits[:0]
+            return logits[torch.tensor(want_rows, dtype=torch.long, device=logits.device)]
         return logits

@@ -123,13 +123,18 @@ class Scheduler:
             self.running.remove(req)
         self.finished.append(req)
 
-    def _reserve(self, req: GenRequest, n: int, plan: List[PlannedEntry]) -> bool:
-        """Pages for n more tokens of a running request, preempting later arrivals if needed."""
+    def _reserve(self, req: GenRequest, n: int, plan: List[PlannedEntry]) -> Optional[bool]:
+        """Pages for n more tokens of a running request.  While the pool is short the most
+        recently admitted running request is preempted; if that is ``req`` itself it goes
+        back to the queue (None), unless it is alone, in which case nothing can help (False)."""
         while not self.cache.reserve(req.cache_req, n):
-            others = [r for r in self.running if r is not req]
-            if not others:
-                return False
-            self._preempt(max(others, key=lambda r: r.admitted_at), plan)
+            victim = max(self.running, key=lambda r: r.admitted_at)
+            if victim is req:
+                if len(self.running) == 1:
+                    return False
+                self._preempt(req, plan)
+                return None
+            self._preempt(victim, plan)
         return True
 
     def plan(self) -> List[PlannedEntry]:
@@ -144,7 +149,10 @@ class Scheduler:
             n = min(req.n_pending, self.ubatch, budget)
             if n <= 0:
                 continue
-            if not self._reserve(req, n, plan):
+            got = self._reserve(req, n, plan)
+            if got is None:
+                continue
+            if got is False:
                 # alone and out of pages: the reply ends here (lua/lgml/engine.lua:3183-3186)
                 self._finish(req, "length")
                 continue

@@ -300,7 +300,62 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Op
     return y if out_dtype == torch.float32 else y.to(out_dtype)
 
 
+SM_COUNT = 148  # B200
+
+
+def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, page: int = 64) -> int:
+    """How many ranges the keys of a token are cut into, so that the grid fills the SMs
+    a few times over; at most one range per page."""
+    ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
+    pages = max(1, -(-max_kv_len // page))
+    return max(1, min(pages, (4 * SM_COUNT) // max(ctas, 1)))
+
+
+def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                     k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                     status: torch.Tensor, n_splits: int, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bfloat16 split-KV attention: each token over its request's cells.  Scratch (float32,
+    ``decode_attention_scratch_floats`` elements) is needed when n_splits > 1."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d):
+        raise KernelError(f"decode_attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads of {d}")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or v_pages.shape != k_pages.shape:
+        raise KernelError("decode_attention: pages and block table must be contiguous")
+    if n_splits > 1:
+        need = n * n_heads * n_splits * (d + 2)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        _need(scratch, "scratch", torch.float32, 1)
+        if scratch.numel() < need:
+            raise KernelError(f"decode_attention: scratch of {scratch.numel()} floats, {need} needed")
+    fn = _fn("attention_decode", "lgml_decode_attention", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                           c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check("attention_decode", fn(_ptr(q), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_pages),
+                                  _ptr(v_pages), n_pages, page, _ptr(out), ldo, _ptr(scratch if n_splits > 1 else None), n_splits, n, n_heads, hkv, d,
+                                  float(scale), int(window or 0), _ptr(status), _stream()), "decode_attention")
+    return out
+
+
+# a portion of at most this many tokens per request is run by the decode kernel
+DECODE_MAX_Q = 8
+
+
 def paged_attention(q, batch, cache, out, n_heads: int, scale: float, window: int, status: torch.Tensor) -> torch.Tensor:
     """bfloat16 attention over the paged cache; picks the kernel by the batch's shape."""
+    d = cache.k.shape[3]
+    if batch.max_q_len <= DECODE_MAX_Q and d % 16 == 0 and cache.k.shape[2] == 64:
+        hkv = cache.k.shape[1]
+        n_splits = batch.decode_splits if getattr(batch, "decode_splits", None) else decode_splits(q.shape[0], hkv, n_heads // hkv, batch.max_kv_len)
+        return decode_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
+                                window, status, n_splits)
     return paged_attention_ref(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads,
                                scale, window, status)

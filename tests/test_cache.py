@@ -1,0 +1,141 @@
+"""The cache manager's bookkeeping (no GPU): no page lost, held twice or freed twice,
+under random orders of requests; windows give pages back; state slots."""
+import random
+
+import pytest
+import torch
+
+from lgml_b200.cache import CacheManager, FixedState, NoSlot, PagedKV, PagePool, PoolFull
+
+
+def test_pool_takes_lowest_first_and_refuses_double_free():
+    p = PagePool(5)
+    got = [p.take() for _ in range(5)]
+    assert got == [0, 1, 2, 3, 4]                      # lowest free first (lua/lgml/kvpool.lua:102-116)
+    with pytest.raises(PoolFull, match="kv pool full"):
+        p.take()
+    p.release(3)
+    p.release(1)
+    assert p.take() == 1 and p.take() == 3
+    p.release(2)
+    with pytest.raises(ValueError, match="twice"):
+        p.release(2)
+    with pytest.raises(ValueError, match="outside"):
+        p.release(9)
+    p.ref(0)
+    p.release(0)
+    assert p.refcount(0) == 1 and p.n_free == 1
+    p.check()
+
+
+def manager(n_pages=8, slots=4, layout=None, **kw):
+    layout = layout or {0: PagedKV(2, 8), 1: PagedKV(2, 8)}
+    return CacheManager(layout, n_pages=n_pages, max_slots=slots, dtype=torch.float32, device="cpu", **kw)
+
+
+def test_layers_with_equal_needs_share_a_group():
+    cm = manager(layout={0: PagedKV(2, 8), 1: PagedKV(2, 8), 2: PagedKV(2, 8, window=100), 3: FixedState((4,)), 4: None})
+    assert len(cm.groups) == 2 and cm.groups[0].layers == [0, 1] and cm.groups[1].layers == [2]
+    assert cm.groups[0].k[1].shape == (8, 2, 64, 8)
+    assert len(cm.state_groups) == 1 and cm.state_groups[0].state[3].shape == (4, 4)
+
+
+def test_reserve_commit_close():
+    cm = manager(n_pages=4)
+    a = cm.open("a")
+    assert cm.reserve(a, 65) and a.tables[0] == [0, 1]
+    assert cm.reserve(a, 65) and a.tables[0] == [0, 1]          # asking again takes nothing
+    cm.commit(a, 65)
+    assert cm.reserve(a, 1) and len(a.tables[0]) == 2            # position 65 is in page 1
+    b = cm.open("b")
+    assert cm.reserve(b, 128) and b.tables[0] == [2, 3]
+    assert not cm.reserve(a, 64)                                 # needs a third page, none free
+    assert a.tables[0] == [0, 1]                                 # a failed reserve takes nothing
+    cm.check()
+    cm.close(b)
+    assert cm.reserve(a, 64) and a.tables[0] == [0, 1, 2]        # b's page is used again
+    with pytest.raises(ValueError, match="twice"):
+        cm.close(b)
+    cm.close(a)
+    assert cm.n_free_pages == 4 and not cm.live
+    cm.check()
+
+
+def test_failed_reserve_rolls_back_every_group():
+    cm = manager(n_pages=3, layout={0: PagedKV(2, 8), 1: PagedKV(1, 16)})
+    a = cm.open("a")
+    hog = cm.open("hog")
+    cm.groups[1].pool.take(), cm.groups[1].pool.take()           # only the second group is short
+    assert not cm.reserve(a, 128)
+    assert a.tables == [[], []] and cm.groups[0].pool.n_free == 3
+    cm.close(hog)
+
+
+def test_slots_run_out_and_come_back():
+    cm = manager(slots=2)
+    a, b = cm.open("a"), cm.open("b")
+    with pytest.raises(NoSlot):
+        cm.open("c")
+    with pytest.raises(ValueError, match="already live"):
+        cm.open("a")
+    slot = a.slot
+    cm.close(a)
+    assert cm.open("c").slot == slot
+
+
+def test_window_gives_pages_back():
+    cm = manager(n_pages=16, layout={0: PagedKV(2, 8), 1: PagedKV(2, 8, window=70)}, max_step_tokens=64)
+    r = cm.open("r")
+    held = []
+    for _ in range(10):
+        assert cm.reserve(r, 64)
+        cm.commit(r, 64)
+        held.append(cm.groups[1].pool.n_held)
+        cm.check()
+    assert cm.groups[0].pool.n_held == 10                        # the full group keeps everything
+    assert max(held) <= 3                                        # the window group keeps ceil(70/64)+1
+    # the pages still held cover every position a later query can reach
+    lowest = r.n_tokens - 70 + 1
+    assert all(p >= 0 for p in r.tables[1][lowest // 64:]) and all(p == -1 for p in r.tables[1][: lowest // 64])
+    cm.close(r)
+    cm.check()
+    assert cm.groups[1].pool.n_held == 0
+
+
+def test_state_slots_are_zeroed_at_open():
+    cm = manager(layout={0: FixedState((3,))}, slots=2)
+    a = cm.open("a")
+    cm.state_groups[0].state[0][a.slot] += 5.0
+    cm.close(a)
+    b = cm.open("b")
+    assert b.slot == a.slot and float(cm.state_groups[0].state[0][b.slot].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_the_books(seed):
+    """Random opens, reserves, commits and closes: the invariants hold at every point and
+    everything comes back at the end."""
+    rng = random.Random(seed)
+    cm = manager(n_pages=12, slots=4, layout={0: PagedKV(2, 8), 1: PagedKV(2, 8, window=90)}, max_step_tokens=80)
+    live, n = {}, 0
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.25 and len(live) < 4:
+            live[n] = cm.open(n)
+            n += 1
+        elif op < 0.85 and live:
+            rid = rng.choice(list(live))
+            k = rng.choice([1, 1, 2, 17, 64, 80])
+            if cm.reserve(live[rid], k):
+                cm.commit(live[rid], k)
+            else:
+                before = [list(t) for t in live[rid].tables]
+                assert before == live[rid].tables
+        elif live:
+            rid = rng.choice(list(live))
+            cm.close(live.pop(rid))
+        cm.check()
+    for r in live.values():
+        cm.close(r)
+    cm.check()
+    assert all(g.pool.n_held == 0 for g in cm.groups)
