@@ -1,0 +1,279 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens per second of the Llama-3.1-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on standard output.  A "step" is one decode step of a batch of 8 requests,
+each holding a 2,048-token prompt in the cache (context 4,096), random weights, random
+token ids.  ``value`` is decoded tokens per second timed on the device with CUDA events
+around K steps of the engine's step function and its sampling kernel; ``e2e`` is the same
+through the Python entry point (``Engine.generate``: host token lists in, host token lists
+out, every step copies its inputs from pinned memory and reads the sampled tokens back).
+``prefill`` is one 2,048-token prompt in one step; ``points`` adds decode at batch 1 and
+64; ``roofline`` is the bytes a decode step has to read (every weight once and the cache
+of the live requests) over its time, against the measured copy bandwidth.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA31_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False,
+    "max_position_embeddings": 4096, "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+PROMPT_LEN = 2048
+CONTEXT = 4096
+BATCH = 8
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+        except (ValueError, KeyError, TypeError):
+            pass
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def weight_bytes(cfg) -> int:
+    """Bytes of every weight a decode step reads once (bfloat16): the layers and the head."""
+    E, F, H, G, D, V, L = (cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                           cfg.head_dim, cfg.vocab_size, cfg.num_hidden_layers)
+    per_layer = (H + 2 * G) * D * E + E * H * D + 3 * F * E
+    return 2 * (L * per_layer + V * E) + 4 * (2 * L + 1) * E
+
+
+def step_flops(cfg, n_tokens: int, kv_lens) -> float:
+    """Matrix products (2 flops per weight per token) plus causal attention."""
+    E, F, H, G, D, V, L = (cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                           cfg.head_dim, cfg.vocab_size, cfg.num_hidden_layers)
+    per_layer = (H + 2 * G) * D * E + E * H * D + 3 * F * E
+    mm = 2.0 * n_tokens * L * per_layer + 2.0 * V * E          # the head runs on one row
+    att = sum(4.0 * H * D * L * (k * (k + 1) / 2) for k in kv_lens)   # q.k and p.v over the causal triangle
+    return mm + att
+
+
+def run_decode(runner, cfg, batch: int, steps: int, warmup: int, seed: int = 0):
+    """Prefill ``batch`` prompts, then time ``steps`` decode steps on the device."""
+    import torch
+
+    from lgml_b200 import ops
+
+    g = torch.Generator().manual_seed(seed)
+    reqs = [runner.open(("bench", batch, i)) for i in range(batch)]
+    try:
+        for r in reqs:
+            ids = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist()
+            for p in range(0, PROMPT_LEN, 512):
+                runner.step([(r, ids[p:p + 512], [])])
+        cur = torch.randint(0, cfg.vocab_size, (batch,), generator=g).tolist()
+        tok = torch.empty(batch, dtype=torch.int32, device=runner.rt.device)
+        host_tok = torch.empty(batch, dtype=torch.int32).pin_memory()
+
+        def one():
+            nonlocal cur
+            logits = runner.step([(r, [t], [0]) for r, t in zip(reqs, cur)])
+            ops.argmax_rows(logits, tok)
+            host_tok.copy_(tok, non_blocking=False)
+            cur = host_tok.tolist()
+
+        for _ in range(warmup):
+            one()
+        launches0 = ops.launch_count()
+        replays0 = runner.graph_replays
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        kv_tokens = sum(r.n_tokens for r in reqs)
+        launches = ops.launch_count() - launches0 + (runner.graph_replays - replays0) * runner.graph_kernels(batch)
+        runner.rt.check_status()
+        return ms / steps, kv_tokens, launches
+    finally:
+        for r in reqs:
+            runner.close(r)
+
+
+def run_prefill(runner, cfg, reps: int = 3, seed: int = 1):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    best = None
+    for i in range(reps + 1):
+        ids = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist()
+        r = runner.open(("prefill", i))
+        try:
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step([(r, ids, [PROMPT_LEN - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(end)
+            if i > 0:                      # the first run loads kernels
+                best = ms if best is None else min(best, ms)
+        finally:
+            runner.close(r)
+    return best
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "mischief/lgml is Lua on a ggml fork fetched over the network with a "
+                          "Vulkan GPU path; it has no pip-installable package and cannot be built or run offline on this box"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    import lgml_b200
+    from lgml_b200 import ops
+    from lgml_b200.config import config_from_dict
+    from lgml_b200.engine.runner import ModelRunner
+
+    d = dict(LLAMA31_8B)
+    full_layers = d["num_hidden_layers"]
+    if args.layers:
+        d["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(d)
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    n_pages = 64 * (CONTEXT // 64) + 8           # room for 64 requests of the benchmark context
+    runner = ModelRunner.from_config(cfg, seed=0, dtype=torch.bfloat16, n_pages=n_pages, max_slots=64, max_step_tokens=PROMPT_LEN)
+
+    prefill_ms = run_prefill(runner, cfg)
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, kv_tokens, launches = run_decode(runner, cfg, BATCH, args.steps, warmup)
+    clock_rec = clocks.stop()
+    points = {}
+    if not args.skip_points:
+        for b, k in ((1, min(args.steps, 64)), (64, min(args.steps, 32))):
+            ms_b, _, _ = run_decode(runner, cfg, b, k, warmup)
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+
+    value = BATCH * 1000.0 / ms_step
+    kv_bytes = kv_tokens * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * cfg.num_hidden_layers
+    step_bytes = weight_bytes(cfg) + kv_bytes
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    pf_flops = step_flops(cfg, PROMPT_LEN, [PROMPT_LEN])
+    prefill = {"value": round(PROMPT_LEN * 1000.0 / prefill_ms, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
+               "frac": round(pf_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12), 4)}
+
+    # end to end through the Python entry point, on the same weights
+    del runner
+    torch.cuda.empty_cache()
+    eng = lgml_b200.Engine(config=cfg, random_weights=0, dtype="bfloat16", n_ctx=CONTEXT, kv_tokens=BATCH * CONTEXT, slots=BATCH, ubatch=512,
+                           max_batch_tokens=2048)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(BATCH)]
+    e2e_steps = min(args.steps, 64) + warmup
+    eng.generate(prompts, max_tokens=e2e_steps, temperature=0.0, stop=[])
+    e2e = eng.decode_rate(skip=warmup)
+
+    rec = {
+        "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts, context 4,096)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform-random token ids",
+        "config": {"model": "Llama-3.1-8B shape", "layers": cfg.num_hidden_layers, "layers_of_model": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page": 64, "parallelism": "single GPU",
+                   "l2": "inputs exceed L2 (a step reads %.1f GB)" % (step_bytes / 1e9), "peaks": peak_src},
+        "clocks": clock_rec,
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"], "steps": e2e["steps"]},
+        "gpu_launches": int(launches),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4)},
+        "points": points,
+        "kernel_libraries": lgml_b200.csrc.loaded_libraries(),
+    }
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -3,7 +3,8 @@
 Option names and meanings follow mischief/lgml's ``engine.new``
 (``lua/lgml/engine.lua:376-467``): ``model`` (a folder with config.json and
 safetensors here), ``n_ctx`` (the size of the cache pool all slots share, and the
-most tokens of one request), ``slots`` (the most requests kept at once, default 4:
+most tokens of one request; ``kv_tokens``, which the reference does not have, makes
+the pool larger than one request's context), ``slots`` (the most requests kept at once, default 4:
 ``lua/lgml/kvpool.lua:28``), ``ubatch`` (prompt tokens per request per step,
 default 512), ``max_tokens`` (default reply length: the free context),
 ``sampling`` (sampler defaults, a request's values replace them),
@@ -36,7 +37,7 @@ def parse_dtype(name) -> torch.dtype:
 
 class Engine:
     def __init__(self, model=None, *, config=None, random_weights: Optional[int] = None, dtype="bfloat16", n_ctx: Optional[int] = None,
-                 slots: int = 4, ubatch: int = UBATCH, max_batch_tokens: Optional[int] = None, max_tokens: Optional[int] = None,
+                 kv_tokens: Optional[int] = None, slots: int = 4, ubatch: int = UBATCH, max_batch_tokens: Optional[int] = None, max_tokens: Optional[int] = None,
                  sampling: Optional[dict] = None, repeat_stop_tokens: int = REPEAT_STOP, device="cuda:0"):
         dt = parse_dtype(dtype)
         if model is None and config is None:
@@ -50,7 +51,8 @@ class Engine:
         max_pos = cfg.max_position_embeddings
         n_ctx = min(n_ctx or max_pos, max_pos)
         self.n_ctx = n_ctx
-        n_pages = -(-n_ctx // 64)
+        # the pool all slots share: n_ctx tokens as in the reference, or kv_tokens when given
+        n_pages = -(-(kv_tokens or n_ctx) // 64)
         max_batch_tokens = max_batch_tokens or max(ubatch, 2048)
         kw = dict(n_pages=n_pages, max_slots=slots, max_step_tokens=max_batch_tokens)
         if model is not None:
@@ -65,10 +67,13 @@ class Engine:
         self.eos_ids = list(getattr(cfg, "eos_token_ids", []) or [])
         self._next_id = 0
         self.timings: Dict[str, float] = {}
+        # one record per scheduler turn: wall seconds, prompt tokens, decoded tokens, bytes copied each way
+        self.turn_log: List[dict] = []
 
     # ---- one scheduler turn -------------------------------------------------------------
     def _turn(self) -> List[GenRequest]:
         sch = self.scheduler
+        t_start = time.perf_counter()
         plan = sch.plan()
         if not plan:
             return []
@@ -91,7 +96,23 @@ class Engine:
             for e, t in zip(rows, toks):
                 sampled[e.request.id] = int(t)
         self.rt.check_status()
-        return sch.complete(plan, sampled)
+        done = sch.complete(plan, sampled)
+        n_decode = sum(1 for e in plan if len(e.tokens) == 1 and e.sample)
+        self.turn_log.append({"s": time.perf_counter() - t_start, "tokens": sum(len(e.tokens) for e in plan),
+                              "decode": n_decode, "pure_decode": n_decode == len(plan),
+                              "h2d": self.runner.last_batch.h2d_bytes + 12 * len(rows), "d2h": 4 * len(rows) + 4})
+        return done
+
+    def decode_rate(self, skip: int = 0) -> dict:
+        """Decoded tokens per second over the turns that held only decode tokens (the
+        reference reports the same as ``predicted_per_second``, ``lua/lgml/engine.lua:3225-3239``),
+        leaving out the first ``skip`` of them."""
+        turns = [t for t in self.turn_log if t["pure_decode"]][skip:]
+        secs = sum(t["s"] for t in turns)
+        toks = sum(t["decode"] for t in turns)
+        n = max(len(turns), 1)
+        return {"tok_s": toks / secs if secs > 0 else 0.0, "steps": len(turns),
+                "h2d_bytes_per_step": sum(t["h2d"] for t in turns) // n, "d2h_bytes_per_step": sum(t["d2h"] for t in turns) // n}
 
     # ---- public --------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None, stop: Optional[Sequence[int]] = None,
@@ -104,6 +125,7 @@ class Engine:
         opts = {**self.sampling_defaults, **sampling}
         stop_ids = list(stop) if stop is not None else self.eos_ids
         reqs = []
+        self.turn_log = []
         t0 = time.perf_counter()
         for i, p in enumerate(prompts):
             p = [int(t) for t in p]

@@ -108,6 +108,9 @@ class ModelRunner:
             for t in tokens:
                 if not 0 <= int(t) < vocab:
                     raise StepError(f"request {req.id!r}: token id {t} is outside the vocabulary of {vocab}")
+            for i in want:
+                if not 0 <= int(i) < len(tokens):
+                    raise StepError(f"request {req.id!r}: wanted place {i} is outside the {len(tokens)} tokens it brings")
             if max_pos is not None and req.n_tokens + len(tokens) > max_pos:
                 raise StepError(f"request {req.id!r}: context full ({req.n_tokens} + {len(tokens)} tokens > {max_pos} positions)")
 
@@ -137,6 +140,11 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += sum(len(e[1]) for e in entries)
         return logits
+
+    def graph_kernels(self, batch_size: int) -> int:
+        """Launches of this package's kernels that one replay of the graph of ``batch_size`` holds."""
+        slot = self._graphs.get(batch_size)
+        return slot.get("kernels", 0) if slot else 0
 
     def _graph_step(self, entries, stage) -> torch.Tensor:
         """A decode step through a captured graph.  The first step of a batch size runs
@@ -170,8 +178,10 @@ class ModelRunner:
             batch.decode_splits = ops.decode_splits(S, hkv, 1, batch.max_kv_len)
             slot["splits"] = batch.decode_splits
             g = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
             with torch.cuda.graph(g):
                 slot["logits"] = self.model.forward(self.rt, batch)
+            slot["kernels"] = ops.launch_count() - before
             slot["graph"] = g
         slot["graph"].replay()
         self.graph_replays += 1

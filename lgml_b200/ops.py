@@ -71,7 +71,19 @@ def _fn(lib_name: str, fn_name: str, argtypes):
     return fn
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launchers of this package have been called (a launcher starts one
+    kernel; split-KV attention starts two).  Launches replayed by a CUDA graph are not
+    counted here; the runner knows how many a graph holds."""
+    return _launches
+
+
 def _check(lib_name: str, rc: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if rc != 0:
         err = getattr(csrc.load(lib_name), f"lgml_{lib_name}_last_error")
         err.restype = ctypes.c_char_p
