@@ -63,7 +63,8 @@ def test_all_cuttings_match_oracle(tiny, dtype):
         results[name] = H.run_trace(runner, trace)
         assert runner.cache.groups[0].pool.n_held == 0
     # mixed, with a pool that cannot hold all requests at once: pages are used again
-    max_tokens = 64 * (pages_one + 3)
+    total_pages = sum(-(-len(s) // 64) for s in seqs.values())
+    max_tokens = 64 * min(2 * pages_one + 2, total_pages - 2)
     trace = H.trace_mixed(seqs, max_tokens=max_tokens, seed=7)
     assert max(len(st["entries"]) for st in trace) >= 3
     runner = make_runner(folder, dtype, n_pages=max_tokens // 64)
