@@ -39,6 +39,8 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_ref": ("attention_ref.cu", []),
     "sampling": ("sampling.cu", []),
     "attention_decode": ("attention_decode.cu", []),
+    "gemm_tcgen05": ("gemm_tcgen05.cu", []),
+    "attention_decode_noalloc": ("attention_decode_noalloc.cu", []),
 }
 
 _HEADERS = ["common.cuh"]
@@ -104,7 +106,9 @@ def _digest(name: str) -> str:
 
 
 # extra headers a library includes (its hash covers them)
-LIBRARY_HEADERS: Dict[str, List[str]] = {}
+LIBRARY_HEADERS: Dict[str, List[str]] = {
+    "attention_decode_noalloc": ["attention_decode.cu", "attention_decode_noalloc.h"],
+}
 
 
 def library_path(name: str) -> Path:

@@ -18,6 +18,7 @@ _STATUS_TEXT = {
     1: "a token id was outside the vocabulary",
     2: "a key/value write had no page in the block table",
     3: "attention met a position without a page in the block table",
+    10: "a tensor-core matrix product gave up waiting for its own copies or products",
 }
 
 
@@ -48,7 +49,7 @@ class Runtime:
         if self.dtype == torch.float32:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
             return ops.gemm_f32(x, w, out, bias)
-        return ops.gemm_bf16(x, w, out_dtype, bias, backend=self.gemm_backend)
+        return ops.gemm_bf16(x, w, out_dtype, bias, backend=self.gemm_backend, status=self.status)
 
     # ---- attention ---------------------------------------------------------------------
     def attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int) -> torch.Tensor:

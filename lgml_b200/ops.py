@@ -292,24 +292,84 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.
 # bfloat16 matrix products and the fast attention paths
 # ----------------------------------------------------------------------------------------
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
-              backend: str = "auto") -> torch.Tensor:
-    """y[M,N] = x[M,K] . w[N,K]^T (+ bias) with bfloat16 operands and float32 accumulation;
-    y is bfloat16 or float32.  ``backend``: "cublas" calls the library product (the reference
-    engine's matrix products are a library's too); "auto" is the same until a hand-written
-    tensor-core kernel takes the shape."""
+def tcgen05_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """TMA wants 16-byte aligned operands whose row strides are multiples of 16 bytes."""
+    return (x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def tcgen05_splits(M: int, N: int, K: int) -> int:
+    """K ranges for a product with few tokens: enough CTAs to cover the SMs about twice,
+    each with at least four 64-wide K blocks."""
+    if M > 256:
+        return 1
+    tiles = -(-N // 128)
+    k_blocks = -(-K // 64)
+    return max(1, min((2 * SM_COUNT) // tiles, k_blocks // 4, 16))
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor], status: torch.Tensor,
+                 n_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M,N] = x[M,K] . w[N,K]^T (+ bias) on tcgen05 tensor cores; bfloat16 in, float32
+    accumulation, out bfloat16 or float32."""
     _need(x, "gemm input", torch.bfloat16, 2)
     _need(w, "gemm weight", torch.bfloat16, 2)
-    if x.shape[1] != w.shape[1]:
-        raise KernelError(f"gemm_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
-    if x.shape[0] == 0:
-        return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
+    _need(out, "gemm output", ndim=2)
+    ldx, ldw, ldy = _rows_contiguous(x, "gemm input"), _rows_contiguous(w, "gemm weight"), _rows_contiguous(out, "gemm output")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_tcgen05: shapes or types disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise KernelError("gemm_tcgen05: bias length is not N")
+    if n_splits is None:
+        n_splits = tcgen05_splits(M, N, K)
+    n_splits = max(1, min(n_splits, -(-K // 64)))
+    if n_splits > 1:
+        need = n_splits * M * N
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=x.device)
+        if scratch.numel() < need or scratch.dtype != torch.float32:
+            raise KernelError(f"gemm_tcgen05: scratch of {scratch.numel()} floats, {need} needed")
+    fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                   c_int, c_void_p, c_void_p, c_void_p])
+    _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), 1 if out.dtype == torch.float32 else 0, M, N, K, ldx, ldw, ldy,
+                              n_splits, _ptr(scratch if n_splits > 1 else None), _ptr(status), _stream()), "gemm_tcgen05")
+    return out
+
+
+def gemm_cublas(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The library product (the reference engine's matrix products are a library's too)."""
     if bias is None and out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     y = torch.mm(x, w.t(), out_dtype=torch.float32)
     if bias is not None:
         y += bias
     return y if out_dtype == torch.float32 else y.to(out_dtype)
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
+              backend: str = "auto", status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[M,N] = x[M,K] . w[N,K]^T (+ bias) with bfloat16 operands and float32 accumulation;
+    y is bfloat16 or float32.  ``backend``: "tcgen05" is the hand-written tensor-core kernel,
+    "cublas" the library product; "auto" takes tcgen05 whenever its operands fit TMA's
+    alignment rules."""
+    _need(x, "gemm input", torch.bfloat16, 2)
+    _need(w, "gemm weight", torch.bfloat16, 2)
+    if x.shape[1] != w.shape[1]:
+        raise KernelError(f"gemm_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if x.shape[0] == 0:
+        return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
+    if backend == "cublas" or (backend == "auto" and not tcgen05_supports(x, w)):
+        return gemm_cublas(x, w, out_dtype, bias)
+    if backend not in ("auto", "tcgen05"):
+        raise KernelError(f"unknown gemm backend '{backend}'")
+    if status is None:
+        raise KernelError("gemm_bf16: the tcgen05 kernel needs the status word")
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+    return gemm_tcgen05(x, w, out, bias, status)
 
 
 SM_COUNT = 148  # B200
