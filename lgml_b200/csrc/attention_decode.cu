@@ -9,11 +9,14 @@
 // result (running maximum m, sum l, weighted values O) in scratch memory; a second kernel
 // merges the splits in a fixed order.  With one split the result is written directly.
 //
-// Per page of 64 keys a CTA does three phases: (1) scores: two threads per key read the
-// key row with 16-byte loads and dot it with all query heads, which sit in shared memory as
-// float32; (2) online softmax per head by one warp; (3) values: threads own pairs of output
-// dimensions and walk the keys.  Softmax, sums and the output accumulators are float32
-// (lua/lgml/transformer.lua:1805-1816 for the formula, :1845 for the scale).
+// A page of one KV head is contiguous in the cache ([page][kv head][64][D]), so one thread
+// brings it into shared memory with a bulk asynchronous copy (cp.async.bulk, completion on an
+// mbarrier); two stages are kept in flight so the copy of the next pages overlaps the math
+// of this one.  Per page: (1) scores, 8 lanes per key, each lane 16-byte chunks of the row,
+// reduced by shuffles; (2) online softmax per head by one warp; (3) values, threads own 8
+// output dimensions and walk the keys.  Softmax, sums and the output accumulators are float32
+// (lua/lgml/transformer.lua:1805-1816 for the formula, :1845 for the scale).  Waits on the
+// mbarriers are bounded; a wait that runs out sets `status` and the CTA winds down.
 #include <math.h>
 
 #include "common.cuh"
@@ -24,9 +27,36 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int THREADS = 128;
 constexpr int MAX_D = 256;
+constexpr int STAGES = 2;
+constexpr uint32_t SPIN_LIMIT = 4u << 20;
+constexpr int STATUS_TIMEOUT = 11;
 
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(status, STATUS_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 
 template <int G>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
@@ -35,13 +65,22 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo,
     float *__restrict__ part_o, float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int D, int n_chunks,
     float scale, int window, int *__restrict__ status) {
-    extern __shared__ float smem[];
-    float *qs = smem;                       // [D][G]
-    float *S = qs + D * G;                  // [PAGE][G] scores, then probabilities
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    // [STAGES][K page | V page] bf16, then the float arrays
+    const int page_bytes = PAGE * D * 2;
+    uint8_t *kv_s = smem_raw;
+    const int n_chunk_ = D / 8;
+    const size_t red_bytes = sizeof(float) * (size_t)min(THREADS / n_chunk_, PAGE) * G * D;
+    const size_t stage_bytes = (size_t)STAGES * 2 * page_bytes;
+    float *qs = reinterpret_cast<float *>(smem_raw + (stage_bytes > red_bytes ? stage_bytes : red_bytes));   // [G][D]
+    float *S = qs + G * D;                  // [PAGE][G] scores, then probabilities
     float *m_s = S + PAGE * G;              // [G]
     float *l_s = m_s + G;                   // [G]
     float *corr_s = l_s + G;                // [G]
-    float *red = corr_s + G;                // [KG][G][D] for the final sum over key groups
+    float *red = reinterpret_cast<float *>(kv_s);   // [key groups][G][D] for the final sum: the page stages are free by then
+    __shared__ uint64_t full_bar[STAGES];
 
     const int t = blockIdx.x;
     const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
@@ -61,70 +100,138 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const int pps = (span + n_splits - 1) / n_splits;
     const int pb = first_page + split * pps;
     const int pe = min(pb + pps, n_pages_seq);
+    const int n_iter = max(pe - pb, 0);
 
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[s])), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     // queries to shared memory as float32, pre-multiplied by the scale
-    for (int i = tid; i < D * G; i += THREADS) {
-        const int d = i / G, g = i - d * G;
+    for (int i = tid; i < G * D; i += THREADS) {
+        const int g = i / D, d = i - g * D;
         qs[i] = g < g_count ? to_f32(q[(size_t)t * ldq + (size_t)(h0 + g) * D + d]) * scale : 0.f;
     }
     if (tid < G) {
         m_s[tid] = -INFINITY;
         l_s[tid] = 0.f;
     }
-    const int NPAIR = D / 2;
-    const int KG = THREADS / NPAIR > PAGE ? PAGE : THREADS / NPAIR;   // key groups of the value phase
-    const bool pv_active = tid < KG * NPAIR;
-    const int kgroup = tid / NPAIR, pi = tid - kgroup * NPAIR;
-    float acc[G][2];
-#pragma unroll
-    for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = 0.f;
     __syncthreads();
 
-    const int key_local = tid >> 1, half = tid & 1;
-    const int half_d = D / 2;
-    const int nvec = half_d / 8;                                   // 16-byte loads per thread per key
-
-    for (int pg = pb; pg < pe; ++pg) {
+    // Issue the copy of the page of iteration `it` into stage it % STAGES: only the rows the
+    // query can see (rows 0 .. last valid key); a page the table does not hold is skipped.
+    auto issue = [&](int it) {
+        const int pg = pb + it;
         const int page = table[pg];
-        if (page < 0 || page >= n_pages) {                         // the table does not hold this block: flag, skip
-            if (tid == 0) atomicExch(status, 3);
-            continue;
+        uint64_t *bar = &full_bar[it % STAGES];
+        if (page < 0 || page >= n_pages) {
+            atomicExch(status, 3);
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+            return;
         }
-        const int k_begin = max(lo - pg * PAGE, 0), k_end = min(pos - pg * PAGE + 1, PAGE);
-        const __nv_bfloat16 *kp = k_pages + ((size_t)page * Hkv + kvh) * PAGE * D;
-        const __nv_bfloat16 *vp = v_pages + ((size_t)page * Hkv + kvh) * PAGE * D;
+        const int k_end = min(pos - pg * PAGE + 1, PAGE);
+        const uint32_t bytes = (uint32_t)k_end * D * 2;
+        const size_t off = ((size_t)page * Hkv + kvh) * PAGE * D;
+        uint8_t *dst = kv_s + (size_t)(it % STAGES) * 2 * page_bytes;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(2 * bytes) : "memory");
+        bulk_load(dst, k_pages + off, bytes, bar);
+        bulk_load(dst + page_bytes, v_pages + off, bytes, bar);
+    };
+    if (tid == 0)
+        for (int it = 0; it < min(n_iter, STAGES); ++it) issue(it);
 
-        // ---- (1) scores --------------------------------------------------------------------
-        float s[G];
+    const int n_chunk = D / 8;                         // 16-byte chunks per row
+    // value phase: thread = (key group, chunk of 8 dims)
+    const int KG = min(THREADS / n_chunk, PAGE);
+    const bool pv_active = tid < KG * n_chunk;
+    const int kgroup = tid / n_chunk, vchunk = tid - kgroup * n_chunk;
+    float acc[G][8];
 #pragma unroll
-        for (int g = 0; g < G; ++g) s[g] = 0.f;
-        const bool key_ok = key_local >= k_begin && key_local < k_end;
-        if (key_ok) {
-            const uint4 *row = reinterpret_cast<const uint4 *>(kp + (size_t)key_local * D + half * half_d);
-            const float *qh = qs + (size_t)half * half_d * G;
-#pragma unroll 4
-            for (int c = 0; c < nvec; ++c) {
-                const uint4 kk = row[c];
-                const uint32_t w[4] = {kk.x, kk.y, kk.z, kk.w};
+    for (int g = 0; g < G; ++g)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float k0 = bf16_lo(w[e]), k1 = bf16_hi(w[e]);
-                    const float *q0 = qh + (size_t)(c * 8 + e * 2) * G;
+        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+    // score phase: 8 lanes per key, 4 keys per warp at a time
+    const int sub = lane & 7, key_in_warp = lane >> 3;
+    bool alive = true;
+
+    for (int it = 0; it < n_iter; ++it) {
+        const int pg = pb + it;
+        const int page = table[pg];
+        const bool have = page >= 0 && page < n_pages;
+        if (alive && !mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1, status)) alive = false;
+        const int k_begin = max(lo - pg * PAGE, 0), k_end = min(pos - pg * PAGE + 1, PAGE);
+        const uint8_t *kp = kv_s + (size_t)(it % STAGES) * 2 * page_bytes;
+        const uint8_t *vp = kp + page_bytes;
+
+        // ---- (1) scores: warp w takes keys 16w .. 16w+15; lane = (key_in_warp, sub): four keys at a
+        // time, 8 lanes per key, lane `sub` owning the 16-byte chunks sub, sub + 8, ... of the row.
+        // The queries of a chunk are held in registers while the 4 x 4 keys of the warp go by.
+        {
+            const uint4 *rows4[4];
+            bool key_ok[4];
 #pragma unroll
-                    for (int g = 0; g < G; ++g) s[g] = fmaf(q0[g], k0, s[g]);
+            for (int kk = 0; kk < 4; ++kk) {
+                const int key = warp * 16 + kk * 4 + key_in_warp;
+                key_ok[kk] = have && alive && key >= k_begin && key < k_end;
+                rows4[kk] = reinterpret_cast<const uint4 *>(kp + (size_t)key * D * 2);
+            }
+            constexpr int GB = G < 4 ? G : 4;           // query heads held in registers at a time
+            float s[4][G];
 #pragma unroll
-                    for (int g = 0; g < G; ++g) s[g] = fmaf(q0[G + g], k1, s[g]);
+            for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                for (int g = 0; g < G; ++g) s[kk][g] = 0.f;
+            for (int c = sub; c < n_chunk; c += 8) {
+#pragma unroll
+                for (int g0 = 0; g0 < G; g0 += GB) {
+                    float qr[GB][8];
+#pragma unroll
+                    for (int g = 0; g < GB; ++g) {
+                        if (g0 + g < G) {
+                            const float4 lo4 = *reinterpret_cast<const float4 *>(qs + (size_t)(g0 + g) * D + c * 8);
+                            const float4 hi4 = *reinterpret_cast<const float4 *>(qs + (size_t)(g0 + g) * D + c * 8 + 4);
+                            qr[g][0] = lo4.x; qr[g][1] = lo4.y; qr[g][2] = lo4.z; qr[g][3] = lo4.w;
+                            qr[g][4] = hi4.x; qr[g][5] = hi4.y; qr[g][6] = hi4.z; qr[g][7] = hi4.w;
+                        }
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        if (key_ok[kk]) {
+                            const uint4 kv4 = rows4[kk][c];
+                            const uint32_t w[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
+#pragma unroll
+                            for (int g = 0; g < GB; ++g) {
+                                if (g0 + g < G) {
+                                    float a = s[kk][g0 + g];
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) a = fmaf(qr[g][2 * e], bf16_lo(w[e]), fmaf(qr[g][2 * e + 1], bf16_hi(w[e]), a));
+                                    s[kk][g0 + g] = a;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float v = s[kk][g];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    s[kk][g] = v;
+                }
+                if (sub == 0) {
+                    const int key = warp * 16 + kk * 4 + key_in_warp;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) S[key * G + g] = key_ok[kk] ? s[kk][g] : -INFINITY;
                 }
             }
         }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-            if (half == 0) S[key_local * G + g] = key_ok ? s[g] : -INFINITY;
-        }
         __syncthreads();
 
-        // ---- (2) online softmax, one warp per head -----------------------------------------
+        // ---- (2) online softmax, one warp per head ---------------------------------------------
         for (int g = warp; g < G; g += THREADS / 32) {
             const float s0 = S[lane * G + g], s1 = S[(lane + 32) * G + g];
             const float mx = warp_max(fmaxf(s0, s1));
@@ -147,37 +254,49 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         }
         __syncthreads();
 
-        // ---- (3) values --------------------------------------------------------------------
+        // ---- (3) values --------------------------------------------------------------------------
         if (pv_active) {
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 const float c = corr_s[g];
-                acc[g][0] *= c;
-                acc[g][1] *= c;
-            }
-            const uint32_t *vcol = reinterpret_cast<const uint32_t *>(vp) + pi;
-#pragma unroll 4
-            for (int key = k_begin + kgroup; key < k_end; key += KG) {
-                const uint32_t vv = vcol[(size_t)key * NPAIR];
-                const float v0 = bf16_lo(vv), v1 = bf16_hi(vv);
-                const float *p = S + key * G;
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    acc[g][0] = fmaf(p[g], v0, acc[g][0]);
-                    acc[g][1] = fmaf(p[g], v1, acc[g][1]);
+                for (int e = 0; e < 8; ++e) acc[g][e] *= c;
+            }
+            if (have && alive) {
+                for (int key = k_begin + kgroup; key < k_end; key += KG) {
+                    const uint4 vv = *reinterpret_cast<const uint4 *>(vp + ((size_t)key * D + vchunk * 8) * 2);
+                    const uint32_t w[4] = {vv.x, vv.y, vv.z, vv.w};
+                    const float *p = S + key * G;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float pg_ = p[g];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[g][2 * e] = fmaf(pg_, bf16_lo(w[e]), acc[g][2 * e]);
+                            acc[g][2 * e + 1] = fmaf(pg_, bf16_hi(w[e]), acc[g][2 * e + 1]);
+                        }
+                    }
                 }
             }
         }
         __syncthreads();
+        // the stage is free: bring in the page two iterations ahead
+        if (tid == 0 && alive && it + STAGES < n_iter) issue(it + STAGES);
+    }
+    // If a wait ran out, copies may still be in flight: give them a bounded time to land
+    // before the shared memory can be handed to another CTA.
+    if (!alive && tid == 0) {
+        for (int it = max(n_iter - STAGES, 0); it < n_iter; ++it)
+            for (uint32_t spin = 0; spin < SPIN_LIMIT && !mbar_try_wait(&full_bar[it % STAGES], (it / STAGES) & 1); ++spin) {
+            }
     }
 
     // ---- sum over key groups, then write ------------------------------------------------------
     if (pv_active) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            red[((size_t)kgroup * G + g) * D + 2 * pi] = acc[g][0];
-            red[((size_t)kgroup * G + g) * D + 2 * pi + 1] = acc[g][1];
-        }
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) red[((size_t)kgroup * G + g) * D + vchunk * 8 + e] = acc[g][e];
     }
     __syncthreads();
     for (int i = tid; i < g_count * D; i += THREADS) {
@@ -199,6 +318,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 // Merge the splits of one (token, head) in split order.
 __global__ void decode_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                                       __nv_bfloat16 *__restrict__ out, int ldo, int n_splits, int H, int D) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const float2 *ml = part_ml + ((size_t)t * H + h) * n_splits;
     float mm = -INFINITY;
@@ -215,10 +336,11 @@ __global__ void decode_combine_kernel(const float *__restrict__ part_o, const fl
 }
 
 size_t smem_bytes(int G, int D) {
-    const int npair = D / 2;
-    int kg = THREADS / npair;
+    const int n_chunk = D / 8;
+    int kg = THREADS / n_chunk;
     if (kg > PAGE) kg = PAGE;
-    return sizeof(float) * ((size_t)D * G + (size_t)PAGE * G + 3 * G + (size_t)kg * G * D);
+    size_t stages = (size_t)STAGES * 2 * PAGE * D * 2, red = sizeof(float) * (size_t)kg * G * D;
+    return (stages > red ? stages : red) + sizeof(float) * ((size_t)D * G + (size_t)PAGE * G + 3 * G);
 }
 
 template <int G>
@@ -227,8 +349,11 @@ int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, con
            float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int D, int n_chunks, float scale, int window,
            int *status, cudaStream_t stream) {
     const size_t smem = smem_bytes(G, D);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decode_attention_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    decode_attention_kernel<G><<<grid, THREADS, smem, stream>>>(q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("decode_attention: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    lgml_launch(decode_attention_kernel<G>, grid, THREADS, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
                                                                v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, D,
                                                                n_chunks, scale, window, status);
     return 0;
@@ -252,6 +377,7 @@ LGML_API int lgml_decode_attention(const void *q, int ldq, const int *positions,
     LGML_REQUIRE(D >= 16 && D <= MAX_D && D % 16 == 0, "decode_attention: head_dim %d must be a multiple of 16 up to %d", D, MAX_D);
     LGML_REQUIRE(n_splits >= 1 && n_splits <= 65535, "decode_attention: bad split count %d", n_splits);
     LGML_REQUIRE(n_splits == 1 || scratch != nullptr, "decode_attention: %d splits need scratch memory", n_splits);
+    LGML_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0, "decode_attention: the cache must be 16-byte aligned");
     if (n_tokens == 0) return 0;
     const int group = H / Hkv;
     const int n_chunks = (group + 7) / 8;
@@ -262,21 +388,23 @@ LGML_API int lgml_decode_attention(const void *q, int ldq, const int *positions,
     float2 *part_ml = reinterpret_cast<float2 *>(scratch + (size_t)n_tokens * H * n_splits * D);
     const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
+    int lrc = 0;
 #define LGML_CASE(GG)                                                                                                             \
     case GG:                                                                                                                      \
-        launch<GG>(grid, qq, ldq, positions, seq_of_token, block_table, max_blocks, kk, vv, n_pages, oo, ldo, part_o, part_ml,    \
-                   n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);                                                 \
+        lrc = launch<GG>(grid, qq, ldq, positions, seq_of_token, block_table, max_blocks, kk, vv, n_pages, oo, ldo, part_o, part_ml, \
+                         n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);                                           \
         break;
     switch (G) {
         LGML_CASE(1) LGML_CASE(2) LGML_CASE(3) LGML_CASE(4) LGML_CASE(5) LGML_CASE(6) LGML_CASE(7) LGML_CASE(8)
         default: LGML_FAIL("decode_attention: group of %d heads not handled", G);
     }
 #undef LGML_CASE
+    if (lrc) return lrc;
     int rc = lgml_launch_status("decode_attention");
     if (rc) return rc;
     if (n_splits > 1) {
         dim3 cgrid(n_tokens, H);
-        decode_combine_kernel<<<cgrid, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, oo, ldo, n_splits, H, D);
+        lgml_launch(decode_combine_kernel, cgrid, D >= 128 ? 128 : 64, 0, stream, part_o, part_ml, oo, ldo, n_splits, H, D);
         rc = lgml_launch_status("decode_combine");
     }
     return rc;

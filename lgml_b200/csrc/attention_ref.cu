@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
     const int *__restrict__ block_table, int max_blocks, const T *__restrict__ k_pages, const T *__restrict__ v_pages,
     int n_pages, int page_size, T *__restrict__ out, int ldo, int H, int Hkv, int D, float scale, int window,
     int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float qs[MAX_D];
     __shared__ float acc_w[WARPS][MAX_D];
     __shared__ float m_w[WARPS], l_w[WARPS];
@@ -104,11 +106,11 @@ LGML_API int lgml_paged_attention_ref(const void *q, int dtype, int ldq, const i
     if (n_tokens == 0) return 0;
     dim3 grid(n_tokens, H);
     if (dtype == LGML_F32)
-        paged_attention_ref_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
+        lgml_launch(paged_attention_ref_kernel<float>, grid, WARPS * 32, 0, stream, 
             (const float *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const float *)k_pages, (const float *)v_pages,
             n_pages, page_size, (float *)out, ldo, H, Hkv, D, scale, window, status);
     else if (dtype == LGML_BF16)
-        paged_attention_ref_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
+        lgml_launch(paged_attention_ref_kernel<__nv_bfloat16>, grid, WARPS * 32, 0, stream, 
             (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages,
             (const __nv_bfloat16 *)v_pages, n_pages, page_size, (__nv_bfloat16 *)out, ldo, H, Hkv, D, scale, window, status);
     else

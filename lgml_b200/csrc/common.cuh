@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define LGML_API extern "C" __attribute__((visibility("default")))
 
@@ -33,6 +34,42 @@ static inline int lgml_launch_status(const char *what) {
         return (int)e;
     }
     return 0;
+}
+
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of this package is launched with the "programmatic stream serialization"
+// attribute: the next kernel in the stream may start (its blocks become resident, and may do
+// work that does not depend on earlier kernels, such as fetching weights) once all blocks of
+// this one have called pdl_trigger().  A kernel calls pdl_wait() before it reads anything an
+// earlier kernel wrote and before it writes anything at all; the wait returns when the
+// kernels before it have completed and their writes are visible.  Decoding is a chain of many
+// short kernels, and this overlaps each kernel's start-up with its predecessor's tail.
+// LGML_PDL=0 in the environment turns the attribute off (the instructions are then no-ops).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static inline bool lgml_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char *e = getenv("LGML_PDL");
+        enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return enabled != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t lgml_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = lgml_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 // Element types: 0 = float32, 1 = bfloat16.

@@ -11,26 +11,29 @@ LGML_DEFINE_LAST_ERROR(lgml_elementwise)
 template <typename TW>
 __global__ void embed_rows_kernel(const TW *__restrict__ table, const int *__restrict__ ids,
                                   float *__restrict__ out, int width, int vocab, int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
-    if (id < 0 || id >= vocab) {  // the host checks ids first; never read out of the table
-        if (threadIdx.x == 0) atomicExch(status, 1);
-        for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = 0.f;
-        return;
-    }
-    const TW *row = table + (size_t)id * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = to_f32(row[i]);
+    const bool ok = id >= 0 && id < vocab;           // the host checks ids first; never read out of the table
+    if (!ok && threadIdx.x == 0 && blockIdx.y == 0) atomicExch(status, 1);
+    const TW *row = table + (size_t)(ok ? id : 0) * width;
+    const int i0 = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (i0 + j < width) out[(size_t)t * width + i0 + j] = ok ? to_f32(row[i0 + j]) : 0.f;
 }
 
 LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids, float *out, int n_tokens,
                              int width, int vocab, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes");
     if (n_tokens == 0) return 0;
-    const int threads = width >= 1024 ? 256 : 128;
+    const int threads = 128;
+    dim3 grid(n_tokens, (width + threads * 4 - 1) / (threads * 4));
     if (table_dtype == LGML_F32)
-        embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>((const float *)table, ids, out, width, vocab, status);
+        lgml_launch(embed_rows_kernel<float>, grid, threads, 0, stream, (const float *)table, ids, out, width, vocab, status);
     else if (table_dtype == LGML_BF16)
-        embed_rows_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16 *)table, ids, out, width, vocab, status);
+        lgml_launch(embed_rows_kernel<__nv_bfloat16>, grid, threads, 0, stream, (const __nv_bfloat16 *)table, ids, out, width, vocab, status);
     else
         LGML_FAIL("embed_rows: unknown table type %d", table_dtype);
     return lgml_launch_status("embed_rows");
@@ -45,8 +48,11 @@ LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids,
 // One block per output row; the mean square is summed in a fixed order.
 // ---------------------------------------------------------------------------------------
 template <typename TD, typename TO>
-__global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta, const float *__restrict__ weight,
+__global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta, int n_parts, long long part_stride,
+                               const float *__restrict__ delta_bias, const float *__restrict__ weight,
                                const int *__restrict__ rows, TO *__restrict__ out, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[32];
     extern __shared__ float cache[];  // the row, so that x is read once
     const int r = blockIdx.x;
@@ -54,10 +60,15 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
     float *xr = x + src * width;
     const TD *dr = delta ? delta + src * width : nullptr;
     float ss = 0.f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = xr[i];
         if (dr) {
-            v += to_f32(dr[i]);
+            // the parts are the partial sums of a matrix product cut along K: added in order
+            float d = to_f32(dr[i]);
+            for (int p = 1; p < n_parts; ++p) d += to_f32(dr[(size_t)p * part_stride + i]);
+            if (delta_bias) d += delta_bias[i];
+            v += d;
             if (!rows) xr[i] = v;
         }
         cache[i] = v;
@@ -65,35 +76,43 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
     }
     const float total = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
+#pragma unroll 4
     for (int i = threadIdx.x; i < width; i += blockDim.x)
         out[(size_t)r * width + i] = from_f32<TO>(cache[i] * inv * weight[i]);
 }
 
 template <typename TD>
-static int rmsnorm_dispatch(float *x, const TD *delta, const float *weight, const int *rows, void *out, int out_dtype,
-                            int n_rows, int width, float eps, cudaStream_t stream) {
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long part_stride, const float *delta_bias,
+                            const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
+                            cudaStream_t stream) {
+    // one block per row; the block's size depends on the width only, so a row's sum is formed
+    // in the same order whatever else is in the batch
+    const int threads = width >= 4096 ? 1024 : (width >= 1024 ? 512 : (width >= 256 ? 256 : 128));
     const size_t smem = (size_t)width * sizeof(float);
     if (out_dtype == LGML_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<TD, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        rmsnorm_kernel<TD, float><<<n_rows, threads, smem, stream>>>(x, delta, weight, rows, (float *)out, width, eps);
+        lgml_launch(rmsnorm_kernel<TD, float>, n_rows, threads, smem, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<TD, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        rmsnorm_kernel<TD, __nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, delta, weight, rows, (__nv_bfloat16 *)out, width, eps);
+        lgml_launch(rmsnorm_kernel<TD, __nv_bfloat16>, n_rows, threads, smem, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps);
     }
     return lgml_launch_status("rmsnorm");
 }
 
-LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, const float *weight, const int *rows, void *out,
-                          int out_dtype, int n_rows, int width, float eps, cudaStream_t stream) {
+// delta: null, or [n_parts][rows of x][width] (part_stride elements between parts) whose parts
+// are summed in order, plus delta_bias[width] if given.
+LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, int n_parts, long long part_stride, const float *delta_bias,
+                          const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
+                          cudaStream_t stream) {
     LGML_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes");
     LGML_REQUIRE((size_t)width * sizeof(float) <= 200 * 1024, "rmsnorm: width %d is over the %d a row buffer holds", width, 200 * 1024 / 4);
     LGML_REQUIRE(out_dtype == LGML_F32 || out_dtype == LGML_BF16, "rmsnorm: unknown output type %d", out_dtype);
+    LGML_REQUIRE(delta == nullptr || n_parts >= 1, "rmsnorm: a delta has at least one part");
     if (n_rows == 0) return 0;
     if (delta == nullptr || delta_dtype == LGML_F32)
-        return rmsnorm_dispatch<float>(x, (const float *)delta, weight, rows, out, out_dtype, n_rows, width, eps, stream);
+        return rmsnorm_dispatch<float>(x, (const float *)delta, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, stream);
     if (delta_dtype == LGML_BF16)
-        return rmsnorm_dispatch<__nv_bfloat16>(x, (const __nv_bfloat16 *)delta, weight, rows, out, out_dtype, n_rows, width, eps, stream);
+        return rmsnorm_dispatch<__nv_bfloat16>(x, (const __nv_bfloat16 *)delta, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, stream);
     LGML_FAIL("rmsnorm: unknown delta type %d", delta_dtype);
 }
 
@@ -102,27 +121,30 @@ LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, const fl
 // (lua/lgml/transformer.lua:2047-2048; silu(a) = a * sigmoid(a), src/lgml.c:1476-1482)
 // ---------------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ act, int n_tokens, int width) {
+__global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ act, int n_tokens, int width, int paired) {
+    pdl_trigger();
+    pdl_wait();
     const size_t total = (size_t)n_tokens * width;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / width, f = i - t * width;
-        const float g = to_f32(gu[t * 2 * width + f]);
-        const float u = to_f32(gu[t * 2 * width + width + f]);
+        const float g = to_f32(gu[t * 2 * width + (paired ? 2 * f : f)]);
+        const float u = to_f32(gu[t * 2 * width + (paired ? 2 * f + 1 : width + f)]);
         const float s = g / (1.0f + expf(-g));
         act[i] = from_f32<T>(s * u);
     }
 }
 
-LGML_API int lgml_silu_mul(const void *gu, void *act, int dtype, int n_tokens, int width, cudaStream_t stream) {
+// paired: gate and up of feature f are at columns 2f and 2f + 1; else at f and width + f.
+LGML_API int lgml_silu_mul(const void *gu, void *act, int dtype, int n_tokens, int width, int paired, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && width > 0, "silu_mul: bad sizes");
     if (n_tokens == 0) return 0;
     const size_t total = (size_t)n_tokens * width;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == LGML_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float *)gu, (float *)act, n_tokens, width);
+        lgml_launch(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float *)gu, (float *)act, n_tokens, width, paired);
     else if (dtype == LGML_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)act, n_tokens, width);
+        lgml_launch(silu_mul_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16 *)gu, (__nv_bfloat16 *)act, n_tokens, width, paired);
     else
         LGML_FAIL("silu_mul: unknown type %d", dtype);
     return lgml_launch_status("silu_mul");
@@ -133,6 +155,8 @@ LGML_API int lgml_silu_mul(const void *gu, void *act, int dtype, int n_tokens, i
 // ---------------------------------------------------------------------------------------
 template <typename TD>
 __global__ void residual_add_kernel(float *__restrict__ x, const TD *__restrict__ delta, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         x[i] += to_f32(delta[i]);
 }
@@ -144,9 +168,9 @@ LGML_API int lgml_residual_add(float *x, const void *delta, int delta_dtype, lon
     const long long want = (total + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (delta_dtype == LGML_F32)
-        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float *)delta, (size_t)total);
+        lgml_launch(residual_add_kernel<float>, blocks, threads, 0, stream, x, (const float *)delta, (size_t)total);
     else if (delta_dtype == LGML_BF16)
-        residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16 *)delta, (size_t)total);
+        lgml_launch(residual_add_kernel<__nv_bfloat16>, blocks, threads, 0, stream, x, (const __nv_bfloat16 *)delta, (size_t)total);
     else
         LGML_FAIL("residual_add: unknown type %d", delta_dtype);
     return lgml_launch_status("residual_add");
@@ -167,6 +191,8 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
 
 template <typename T>
 __global__ void fill_normal_kernel(T *__restrict__ out, size_t n, float mean, float sd, uint64_t seed) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const uint64_t h = splitmix64(seed ^ splitmix64(i));
         const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
@@ -183,9 +209,9 @@ LGML_API int lgml_fill_normal(void *out, int dtype, long long n, float mean, flo
     const long long want = (n + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 32 ? want : 148 * 32);
     if (dtype == LGML_F32)
-        fill_normal_kernel<float><<<blocks, threads, 0, stream>>>((float *)out, (size_t)n, mean, sd, seed);
+        lgml_launch(fill_normal_kernel<float>, blocks, threads, 0, stream, (float *)out, (size_t)n, mean, sd, seed);
     else if (dtype == LGML_BF16)
-        fill_normal_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16 *)out, (size_t)n, mean, sd, seed);
+        lgml_launch(fill_normal_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16 *)out, (size_t)n, mean, sd, seed);
     else
         LGML_FAIL("fill_normal: unknown type %d", dtype);
     return lgml_launch_status("fill_normal");

@@ -14,6 +14,8 @@ template <typename TO>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float *__restrict__ A, const float *__restrict__ W,
                                                        const float *__restrict__ bias, TO *__restrict__ C, int M, int N, int K,
                                                        int lda, int ldw, int ldc) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -75,9 +77,9 @@ LGML_API int lgml_gemm_f32(const float *A, const float *W, const float *bias, vo
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     LGML_REQUIRE(grid.y <= 65535, "gemm_f32: M=%d is over %d rows", M, 65535 * BM);
     if (out_dtype == LGML_F32)
-        gemm_f32_kernel<float><<<grid, 256, 0, stream>>>(A, W, bias, (float *)C, M, N, K, lda, ldw, ldc);
+        lgml_launch(gemm_f32_kernel<float>, grid, 256, 0, stream, A, W, bias, (float *)C, M, N, K, lda, ldw, ldc);
     else if (out_dtype == LGML_BF16)
-        gemm_f32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(A, W, bias, (__nv_bfloat16 *)C, M, N, K, lda, ldw, ldc);
+        lgml_launch(gemm_f32_kernel<__nv_bfloat16>, grid, 256, 0, stream, A, W, bias, (__nv_bfloat16 *)C, M, N, K, lda, ldw, ldc);
     else
         LGML_FAIL("gemm_f32: unknown output type %d", out_dtype);
     return lgml_launch_status("gemm_f32");

@@ -128,6 +128,7 @@ struct Params {
     int k_blocks;     // ceil(K / 64)
     int kb_per_split; // k blocks per grid.z slice
     int transposed;   // 1: the tile is y^T (A = weights, B = tokens)
+    int swiglu;       // 1: feature rows come in (gate, up) pairs; the output is silu(gate) * up, half as wide
     int out_f32;      // output element type
     int ldo;          // row stride of the output in elements
     long long split_stride;   // elements between the partial results of two splits (0: no split)
@@ -146,6 +147,7 @@ struct Smem {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b, const Params p) {
+    pdl_trigger();   // the next kernel may start its own set-up and weight fetch
     extern __shared__ uint8_t smem_raw[];
     // tiles want 1024-byte alignment for the 128-byte swizzle
     uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -181,10 +183,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            // Weights do not depend on the kernels before this one: fetch them for the first
+            // stages at once, then wait for the earlier kernels, then fetch the activations.
+            const int pre = min(n_kb, STAGES);
+            for (int i = 0; i < pre; ++i) {
+                uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], Smem<BN>::STAGE_BYTES);
+                if (p.transposed) tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
+                else tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
+                if (p.transposed) tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
+                else tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
+            }
+            int issued = pre;
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag, p.status)) break;
                 if (*abort_flag) break;
                 uint8_t *a_dst = tiles + (size_t)s * Smem<BN>::STAGE_BYTES;
                 uint8_t *b_dst = a_dst + Smem<BN>::A_BYTES;
@@ -228,6 +245,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         }
     } else {
         // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32 * (w % 4) .. + 31 ----------------
+        pdl_wait();   // nothing is written before the earlier kernels are done (an empty K range gets here at once)
         const bool ok = mbar_wait(&acc_bar, 0, abort_flag, p.status);
         tcgen05_fence_after();
         const int quarter = warp & 3;
@@ -245,8 +263,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                 tcgen05_wait_ld();
                 if (p.transposed) {
                     // tile row = feature (a_row), tile column = token: y[token][feature]
-                    if (a_row < p.rows_a) {
-                        const float b = p.bias ? p.bias[a_row] : 0.f;
+                    const bool row_ok = a_row < p.rows_a;
+                    const float b = (p.bias && row_ok) ? p.bias[a_row] : 0.f;
+                    if (p.swiglu) {
+                        // lanes 2i and 2i+1 hold the gate and the up row of feature a_row / 2
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float v = __uint_as_float(r[j]) + b;
+                            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+                            const int token = tile_b * BN + c0 + j;
+                            if (row_ok && (lane & 1) == 0 && token < p.rows_b) {
+                                const float act = v / (1.0f + expf(-v)) * up;
+                                const size_t o = (size_t)token * p.ldo + (a_row >> 1);
+                                if (f32) out_f[o] = act;
+                                else out_h[o] = __float2bfloat16_rn(act);
+                            }
+                        }
+                    } else if (row_ok) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int token = tile_b * BN + c0 + j;
@@ -264,30 +297,55 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + ((p.bias && f0 + j < p.rows_b) ? p.bias[f0 + j] : 0.f);
-                        const size_t o = (size_t)a_row * p.ldo + f0;
-                        if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0) {
-                            // whole run in range and 16-byte aligned (f0 is a multiple of 16): vector stores
-                            if (f32) {
-                                float4 *dst = reinterpret_cast<float4 *>(out_f + o);
+                        if (p.swiglu) {
+                            // columns 2j and 2j+1 are the gate and the up of feature (f0 / 2) + j
+                            const size_t o = (size_t)a_row * p.ldo + (f0 >> 1);
+                            float act[8];
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            } else {
-                                uint32_t h[8];
+                            for (int j = 0; j < 8; ++j) act[j] = v[2 * j] / (1.0f + expf(-v[2 * j])) * v[2 * j + 1];
+                            if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0 && !f32) {
+                                uint32_t h[4];
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    __nv_bfloat162 pr = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 pr = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
                                     h[j] = *reinterpret_cast<uint32_t *>(&pr);
                                 }
-                                uint4 *dst = reinterpret_cast<uint4 *>(out_h + o);
-                                dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-                                dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                                *reinterpret_cast<uint4 *>(out_h + o) = make_uint4(h[0], h[1], h[2], h[3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    if (f0 + 2 * j + 1 < p.rows_b) {
+                                        if (f32) out_f[o + j] = act[j];
+                                        else out_h[o + j] = __float2bfloat16_rn(act[j]);
+                                    }
+                                }
                             }
                         } else {
+                            const size_t o = (size_t)a_row * p.ldo + f0;
+                            if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0) {
+                                // whole run in range and 16-byte aligned (f0 is a multiple of 16): vector stores
+                                if (f32) {
+                                    float4 *dst = reinterpret_cast<float4 *>(out_f + o);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                if (f0 + j < p.rows_b) {
-                                    if (f32) out_f[o + j] = v[j];
-                                    else out_h[o + j] = __float2bfloat16_rn(v[j]);
+                                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                                } else {
+                                    uint32_t h[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        __nv_bfloat162 pr = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                        h[j] = *reinterpret_cast<uint32_t *>(&pr);
+                                    }
+                                    uint4 *dst = reinterpret_cast<uint4 *>(out_h + o);
+                                    dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                                    dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) {
+                                    if (f0 + j < p.rows_b) {
+                                        if (f32) out_f[o + j] = v[j];
+                                        else out_h[o + j] = __float2bfloat16_rn(v[j]);
+                                    }
                                 }
                             }
                         }
@@ -315,6 +373,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
 template <typename TO>
 __global__ void splitk_reduce_kernel(const float *__restrict__ part, long long split_stride, int n_splits, const float *__restrict__ bias,
                                      TO *__restrict__ out, int ldo, int rows, int cols) {
+    pdl_trigger();
+    pdl_wait();
     const long long total = (long long)rows * cols;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
@@ -366,7 +426,7 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, dim3 g
         if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    gemm_tcgen05_kernel<BN, STAGES><<<grid, THREADS, smem, stream>>>(ma, mb, p);
+    lgml_launch(gemm_tcgen05_kernel<BN, STAGES>, grid, THREADS, smem, stream, ma, mb, p);
     return lgml_launch_status("gemm_tcgen05");
 }
 
@@ -379,10 +439,15 @@ LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) 
 
 // y[M, N] = x[M, K] . w[N, K]^T (+ bias[N]);  x, w bfloat16 with row strides ldx, ldw (elements);
 // y bfloat16 or float32 with row stride ldy.  n_splits > 1 cuts K and needs `scratch`.
+// swiglu: the rows of w come in (gate, up) pairs and y[M, N / 2] = silu(gate) * up (no K split then).
+// reduce = 0 with n_splits > 1 leaves the partial sums [n_splits, M, N] in scratch for the next
+// kernel to add (bias is then not applied).
 LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx,
-                               int ldw, int ldy, int n_splits, float *scratch, int *status, cudaStream_t stream) {
+                               int ldw, int ldy, int n_splits, float *scratch, int swiglu, int reduce, int *status,
+                               cudaStream_t stream) {
     LGML_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
-    LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= N, "gemm_tcgen05: a leading dimension is smaller than its row");
+    LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: a leading dimension is smaller than its row");
+    LGML_REQUIRE(!swiglu || (N % 2 == 0 && n_splits == 1), "gemm_tcgen05: the gated epilogue needs an even N and no K split");
     LGML_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: row strides (%d, %d) must be multiples of 8 elements (16 bytes) for TMA", ldx, ldw);
     LGML_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned for TMA");
     LGML_REQUIRE(n_splits >= 1 && n_splits <= 64, "gemm_tcgen05: bad split count %d", n_splits);
@@ -399,6 +464,7 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
     p.out = n_splits > 1 ? (void *)scratch : y;
     p.bias = n_splits > 1 ? nullptr : bias;
     p.status = status;
+    p.swiglu = swiglu;
     CUtensorMap ma, mb;
     int rc;
     dim3 grid;
@@ -430,15 +496,15 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         default: rc = launch<256, 4>(ma, mb, p, grid, stream); break;
     }
     if (rc) return rc;
-    if (n_splits > 1) {
+    if (n_splits > 1 && reduce) {
         const long long total = (long long)M * N;
         const int threads = 256;
         const long long want = (total + threads - 1) / threads;
         const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
         if (y_f32)
-            splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(scratch, p.split_stride, n_splits, bias, (float *)y, ldy, M, N);
+            lgml_launch(splitk_reduce_kernel<float>, blocks, threads, 0, stream, scratch, p.split_stride, n_splits, bias, (float *)y, ldy, M, N);
         else
-            splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(scratch, p.split_stride, n_splits, bias, (__nv_bfloat16 *)y, ldy, M, N);
+            lgml_launch(splitk_reduce_kernel<__nv_bfloat16>, blocks, threads, 0, stream, scratch, p.split_stride, n_splits, bias, (__nv_bfloat16 *)y, ldy, M, N);
         rc = lgml_launch_status("gemm_tcgen05 split reduce");
     }
     return rc;

@@ -47,6 +47,8 @@ __device__ Best block_argmax(const float *row, int V, Best *smem) {
 __global__ void __launch_bounds__(THREADS) sample_rows_kernel(const float *__restrict__ logits, int ld, int V,
                                                               const float *__restrict__ temperature,
                                                               const double *__restrict__ uniform, int *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ Best best_s[32];
     __shared__ double part[THREADS];
     const int r = blockIdx.x;
@@ -100,18 +102,70 @@ __global__ void __launch_bounds__(THREADS) sample_rows_kernel(const float *__res
     }
 }
 
-__global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float *__restrict__ logits, int ld, int V, int *__restrict__ out) {
+// argmax in two passes so that a few rows still use the whole GPU: each row is cut into
+// AM_CHUNKS ranges, one block finds the best of a range, then one warp picks among the ranges.
+constexpr int AM_CHUNKS = 32;
+constexpr int AM_THREADS = 256;
+
+__global__ void __launch_bounds__(AM_THREADS) argmax_partial_kernel(const float *__restrict__ logits, int ld, int V,
+                                                                    float *__restrict__ part_v, int *__restrict__ part_i) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ Best best_s[32];
-    const Best top = block_argmax(logits + (size_t)blockIdx.x * ld, V, best_s);
-    if (threadIdx.x == 0) out[blockIdx.x] = top.i;
+    const int r = blockIdx.x, c = blockIdx.y;
+    const int per = (V + AM_CHUNKS - 1) / AM_CHUNKS;
+    const int b = c * per, e = min(V, b + per);
+    const float *row = logits + (size_t)r * ld;
+    Best best{-INFINITY, 0x7fffffff};
+#pragma unroll 4
+    for (int i = b + threadIdx.x; i < e; i += AM_THREADS) {
+        const float v = row[i];
+        if (v > best.v || (v == best.v && i < best.i)) best = Best{v, i};
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) best_s[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Best total = best_s[0];
+        for (int w = 1; w < AM_THREADS / 32; ++w) total = better(total, best_s[w]);
+        part_v[r * AM_CHUNKS + c] = total.v;
+        part_i[r * AM_CHUNKS + c] = total.i;
+    }
+}
+
+__global__ void argmax_final_kernel(const float *__restrict__ part_v, const int *__restrict__ part_i, int *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, lane = threadIdx.x;
+    Best best{part_v[r * AM_CHUNKS + lane], part_i[r * AM_CHUNKS + lane]};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (lane == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;   // a row of NaN or -inf: index 0
 }
 }  // namespace
 
-LGML_API int lgml_argmax_rows(const float *logits, int ld, int n_rows, int V, int *out, cudaStream_t stream) {
+// scratch: n_rows * 32 floats and n_rows * 32 ints (lgml_argmax_scratch_words words in all).
+LGML_API long long lgml_argmax_scratch_words(int n_rows) { return 2LL * n_rows * AM_CHUNKS; }
+
+LGML_API int lgml_argmax_rows(const float *logits, int ld, int n_rows, int V, int *out, void *scratch, cudaStream_t stream) {
     LGML_REQUIRE(n_rows >= 0 && V > 0 && ld >= V, "argmax_rows: bad sizes");
+    LGML_REQUIRE(scratch != nullptr || n_rows == 0, "argmax_rows: scratch memory is missing");
     if (n_rows == 0) return 0;
-    argmax_rows_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, V, out);
-    return lgml_launch_status("argmax_rows");
+    float *part_v = (float *)scratch;
+    int *part_i = (int *)scratch + (size_t)n_rows * AM_CHUNKS;
+    lgml_launch(argmax_partial_kernel, dim3(n_rows, AM_CHUNKS), AM_THREADS, 0, stream, logits, ld, V, part_v, part_i);
+    int rc = lgml_launch_status("argmax_rows");
+    if (rc) return rc;
+    lgml_launch(argmax_final_kernel, n_rows, 32, 0, stream, (const float *)part_v, (const int *)part_i, out);
+    return lgml_launch_status("argmax_rows final");
 }
 
 // temperature[r] <= 0 takes the argmax of row r; uniform[r] in [0, 1) is used otherwise.
@@ -119,6 +173,6 @@ LGML_API int lgml_sample_rows(const float *logits, int ld, int n_rows, int V, co
                               int *out, cudaStream_t stream) {
     LGML_REQUIRE(n_rows >= 0 && V > 0 && ld >= V, "sample_rows: bad sizes");
     if (n_rows == 0) return 0;
-    sample_rows_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, V, temperature, uniform, out);
+    lgml_launch(sample_rows_kernel, n_rows, THREADS, 0, stream, logits, ld, V, temperature, uniform, out);
     return lgml_launch_status("sample_rows");
 }

@@ -83,7 +83,10 @@ class Engine:
         rows = [e for e in plan if e.sample]
         if rows:
             neutral = all(e.request.params.is_neutral for e in rows)
-            if neutral:
+            if neutral and all(e.request.params.greedy for e in rows):
+                out = torch.empty(len(rows), dtype=torch.int32, device=logits.device)
+                toks = ops.argmax_rows(logits, out).cpu().tolist()
+            elif neutral:
                 temps = torch.tensor([e.request.params.temperature for e in rows], dtype=torch.float32).pin_memory()
                 us = torch.tensor([0.0 if e.request.params.greedy else e.request.sampler.uniform() for e in rows],
                                   dtype=torch.float64).pin_memory()

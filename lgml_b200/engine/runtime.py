@@ -43,13 +43,19 @@ class Runtime:
 
     # ---- matrix products ---------------------------------------------------------------
     def linear(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """y = x . w^T (+ bias); x [M,K], w [N,K] in the compute type, y in ``out_dtype``."""
+               out_dtype: Optional[torch.dtype] = None, partials_ok: bool = False):
+        """y = x . w^T (+ bias); x [M,K], w [N,K] in the compute type, y in ``out_dtype``.
+        With ``partials_ok`` the caller accepts ``ops.Partials`` (the partial sums of a product
+        cut along K, which the next kernel adds up) in place of a tensor."""
         out_dtype = out_dtype or self.dtype
         if self.dtype == torch.float32:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
             return ops.gemm_f32(x, w, out, bias)
-        return ops.gemm_bf16(x, w, out_dtype, bias, backend=self.gemm_backend, status=self.status)
+        return ops.gemm_bf16(x, w, out_dtype, bias, backend=self.gemm_backend, status=self.status, partials_ok=partials_ok)
+
+    def fused_swiglu(self, x: torch.Tensor, w_pairs: torch.Tensor) -> bool:
+        """Whether the gated feed-forward can run its first product and activation as one kernel."""
+        return self.dtype == torch.bfloat16 and self.gemm_backend in ("auto", "tcgen05") and ops.tcgen05_supports(x, w_pairs)
 
     # ---- attention ---------------------------------------------------------------------
     def attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int) -> torch.Tensor:

@@ -109,10 +109,29 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status
     return out
 
 
-def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None,
+class Partials:
+    """The float32 partial sums of a matrix product cut along K: ``data`` is
+    [n_parts, rows, width]; the kernel that reads them adds the parts in order and then
+    ``bias`` (per column) if there is one."""
+
+    def __init__(self, data: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        self.data, self.bias = data, bias
+
+    @property
+    def shape(self):
+        return self.data.shape[1:]
+
+    def sum(self) -> torch.Tensor:
+        """The product itself (for a part that does not read partial sums)."""
+        y = self.data.sum(dim=0)
+        return y if self.bias is None else y + self.bias
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
             rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = rmsnorm(x [+ delta]) * weight.  With ``delta`` and no ``rows`` the sum is
-    written back to x (the residual add); with ``rows`` output row r reads x[rows[r]]."""
+    """out = rmsnorm(x [+ delta]) * weight.  With ``delta`` (a tensor, or ``Partials``) and
+    no ``rows`` the sum is written back to x (the residual add); with ``rows`` output row r
+    reads x[rows[r]]."""
     _need(x, "norm input", torch.float32, 2)
     _need(weight, "norm weight", torch.float32, 1)
     _need(out, "norm output", ndim=2)
@@ -126,26 +145,35 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         _need(rows, "row list", torch.int32, 1)
         if rows.numel() != n_rows:
             raise KernelError("rmsnorm: one output row per listed row")
-    ddt = F32
-    if delta is not None:
+    ddt, n_parts, stride, dbias, dptr = F32, 1, 0, None, None
+    if isinstance(delta, Partials):
+        d = delta.data
+        _need(d, "residual delta parts", torch.float32, 3)
+        if tuple(d.shape[1:]) != tuple(x.shape) or not d.is_contiguous():
+            raise KernelError("rmsnorm: delta parts must be [parts, rows, width] and contiguous")
+        n_parts, stride, dbias, dptr = d.shape[0], d.shape[1] * d.shape[2], delta.bias, d
+    elif delta is not None:
         _need(delta, "residual delta", ndim=2)
         if delta.shape != x.shape or not delta.is_contiguous():
             raise KernelError("rmsnorm: delta must have the input's shape and be contiguous")
-        ddt = dtype_code(delta.dtype)
-    fn = _fn("elementwise", "lgml_rmsnorm", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
-    _check("elementwise", fn(_ptr(x), _ptr(delta), ddt, _ptr(weight), _ptr(rows), _ptr(out), dtype_code(out.dtype), n_rows, width, float(eps), _stream()), "rmsnorm")
+        ddt, dptr = dtype_code(delta.dtype), delta
+    fn = _fn("elementwise", "lgml_rmsnorm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_int, c_int, c_float, c_void_p])
+    _check("elementwise", fn(_ptr(x), _ptr(dptr), ddt, n_parts, stride, _ptr(dbias), _ptr(weight), _ptr(rows), _ptr(out),
+                             dtype_code(out.dtype), n_rows, width, float(eps), _stream()), "rmsnorm")
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> torch.Tensor:
+    """out[t, f] = silu(gate[t, f]) * up[t, f]; gate|up are the two halves of a row, or, with
+    ``paired``, neighbours (gate at 2f, up at 2f + 1)."""
     _need(gate_up, "gate|up", ndim=2)
     _need(out, "activation", gate_up.dtype, 2)
     n, two_f = gate_up.shape
     if two_f != 2 * out.shape[1] or out.shape[0] != n or not gate_up.is_contiguous() or not out.is_contiguous():
         raise KernelError(f"silu_mul: shapes disagree: gate|up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
-    fn = _fn("elementwise", "lgml_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check("elementwise", fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, out.shape[1], _stream()), "silu_mul")
+    fn = _fn("elementwise", "lgml_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check("elementwise", fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, out.shape[1], 1 if paired else 0, _stream()), "silu_mul")
     return out
 
 
@@ -200,35 +228,62 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional
 PAIRING = {"half": 0, "adjacent": 1}
 
 
-def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                   inv_freq: torch.Tensor, n_rot: int, pairing: str, k_pages: torch.Tensor, v_pages: torch.Tensor, n_heads: int,
-                  n_kv_heads: int, head_dim: int, status: torch.Tensor, write_kv: bool = True) -> None:
-    """Rotate the first ``n_rot`` dimensions of q (in place) and k by the positions, and
-    store k and v in their cells (``write_kv`` False: rotate q only, for a layer that
-    reads another layer's cache).  ``n_rot`` 0 means no rotation."""
-    _need(qkv, "qkv", ndim=2)
-    ldq = _rows_contiguous(qkv, "qkv")
-    n = qkv.shape[0]
+                  n_kv_heads: int, head_dim: int, status: torch.Tensor, write_kv: bool = True,
+                  q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotate the first ``n_rot`` dimensions of q and k by the positions and store k and v in
+    their cells (``write_kv`` False: q only, for a layer that reads another layer's cache).
+    ``qkv`` is [tokens, (H + 2 Hkv) D] in the cache's type (q is then rotated in place unless
+    ``q_out`` is given), or ``Partials`` of a projection cut along K (``q_out`` is then made
+    if absent).  Returns the rotated q as [tokens, H D] (a view of qkv when in place)."""
+    _need(k_pages, "key pages", ndim=4)
+    _need(v_pages, "value pages", k_pages.dtype, 4)
+    cache_dt = k_pages.dtype
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    bias = None
+    if isinstance(qkv, Partials):
+        src = qkv.data
+        _need(src, "qkv parts", torch.float32, 3)
+        if not src.is_contiguous() or src.shape[2] != width:
+            raise KernelError("rope_kv_write: parts must be [parts, tokens, (H + 2 Hkv) D] and contiguous")
+        n_parts, n, lds, stride, bias = src.shape[0], src.shape[1], width, src.shape[1] * width, qkv.bias
+        if q_out is None:
+            q_out = torch.empty((n, n_heads * head_dim), dtype=cache_dt, device=src.device)
+    else:
+        src = qkv
+        _need(src, "qkv", ndim=2)
+        lds = _rows_contiguous(src, "qkv")
+        n_parts, n, stride = 1, src.shape[0], 0
+        if src.shape[1] != width:
+            raise KernelError("rope_kv_write: qkv width is not (H + 2 Hkv) D")
+        if q_out is None:
+            if src.dtype != cache_dt:
+                raise KernelError(f"rope_kv_write: qkv is {src.dtype} but the cache is {cache_dt}; give q_out")
+            q_out = src[:, : n_heads * head_dim]
+    _need(q_out, "rotated q", cache_dt, 2)
+    ldq = _rows_contiguous(q_out, "rotated q")
     _need(positions, "positions", torch.int32, 1)
     _need(seq_of_token, "request index of tokens", torch.int32, 1)
     _need(block_table, "block table", torch.int32, 2)
     _need(inv_freq, "rotary frequencies", torch.float32, 1)
-    _need(k_pages, "key pages", qkv.dtype, 4)
-    _need(v_pages, "value pages", qkv.dtype, 4)
-    if positions.numel() != n or seq_of_token.numel() != n:
-        raise KernelError("rope_kv_write: one position and one request index per token")
+    if positions.numel() != n or seq_of_token.numel() != n or q_out.shape != (n, n_heads * head_dim):
+        raise KernelError("rope_kv_write: one position, one request index and one q row per token")
     n_pages, hkv, page, d = k_pages.shape
     if (hkv, d) != (n_kv_heads, head_dim) or v_pages.shape != k_pages.shape or not k_pages.is_contiguous() or not v_pages.is_contiguous():
         raise KernelError(f"rope_kv_write: pages {tuple(k_pages.shape)} do not fit {n_kv_heads} KV heads of {head_dim}")
-    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim or not block_table.is_contiguous():
-        raise KernelError("rope_kv_write: qkv width is not (H + 2 Hkv) D, or the block table is not contiguous")
-    if n_rot % 2 or n_rot > head_dim or inv_freq.numel() < n_rot // 2:
+    if not block_table.is_contiguous():
+        raise KernelError("rope_kv_write: the block table is not contiguous")
+    if n_rot % 2 or n_rot > head_dim or inv_freq.numel() < max(n_rot // 2, 1):
         raise KernelError(f"rope_kv_write: n_rot {n_rot} must be even, at most head_dim, and have n_rot / 2 frequencies")
-    fn = _fn("rope_cache", "lgml_rope_kv_write", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check("rope_cache", fn(_ptr(qkv), dtype_code(qkv.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
-                            _ptr(inv_freq), n_rot, PAIRING[pairing], _ptr(k_pages), _ptr(v_pages), n_pages, page, n,
-                            n_heads, n_kv_heads, head_dim, 1 if write_kv else 0, _ptr(status), _stream()), "rope_kv_write")
+    fn = _fn("rope_cache", "lgml_rope_kv_write", [c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                   c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                   c_int, c_int, c_void_p, c_void_p])
+    _check("rope_cache", fn(_ptr(src), dtype_code(src.dtype), lds, n_parts, stride, _ptr(bias), _ptr(q_out), dtype_code(cache_dt), ldq,
+                            _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), n_rot,
+                            PAIRING[pairing], _ptr(k_pages), _ptr(v_pages), n_pages, page, n, n_heads, n_kv_heads, head_dim,
+                            1 if write_kv else 0, _ptr(status), _stream()), "rope_kv_write")
+    return q_out
 
 
 def paged_attention_ref(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
@@ -263,12 +318,20 @@ def paged_attention_ref(q: torch.Tensor, positions: torch.Tensor, seq_of_token: 
 # sampling
 # ----------------------------------------------------------------------------------------
 
-def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = index of the largest logit of row r; the lowest index wins a tie."""
     _need(logits, "logits", torch.float32, 2)
     _need(out, "token output", torch.int32, 1)
     ld = _rows_contiguous(logits, "logits")
-    fn = _fn("sampling", "lgml_argmax_rows", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check("sampling", fn(_ptr(logits), ld, logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax_rows")
+    n = logits.shape[0]
+    if out.numel() != n:
+        raise KernelError("argmax_rows: one output per row")
+    if scratch is None:
+        scratch = torch.empty(max(64 * n, 1), dtype=torch.int32, device=logits.device)
+    if scratch.numel() < 64 * n or scratch.element_size() != 4:
+        raise KernelError("argmax_rows: scratch needs 64 32-bit words per row")
+    fn = _fn("sampling", "lgml_argmax_rows", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check("sampling", fn(_ptr(logits), ld, n, logits.shape[1], _ptr(out), _ptr(scratch), _stream()), "argmax_rows")
     return out
 
 
@@ -308,35 +371,51 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
     return max(1, min((2 * SM_COUNT) // tiles, k_blocks // 4, 16))
 
 
-def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor], status: torch.Tensor,
-                 n_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor], status: torch.Tensor,
+                 n_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None, swiglu: bool = False,
+                 partials_ok: bool = False):
     """out[M,N] = x[M,K] . w[N,K]^T (+ bias) on tcgen05 tensor cores; bfloat16 in, float32
-    accumulation, out bfloat16 or float32."""
+    accumulation, out bfloat16 or float32.  ``swiglu``: the rows of w (and bias) come in
+    (gate, up) pairs and out[M, N/2] = silu(gate) * up.  ``partials_ok``: when K is cut, return
+    ``Partials`` (the float32 partial sums and the bias) instead of adding them up here."""
     _need(x, "gemm input", torch.bfloat16, 2)
     _need(w, "gemm weight", torch.bfloat16, 2)
-    _need(out, "gemm output", ndim=2)
-    ldx, ldw, ldy = _rows_contiguous(x, "gemm input"), _rows_contiguous(w, "gemm weight"), _rows_contiguous(out, "gemm output")
+    ldx, ldw = _rows_contiguous(x, "gemm input"), _rows_contiguous(w, "gemm weight")
     M, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N) or out.dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError(f"gemm_tcgen05: shapes or types disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_tcgen05: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
     if bias is not None:
         _need(bias, "gemm bias", torch.float32, 1)
         if bias.numel() != N:
             raise KernelError("gemm_tcgen05: bias length is not N")
     if n_splits is None:
-        n_splits = tcgen05_splits(M, N, K)
+        n_splits = 1 if swiglu else tcgen05_splits(M, N, K)
     n_splits = max(1, min(n_splits, -(-K // 64)))
+    if swiglu and n_splits != 1:
+        raise KernelError("gemm_tcgen05: the gated epilogue takes no K split")
+    raw = partials_ok and n_splits > 1
     if n_splits > 1:
         need = n_splits * M * N
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.float32, device=x.device)
         if scratch.numel() < need or scratch.dtype != torch.float32:
             raise KernelError(f"gemm_tcgen05: scratch of {scratch.numel()} floats, {need} needed")
+    ldy, y_f32 = n_out, 0
+    if not raw:
+        _need(out, "gemm output", ndim=2)
+        ldy = _rows_contiguous(out, "gemm output")
+        if out.shape != (M, n_out) or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"gemm_tcgen05: output {tuple(out.shape)} {out.dtype} does not fit [{M}, {n_out}]")
+        y_f32 = 1 if out.dtype == torch.float32 else 0
     fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                   c_int, c_void_p, c_void_p, c_void_p])
-    _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), 1 if out.dtype == torch.float32 else 0, M, N, K, ldx, ldw, ldy,
-                              n_splits, _ptr(scratch if n_splits > 1 else None), _ptr(status), _stream()), "gemm_tcgen05")
+                                                   c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(None if raw else out), y_f32, M, N, K, ldx, ldw, ldy,
+                              n_splits, _ptr(scratch if n_splits > 1 else None), 1 if swiglu else 0, 0 if raw else 1, _ptr(status),
+                              _stream()), "gemm_tcgen05")
+    if raw:
+        return Partials(scratch[: n_splits * M * N].view(n_splits, M, N), bias)
     return out
 
 
@@ -351,11 +430,11 @@ def gemm_cublas(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: 
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
-              backend: str = "auto", status: Optional[torch.Tensor] = None) -> torch.Tensor:
+              backend: str = "auto", status: Optional[torch.Tensor] = None, partials_ok: bool = False):
     """y[M,N] = x[M,K] . w[N,K]^T (+ bias) with bfloat16 operands and float32 accumulation;
     y is bfloat16 or float32.  ``backend``: "tcgen05" is the hand-written tensor-core kernel,
     "cublas" the library product; "auto" takes tcgen05 whenever its operands fit TMA's
-    alignment rules."""
+    alignment rules.  With ``partials_ok`` the result may be ``Partials``."""
     _need(x, "gemm input", torch.bfloat16, 2)
     _need(w, "gemm weight", torch.bfloat16, 2)
     if x.shape[1] != w.shape[1]:
@@ -369,7 +448,16 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Op
     if status is None:
         raise KernelError("gemm_bf16: the tcgen05 kernel needs the status word")
     out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
-    return gemm_tcgen05(x, w, out, bias, status)
+    return gemm_tcgen05(x, w, out, bias, status, partials_ok=partials_ok)
+
+
+def gemm_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, bias_pairs: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:
+    """act[M, F] = silu(x . gate^T) * (x . up^T) in one kernel; ``w_pairs`` [2F, K] holds the
+    gate and up rows of each feature next to each other (gate first)."""
+    out = torch.empty((x.shape[0], w_pairs.shape[0] // 2), dtype=torch.bfloat16, device=x.device)
+    if x.shape[0] == 0:
+        return out
+    return gemm_tcgen05(x, w_pairs, out, bias_pairs, status, swiglu=True)
 
 
 SM_COUNT = 148  # B200
@@ -380,7 +468,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, p
     a few times over; at most one range per page."""
     ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
     pages = max(1, -(-max_kv_len // page))
-    return max(1, min(pages, (4 * SM_COUNT) // max(ctas, 1)))
+    return max(1, min(pages, (3 * SM_COUNT) // max(ctas, 1)))
 
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,

@@ -65,13 +65,15 @@ class Attention(Part):
         ``k``, ``v`` (pages), ``block_table`` and ``writable`` (False when the cache
         belongs to another layer, which has already written this step's cells)."""
         H, D = self.n_heads, self.head_dim
-        qkv = rt.linear(h, self.wqkv, bias=self.bqkv)
-        ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, cache.block_table, self.position.inv_freq,
-                          self.position.n_rot, self.position.pairing, cache.k, cache.v, H, self.n_kv_heads, D,
-                          rt.status, write_kv=cache.writable)
+        # the products may come back as partial sums over K (few tokens): the kernel that
+        # reads them next adds them up, so no pass is spent on that alone
+        qkv = rt.linear(h, self.wqkv, bias=self.bqkv, partials_ok=True)
+        q = ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, cache.block_table, self.position.inv_freq,
+                              self.position.n_rot, self.position.pairing, cache.k, cache.v, H, self.n_kv_heads, D,
+                              rt.status, write_kv=cache.writable)
         o = torch.empty((h.shape[0], H * D), dtype=h.dtype, device=h.device)
-        rt.attention(qkv[:, : H * D], batch, cache, o, H, self.scale, self.window or 0)
-        return rt.linear(o, self.wo, bias=self.bo)
+        rt.attention(q, batch, cache, o, H, self.scale, self.window or 0)
+        return rt.linear(o, self.wo, bias=self.bo, partials_ok=True)
 
 
 register_part("mixer", "attention", Attention)

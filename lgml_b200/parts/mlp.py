@@ -28,17 +28,30 @@ class GatedMLP(Part):
         return specs
 
     def bind(self, prefix, tensors, rt):
-        self.wgu = torch.cat([tensors[prefix + ".gate_proj.weight"], tensors[prefix + ".up_proj.weight"]], dim=0).contiguous()
+        wg, wu = tensors[prefix + ".gate_proj.weight"], tensors[prefix + ".up_proj.weight"]
         self.wd = tensors[prefix + ".down_proj.weight"]
+        bg = bu = None
         if self.bias:
-            self.bgu = torch.cat([tensors[prefix + ".gate_proj.bias"], tensors[prefix + ".up_proj.bias"]], dim=0).contiguous()
+            bg, bu = tensors[prefix + ".gate_proj.bias"], tensors[prefix + ".up_proj.bias"]
             self.bd = tensors[prefix + ".down_proj.bias"]
+        # bfloat16: the gate and up rows of a feature lie next to each other, so the product's
+        # epilogue has both and applies the activation itself; float32: gate rows, then up rows.
+        self.paired = rt.dtype == torch.bfloat16
+        if self.paired:
+            self.wgu = torch.stack([wg, wu], dim=1).reshape(2 * self.inner, self.width).contiguous()
+            self.bgu = torch.stack([bg, bu], dim=1).reshape(2 * self.inner).contiguous() if self.bias else None
+        else:
+            self.wgu = torch.cat([wg, wu], dim=0).contiguous()
+            self.bgu = torch.cat([bg, bu], dim=0).contiguous() if self.bias else None
 
     def forward(self, rt, h):
-        gu = rt.linear(h, self.wgu, bias=self.bgu)
-        act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        ops.silu_mul(gu, act)
-        return rt.linear(act, self.wd, bias=self.bd)
+        if self.paired and rt.fused_swiglu(h, self.wgu):
+            act = ops.gemm_bf16_swiglu(h, self.wgu, self.bgu, rt.status)
+        else:
+            gu = rt.linear(h, self.wgu, bias=self.bgu)
+            act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+            ops.silu_mul(gu, act, paired=self.paired)
+        return rt.linear(act, self.wd, bias=self.bd, partials_ok=True)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)
