@@ -131,16 +131,13 @@ def run_decode(runner, cfg, batch: int, steps: int, warmup: int, seed: int = 0):
             ids = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist()
             for p in range(0, PROMPT_LEN, 512):
                 runner.step([(r, ids[p:p + 512], [])])
-        cur = torch.randint(0, cfg.vocab_size, (batch,), generator=g).tolist()
-        tok = torch.empty(batch, dtype=torch.int32, device=runner.rt.device)
-        host_tok = torch.empty(batch, dtype=torch.int32).pin_memory()
+        tok = torch.randint(0, cfg.vocab_size, (batch,), generator=g).to(torch.int32).to(runner.rt.device)
+        scratch = torch.empty(64 * batch, dtype=torch.int32, device=runner.rt.device)
 
         def one():
-            nonlocal cur
-            logits = runner.step([(r, [t], [0]) for r, t in zip(reqs, cur)])
-            ops.argmax_rows(logits, tok)
-            host_tok.copy_(tok, non_blocking=False)
-            cur = host_tok.tolist()
+            # the sampled ids stay on the device and feed the next step
+            logits = runner.decode_step(reqs, tok)
+            ops.argmax_rows(logits, tok, scratch)
 
         for _ in range(warmup):
             one()

@@ -27,7 +27,6 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int THREADS = 128;
 constexpr int MAX_D = 256;
-constexpr int STAGES = 2;
 constexpr uint32_t SPIN_LIMIT = 4u << 20;
 constexpr int STATUS_TIMEOUT = 11;
 
@@ -58,7 +57,7 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
                  : "memory");
 }
 
-template <int G>
+template <int G, int STAGES>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
@@ -81,6 +80,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     float *corr_s = l_s + G;                // [G]
     float *red = reinterpret_cast<float *>(kv_s);   // [key groups][G][D] for the final sum: the page stages are free by then
     __shared__ uint64_t full_bar[STAGES];
+    __shared__ int stage_ok[STAGES];   // whether the stage holds a page (the table had one)
 
     const int t = blockIdx.x;
     const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
@@ -120,15 +120,16 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 
     // Issue the copy of the page of iteration `it` into stage it % STAGES: only the rows the
     // query can see (rows 0 .. last valid key); a page the table does not hold is skipped.
-    auto issue = [&](int it) {
+    auto issue = [&](int it, int page) {
         const int pg = pb + it;
-        const int page = table[pg];
         uint64_t *bar = &full_bar[it % STAGES];
         if (page < 0 || page >= n_pages) {
             atomicExch(status, 3);
+            stage_ok[it % STAGES] = 0;
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
             return;
         }
+        stage_ok[it % STAGES] = 1;
         const int k_end = min(pos - pg * PAGE + 1, PAGE);
         const uint32_t bytes = (uint32_t)k_end * D * 2;
         const size_t off = ((size_t)page * Hkv + kvh) * PAGE * D;
@@ -137,8 +138,14 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         bulk_load(dst, k_pages + off, bytes, bar);
         bulk_load(dst + page_bytes, v_pages + off, bytes, bar);
     };
-    if (tid == 0)
-        for (int it = 0; it < min(n_iter, STAGES); ++it) issue(it);
+    if (tid == 0) {
+        int first[STAGES];
+#pragma unroll
+        for (int it = 0; it < STAGES; ++it) first[it] = it < n_iter ? table[pb + it] : -1;   // the loads overlap
+#pragma unroll
+        for (int it = 0; it < STAGES; ++it)
+            if (it < n_iter) issue(it, first[it]);
+    }
 
     const int n_chunk = D / 8;                         // 16-byte chunks per row
     // value phase: thread = (key group, chunk of 8 dims)
@@ -156,9 +163,11 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 
     for (int it = 0; it < n_iter; ++it) {
         const int pg = pb + it;
-        const int page = table[pg];
-        const bool have = page >= 0 && page < n_pages;
+        // the table entry of the page STAGES iterations ahead: read now, used at the end of this iteration
+        int page_ahead = -1;
+        if (tid == 0 && it + STAGES < n_iter) page_ahead = table[pg + STAGES];
         if (alive && !mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1, status)) alive = false;
+        const bool have = stage_ok[it % STAGES] != 0;
         const int k_begin = max(lo - pg * PAGE, 0), k_end = min(pos - pg * PAGE + 1, PAGE);
         const uint8_t *kp = kv_s + (size_t)(it % STAGES) * 2 * page_bytes;
         const uint8_t *vp = kp + page_bytes;
@@ -281,7 +290,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         }
         __syncthreads();
         // the stage is free: bring in the page two iterations ahead
-        if (tid == 0 && alive && it + STAGES < n_iter) issue(it + STAGES);
+        if (tid == 0 && alive && it + STAGES < n_iter) issue(it + STAGES, page_ahead);
     }
     // If a wait ran out, copies may still be in flight: give them a bounded time to land
     // before the shared memory can be handed to another CTA.
@@ -335,7 +344,7 @@ __global__ void decode_combine_kernel(const float *__restrict__ part_o, const fl
     }
 }
 
-size_t smem_bytes(int G, int D) {
+size_t smem_bytes(int G, int D, int STAGES) {
     const int n_chunk = D / 8;
     int kg = THREADS / n_chunk;
     if (kg > PAGE) kg = PAGE;
@@ -343,20 +352,33 @@ size_t smem_bytes(int G, int D) {
     return (stages > red ? stages : red) + sizeof(float) * ((size_t)D * G + (size_t)PAGE * G + 3 * G);
 }
 
+template <int G, int STAGES>
+int launch_stages(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
+           int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo,
+           float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int D, int n_chunks, float scale, int window,
+           int *status, cudaStream_t stream) {
+    const size_t smem = smem_bytes(G, D, STAGES);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<G, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("decode_attention: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    lgml_launch(decode_attention_kernel<G, STAGES>, grid, THREADS, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
+                                                               v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, D,
+                                                               n_chunks, scale, window, status);
+    return 0;
+}
+
+// Three stages while a page of K and V (2 x 64 x D bfloat16) is at most 32 KB, else two.
 template <int G>
 int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
            int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo,
            float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int D, int n_chunks, float scale, int window,
            int *status, cudaStream_t stream) {
-    const size_t smem = smem_bytes(G, D);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) LGML_FAIL("decode_attention: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    }
-    lgml_launch(decode_attention_kernel<G>, grid, THREADS, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
-                                                               v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, D,
-                                                               n_chunks, scale, window, status);
-    return 0;
+    if (D <= 128)
+        return launch_stages<G, 3>(grid, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages, v_pages, n_pages, out, ldo,
+                                   part_o, part_ml, n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);
+    return launch_stages<G, 2>(grid, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages, v_pages, n_pages, out, ldo,
+                               part_o, part_ml, n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);
 }
 }  // namespace
 

@@ -54,31 +54,75 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
-    extern __shared__ float cache[];  // the row, so that x is read once
+    constexpr int PER = 8;            // elements a thread keeps in registers; wider rows loop
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float *xr = x + src * width;
     const TD *dr = delta ? delta + src * width : nullptr;
     float ss = 0.f;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = xr[i];
+    for (int base = 0; base < width; base += PER * blockDim.x) {
+        // all loads of this round first, so that they are in flight together
+        float v[PER], d[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = base + j * blockDim.x + threadIdx.x;
+            v[j] = i < width ? xr[i] : 0.f;
+            d[j] = (dr && i < width) ? to_f32(dr[i]) : 0.f;
+        }
         if (dr) {
             // the parts are the partial sums of a matrix product cut along K: added in order
-            float d = to_f32(dr[i]);
-            for (int p = 1; p < n_parts; ++p) d += to_f32(dr[(size_t)p * part_stride + i]);
-            if (delta_bias) d += delta_bias[i];
-            v += d;
-            if (!rows) xr[i] = v;
+            for (int p = 1; p < n_parts; ++p) {
+                float e[PER];
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    const int i = base + j * blockDim.x + threadIdx.x;
+                    e[j] = i < width ? to_f32(dr[(size_t)p * part_stride + i]) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < PER; ++j) d[j] += e[j];
+            }
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const int i = base + j * blockDim.x + threadIdx.x;
+                if (i < width) {
+                    if (delta_bias) d[j] += delta_bias[i];
+                    v[j] += d[j];
+                    if (!rows) xr[i] = v[j];
+                }
+            }
         }
-        cache[i] = v;
-        ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) ss = fmaf(v[j], v[j], ss);
     }
     const float total = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
-#pragma unroll 4
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-        out[(size_t)r * width + i] = from_f32<TO>(cache[i] * inv * weight[i]);
+    // second pass: with a delta the row was just written (or, with a row list, is summed again the same way)
+    for (int base = 0; base < width; base += PER * blockDim.x) {
+        float v[PER], w[PER];
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = base + j * blockDim.x + threadIdx.x;
+            w[j] = i < width ? weight[i] : 0.f;
+            v[j] = i < width ? xr[i] : 0.f;
+        }
+        if (dr && rows) {
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {
+                const int i = base + j * blockDim.x + threadIdx.x;
+                if (i < width) {
+                    float d = to_f32(dr[i]);
+                    for (int p = 1; p < n_parts; ++p) d += to_f32(dr[(size_t)p * part_stride + i]);
+                    if (delta_bias) d += delta_bias[i];
+                    v[j] += d;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int i = base + j * blockDim.x + threadIdx.x;
+            if (i < width) out[(size_t)r * width + i] = from_f32<TO>(v[j] * inv * w[j]);
+        }
+    }
 }
 
 template <typename TD>
@@ -87,15 +131,11 @@ static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long pa
                             cudaStream_t stream) {
     // one block per row; the block's size depends on the width only, so a row's sum is formed
     // in the same order whatever else is in the batch
-    const int threads = width >= 4096 ? 1024 : (width >= 1024 ? 512 : (width >= 256 ? 256 : 128));
-    const size_t smem = (size_t)width * sizeof(float);
-    if (out_dtype == LGML_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<TD, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lgml_launch(rmsnorm_kernel<TD, float>, n_rows, threads, smem, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<TD, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lgml_launch(rmsnorm_kernel<TD, __nv_bfloat16>, n_rows, threads, smem, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps);
-    }
+    const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    if (out_dtype == LGML_F32)
+        lgml_launch(rmsnorm_kernel<TD, float>, n_rows, threads, 0, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps);
+    else
+        lgml_launch(rmsnorm_kernel<TD, __nv_bfloat16>, n_rows, threads, 0, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps);
     return lgml_launch_status("rmsnorm");
 }
 
@@ -105,7 +145,6 @@ LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, int n_pa
                           const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
                           cudaStream_t stream) {
     LGML_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes");
-    LGML_REQUIRE((size_t)width * sizeof(float) <= 200 * 1024, "rmsnorm: width %d is over the %d a row buffer holds", width, 200 * 1024 / 4);
     LGML_REQUIRE(out_dtype == LGML_F32 || out_dtype == LGML_BF16, "rmsnorm: unknown output type %d", out_dtype);
     LGML_REQUIRE(delta == nullptr || n_parts >= 1, "rmsnorm: a delta has at least one part");
     if (n_rows == 0) return 0;

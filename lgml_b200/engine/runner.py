@@ -143,52 +143,67 @@ class ModelRunner:
 
     def graph_kernels(self, batch_size: int) -> int:
         """Launches of this package's kernels that one replay of the graph of ``batch_size`` holds."""
-        slot = self._graphs.get(batch_size)
-        return slot.get("kernels", 0) if slot else 0
+        g = self._graphs.get(batch_size)
+        return g.kernels if g else 0
 
-    def _graph_step(self, entries, stage) -> torch.Tensor:
+    def _graph_step(self, entries, stage, device_tokens=None) -> torch.Tensor:
         """A decode step through a captured graph.  The first step of a batch size runs
         eagerly (it also loads the kernels); the second captures; later ones replay.  The
         graph computes the logits of every token; the wanted rows are picked after it."""
+        from .graph import DecodeGraph
+
         S = len(entries)
-        reqs, toks = [e[0] for e in entries], [e[1] for e in entries]
-        all_rows = [[0]] * S
+        reqs = [e[0] for e in entries]
         if S not in self._graph_seen:
             self._graph_seen.add(S)
+            toks = [e[1] for e in entries]
+            if device_tokens is not None:
+                toks = [[int(t)] for t in device_tokens.cpu().tolist()]
             batch = StepBatch(self.cache, reqs, toks, [e[2] for e in entries], self.rt.device, stage[0])
             stage[1] = torch.cuda.Event()
             stage[1].record()
             self.last_batch = batch
             return self.model.forward(self.rt, batch)
-        slot = self._graphs.get(S)
-        if slot is None:
-            buf = torch.zeros(StepBatch.buffer_ints(S, S, S, self._graph_widths), dtype=torch.int32, device=self.rt.device)
-            slot = {"buffer": buf, "graph": None, "logits": None}
-            self._graphs[S] = slot
-        batch = StepBatch(self.cache, reqs, toks, all_rows, self.rt.device, stage[0], table_widths=self._graph_widths,
-                          device_buffer=slot["buffer"])
-        stage[1] = torch.cuda.Event()
-        stage[1].record()
-        self.last_batch = batch
-        if slot["graph"] is None:
-            # sized for the longest context the tables can describe, so the capture fits every later step
-            hkv = max((g.spec.n_kv_heads for g in self.cache.groups), default=1)
-            batch.max_kv_len = max(self._graph_widths, default=1) * self.cache.page_size
-            from .. import ops
-            batch.decode_splits = ops.decode_splits(S, hkv, 1, batch.max_kv_len)
-            slot["splits"] = batch.decode_splits
-            g = torch.cuda.CUDAGraph()
-            before = ops.launch_count()
-            with torch.cuda.graph(g):
-                slot["logits"] = self.model.forward(self.rt, batch)
-            slot["kernels"] = ops.launch_count() - before
-            slot["graph"] = g
-        slot["graph"].replay()
+        g = self._graphs.get(S)
+        if g is None:
+            g = self._graphs[S] = DecodeGraph(self, S)
+        logits = g.run(reqs, None if device_tokens is not None else [e[1][0] for e in entries], device_tokens)
+        self.last_batch = g.batch
         self.graph_replays += 1
-        logits = slot["logits"]
+        if all(len(e[2]) == 1 for e in entries):
+            return logits
         want_rows = [i for i, e in enumerate(entries) for _ in e[2]]
-        if want_rows != list(range(S)) or any(len(e[2]) != 1 for e in entries):
-            if not want_rows:
-                return logits[:0]
-            return logits[torch.tensor(want_rows, dtype=torch.long, device=logits.device)]
+        if not want_rows:
+            return logits[:0]
+        return logits[torch.tensor(want_rows, dtype=torch.long, device=logits.device)]
+
+    def decode_step(self, requests: Sequence[Request], device_tokens: torch.Tensor) -> torch.Tensor:
+        """One decode step whose token ids are already on the device (int32, one per request),
+        for example the output of the sampling kernel of the step before: the host need not
+        see the tokens before the next step is launched.  Ids out of the vocabulary are
+        caught by the embedding kernel (status 1) instead of the host.  Returns the logits of
+        every request's token."""
+        if device_tokens.dtype != torch.int32 or device_tokens.numel() != len(requests) or not device_tokens.is_cuda:
+            raise StepError("decode_step takes one int32 token id per request, on the device")
+        entries = [(r, [0], [0]) for r in requests]
+        self.validate(entries)
+        for r in requests:
+            if not self.cache.reserve(r, 1):
+                raise PoolFull(f"kv pool full: request {r.id!r} needs a page, {self.cache.n_free_pages} of {self.cache.n_pages} are free")
+        stage = self._pinned[self.steps % len(self._pinned)]
+        if stage[1] is not None:
+            stage[1].synchronize()
+        if self.use_graphs and len(requests) <= MAX_GRAPH_BATCH:
+            logits = self._graph_step(entries, stage, device_tokens=device_tokens)
+        else:
+            toks = [[int(t)] for t in device_tokens.cpu().tolist()]
+            batch = StepBatch(self.cache, list(requests), toks, [[0]] * len(requests), self.rt.device, stage[0])
+            stage[1] = torch.cuda.Event()
+            stage[1].record()
+            self.last_batch = batch
+            logits = self.model.forward(self.rt, batch)
+        for r in requests:
+            self.cache.commit(r, 1)
+        self.steps += 1
+        self.tokens_run += len(requests)
         return logits

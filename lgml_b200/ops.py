@@ -468,7 +468,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, p
     a few times over; at most one range per page."""
     ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
     pages = max(1, -(-max_kv_len // page))
-    return max(1, min(pages, (3 * SM_COUNT) // max(ctas, 1)))
+    return max(1, min(pages, (2 * SM_COUNT) // max(ctas, 1)))
 
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
