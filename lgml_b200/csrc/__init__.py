@@ -40,6 +40,7 @@ LIBRARIES: Dict[str, tuple] = {
     "sampling": ("sampling.cu", []),
     "attention_decode": ("attention_decode.cu", []),
     "gemm_tcgen05": ("gemm_tcgen05.cu", []),
+    "attention_prefill": ("attention_prefill.cu", []),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", []),
 }
 

@@ -25,7 +25,9 @@ LGML_DEFINE_LAST_ERROR(lgml_attention_decode)
 
 namespace {
 constexpr int PAGE = 64;
-constexpr int THREADS = 128;
+constexpr int THREADS = 256;
+constexpr int KEYS_PER_WARP = PAGE / (THREADS / 32);   // 8
+constexpr int KK = KEYS_PER_WARP / 4;                  // groups of 4 keys a warp walks per page
 constexpr int MAX_D = 256;
 constexpr uint32_t SPIN_LIMIT = 4u << 20;
 constexpr int STATUS_TIMEOUT = 11;
@@ -58,7 +60,7 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
 }
 
 template <int G, int STAGES>
-__global__ void __launch_bounds__(THREADS) decode_attention_kernel(
+__global__ void __launch_bounds__(THREADS, 2) decode_attention_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo,
@@ -172,22 +174,22 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         const uint8_t *kp = kv_s + (size_t)(it % STAGES) * 2 * page_bytes;
         const uint8_t *vp = kp + page_bytes;
 
-        // ---- (1) scores: warp w takes keys 16w .. 16w+15; lane = (key_in_warp, sub): four keys at a
+        // ---- (1) scores: warp w takes keys 8w .. 8w+7; lane = (key_in_warp, sub): four keys at a
         // time, 8 lanes per key, lane `sub` owning the 16-byte chunks sub, sub + 8, ... of the row.
-        // The queries of a chunk are held in registers while the 4 x 4 keys of the warp go by.
+        // The queries of a chunk are held in registers while the keys of the warp go by.
         {
-            const uint4 *rows4[4];
-            bool key_ok[4];
+            const uint4 *rows4[KK];
+            bool key_ok[KK];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const int key = warp * 16 + kk * 4 + key_in_warp;
+            for (int kk = 0; kk < KK; ++kk) {
+                const int key = warp * KEYS_PER_WARP + kk * 4 + key_in_warp;
                 key_ok[kk] = have && alive && key >= k_begin && key < k_end;
                 rows4[kk] = reinterpret_cast<const uint4 *>(kp + (size_t)key * D * 2);
             }
             constexpr int GB = G < 4 ? G : 4;           // query heads held in registers at a time
-            float s[4][G];
+            float s[KK][G];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
+            for (int kk = 0; kk < KK; ++kk)
 #pragma unroll
                 for (int g = 0; g < G; ++g) s[kk][g] = 0.f;
             for (int c = sub; c < n_chunk; c += 8) {
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
                         }
                     }
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
+                    for (int kk = 0; kk < KK; ++kk) {
                         if (key_ok[kk]) {
                             const uint4 kv4 = rows4[kk][c];
                             const uint32_t w[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
                 }
             }
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
+            for (int kk = 0; kk < KK; ++kk) {
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     float v = s[kk][g];
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
                     s[kk][g] = v;
                 }
                 if (sub == 0) {
-                    const int key = warp * 16 + kk * 4 + key_in_warp;
+                    const int key = warp * KEYS_PER_WARP + kk * 4 + key_in_warp;
 #pragma unroll
                     for (int g = 0; g < G; ++g) S[key * G + g] = key_ok[kk] ? s[kk][g] : -INFINITY;
                 }

@@ -71,7 +71,23 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
         }
         if (dr) {
             // the parts are the partial sums of a matrix product cut along K: added in order
-            for (int p = 1; p < n_parts; ++p) {
+            // four parts are fetched together (their loads overlap), then added in order
+            int p = 1;
+            for (; p + 4 <= n_parts; p += 4) {
+                float e[4][PER];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) {
+                        const int i = base + j * blockDim.x + threadIdx.x;
+                        e[q][j] = i < width ? to_f32(dr[(size_t)(p + q) * part_stride + i]) : 0.f;
+                    }
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) d[j] += e[q][j];
+            }
+            for (; p < n_parts; ++p) {
                 float e[PER];
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {

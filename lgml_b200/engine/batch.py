@@ -57,6 +57,7 @@ class StepBatch:
         self.max_q_len = max(lens) if lens else 0
         self.max_kv_len = max(self.kv_lens) if lens else 0
         self.decode_splits = None       # a fixed split count (set by a captured graph)
+        self._tiles = {}
 
         flat: List[int] = []
         for t in tokens:
@@ -119,6 +120,22 @@ class StepBatch:
         r = take(max(len(rows), 1))
         self.logit_rows = r[: len(rows)]
         self.block_tables = [take(S * w).view(S, w) for w in self.table_width]
+
+    def attention_tiles(self, tile_tokens: int) -> torch.Tensor:
+        """The new tokens cut into tiles of at most ``tile_tokens`` consecutive tokens of one
+        request, for the prefill attention kernel: int32 [n_tiles, 4] on the device, rows
+        (request row, first token row, tokens, 0).  Made once per tile size."""
+        cached = self._tiles.get(tile_tokens)
+        if cached is None:
+            rows = []
+            start = 0
+            for s, n in enumerate(self.seq_lens):
+                for t0 in range(0, n, tile_tokens):
+                    rows.append((s, start + t0, min(tile_tokens, n - t0), 0))
+                start += n
+            cached = torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(self.token_ids.device)
+            self._tiles[tile_tokens] = cached
+        return cached
 
     @staticmethod
     def buffer_ints(n_tokens: int, n_seqs: int, n_rows: int, table_widths: Sequence[int]) -> int:

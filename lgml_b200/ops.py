@@ -505,17 +505,57 @@ def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: tor
     return out
 
 
+def prefill_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
+    """Tokens per tile of the prefill attention kernel for this grouping of heads."""
+    hpc = min(n_heads // n_kv_heads, 8)
+    return 16 * (8 // hpc)
+
+
+def prefill_attention(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor,
+                      k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                      status: torch.Tensor) -> torch.Tensor:
+    """bfloat16 tensor-core attention for prompts and portions.  ``tiles`` is int32
+    [n_tiles, 4]: (request row, first token row, tokens, 0), each tile within one request
+    and at most ``prefill_tile_tokens`` long."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    _need(positions, "positions", torch.int32, 1)
+    _need(tiles, "tiles", torch.int32, 2)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4:
+        raise KernelError(f"prefill_attention: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
+        raise KernelError("prefill_attention: pages, block table and tiles must be contiguous")
+    fn = _fn("attention_prefill", "lgml_prefill_attention", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                             c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check("attention_prefill", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
+                                   _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
+                                   int(window or 0), _ptr(status), _stream()), "prefill_attention")
+    return out
+
+
 # a portion of at most this many tokens per request is run by the decode kernel
 DECODE_MAX_Q = 8
 
 
 def paged_attention(q, batch, cache, out, n_heads: int, scale: float, window: int, status: torch.Tensor) -> torch.Tensor:
-    """bfloat16 attention over the paged cache; picks the kernel by the batch's shape."""
+    """bfloat16 attention over the paged cache; picks the kernel by the batch's shape: the
+    split-KV kernel when every request brings a few tokens, the tensor-core kernel for
+    prompts and portions (head sizes up to 128), the general kernel otherwise."""
     d = cache.k.shape[3]
-    if batch.max_q_len <= DECODE_MAX_Q and d % 16 == 0 and cache.k.shape[2] == 64:
-        hkv = cache.k.shape[1]
-        n_splits = batch.decode_splits if getattr(batch, "decode_splits", None) else decode_splits(q.shape[0], hkv, n_heads // hkv, batch.max_kv_len)
-        return decode_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
-                                window, status, n_splits)
+    hkv = cache.k.shape[1]
+    if cache.k.shape[2] == 64 and d % 16 == 0:
+        if batch.max_q_len <= DECODE_MAX_Q:
+            n_splits = batch.decode_splits if getattr(batch, "decode_splits", None) else decode_splits(q.shape[0], hkv, n_heads // hkv, batch.max_kv_len)
+            return decode_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
+                                    window, status, n_splits)
+        if d <= 128:
+            tiles = batch.attention_tiles(prefill_tile_tokens(n_heads, hkv))
+            return prefill_attention(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window, status)
     return paged_attention_ref(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads,
                                scale, window, status)

@@ -1,0 +1,426 @@
+"""Each kernel alone against a plain float64 reference written here, at sizes other than the
+engine's: widths and vocabularies that are no power of two, odd head counts and groups, head
+sizes in steps of 16.  Attention is fed shuffled block tables, a pool whose foreign pages and
+unwritten cells hold NaN, and queries aimed at one far key so that a wrong cell would show."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+# ---------------------------------------------------------------------------------------------
+# norms, embedding, activation
+# ---------------------------------------------------------------------------------------------
+
+def ref_rmsnorm(x, w, eps):
+    x = x.double()
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+
+
+@pytest.mark.parametrize("width", [120, 1000, 4096, 5000, 9000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_plain_delta_parts_rows(width, out_dtype):
+    from lgml_b200 import ops
+
+    torch.manual_seed(width)
+    n, eps = 7, 3e-6
+    x0 = torch.randn(n, width) * 3
+    w = 1 + 0.1 * torch.randn(width)
+    tol = dict(atol=2e-6, rtol=2e-6) if out_dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    # plain
+    x = x0.to(DEV)
+    out = torch.empty(n, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w.to(DEV), eps, out)
+    assert torch.allclose(out.double().cpu(), ref_rmsnorm(x0, w, eps), **tol)
+    # residual add of a bfloat16 delta, written back
+    delta = torch.randn(n, width).to(torch.bfloat16)
+    x = x0.to(DEV)
+    ops.rmsnorm(x, w.to(DEV), eps, out, delta=delta.to(DEV))
+    want_x = x0.double() + delta.double()
+    assert torch.allclose(x.double().cpu(), want_x, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(out.double().cpu(), ref_rmsnorm(want_x, w, eps), **tol)
+    # partial sums of a product cut along K, with a bias, and a row gather (x untouched)
+    parts = torch.randn(6, n, width)
+    bias = torch.randn(width)
+    rows = torch.tensor([5, 0, 5, 2], dtype=torch.int32)
+    x = x0.to(DEV)
+    outr = torch.empty(4, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w.to(DEV), eps, outr, delta=ops.Partials(parts.to(DEV), bias.to(DEV)), rows=rows.to(DEV))
+    want_x = x0.double() + parts.double().sum(0) + bias.double()
+    assert torch.equal(x.cpu(), x0)
+    assert torch.allclose(outr.double().cpu(), ref_rmsnorm(want_x[rows.long()], w, eps), **tol)
+    # the same sum without the row list is written back
+    ops.rmsnorm(x, w.to(DEV), eps, out, delta=ops.Partials(parts.to(DEV), bias.to(DEV)))
+    assert torch.allclose(x.double().cpu(), want_x, atol=1e-5, rtol=1e-6)
+
+
+def test_rmsnorm_row_does_not_depend_on_the_batch():
+    from lgml_b200 import ops
+
+    torch.manual_seed(0)
+    w = torch.rand(777, device=DEV) + 0.5
+    x = torch.randn(9, 777, device=DEV)
+    a = torch.empty(9, 777, device=DEV)
+    b = torch.empty(1, 777, device=DEV)
+    ops.rmsnorm(x.clone(), w, 1e-5, a)
+    ops.rmsnorm(x[4:5].clone(), w, 1e-5, b)
+    assert torch.equal(a[4], b[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(dtype):
+    from lgml_b200 import ops
+
+    torch.manual_seed(1)
+    table = torch.randn(331, 120).to(dtype)
+    ids = torch.tensor([0, 330, 17, 17, 200], dtype=torch.int32)
+    out = torch.empty(5, 120, device=DEV)
+    st = status()
+    ops.embed_rows(table.to(DEV), ids.to(DEV), out, st)
+    assert torch.equal(out.cpu(), table[ids.long()].float()) and int(st.item()) == 0
+    # an id outside the table is flagged and read as zeros, never out of bounds
+    ops.embed_rows(table.to(DEV), torch.tensor([3, 331, -1, 4, 5], dtype=torch.int32, device=DEV), out, st)
+    assert int(st.item()) == 1 and float(out[1].abs().sum()) == 0.0 and float(out[2].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("paired", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(paired, dtype):
+    from lgml_b200 import ops
+
+    torch.manual_seed(2)
+    g, u = torch.randn(5, 200).to(dtype), torch.randn(5, 200).to(dtype)
+    gu = torch.stack([g, u], 2).reshape(5, 400) if paired else torch.cat([g, u], 1)
+    out = torch.empty(5, 200, dtype=dtype, device=DEV)
+    ops.silu_mul(gu.contiguous().to(DEV), out, paired=paired)
+    want = g.double() * torch.sigmoid(g.double()) * u.double()
+    tol = dict(atol=1e-6, rtol=1e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    assert torch.allclose(out.double().cpu(), want, **tol)
+
+
+def test_fill_normal_is_seeded():
+    from lgml_b200 import ops
+
+    a = torch.empty(1 << 20, device=DEV)
+    b = torch.empty(1 << 20, device=DEV)
+    ops.fill_normal(a, 1.0, 0.02, 7)
+    ops.fill_normal(b, 1.0, 0.02, 7)
+    assert torch.equal(a, b)
+    ops.fill_normal(b, 1.0, 0.02, 8)
+    assert not torch.equal(a, b)
+    assert abs(float(a.mean()) - 1.0) < 1e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    z = (a - 1.0) / 0.02
+    assert abs(float((z.abs() < 1).float().mean()) - 0.6827) < 5e-3
+
+
+# ---------------------------------------------------------------------------------------------
+# matrix products
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 200, 120), (70, 331, 257), (3, 1000, 96)])
+def test_gemm_f32_is_exact_and_batch_invariant(M, N, K):
+    from lgml_b200 import ops
+
+    torch.manual_seed(M * N)
+    a, w, b = torch.randn(M, K), torch.randn(N, K), torch.randn(N)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_f32(a.to(DEV), w.to(DEV), out, b.to(DEV))
+    want = a.double() @ w.double().t() + b.double()
+    assert torch.allclose(out.double().cpu(), want, atol=1e-5 * math.sqrt(K), rtol=1e-6)
+    one = torch.empty(1, N, device=DEV)
+    ops.gemm_f32(a[M - 1:].contiguous().to(DEV), w.to(DEV), one, b.to(DEV))
+    assert torch.equal(one[0], out[M - 1])          # a row's bits do not depend on the other rows
+
+
+@pytest.mark.parametrize("M,N,K,bias,f32,splits", [
+    (1, 128, 64, False, False, None), (8, 331 * 8, 120, True, True, None), (5, 200, 192, True, False, 3),
+    (64, 1000, 1096, True, True, 4), (100, 320, 96, False, False, None), (129, 520, 264, True, False, None),
+    (300, 648, 200, True, True, None), (700, 1200, 520, False, False, None),
+])
+def test_gemm_tcgen05(M, N, K, bias, f32, splits):
+    from lgml_b200 import ops
+
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N) if bias else None
+    st = status()
+    out = torch.full((M, N), float("nan"), dtype=torch.float32 if f32 else torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05(x.to(DEV), w.to(DEV), out, None if b is None else b.to(DEV), st, n_splits=splits)
+    want = x.double() @ w.double().t() + (b.double() if bias else 0)
+    scale = float(want.abs().max())
+    err = float((out.double().cpu() - want).abs().max())
+    assert int(st.item()) == 0
+    assert err <= scale * (5e-5 if f32 else 6e-3), (err, scale)
+
+
+def test_gemm_tcgen05_gated_epilogue_and_partials():
+    from lgml_b200 import ops
+
+    torch.manual_seed(5)
+    st = status()
+    for M, F, K in [(6, 100, 96), (300, 176, 120)]:
+        x = torch.randn(M, K).to(torch.bfloat16)
+        wg, wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16), (torch.randn(F, K) * 0.1).to(torch.bfloat16)
+        bg, bu = torch.randn(F), torch.randn(F)
+        pairs = torch.stack([wg, wu], 1).reshape(2 * F, K).contiguous()
+        bp = torch.stack([bg, bu], 1).reshape(2 * F).contiguous()
+        out = ops.gemm_bf16_swiglu(x.to(DEV), pairs.to(DEV), bp.to(DEV), st)
+        g = x.double() @ wg.double().t() + bg.double()
+        u = x.double() @ wu.double().t() + bu.double()
+        want = g * torch.sigmoid(g) * u
+        assert float((out.double().cpu() - want).abs().max()) <= 6e-3 * float(want.abs().max())
+    x = torch.randn(9, 520).to(torch.bfloat16)
+    w = (torch.randn(200, 520) * 0.1).to(torch.bfloat16)
+    b = torch.randn(200)
+    pr = ops.gemm_tcgen05(x.to(DEV), w.to(DEV), None, b.to(DEV), st, n_splits=3, partials_ok=True)
+    assert isinstance(pr, ops.Partials) and pr.data.shape == (3, 9, 200)
+    want = x.double() @ w.double().t() + b.double()
+    assert float((pr.sum().double().cpu() - want).abs().max()) <= 5e-5 * float(want.abs().max())
+    assert int(st.item()) == 0
+
+
+def test_gemm_bf16_falls_back_when_tma_cannot_take_the_operands():
+    from lgml_b200 import ops
+
+    x = torch.randn(4, 100).to(torch.bfloat16).to(DEV)        # a row of 200 bytes: no multiple of 16
+    w = torch.randn(50, 100).to(torch.bfloat16).to(DEV)
+    assert not ops.tcgen05_supports(x, w)
+    y = ops.gemm_bf16(x, w, torch.float32, status=status())
+    assert torch.allclose(y.double().cpu(), x.double().cpu() @ w.double().cpu().t(), atol=1e-2, rtol=1e-2)
+
+
+# ---------------------------------------------------------------------------------------------
+# rotary encoding and cache write
+# ---------------------------------------------------------------------------------------------
+
+def ref_rope(x, pos, inv_freq, pairing, n_rot):
+    x = x.double().clone()
+    ang = pos.double()[:, None] * inv_freq.double()[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    if pairing == "adjacent":
+        a, b = x[..., 0:n_rot:2].clone(), x[..., 1:n_rot:2].clone()
+        x[..., 0:n_rot:2], x[..., 1:n_rot:2] = a * c - b * s, a * s + b * c
+    else:
+        h = n_rot // 2
+        a, b = x[..., :h].clone(), x[..., h:n_rot].clone()
+        x[..., :h], x[..., h:n_rot] = a * c - b * s, a * s + b * c
+    return x
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing,n_rot,from_parts", [("half", 48, False), ("adjacent", 48, False), ("half", 32, False), ("half", 48, True), ("half", 0, False)])
+def test_rope_kv_write(dtype, pairing, n_rot, from_parts):
+    from lgml_b200 import ops
+
+    torch.manual_seed(3)
+    H, G, D, page = 5, 5 if n_rot == 32 else 1, 48, 64
+    lens, pos0 = [3, 70, 1], [62, 0, 127]              # the first request crosses a page edge
+    n = sum(lens)
+    positions = torch.tensor([p + i for p, ln in zip(pos0, lens) for i in range(ln)], dtype=torch.int32)
+    seq_of = torch.tensor([s for s, ln in enumerate(lens) for _ in range(ln)], dtype=torch.int32)
+    table = torch.tensor([[7, 2, -1], [4, 9, -1], [0, 5, -1]], dtype=torch.int32)
+    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / max(n_rot, 2)) for i in range(max(n_rot // 2, 1))], dtype=torch.float32)
+    width = (H + 2 * G) * D
+    st = status()
+    k_pages = torch.full((12, G, page, D), float("nan"), dtype=dtype, device=DEV)
+    v_pages = torch.full((12, G, page, D), float("nan"), dtype=dtype, device=DEV)
+    if from_parts:
+        parts = torch.randn(3, n, width)
+        bias = torch.randn(width)
+        full = (parts.double().sum(0) + bias.double())
+        q = ops.rope_kv_write(ops.Partials(parts.to(DEV), bias.to(DEV)), positions.to(DEV), seq_of.to(DEV), table.to(DEV), inv_freq.to(DEV),
+                              n_rot, pairing, k_pages, v_pages, H, G, D, st)
+    else:
+        qkv = torch.randn(n, width).to(dtype)
+        full = qkv.double()
+        dev_qkv = qkv.to(DEV)
+        q = ops.rope_kv_write(dev_qkv, positions.to(DEV), seq_of.to(DEV), table.to(DEV), inv_freq.to(DEV), n_rot, pairing,
+                              k_pages, v_pages, H, G, D, st)
+    assert int(st.item()) == 0
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=1e-2)
+    want_q = ref_rope(full[:, : H * D].reshape(n, H, D), positions, inv_freq[: n_rot // 2], pairing, n_rot)
+    want_k = ref_rope(full[:, H * D:(H + G) * D].reshape(n, G, D), positions, inv_freq[: n_rot // 2], pairing, n_rot)
+    want_v = full[:, (H + G) * D:].reshape(n, G, D)
+    assert torch.allclose(q.double().cpu().reshape(n, H, D), want_q, **tol)
+    kc, vc = k_pages.double().cpu(), v_pages.double().cpu()
+    written = torch.zeros(12, page, dtype=torch.bool)
+    for t in range(n):
+        p = int(positions[t])
+        pg = int(table[int(seq_of[t]), p // page])
+        assert torch.allclose(kc[pg, :, p % page, :], want_k[t], **tol)
+        assert torch.allclose(vc[pg, :, p % page, :], want_v[t], **tol)
+        written[pg, p % page] = True
+    assert bool(torch.isnan(kc.permute(0, 2, 1, 3)[~written]).all())           # no other cell was touched
+    assert bool(torch.isnan(vc.permute(0, 2, 1, 3)[~written]).all())
+
+
+# ---------------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------------
+
+def make_attention_case(seed, H, G, D, kv_lens, q_lens, dtype, n_pages=40, aim=True):
+    """Requests with kv_lens cached tokens of which the last q_lens are this step's queries.
+    Pages are shuffled; every cell no request owns holds NaN."""
+    g = torch.Generator().manual_seed(seed)
+    page = 64
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    k_pages = torch.full((n_pages, G, page, D), float("nan"))
+    v_pages = torch.full((n_pages, G, page, D), float("nan"))
+    width = max(-(-max(kv_lens) // page), 1) + 1
+    table = torch.full((len(kv_lens), width), -1, dtype=torch.int32)
+    ks, vs, qs, positions, seq_of = [], [], [], [], []
+    for s, (n, nq) in enumerate(zip(kv_lens, q_lens)):
+        k, v = torch.randn(n, G, D, generator=g), torch.randn(n, G, D, generator=g)
+        q = torch.randn(nq, H, D, generator=g)
+        if aim and n > 3:
+            # aim the last query of every head at one far key: its score stands out by ~12
+            far = 1 if n < 70 else n - 67
+            for h in range(H):
+                kk = k[far, h // (H // G)]
+                q[-1, h] = kk / kk.norm() * 12.0 * math.sqrt(D) / kk.norm()
+        k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+        for b in range(-(-n // page)):
+            table[s, b] = perm.pop()
+            rows = slice(b * page, min((b + 1) * page, n))
+            k_pages[table[s, b], :, : rows.stop - rows.start] = k[rows].transpose(0, 1).float()
+            v_pages[table[s, b], :, : rows.stop - rows.start] = v[rows].transpose(0, 1).float()
+        ks.append(k.double()); vs.append(v.double()); qs.append(q.double())
+        positions += list(range(n - nq, n))
+        seq_of += [s] * nq
+    q_all = torch.cat([q.reshape(q.shape[0], H * D) for q in qs]).to(dtype)
+    return dict(q=q_all, k_pages=k_pages.to(dtype), v_pages=v_pages.to(dtype), table=table, positions=torch.tensor(positions, dtype=torch.int32),
+                seq_of=torch.tensor(seq_of, dtype=torch.int32), ks=ks, vs=vs, qs=qs, H=H, G=G, D=D, kv_lens=kv_lens, q_lens=q_lens)
+
+
+def ref_attention(case, scale, window):
+    outs = []
+    H, G, D = case["H"], case["G"], case["D"]
+    for k, v, q, n, nq in zip(case["ks"], case["vs"], case["qs"], case["kv_lens"], case["q_lens"]):
+        o = torch.empty(nq, H, D, dtype=torch.float64)
+        for i in range(nq):
+            p = n - nq + i
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(H):
+                s = (k[lo:p + 1, h // (H // G)] @ q[i, h]) * scale
+                o[i, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // (H // G)]
+        outs.append(o.reshape(nq, H * D))
+    return torch.cat(outs)
+
+
+class FakeBatch:
+    def __init__(self, case):
+        self.positions, self.seq_of_token = case["positions"].to(DEV), case["seq_of"].to(DEV)
+        self.max_q_len, self.max_kv_len = max(case["q_lens"]), max(case["kv_lens"])
+        self.seq_lens = case["q_lens"]
+        self.decode_splits = None
+
+    def attention_tiles(self, tt):
+        rows, start = [], 0
+        for s, n in enumerate(self.seq_lens):
+            rows += [(s, start + t0, min(tt, n - t0), 0) for t0 in range(0, n, tt)]
+            start += n
+        return torch.tensor(rows, dtype=torch.int32, device=DEV)
+
+
+ATT_SHAPES = [(4, 4, 16), (6, 2, 32), (5, 5, 48), (8, 1, 64), (12, 4, 128), (9, 1, 80)]
+
+
+def run_attention(kind, case, window, n_splits=None):
+    from lgml_b200 import ops
+
+    st = status()
+    H, D = case["H"], case["D"]
+    scale = D ** -0.5
+    q = case["q"].to(DEV)
+    out = torch.full_like(q, float("nan"))
+    kp, vp, tab = case["k_pages"].to(DEV), case["v_pages"].to(DEV), case["table"].to(DEV)
+    b = FakeBatch(case)
+    if kind == "ref":
+        ops.paged_attention_ref(q, b.positions, b.seq_of_token, tab, kp, vp, out, H, scale, window, st)
+    elif kind == "decode":
+        ops.decode_attention(q, b.positions, b.seq_of_token, tab, kp, vp, out, H, scale, window, st, n_splits)
+    else:
+        tiles = b.attention_tiles(ops.prefill_tile_tokens(H, case["G"]))
+        ops.prefill_attention(q, b.positions, tiles, tab, kp, vp, out, H, scale, window, st)
+    assert int(st.item()) == 0
+    return out.double().cpu(), ref_attention(case, scale, window)
+
+
+@pytest.mark.parametrize("H,G,D", ATT_SHAPES + [(2, 2, 256), (3, 1, 40)])
+@pytest.mark.parametrize("dtype,window", [(torch.float32, 0), (torch.float32, 37), (torch.bfloat16, 0)])
+def test_attention_ref_kernel(H, G, D, dtype, window):
+    case = make_attention_case(1, H, G, D, kv_lens=[200, 1, 65, 130], q_lens=[200, 1, 2, 7], dtype=dtype)
+    got, want = run_attention("ref", case, window)
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    assert torch.isfinite(got).all() and torch.allclose(got, want, **tol)
+
+
+@pytest.mark.parametrize("H,G,D", ATT_SHAPES + [(16, 1, 32), (4, 2, 256)])
+@pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 5), (100, 3)])
+def test_attention_decode_kernel(H, G, D, window, n_splits):
+    case = make_attention_case(2, H, G, D, kv_lens=[700, 64, 1, 333, 129, 65], q_lens=[1, 1, 1, 3, 1, 2], dtype=torch.bfloat16)
+    got, want = run_attention("decode", case, window, n_splits)
+    assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("H,G,D", ATT_SHAPES + [(3, 3, 112)])
+@pytest.mark.parametrize("window", [0, 90])
+def test_attention_prefill_kernel(H, G, D, window):
+    case = make_attention_case(3, H, G, D, kv_lens=[300, 70, 1, 129, 64], q_lens=[300, 33, 1, 65, 2], dtype=torch.bfloat16)
+    got, want = run_attention("prefill", case, window)
+    assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
+
+
+def test_attention_finds_the_far_key():
+    """The aimed query's output is that key's value, in every kernel."""
+    case = make_attention_case(4, 4, 2, 64, kv_lens=[500], q_lens=[1], dtype=torch.bfloat16)
+    far = 500 - 67
+    for kind, splits in (("ref", None), ("decode", 4), ("prefill", None)):
+        got, _ = run_attention(kind, case, 0, splits)
+        for h in range(4):
+            v_far = case["vs"][0][far, h // 2]
+            assert float((got[0, h * 64:(h + 1) * 64] - v_far).abs().max()) < 0.15, kind
+
+
+# ---------------------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------------------
+
+def test_argmax_lowest_index_wins_and_odd_vocabulary():
+    from lgml_b200 import ops
+
+    torch.manual_seed(6)
+    logits = torch.randn(5, 128257)
+    logits[0, 77] = logits[0, 100000] = 50.0          # a tie
+    logits[1, 128256] = 60.0                          # the last column
+    logits[2] = float("-inf")
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.argmax_rows(logits.to(DEV), out)
+    got = out.cpu().tolist()
+    assert got[0] == 77 and got[1] == 128256 and got[2] == 0
+    assert got[3:] == torch.argmax(logits[3:], 1).tolist()
+
+
+def test_sample_rows_matches_the_host_sampler():
+    from lgml_b200 import ops
+    from lgml_b200.sampling import Sampler, SamplingParams
+
+    torch.manual_seed(7)
+    V, R = 5003, 64
+    logits = torch.randn(R, V) * 3
+    temps = [0.0, 0.7, 1.0, 1.5] * (R // 4)
+    samplers = [Sampler(SamplingParams.neutral(t, seed=100 + i)) for i, t in enumerate(temps)]
+    twins = [Sampler(SamplingParams.neutral(t, seed=100 + i)) for i, t in enumerate(temps)]
+    us = [0.0 if t <= 0 else s.uniform() for s, t in zip(samplers, temps)]
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits.to(DEV), torch.tensor(temps, device=DEV), torch.tensor(us, dtype=torch.float64, device=DEV), out)
+    host = [tw.sample(logits[i].numpy()) for i, tw in enumerate(twins)]
+    assert out.cpu().tolist() == host

@@ -1,0 +1,105 @@
+"""The host sampler: the reference's options, order and arithmetic (no GPU).
+Modelled on mischief/lgml's test/test_sample.lua: greedy, determinism under a seed,
+penalties, logit_bias, logprobs, the sets top-k / top-p / min-p keep, and a frequency fit."""
+import math
+
+import numpy as np
+import pytest
+
+from lgml_b200.sampling import DEFAULTS, Sampler, SamplingParams, Xoshiro256
+
+
+def test_defaults_are_the_reference_defaults():
+    p = SamplingParams()
+    assert (p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.repeat_last_n) == (0.8, 40, 0.95, 0.05, 1.0, 64)
+    assert DEFAULTS["frequency_penalty"] == 0.0 and DEFAULTS["presence_penalty"] == 0.0
+    assert not p.is_neutral and SamplingParams.neutral(0.8).is_neutral
+    assert SamplingParams.preset("greedy").greedy
+    with pytest.raises(ValueError):
+        SamplingParams.preset("nope")
+    with pytest.raises(ValueError):
+        SamplingParams(repeat_penalty=0.0)
+
+
+def test_generator_is_xoshiro256_starstar_seeded_by_splitmix64():
+    # splitmix64(0) gives the well-known first outputs; xoshiro256** then runs on that state
+    g = Xoshiro256(0)
+    assert g.s == [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F, 0xF88BB8A8724C81EC]
+    a = [Xoshiro256(42).next() for _ in range(1)]
+    b = Xoshiro256(42)
+    assert b.next() == a[0]
+    u = [Xoshiro256(7).double() for _ in range(3)]
+    assert all(0.0 <= x < 1.0 for x in u)
+
+
+def test_greedy_and_ties():
+    s = Sampler(SamplingParams(temperature=0.0))
+    l = np.array([0.1, 3.0, -1.0, 3.0], dtype=np.float32)
+    assert s.sample(l) == 1                              # lowest index wins a tie
+
+
+def test_same_seed_same_draws():
+    l = np.random.default_rng(0).normal(size=500).astype(np.float32)
+    a = Sampler(SamplingParams(seed=5))
+    b = Sampler(SamplingParams(seed=5))
+    c = Sampler(SamplingParams(seed=6))
+    da, db, dc = [a.sample(l) for _ in range(50)], [b.sample(l) for _ in range(50)], [c.sample(l) for _ in range(50)]
+    assert da == db and da != dc
+
+
+def test_top_k_top_p_min_p_keep_the_right_sets():
+    l = np.log(np.array([0.5, 0.25, 0.125, 0.0625, 0.0625], dtype=np.float64)).astype(np.float32)
+    def support(**kw):
+        s = Sampler(SamplingParams(temperature=1.0, seed=1, **{**dict(top_k=0, top_p=1.0, min_p=0.0), **kw}))
+        return {s.sample(l) for _ in range(400)}
+    assert support(top_k=2) == {0, 1}
+    assert support(top_p=0.7) == {0, 1}                   # 0.5 < 0.7 <= 0.75
+    assert support(top_p=0.5) == {0}
+    assert support(min_p=0.3) == {0, 1}                   # p >= 0.3 * 0.5
+    assert support() == {0, 1, 2, 3, 4}
+
+
+def test_penalties_and_bias():
+    l = np.array([2.0, 1.9, -1.0, 0.0], dtype=np.float32)
+    s = Sampler(SamplingParams(temperature=0.0, repeat_penalty=2.0))
+    assert s.sample(l) == 0
+    s.accept(0)
+    assert s.sample(l) == 1                               # 2.0 / 2 < 1.9
+    s = Sampler(SamplingParams(temperature=0.0, frequency_penalty=0.2, presence_penalty=0.0))
+    s.accept(0); s.accept(0)
+    assert s.sample(l) == 1                               # 2.0 - 2 * 0.2 < 1.9
+    s = Sampler(SamplingParams(temperature=0.0, repeat_penalty=2.0))
+    s.accept(2)
+    s.sample(l)
+    assert s.last_logits[2] == -2.0                       # a negative logit is multiplied
+    s = Sampler(SamplingParams(temperature=0.0, logit_bias={3: 5.0}))
+    assert s.sample(l) == 3
+    s = Sampler(SamplingParams(temperature=0.0, repeat_penalty=2.0, repeat_last_n=1))
+    s.accept(0); s.accept(1)                              # only the last id is remembered
+    assert s.sample(l) == 0
+    s.reset()
+    assert s.hist == []
+
+
+def test_logprobs():
+    l = np.array([1.0, 2.0, 3.0], dtype=np.float32)
+    s = Sampler(SamplingParams(temperature=0.0))
+    with pytest.raises(RuntimeError):
+        s.logprobs(0)
+    s.sample(l)
+    lp, top = s.logprobs(2, 2)
+    lse = math.log(sum(math.exp(x) for x in (1.0, 2.0, 3.0)))
+    assert abs(lp - (3.0 - lse)) < 1e-6 and [t[0] for t in top] == [2, 1]
+
+
+def test_draw_frequencies_fit_the_softmax():
+    """20 000 draws at temperature 0.8 stay within 4 sigma of softmax(l / 0.8) (test/test_sample.lua:182-185)."""
+    l = np.array([0.0, 1.0, 2.0, 0.5, -1.0], dtype=np.float32)
+    p = np.exp(l.astype(np.float64) / 0.8)
+    p /= p.sum()
+    s = Sampler(SamplingParams.neutral(0.8, seed=123))
+    n = 20000
+    counts = np.bincount([s.sample(l) for _ in range(n)], minlength=5)
+    for i in range(5):
+        sigma = math.sqrt(n * p[i] * (1 - p[i]))
+        assert abs(counts[i] - n * p[i]) < 4 * sigma
