@@ -39,7 +39,7 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         # decode steps (one token per request) replay a CUDA graph captured per batch size
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and getattr(model, "graph_safe", False)
         self._graphs = {}
         self._graph_seen = set()
         max_pos = model.max_position or (n_pages * self.cache.page_size)

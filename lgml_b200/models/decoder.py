@@ -47,6 +47,8 @@ class DecoderModel:
                 if self.schedule[call.cache].cache is not None:
                     raise ValueError(f"schedule entry {ci} reads the cache of entry {call.cache}, which has none of its own")
         self.vocab_size = head.vocab
+        parts = [embedding, final_norm, head] + self.blocks
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         self.max_position = getattr(config, "max_position_embeddings", None)
 
     # ---- weights -----------------------------------------------------------------------

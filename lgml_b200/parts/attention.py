@@ -25,6 +25,7 @@ from .base import Part, register_part
 
 
 class Attention(Part):
+    graph_safe = True
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position, bias: bool = False,
                  out_bias: Optional[bool] = None, window: Optional[int] = None, scale: Optional[float] = None):
         if n_heads % n_kv_heads:

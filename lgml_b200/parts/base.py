@@ -53,7 +53,15 @@ def registered(kind: str) -> List[str]:
 
 
 class Part:
-    """Base of all parts: by default no tensors."""
+    """Base of all parts: by default no tensors.
+
+    ``graph_safe`` says that ``forward`` only launches work whose shape and addresses are
+    fixed by the batch's shape (everything else it reads on the device), so a decode step
+    through it can be captured into a CUDA graph and replayed.  A part that loops over
+    requests on the host, or reads host values of the batch, leaves it False and the runner
+    then runs every step eagerly."""
+
+    graph_safe = False
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         return []

@@ -35,6 +35,10 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec() if self.mixer is not None else None
 
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+
     def forward(self, rt, x, pending, batch, cache):
         if self.mixer is not None:
             h = self.mixer_norm.forward(rt, x, rt.dtype, delta=pending)

@@ -14,6 +14,7 @@ from .base import Part
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
     def __init__(self, vocab: int, width: int, name: str = "model.embed_tokens.weight"):
         self.vocab, self.width, self.name = vocab, width, name
         self.table = None
@@ -30,6 +31,7 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    graph_safe = True
     def __init__(self, vocab: int, width: int, tied_to: TokenEmbedding = None, name: str = "lm_head.weight"):
         self.vocab, self.width, self.tied_to, self.name = vocab, width, tied_to, name
         self.weight = None

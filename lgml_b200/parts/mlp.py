@@ -12,6 +12,7 @@ from .base import Part, register_part
 
 
 class GatedMLP(Part):
+    graph_safe = True
     def __init__(self, width: int, inner: int, activation: str = "silu", bias: bool = False):
         if activation != "silu":
             raise ValueError(f"activation '{activation}' is not supported (only 'silu')")

@@ -11,6 +11,7 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
+    graph_safe = True
     def __init__(self, width: int, eps: float):
         self.width = width
         self.eps = float(eps)

@@ -53,6 +53,7 @@ def frequency_factors(head_dim: int, theta: float, scaling, n_rot: Optional[int]
 
 
 class Rope(Part):
+    graph_safe = True
     def __init__(self, head_dim: int, theta: float, scaling=None, n_rot: Optional[int] = None, pairing: str = "half",
                  factors_tensor: Optional[str] = None):
         self.head_dim = head_dim
@@ -83,6 +84,7 @@ class Rope(Part):
 
 
 class NoPosition(Part):
+    graph_safe = True
     """No position encoding: the mixer leaves q and k as they are."""
 
     n_rot = 0

@@ -1,0 +1,172 @@
+"""Generation through the entry points: greedy and seeded temperature sampling equal the
+plain implementation's; a pool too small for all requests (preemption) changes no reply;
+bin/trace_run as a separate process; the command line."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+from tests.plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {
+        ("A", "float32"): H.make_folder(tmp_path_factory.mktemp("engA"), H.TINY_A, 0, dtype="float32", sharpen=12.0),
+        ("B", "float32"): H.make_folder(tmp_path_factory.mktemp("engB"), H.TINY_B, 1, dtype="float32", sharpen=12.0),
+        ("B", "bfloat16"): H.make_folder(tmp_path_factory.mktemp("engBh"), H.TINY_B, 1, dtype="bfloat16", sharpen=6.0),
+    }
+
+
+def test_greedy_generation_equals_the_plain_implementation(folders):
+    """tiny-A: prompts of 5 / 17 / 31 tokens, 16 greedy tokens each, in one call."""
+    import lgml_b200
+
+    folder = folders[("A", "float32")]
+    cfg, w = P.load_folder(folder)
+    prompts = [H.random_ids(n, 256, 40 + n) for n in (5, 17, 31)]
+    eng = lgml_b200.Engine(str(folder), dtype="float32", slots=4)
+    got = eng.generate(prompts, max_tokens=16, temperature=0.0)
+    for p, g in zip(prompts, got):
+        assert g == P.greedy(cfg, w, p, 16)
+    # Engine.greedy, the counterpart of generate.greedy, with a stop id
+    ids, t = eng.greedy(prompts[1], 16)
+    assert ids == got[1] and t["n_decode"] == 15 and t["prefill"] > 0
+    stop_at = got[1][4]
+    ids, _ = eng.greedy(prompts[1], 16, stop=[stop_at])
+    assert ids == got[1][: got[1].index(stop_at) + 1]
+    assert not eng.runner.cache.live and eng.runner.cache.n_free_pages == eng.runner.cache.n_pages
+
+
+def plain_sampled(cfg, w, prompt, n_new, temperature, seed):
+    """Seeded sampling replayed on the plain implementation's logits with the host sampler."""
+    from lgml_b200.sampling import Sampler, SamplingParams
+
+    s = Sampler(SamplingParams.neutral(temperature, seed=seed))
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        logits = P.forward(cfg, w, ids)[-1].float().numpy()
+        t = s.sample(logits)
+        s.accept(t)
+        out.append(t)
+        ids.append(t)
+    return out
+
+
+def test_seeded_sampling_with_chunked_prefill_mixed_with_decodes(folders):
+    """tiny-B: prompts of 1 / 40 / 77 / 130 tokens, portions of 32 beside decoded tokens,
+    24 samples each at temperature 0.8 from per-request seeded streams."""
+    import lgml_b200
+    from lgml_b200.sampling import NEUTRAL
+
+    folder = folders[("B", "float32")]
+    cfg, w = P.load_folder(folder)
+    prompts = [H.random_ids(n, 320, 60 + n) for n in (1, 40, 77, 130)]
+    eng = lgml_b200.Engine(str(folder), dtype="float32", slots=4, ubatch=32, max_batch_tokens=64, kv_tokens=64 * 12)
+    got = eng.generate(prompts, max_tokens=24, temperature=0.8, seed=11, **NEUTRAL)
+    assert any(t["decode"] > 0 and not t["pure_decode"] for t in eng.turn_log)       # a decoded token beside a prompt portion
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert g == plain_sampled(cfg, w, p, 24, 0.8, 11 + i), i
+
+
+def test_preemption_keeps_every_reply_whole(folders):
+    """A pool that cannot hold all requests as they grow: requests are preempted and
+    prefilled again, and every reply equals the reply with room to spare."""
+    import lgml_b200
+
+    folder = folders[("B", "float32")]
+    prompts = [H.random_ids(n, 320, 80 + n) for n in (60, 50, 40, 30)]
+    roomy = lgml_b200.Engine(str(folder), dtype="float32", slots=4, kv_tokens=64 * 16)
+    want = roomy.generate(prompts, max_tokens=90, temperature=0.0)
+    tight = lgml_b200.Engine(str(folder), dtype="float32", slots=4, kv_tokens=64 * 5)
+    reqs = tight.generate(prompts, max_tokens=90, temperature=0.0, return_details=True)
+    assert tight.scheduler.stats["preemptions"] >= 1
+    assert [r.generated for r in reqs] == want
+    assert all(r.finish_reason == "length" for r in reqs)
+    tight.runner.cache.check()
+    assert tight.runner.cache.n_free_pages == 5
+
+
+def test_full_sampler_chain_runs_on_host_logits(folders):
+    import lgml_b200
+
+    folder = folders[("B", "bfloat16")]
+    eng = lgml_b200.Engine(str(folder), dtype="bfloat16", slots=2)
+    prompts = [H.random_ids(20, 320, 1), H.random_ids(9, 320, 2)]
+    a = eng.generate(prompts, max_tokens=12, seed=3, temperature=0.9, top_k=20, top_p=0.9, min_p=0.02, repeat_penalty=1.1)
+    b = eng.generate(prompts, max_tokens=12, seed=3, temperature=0.9, top_k=20, top_p=0.9, min_p=0.02, repeat_penalty=1.1)
+    assert a == b and all(len(x) == 12 and all(0 <= t < 320 for t in x) for x in a)
+    stop = a[0][3]
+    c = eng.generate(prompts[:1], max_tokens=12, seed=3, stop=[stop], temperature=0.9, top_k=20, top_p=0.9, min_p=0.02, repeat_penalty=1.1)
+    assert c[0] == a[0][: a[0].index(stop) + 1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_as_a_process(folders, dtype, tmp_path):
+    """bin/trace_run in a separate process: a mixed trace with page reuse, logits files and
+    'done' lines, compared with the plain implementation."""
+    folder = folders[("B", dtype)]
+    seqs = {f"r{i}": H.random_ids(n, 320, 300 + i) for i, n in enumerate([25, 101, 154, 64, 130])}
+    steps = H.trace_mixed(seqs, max_tokens=64 * 7, seed=5)
+    out = tmp_path / "out"
+    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                           "--max-tokens", str(64 * 7)], input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
+                          capture_output=True, env=env, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    fed = {k: 0 for k in seqs}
+    got = {}
+    for st in steps:
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        rows = np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(n_want, 320)
+        r = 0
+        for e in st["entries"]:
+            for i in e["want"]:
+                got[(e["id"], fed[e["id"]] + i)] = torch.from_numpy(rows[r].copy())
+                r += 1
+            fed[e["id"]] += len(e["tokens"])
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=1.5e-2, rtol=1.5e-2)
+    H.compare_with_oracle(got, folder, seqs, **tol)
+
+
+def test_command_line(folders):
+    folder = folders[("A", "float32")]
+    cfg, w = P.load_folder(folder)
+    prompt = H.random_ids(9, 256, 5)
+    proc = subprocess.run([sys.executable, "-m", "lgml_b200", "-m", str(folder), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                           "-n", "6", "--temperature", "0", "-c", "128", "-np", "2", "-ub", "4"], cwd=ROOT, text=True, capture_output=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [int(t) for t in proc.stdout.strip().splitlines()[-1].split(",")] == P.greedy(cfg, w, prompt, 6)
+
+
+def test_errors_are_loud(folders, tmp_path):
+    import lgml_b200
+    from lgml_b200.engine.runner import ModelRunner, StepError
+    from lgml_b200.cache import PoolFull
+
+    folder = folders[("A", "float32")]
+    runner = ModelRunner.from_folder(folder, torch.float32, "cuda:0", n_pages=1, max_slots=2)
+    r = runner.open("r")
+    with pytest.raises(StepError, match="vocabulary"):
+        runner.step([(r, [256], [0])])
+    with pytest.raises(StepError, match="twice"):
+        runner.step([(r, [1], [0]), (r, [2], [0])])
+    with pytest.raises(StepError, match="wanted place"):
+        runner.step([(r, [1, 2], [2])])
+    with pytest.raises(PoolFull, match="kv pool full"):
+        runner.step([(r, [1] * 65, [])])
+    big = ModelRunner.from_folder(folder, torch.float32, "cuda:0", n_pages=4, max_slots=1)
+    with pytest.raises(StepError, match="context full"):
+        big.step([(big.open("s"), [1] * 129, [])])
+    with pytest.raises(RuntimeError, match="CUDA"):
+        lgml_b200.Engine(str(folder), device="cpu")
