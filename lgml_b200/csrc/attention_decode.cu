@@ -1,22 +1,25 @@
-// Paged attention for decoding (and short portions), bfloat16 cache, float32 math.
+// Paged attention for decoding (and short portions), bfloat16 cache, float32 softmax, on
+// tensor cores.
 //
 // Every query token is independent: token t of request s at position p attends to the
 // cells of s at positions <= p (the last `window` of them if a window is set).  The work of
 // one token is cut by KV head and, along the keys, into `n_splits` ranges of whole pages;
-// one CTA handles (token, KV head [x chunk of its query heads], split).  The query heads
-// that share a KV head (grouped-query attention) are processed together, so each key and
-// value is read from HBM once for all of them.  A split leaves an unnormalised partial
+// one CTA handles (token, KV head [x chunk of up to 8 of its query heads], split).  The query
+// heads that share a KV head (grouped-query attention) are processed together, so each key
+// and value is read from HBM once for all of them.  A split leaves an unnormalised partial
 // result (running maximum m, sum l, weighted values O) in scratch memory; a second kernel
 // merges the splits in a fixed order.  With one split the result is written directly.
 //
-// A page of one KV head is contiguous in the cache ([page][kv head][64][D]), so one thread
-// brings it into shared memory with a bulk asynchronous copy (cp.async.bulk, completion on an
-// mbarrier); two stages are kept in flight so the copy of the next pages overlaps the math
-// of this one.  Per page: (1) scores, 8 lanes per key, each lane 16-byte chunks of the row,
-// reduced by shuffles; (2) online softmax per head by one warp; (3) values, threads own 8
-// output dimensions and walk the keys.  Softmax, sums and the output accumulators are float32
-// (lua/lgml/transformer.lua:1805-1816 for the formula, :1845 for the scale).  Waits on the
-// mbarriers are bounded; a wait that runs out sets `status` and the CTA winds down.
+// With one query per head there is no tall Q tile, so the products are turned round: the keys
+// are the M side of the tensor-core tile and the (up to 8) heads the N side:
+//     S^T[64 keys, 8 heads] = K[64, D] . Q^T[D, 8]        (mma.sync m16n8k16, 4 x D/16 per page)
+//     O^T[D, 8 heads]      += V^T[D, 64] . P^T[64, 8]      (D/16 x 4 per page)
+// K is read row-major as the A operand (ldmatrix), V transposed (ldmatrix.trans), Q^T sits in
+// registers for the whole kernel and P^T goes through shared memory as bfloat16.  Pages are
+// copied into padded shared-memory rows with cp.async, three stages deep (two for head sizes
+// over 128), so the copies of the next pages overlap the math of this one.  Softmax, the
+// running sums and the output accumulators are float32 (lua/lgml/transformer.lua:1805-1816
+// for the formula, :1845 for the scale).
 #include <math.h>
 
 #include "common.cuh"
@@ -25,72 +28,61 @@ LGML_DEFINE_LAST_ERROR(lgml_attention_decode)
 
 namespace {
 constexpr int PAGE = 64;
-constexpr int THREADS = 256;
-constexpr int KEYS_PER_WARP = PAGE / (THREADS / 32);   // 8
-constexpr int KK = KEYS_PER_WARP / 4;                  // groups of 4 keys a warp walks per page
+constexpr int THREADS = 128;
+constexpr int WARPS = THREADS / 32;
 constexpr int MAX_D = 256;
-constexpr uint32_t SPIN_LIMIT = 4u << 20;
-constexpr int STATUS_TIMEOUT = 11;
+constexpr int NH = 8;                  // heads per CTA = the N of the tensor-core tile
+constexpr int PLD = PAGE + 8;          // padded row of P^T (bfloat16)
 
-__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
+__device__ __forceinline__ void cp_async_16(void *dst, const void *src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicExch(status, STATUS_TIMEOUT);
-    return false;
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int G, int STAGES>
-__global__ void __launch_bounds__(THREADS, 2) decode_attention_kernel(
+// KS = D / 16.  G here is only the count of heads this CTA really has (<= 8).
+template <int KS, int STAGES>
+__global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo,
-    float *__restrict__ part_o, float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int D, int n_chunks,
+    float *__restrict__ part_o, float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks,
     float scale, int window, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    // [STAGES][K page | V page] bf16, then the float arrays
-    const int page_bytes = PAGE * D * 2;
-    uint8_t *kv_s = smem_raw;
-    const int n_chunk_ = D / 8;
-    const size_t red_bytes = sizeof(float) * (size_t)min(THREADS / n_chunk_, PAGE) * G * D;
-    const size_t stage_bytes = (size_t)STAGES * 2 * page_bytes;
-    float *qs = reinterpret_cast<float *>(smem_raw + (stage_bytes > red_bytes ? stage_bytes : red_bytes));   // [G][D]
-    float *S = qs + G * D;                  // [PAGE][G] scores, then probabilities
-    float *m_s = S + PAGE * G;              // [G]
-    float *l_s = m_s + G;                   // [G]
-    float *corr_s = l_s + G;                // [G]
-    float *red = reinterpret_cast<float *>(kv_s);   // [key groups][G][D] for the final sum: the page stages are free by then
-    __shared__ uint64_t full_bar[STAGES];
-    __shared__ int stage_ok[STAGES];   // whether the stage holds a page (the table had one)
+    constexpr int D = KS * 16;
+    constexpr int LD = D + 8;                       // padded row of the K and V stages (elements)
+    constexpr int MT = (KS + WARPS - 1) / WARPS;    // output m tiles (16 dims) per warp
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16 *kv_s = reinterpret_cast<__nv_bfloat16 *>(smem_raw);       // [STAGES][K | V][PAGE][LD]
+    float *S = reinterpret_cast<float *>(kv_s + (size_t)STAGES * 2 * PAGE * LD);   // [PAGE][NH] scores
+    __nv_bfloat16 *Pt = reinterpret_cast<__nv_bfloat16 *>(S + PAGE * NH);    // [NH][PLD] probabilities, transposed
+    __shared__ float m_s[NH], l_s[NH], corr_s[NH];
+    __shared__ int stage_ok[STAGES];
 
     const int t = blockIdx.x;
     const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
     const int split = blockIdx.z;
     const int group = H / Hkv;
-    const int h0 = kvh * group + chunk * G;                       // first query head of this CTA
-    const int g_count = min(G, group - chunk * G);                // heads it really has
+    const int h0 = kvh * group + chunk * heads_per_cta;                 // first query head of this CTA
+    const int g_count = min(heads_per_cta, group - chunk * heads_per_cta);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int mat = lane >> 3, mrow = lane & 7;
 
     const int pos = positions[t];
     const int seq = seq_of_token[t];
@@ -104,147 +96,85 @@ __global__ void __launch_bounds__(THREADS, 2) decode_attention_kernel(
     const int pe = min(pb + pps, n_pages_seq);
     const int n_iter = max(pe - pb, 0);
 
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[s])), "r"(1));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // Q^T as B fragments: b0 holds (d = 16 ks + 2 (lane % 4) + {0, 1}, head = lane / 4), b1 the same 8 dims on
+    uint32_t qb[KS][2];
+    {
+        const int head = lane >> 2;
+        const __nv_bfloat16 *qrow = q + (size_t)t * ldq + (size_t)(h0 + head) * D + (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qb[ks][0] = head < g_count ? *reinterpret_cast<const uint32_t *>(qrow + ks * 16) : 0u;
+            qb[ks][1] = head < g_count ? *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8) : 0u;
+        }
     }
-    // queries to shared memory as float32, pre-multiplied by the scale
-    for (int i = tid; i < G * D; i += THREADS) {
-        const int g = i / D, d = i - g * D;
-        qs[i] = g < g_count ? to_f32(q[(size_t)t * ldq + (size_t)(h0 + g) * D + d]) * scale : 0.f;
-    }
-    if (tid < G) {
+    for (int i = tid; i < NH * PLD; i += THREADS) Pt[i] = __float2bfloat16_rn(0.f);   // heads this CTA does not have stay zero
+    if (tid < NH) {
         m_s[tid] = -INFINITY;
         l_s[tid] = 0.f;
+        corr_s[tid] = 1.f;
     }
-    __syncthreads();
 
-    // Issue the copy of the page of iteration `it` into stage it % STAGES: only the rows the
-    // query can see (rows 0 .. last valid key); a page the table does not hold is skipped.
-    auto issue = [&](int it, int page) {
+    // Copy the page of iteration `it` into stage it % STAGES; rows past the last visible key are zero.
+    auto load_page = [&](int it) {
         const int pg = pb + it;
-        uint64_t *bar = &full_bar[it % STAGES];
-        if (page < 0 || page >= n_pages) {
-            atomicExch(status, 3);
-            stage_ok[it % STAGES] = 0;
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-            return;
+        const int stage = it % STAGES;
+        const int page = table[pg];
+        const bool have = page >= 0 && page < n_pages;
+        if (tid == 0) {
+            stage_ok[stage] = have ? 1 : 0;
+            if (!have) atomicExch(status, 3);
         }
-        stage_ok[it % STAGES] = 1;
-        const int k_end = min(pos - pg * PAGE + 1, PAGE);
-        const uint32_t bytes = (uint32_t)k_end * D * 2;
-        const size_t off = ((size_t)page * Hkv + kvh) * PAGE * D;
-        uint8_t *dst = kv_s + (size_t)(it % STAGES) * 2 * page_bytes;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(2 * bytes) : "memory");
-        bulk_load(dst, k_pages + off, bytes, bar);
-        bulk_load(dst + page_bytes, v_pages + off, bytes, bar);
+        const int valid_rows = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
+        const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
+        __nv_bfloat16 *ks_ = kv_s + (size_t)stage * 2 * PAGE * LD, *vs_ = ks_ + PAGE * LD;
+        for (int c = tid; c < PAGE * (D / 8); c += THREADS) {
+            const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+            const bool ok = row < valid_rows;
+            cp_async_16(ks_ + row * LD + col, k_pages + off + (size_t)row * D + col, ok);
+            cp_async_16(vs_ + row * LD + col, v_pages + off + (size_t)row * D + col, ok);
+        }
     };
-    if (tid == 0) {
-        int first[STAGES];
 #pragma unroll
-        for (int it = 0; it < STAGES; ++it) first[it] = it < n_iter ? table[pb + it] : -1;   // the loads overlap
-#pragma unroll
-        for (int it = 0; it < STAGES; ++it)
-            if (it < n_iter) issue(it, first[it]);
+    for (int it = 0; it < STAGES - 1; ++it) {
+        if (it < n_iter) load_page(it);
+        cp_async_commit();
     }
 
-    const int n_chunk = D / 8;                         // 16-byte chunks per row
-    // value phase: thread = (key group, chunk of 8 dims)
-    const int KG = min(THREADS / n_chunk, PAGE);
-    const bool pv_active = tid < KG * n_chunk;
-    const int kgroup = tid / n_chunk, vchunk = tid - kgroup * n_chunk;
-    float acc[G][8];
+    float oacc[MT][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
-    // score phase: 8 lanes per key, 4 keys per warp at a time
-    const int sub = lane & 7, key_in_warp = lane >> 3;
-    bool alive = true;
+    for (int i = 0; i < MT; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
     for (int it = 0; it < n_iter; ++it) {
+        if (it + STAGES - 1 < n_iter) load_page(it + STAGES - 1);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        const int stage = it % STAGES;
         const int pg = pb + it;
-        // the table entry of the page STAGES iterations ahead: read now, used at the end of this iteration
-        int page_ahead = -1;
-        if (tid == 0 && it + STAGES < n_iter) page_ahead = table[pg + STAGES];
-        if (alive && !mbar_wait(&full_bar[it % STAGES], (it / STAGES) & 1, status)) alive = false;
-        const bool have = stage_ok[it % STAGES] != 0;
-        const int k_begin = max(lo - pg * PAGE, 0), k_end = min(pos - pg * PAGE + 1, PAGE);
-        const uint8_t *kp = kv_s + (size_t)(it % STAGES) * 2 * page_bytes;
-        const uint8_t *vp = kp + page_bytes;
+        const bool have = stage_ok[stage] != 0;
+        const int k_begin = max(lo - pg * PAGE, 0), k_end = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
+        const __nv_bfloat16 *ks_ = kv_s + (size_t)stage * 2 * PAGE * LD, *vs_ = ks_ + PAGE * LD;
 
-        // ---- (1) scores: warp w takes keys 8w .. 8w+7; lane = (key_in_warp, sub): four keys at a
-        // time, 8 lanes per key, lane `sub` owning the 16-byte chunks sub, sub + 8, ... of the row.
-        // The queries of a chunk are held in registers while the keys of the warp go by.
+        // ---- (1) S^T = K Q^T: warp w takes keys 16w .. 16w + 15 ----------------------------------
         {
-            const uint4 *rows4[KK];
-            bool key_ok[KK];
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int kk = 0; kk < KK; ++kk) {
-                const int key = warp * KEYS_PER_WARP + kk * 4 + key_in_warp;
-                key_ok[kk] = have && alive && key >= k_begin && key < k_end;
-                rows4[kk] = reinterpret_cast<const uint4 *>(kp + (size_t)key * D * 2);
-            }
-            constexpr int GB = G < 4 ? G : 4;           // query heads held in registers at a time
-            float s[KK][G];
-#pragma unroll
-            for (int kk = 0; kk < KK; ++kk)
-#pragma unroll
-                for (int g = 0; g < G; ++g) s[kk][g] = 0.f;
-            for (int c = sub; c < n_chunk; c += 8) {
-#pragma unroll
-                for (int g0 = 0; g0 < G; g0 += GB) {
-                    float qr[GB][8];
-#pragma unroll
-                    for (int g = 0; g < GB; ++g) {
-                        if (g0 + g < G) {
-                            const float4 lo4 = *reinterpret_cast<const float4 *>(qs + (size_t)(g0 + g) * D + c * 8);
-                            const float4 hi4 = *reinterpret_cast<const float4 *>(qs + (size_t)(g0 + g) * D + c * 8 + 4);
-                            qr[g][0] = lo4.x; qr[g][1] = lo4.y; qr[g][2] = lo4.z; qr[g][3] = lo4.w;
-                            qr[g][4] = hi4.x; qr[g][5] = hi4.y; qr[g][6] = hi4.z; qr[g][7] = hi4.w;
-                        }
-                    }
-#pragma unroll
-                    for (int kk = 0; kk < KK; ++kk) {
-                        if (key_ok[kk]) {
-                            const uint4 kv4 = rows4[kk][c];
-                            const uint32_t w[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
-#pragma unroll
-                            for (int g = 0; g < GB; ++g) {
-                                if (g0 + g < G) {
-                                    float a = s[kk][g0 + g];
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) a = fmaf(qr[g][2 * e], bf16_lo(w[e]), fmaf(qr[g][2 * e + 1], bf16_hi(w[e]), a));
-                                    s[kk][g0 + g] = a;
-                                }
-                            }
-                        }
-                    }
-                }
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t a[4];
+                ldmatrix_x4(a, ks_ + (size_t)(warp * 16 + (mat & 1) * 8 + mrow) * LD + ks * 16 + (mat >> 1) * 8);
+                mma_bf16(c, a, qb[ks][0], qb[ks][1]);
             }
 #pragma unroll
-            for (int kk = 0; kk < KK; ++kk) {
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    float v = s[kk][g];
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    v += __shfl_xor_sync(0xffffffffu, v, 4);
-                    s[kk][g] = v;
-                }
-                if (sub == 0) {
-                    const int key = warp * KEYS_PER_WARP + kk * 4 + key_in_warp;
-#pragma unroll
-                    for (int g = 0; g < G; ++g) S[key * G + g] = key_ok[kk] ? s[kk][g] : -INFINITY;
-                }
+            for (int i = 0; i < 4; ++i) {
+                const int key = warp * 16 + (lane >> 2) + (i >> 1) * 8, head = (lane & 3) * 2 + (i & 1);
+                S[key * NH + head] = (key >= k_begin && key < k_end) ? c[i] * scale : -INFINITY;
             }
         }
         __syncthreads();
 
-        // ---- (2) online softmax, one warp per head ---------------------------------------------
-        for (int g = warp; g < G; g += THREADS / 32) {
-            const float s0 = S[lane * G + g], s1 = S[(lane + 32) * G + g];
+        // ---- (2) online softmax, one warp per head -----------------------------------------------
+        for (int g = warp; g < g_count; g += WARPS) {
+            const float s0 = S[lane * NH + g], s1 = S[(lane + 32) * NH + g];
             const float mx = warp_max(fmaxf(s0, s1));
             const float m_old = m_s[g];
             const float m_new = fmaxf(m_old, mx);
@@ -254,9 +184,11 @@ __global__ void __launch_bounds__(THREADS, 2) decode_attention_kernel(
                 p0 = expf(s0 - m_new);
                 p1 = expf(s1 - m_new);
             }
-            const float ls = warp_sum(p0 + p1);
-            S[lane * G + g] = p0;
-            S[(lane + 32) * G + g] = p1;
+            // the sum runs over the probabilities as the product will see them (rounded to bfloat16)
+            const __nv_bfloat16 h0_ = __float2bfloat16_rn(p0), h1_ = __float2bfloat16_rn(p1);
+            const float ls = warp_sum(__bfloat162float(h0_) + __bfloat162float(h1_));
+            Pt[g * PLD + lane] = h0_;
+            Pt[g * PLD + lane + 32] = h1_;
             if (lane == 0) {
                 m_s[g] = m_new;
                 l_s[g] = l_s[g] * corr + ls;
@@ -265,61 +197,54 @@ __global__ void __launch_bounds__(THREADS, 2) decode_attention_kernel(
         }
         __syncthreads();
 
-        // ---- (3) values --------------------------------------------------------------------------
-        if (pv_active) {
+        // ---- (3) O^T += V^T P^T: warp w takes the 16-dim tiles w, w + 4, ... -----------------------
+        {
+            const float ca = corr_s[(lane & 3) * 2], cb = corr_s[(lane & 3) * 2 + 1];
+            uint32_t pb_[4][2];
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float c = corr_s[g];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[g][e] *= c;
+            for (int k2 = 0; k2 < 4; ++k2) {
+                const __nv_bfloat16 *pr = Pt + (lane >> 2) * PLD + k2 * 16 + (lane & 3) * 2;
+                pb_[k2][0] = *reinterpret_cast<const uint32_t *>(pr);
+                pb_[k2][1] = *reinterpret_cast<const uint32_t *>(pr + 8);
             }
-            if (have && alive) {
-                for (int key = k_begin + kgroup; key < k_end; key += KG) {
-                    const uint4 vv = *reinterpret_cast<const uint4 *>(vp + ((size_t)key * D + vchunk * 8) * 2);
-                    const uint32_t w[4] = {vv.x, vv.y, vv.z, vv.w};
-                    const float *p = S + key * G;
 #pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const float pg_ = p[g];
+            for (int mi = 0; mi < MT; ++mi) {
+                const int mt = warp + mi * WARPS;
+                if (mt < KS) {
+                    oacc[mi][0] *= ca;
+                    oacc[mi][1] *= cb;
+                    oacc[mi][2] *= ca;
+                    oacc[mi][3] *= cb;
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            acc[g][2 * e] = fmaf(pg_, bf16_lo(w[e]), acc[g][2 * e]);
-                            acc[g][2 * e + 1] = fmaf(pg_, bf16_hi(w[e]), acc[g][2 * e + 1]);
-                        }
+                    for (int k2 = 0; k2 < 4; ++k2) {
+                        uint32_t a[4];
+                        ldmatrix_x4_trans(a, vs_ + (size_t)(k2 * 16 + (mat >> 1) * 8 + mrow) * LD + mt * 16 + (mat & 1) * 8);
+                        mma_bf16(oacc[mi], a, pb_[k2][0], pb_[k2][1]);
                     }
                 }
             }
         }
-        __syncthreads();
-        // the stage is free: bring in the page two iterations ahead
-        if (tid == 0 && alive && it + STAGES < n_iter) issue(it + STAGES, page_ahead);
+        __syncthreads();   // S, P^T and the stage are free for the next iterations
     }
-    // If a wait ran out, copies may still be in flight: give them a bounded time to land
-    // before the shared memory can be handed to another CTA.
-    if (!alive && tid == 0) {
-        for (int it = max(n_iter - STAGES, 0); it < n_iter; ++it)
-            for (uint32_t spin = 0; spin < SPIN_LIMIT && !mbar_try_wait(&full_bar[it % STAGES], (it / STAGES) & 1); ++spin) {
-            }
-    }
+    cp_async_wait<0>();
 
-    // ---- sum over key groups, then write ------------------------------------------------------
-    if (pv_active) {
+    // ---- write: O^T fragment rows are dims, columns heads ---------------------------------------------
 #pragma unroll
-        for (int g = 0; g < G; ++g)
+    for (int mi = 0; mi < MT; ++mi) {
+        const int mt = warp + mi * WARPS;
+        if (mt >= KS) continue;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) red[((size_t)kgroup * G + g) * D + vchunk * 8 + e] = acc[g][e];
-    }
-    __syncthreads();
-    for (int i = tid; i < g_count * D; i += THREADS) {
-        const int g = i / D, d = i - g * D;
-        float o = 0.f;
-        for (int kg = 0; kg < KG; ++kg) o += red[((size_t)kg * G + g) * D + d];
-        const int h = h0 + g;
-        if (n_splits == 1) {
-            const float l = l_s[g];
-            out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
-        } else {
-            part_o[(((size_t)t * H + h) * n_splits + split) * D + d] = o;
+        for (int i = 0; i < 4; ++i) {
+            const int d = mt * 16 + (lane >> 2) + (i >> 1) * 8, head = (lane & 3) * 2 + (i & 1);
+            if (head >= g_count) continue;
+            const int h = h0 + head;
+            const float o = oacc[mi][i];
+            if (n_splits == 1) {
+                const float l = l_s[head];
+                out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+            } else {
+                part_o[(((size_t)t * H + h) * n_splits + split) * D + d] = o;
+            }
         }
     }
     if (n_splits > 1 && tid < g_count)
@@ -346,41 +271,20 @@ __global__ void decode_combine_kernel(const float *__restrict__ part_o, const fl
     }
 }
 
-size_t smem_bytes(int G, int D, int STAGES) {
-    const int n_chunk = D / 8;
-    int kg = THREADS / n_chunk;
-    if (kg > PAGE) kg = PAGE;
-    size_t stages = (size_t)STAGES * 2 * PAGE * D * 2, red = sizeof(float) * (size_t)kg * G * D;
-    return (stages > red ? stages : red) + sizeof(float) * ((size_t)D * G + (size_t)PAGE * G + 3 * G);
-}
-
-template <int G, int STAGES>
-int launch_stages(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
-           int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo,
-           float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int D, int n_chunks, float scale, int window,
-           int *status, cudaStream_t stream) {
-    const size_t smem = smem_bytes(G, D, STAGES);
+template <int KS, int STAGES>
+int launch_ks(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
+              int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo,
+              float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks, float scale, int window,
+              int *status, cudaStream_t stream) {
+    constexpr int D = KS * 16;
+    const size_t smem = (size_t)STAGES * 2 * PAGE * (D + 8) * 2 + sizeof(float) * PAGE * NH + 2 * NH * PLD;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<G, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<KS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("decode_attention: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    lgml_launch(decode_attention_kernel<G, STAGES>, grid, THREADS, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
-                                                               v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, D,
-                                                               n_chunks, scale, window, status);
+    lgml_launch(decode_attention_kernel<KS, STAGES>, grid, THREADS, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks,
+                k_pages, v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, heads_per_cta, n_chunks, scale, window, status);
     return 0;
-}
-
-// Three stages while a page of K and V (2 x 64 x D bfloat16) is at most 32 KB, else two.
-template <int G>
-int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
-           int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo,
-           float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int D, int n_chunks, float scale, int window,
-           int *status, cudaStream_t stream) {
-    if (D <= 128)
-        return launch_stages<G, 3>(grid, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages, v_pages, n_pages, out, ldo,
-                                   part_o, part_ml, n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);
-    return launch_stages<G, 2>(grid, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages, v_pages, n_pages, out, ldo,
-                               part_o, part_ml, n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);
 }
 }  // namespace
 
@@ -404,25 +308,28 @@ LGML_API int lgml_decode_attention(const void *q, int ldq, const int *positions,
     LGML_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0, "decode_attention: the cache must be 16-byte aligned");
     if (n_tokens == 0) return 0;
     const int group = H / Hkv;
-    const int n_chunks = (group + 7) / 8;
-    const int G = (group + n_chunks - 1) / n_chunks;   // 1..8 query heads per CTA
+    const int n_chunks = (group + NH - 1) / NH;
+    const int heads_per_cta = (group + n_chunks - 1) / n_chunks;   // 1..8 query heads per CTA
     LGML_REQUIRE((long long)Hkv * n_chunks <= 65535, "decode_attention: too many heads");
+    LGML_REQUIRE(ldq % 2 == 0 && ((uintptr_t)q & 3) == 0, "decode_attention: q must be 4-byte aligned with an even row stride");
     dim3 grid(n_tokens, Hkv * n_chunks, n_splits);
     float *part_o = scratch;
     float2 *part_ml = reinterpret_cast<float2 *>(scratch + (size_t)n_tokens * H * n_splits * D);
     const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
     int lrc = 0;
-#define LGML_CASE(GG)                                                                                                             \
-    case GG:                                                                                                                      \
-        lrc = launch<GG>(grid, qq, ldq, positions, seq_of_token, block_table, max_blocks, kk, vv, n_pages, oo, ldo, part_o, part_ml, \
-                         n_splits, H, Hkv, D, n_chunks, scale, window, status, stream);                                           \
-        break;
-    switch (G) {
-        LGML_CASE(1) LGML_CASE(2) LGML_CASE(3) LGML_CASE(4) LGML_CASE(5) LGML_CASE(6) LGML_CASE(7) LGML_CASE(8)
-        default: LGML_FAIL("decode_attention: group of %d heads not handled", G);
+#define LGML_ARGS grid, qq, ldq, positions, seq_of_token, block_table, max_blocks, kk, vv, n_pages, oo, ldo, part_o, part_ml, n_splits, H, Hkv, \
+                  heads_per_cta, n_chunks, scale, window, status, stream
+#define LGML_CASE3(KK) case KK: lrc = launch_ks<KK, 3>(LGML_ARGS); break;
+#define LGML_CASE2(KK) case KK: lrc = launch_ks<KK, 2>(LGML_ARGS); break;
+    switch (D / 16) {
+        LGML_CASE3(1) LGML_CASE3(2) LGML_CASE3(3) LGML_CASE3(4) LGML_CASE3(5) LGML_CASE3(6) LGML_CASE3(7) LGML_CASE3(8)
+        LGML_CASE2(9) LGML_CASE2(10) LGML_CASE2(11) LGML_CASE2(12) LGML_CASE2(13) LGML_CASE2(14) LGML_CASE2(15) LGML_CASE2(16)
+        default: LGML_FAIL("decode_attention: head_dim %d not handled", D);
     }
-#undef LGML_CASE
+#undef LGML_CASE3
+#undef LGML_CASE2
+#undef LGML_ARGS
     if (lrc) return lrc;
     int rc = lgml_launch_status("decode_attention");
     if (rc) return rc;

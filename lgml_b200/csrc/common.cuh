@@ -72,6 +72,34 @@ static inline cudaError_t lgml_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same with a thread-block cluster of `cluster` CTAs along x (1: no cluster).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t lgml_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster,
+                                              Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (lgml_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Element types: 0 = float32, 1 = bfloat16.
 enum { LGML_F32 = 0, LGML_BF16 = 1 };
 

@@ -1,6 +1,8 @@
 // Embedding gather, RMSNorm (with the residual add and a row gather fused in), SwiGLU
 // activation, bias add and the seeded normal fill.  The residual stream is float32 in
 // every mode; norms and the activation compute in float32.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 LGML_DEFINE_LAST_ERROR(lgml_elementwise)
@@ -47,31 +49,39 @@ LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids,
 //                   delta is then added for the gathered rows only and x is not written.
 // One block per output row; the mean square is summed in a fixed order.
 // ---------------------------------------------------------------------------------------
+// A row is spread over a thread-block cluster of CS CTAs (CS = 1 for narrow rows): with few
+// rows (decoding) one CTA per row would leave the row's bytes to a single SM's memory path.
+// Each CTA sums the squares of its slice; the slices' sums are exchanged through distributed
+// shared memory and added in rank order.
 template <typename TD, typename TO>
 __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta, int n_parts, long long part_stride,
                                const float *__restrict__ delta_bias, const float *__restrict__ weight,
-                               const int *__restrict__ rows, TO *__restrict__ out, int width, float eps) {
+                               const int *__restrict__ rows, TO *__restrict__ out, int width, float eps, int cs) {
     pdl_trigger();
     pdl_wait();
+    namespace cg = cooperative_groups;
     __shared__ float red[32];
-    constexpr int PER = 8;            // elements a thread keeps in registers; wider rows loop
-    const int r = blockIdx.x;
+    __shared__ float slice_ss;
+    constexpr int PER = 4;            // elements a thread keeps in registers per round
+    const int r = blockIdx.x / cs, rank = blockIdx.x - r * cs;
+    const int per_cta = ((width + cs - 1) / cs + 3) & ~3;
+    const int c0 = rank * per_cta, c1 = min(width, c0 + per_cta);
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float *xr = x + src * width;
     const TD *dr = delta ? delta + src * width : nullptr;
     float ss = 0.f;
-    for (int base = 0; base < width; base += PER * blockDim.x) {
+    for (int base = c0; base < c1; base += PER * blockDim.x) {
         // all loads of this round first, so that they are in flight together
         float v[PER], d[PER];
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int i = base + j * blockDim.x + threadIdx.x;
-            v[j] = i < width ? xr[i] : 0.f;
-            d[j] = (dr && i < width) ? to_f32(dr[i]) : 0.f;
+            v[j] = i < c1 ? xr[i] : 0.f;
+            d[j] = (dr && i < c1) ? to_f32(dr[i]) : 0.f;
         }
         if (dr) {
-            // the parts are the partial sums of a matrix product cut along K: added in order
-            // four parts are fetched together (their loads overlap), then added in order
+            // the parts are the partial sums of a matrix product cut along K: four are fetched
+            // together (their loads overlap), then added in order
             int p = 1;
             for (; p + 4 <= n_parts; p += 4) {
                 float e[4][PER];
@@ -80,7 +90,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
                     for (int j = 0; j < PER; ++j) {
                         const int i = base + j * blockDim.x + threadIdx.x;
-                        e[q][j] = i < width ? to_f32(dr[(size_t)(p + q) * part_stride + i]) : 0.f;
+                        e[q][j] = i < c1 ? to_f32(dr[(size_t)(p + q) * part_stride + i]) : 0.f;
                     }
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -92,7 +102,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int i = base + j * blockDim.x + threadIdx.x;
-                    e[j] = i < width ? to_f32(dr[(size_t)p * part_stride + i]) : 0.f;
+                    e[j] = i < c1 ? to_f32(dr[(size_t)p * part_stride + i]) : 0.f;
                 }
 #pragma unroll
                 for (int j = 0; j < PER; ++j) d[j] += e[j];
@@ -100,7 +110,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
             for (int j = 0; j < PER; ++j) {
                 const int i = base + j * blockDim.x + threadIdx.x;
-                if (i < width) {
+                if (i < c1) {
                     if (delta_bias) d[j] += delta_bias[i];
                     v[j] += d[j];
                     if (!rows) xr[i] = v[j];
@@ -110,22 +120,30 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
         for (int j = 0; j < PER; ++j) ss = fmaf(v[j], v[j], ss);
     }
-    const float total = block_sum(ss, red);
+    float total = block_sum(ss, red);
+    if (cs > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (threadIdx.x == 0) slice_ss = total;
+        cluster.sync();
+        total = 0.f;
+        for (int k = 0; k < cs; ++k) total += *cluster.map_shared_rank(&slice_ss, k);
+        cluster.sync();               // no CTA leaves while another may still read its slice's sum
+    }
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
     // second pass: with a delta the row was just written (or, with a row list, is summed again the same way)
-    for (int base = 0; base < width; base += PER * blockDim.x) {
+    for (int base = c0; base < c1; base += PER * blockDim.x) {
         float v[PER], w[PER];
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int i = base + j * blockDim.x + threadIdx.x;
-            w[j] = i < width ? weight[i] : 0.f;
-            v[j] = i < width ? xr[i] : 0.f;
+            w[j] = i < c1 ? weight[i] : 0.f;
+            v[j] = i < c1 ? xr[i] : 0.f;
         }
         if (dr && rows) {
 #pragma unroll
             for (int j = 0; j < PER; ++j) {
                 const int i = base + j * blockDim.x + threadIdx.x;
-                if (i < width) {
+                if (i < c1) {
                     float d = to_f32(dr[i]);
                     for (int p = 1; p < n_parts; ++p) d += to_f32(dr[(size_t)p * part_stride + i]);
                     if (delta_bias) d += delta_bias[i];
@@ -136,7 +154,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
             const int i = base + j * blockDim.x + threadIdx.x;
-            if (i < width) out[(size_t)r * width + i] = from_f32<TO>(v[j] * inv * w[j]);
+            if (i < c1) out[(size_t)r * width + i] = from_f32<TO>(v[j] * inv * w[j]);
         }
     }
 }
@@ -145,13 +163,16 @@ template <typename TD>
 static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long part_stride, const float *delta_bias,
                             const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
                             cudaStream_t stream) {
-    // one block per row; the block's size depends on the width only, so a row's sum is formed
-    // in the same order whatever else is in the batch
-    const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    // The cluster and block sizes depend on the width only, so a row's sum is formed in the
+    // same order whatever else is in the batch.
+    const int cs = width >= 2048 ? 8 : (width >= 1024 ? 4 : 1);
+    const int threads = 128;
+    cudaError_t e;
     if (out_dtype == LGML_F32)
-        lgml_launch(rmsnorm_kernel<TD, float>, n_rows, threads, 0, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps);
+        e = lgml_launch_cluster(rmsnorm_kernel<TD, float>, n_rows * cs, threads, 0, stream, cs, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps, cs);
     else
-        lgml_launch(rmsnorm_kernel<TD, __nv_bfloat16>, n_rows, threads, 0, stream, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps);
+        e = lgml_launch_cluster(rmsnorm_kernel<TD, __nv_bfloat16>, n_rows * cs, threads, 0, stream, cs, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps, cs);
+    (void)e;
     return lgml_launch_status("rmsnorm");
 }
 

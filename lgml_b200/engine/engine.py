@@ -82,7 +82,7 @@ class Engine:
         sampled: Dict[Hashable, int] = {}
         rows = [e for e in plan if e.sample]
         if rows:
-            neutral = all(e.request.params.is_neutral for e in rows)
+            neutral = all(e.request.params.on_device for e in rows)
             if neutral and all(e.request.params.greedy for e in rows):
                 out = torch.empty(len(rows), dtype=torch.int32, device=logits.device)
                 toks = ops.argmax_rows(logits, out).cpu().tolist()

@@ -49,17 +49,16 @@ class GenRequest:
     preemptions: int = 0
     repeat_run: int = 0
 
+    tokens: List[int] = field(default_factory=list)   # prompt + generated, kept as one list
+
     def __post_init__(self):
         if self.sampler is None:
             self.sampler = Sampler(self.params)
-
-    @property
-    def tokens(self) -> List[int]:
-        return self.prompt + self.generated
+        self.tokens = list(self.prompt) + list(self.generated)
 
     @property
     def n_pending(self) -> int:
-        return len(self.prompt) + len(self.generated) - self.n_cached
+        return len(self.tokens) - self.n_cached
 
 
 @dataclass
@@ -204,6 +203,7 @@ class Scheduler:
             req.sampler.accept(tok)
             req.repeat_run = req.repeat_run + 1 if (req.generated and req.generated[-1] == tok) else 1
             req.generated.append(tok)
+            req.tokens.append(tok)
             reason = None
             if tok in req.stop_ids:
                 reason = "stop"

@@ -102,6 +102,15 @@ class SamplingParams:
         return not self.temperature > 0.0
 
     @property
+    def on_device(self) -> bool:
+        """The device kernels give this chain's result: nothing alters the logits before the
+        draw, and either the draw is the argmax (temperature <= 0: the filters always keep the
+        maximum, ``src/sample.c:937-940``) or every filter is off."""
+        plain = (not self.logit_bias and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0
+                 and self.presence_penalty == 0.0)
+        return plain and (self.greedy or self.is_neutral)
+
+    @property
     def is_neutral(self) -> bool:
         """No step of the chain but temperature and the draw changes the logits."""
         return (not self.logit_bias and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0
