@@ -143,11 +143,24 @@ class DecodeGraph:
         if device_tokens is not None:
             b.token_ids.copy_(device_tokens)
         if self.graph is None:
-            g = torch.cuda.CUDAGraph()
-            before = ops.launch_count()
-            with torch.cuda.graph(g):
-                self.logits = self.runner.model.forward(self.runner.rt, b)
-            self.kernels = ops.launch_count() - before
-            self.graph = g
+            # Nothing but the step's own launches may touch CUDA while the stream is capturing:
+            # a finaliser that frees device or pinned memory in the middle (Python's collector
+            # can run at any allocation) would invalidate the capture.  So collect first, keep
+            # the collector off during the capture, and let the capture tolerate such calls.
+            import gc
+
+            gc.collect()
+            was_on = gc.isenabled()
+            gc.disable()
+            try:
+                g = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
+                with torch.cuda.graph(g, capture_error_mode="relaxed"):
+                    self.logits = self.runner.model.forward(self.runner.rt, b)
+                self.kernels = ops.launch_count() - before
+                self.graph = g
+            finally:
+                if was_on:
+                    gc.enable()
         self.graph.replay()
         return self.logits
