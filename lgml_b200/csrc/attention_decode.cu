@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const int pb = first_page + split * pps;
     const int pe = min(pb + pps, n_pages_seq);
     const int n_iter = max(pe - pb, 0);
+    const float scale_log2 = scale * 1.4426950408889634f;
 
     // Q^T as B fragments: b0 holds (d = 16 ks + 2 (lane % 4) + {0, 1}, head = lane / 4), b1 the same 8 dims on
     uint32_t qb[KS][2];
@@ -167,7 +168,8 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int key = warp * 16 + (lane >> 2) + (i >> 1) * 8, head = (lane & 3) * 2 + (i & 1);
-                S[key * NH + head] = (key >= k_begin && key < k_end) ? c[i] * scale : -INFINITY;
+                // scores in the base-2 domain: exp(x) = exp2(x log2 e), and exp2 is one instruction
+                S[key * NH + head] = (key >= k_begin && key < k_end) ? c[i] * scale_log2 : -INFINITY;
             }
         }
         __syncthreads();
@@ -180,9 +182,9 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
             const float m_new = fmaxf(m_old, mx);
             float p0 = 0.f, p1 = 0.f, corr = 1.f;
             if (m_new != -INFINITY) {
-                corr = expf(m_old - m_new);
-                p0 = expf(s0 - m_new);
-                p1 = expf(s1 - m_new);
+                corr = exp2f(m_old - m_new);
+                p0 = exp2f(s0 - m_new);
+                p1 = exp2f(s1 - m_new);
             }
             // the sum runs over the probabilities as the product will see them (rounded to bfloat16)
             const __nv_bfloat16 h0_ = __float2bfloat16_rn(p0), h1_ = __float2bfloat16_rn(p1);
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         }
     }
     if (n_splits > 1 && tid < g_count)
-        part_ml[((size_t)t * H + h0 + tid) * n_splits + split] = make_float2(m_s[tid], l_s[tid]);
+        part_ml[((size_t)t * H + h0 + tid) * n_splits + split] = make_float2(m_s[tid] * 0.6931471805599453f, l_s[tid]);   // the maximum back in natural units
 }
 
 // Merge the splits of one (token, head) in split order.

@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(
     const int pos_first = positions[row0], pos_last = pos_first + n_tok - 1;
     const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     const int pg_lo = lo_first / PAGE, pg_hi = pos_last / PAGE;
+    const float scale_log2 = scale * 1.4426950408889634f;
 
     // ---- this warp's queries as A fragments -----------------------------------------------------
     const int r_in = lane >> 2, c_in = (lane & 3) * 2;
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int rr = i >> 1;
-                    float s = sacc[nt][i] * scale;
+                    float s = sacc[nt][i] * scale_log2;   // base-2 domain: exp(x) = exp2(x log2 e)
                     if (edge) {
                         const int kpos = key0 + nt * 8 + c_in + (i & 1);
                         if (kpos > qpos[rr] || (window > 0 && kpos < qpos[rr] - window + 1)) s = -INFINITY;
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(
                 mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
                 mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
                 const float m_new = fmaxf(m_run[rr], mx[rr]);
-                corr[rr] = (m_new == -INFINITY) ? 1.f : expf(m_run[rr] - m_new);
+                corr[rr] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[rr] - m_new);
                 m_run[rr] = m_new;
                 l_run[rr] *= corr[rr];
             }
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int rr = i >> 1;
-                    p[i] = (m_run[rr] == -INFINITY) ? 0.f : expf(sacc[nt][i] - m_run[rr]);
+                    p[i] = (m_run[rr] == -INFINITY) ? 0.f : exp2f(sacc[nt][i] - m_run[rr]);
                     l_run[rr] += p[i];
                 }
                 // the C layout of S is the A layout of P: two n tiles of 8 keys make one k step of 16

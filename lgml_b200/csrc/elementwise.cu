@@ -56,19 +56,26 @@ LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids,
 template <typename TD, typename TO>
 __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta, int n_parts, long long part_stride,
                                const float *__restrict__ delta_bias, const float *__restrict__ weight,
-                               const int *__restrict__ rows, TO *__restrict__ out, int width, float eps, int cs) {
+                               const int *__restrict__ rows, TO *__restrict__ out, int width, float eps, int cs,
+                               int clustered) {
     pdl_trigger();
     pdl_wait();
     namespace cg = cooperative_groups;
     __shared__ float red[32];
     __shared__ float slice_ss;
     constexpr int PER = 4;            // elements a thread keeps in registers per round
-    const int r = blockIdx.x / cs, rank = blockIdx.x - r * cs;
+    // A row is cut into cs slices whose sums of squares are added in slice order.  With few rows
+    // the slices run on the CTAs of a cluster; with many rows one CTA walks the slices itself.
+    // The arithmetic, and so the result, is the same either way.
+    const int r = clustered ? blockIdx.x / cs : blockIdx.x;
+    const int rank0 = clustered ? blockIdx.x - r * cs : 0, rank1 = clustered ? rank0 + 1 : cs;
     const int per_cta = ((width + cs - 1) / cs + 3) & ~3;
-    const int c0 = rank * per_cta, c1 = min(width, c0 + per_cta);
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float *xr = x + src * width;
     const TD *dr = delta ? delta + src * width : nullptr;
+    float total = 0.f;
+    for (int rank = rank0; rank < rank1; ++rank) {
+    const int c0 = rank * per_cta, c1 = min(width, c0 + per_cta);
     float ss = 0.f;
     for (int base = c0; base < c1; base += PER * blockDim.x) {
         // all loads of this round first, so that they are in flight together
@@ -120,8 +127,9 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
         for (int j = 0; j < PER; ++j) ss = fmaf(v[j], v[j], ss);
     }
-    float total = block_sum(ss, red);
-    if (cs > 1) {
+    total += block_sum(ss, red);
+    }
+    if (clustered && cs > 1) {
         cg::cluster_group cluster = cg::this_cluster();
         if (threadIdx.x == 0) slice_ss = total;
         cluster.sync();
@@ -131,6 +139,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
     }
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
     // second pass: with a delta the row was just written (or, with a row list, is summed again the same way)
+    const int c0 = rank0 * per_cta, c1 = min(width, rank1 * per_cta);
     for (int base = c0; base < c1; base += PER * blockDim.x) {
         float v[PER], w[PER];
 #pragma unroll
@@ -166,12 +175,14 @@ static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long pa
     // The cluster and block sizes depend on the width only, so a row's sum is formed in the
     // same order whatever else is in the batch.
     const int cs = width >= 2048 ? 8 : (width >= 1024 ? 4 : 1);
+    const int clustered = (cs > 1 && n_rows <= 64) ? 1 : 0;     // many rows fill the GPU without clusters
+    const int blocks = clustered ? n_rows * cs : n_rows;
     const int threads = 128;
     cudaError_t e;
     if (out_dtype == LGML_F32)
-        e = lgml_launch_cluster(rmsnorm_kernel<TD, float>, n_rows * cs, threads, 0, stream, cs, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps, cs);
+        e = lgml_launch_cluster(rmsnorm_kernel<TD, float>, blocks, threads, 0, stream, clustered ? cs : 1, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps, cs, clustered);
     else
-        e = lgml_launch_cluster(rmsnorm_kernel<TD, __nv_bfloat16>, n_rows * cs, threads, 0, stream, cs, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps, cs);
+        e = lgml_launch_cluster(rmsnorm_kernel<TD, __nv_bfloat16>, blocks, threads, 0, stream, clustered ? cs : 1, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps, cs, clustered);
     (void)e;
     return lgml_launch_status("rmsnorm");
 }

@@ -126,6 +126,7 @@ struct Params {
     int rows_a;       // valid rows of A (tokens, or features when swapped)
     int rows_b;       // valid rows of B
     int k_blocks;     // ceil(K / 64)
+    int tiles_a, tiles_b;   // tiles along the rows of A and of B; tile index = tile_b * tiles_a + tile_a
     int kb_per_split; // k blocks per grid.z slice
     int transposed;   // 1: the tile is y^T (A = weights, B = tokens)
     int swiglu;       // 1: feature rows come in (gate, up) pairs; the output is silu(gate) * up, half as wide
@@ -144,31 +145,39 @@ struct Smem {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 };
 
-template <int BN, int STAGES>
+// NACC accumulators in TMEM: 1 when a CTA owns one tile, 2 when it walks several tiles (then
+// the epilogue of one tile runs while the products of the next fill the other accumulator).
+template <int BN, int STAGES, int NACC>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b, const Params p) {
     pdl_trigger();   // the next kernel may start its own set-up and weight fetch
     extern __shared__ uint8_t smem_raw[];
     // tiles want 1024-byte alignment for the 128-byte swizzle
     uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[NACC], acc_empty[NACC];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     volatile int *abort_flag = &abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int split = blockIdx.z;
     const int kb0 = split * p.kb_per_split;
     const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
     const int n_kb = max(kb1 - kb0, 0);
-    constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+    const int n_tiles = p.tiles_a * p.tiles_b;
+    constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+    constexpr uint32_t TMEM_COLS = ACC_COLS * NACC;
+    static_assert(TMEM_COLS <= 512, "the accumulators do not fit tensor memory");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&acc_bar, 1);
+        for (int a = 0; a < NACC; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 128);      // every epilogue thread arrives
+        }
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -185,30 +194,40 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         if (lane == 0) {
             // Weights do not depend on the kernels before this one: fetch them for the first
             // stages at once, then wait for the earlier kernels, then fetch the activations.
-            const int pre = min(n_kb, STAGES);
-            for (int i = 0; i < pre; ++i) {
-                uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[i], Smem<BN>::STAGE_BYTES);
-                if (p.transposed) tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
-                else tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
+            const int first = blockIdx.x;
+            const int pre = first < n_tiles ? min(n_kb, STAGES) : 0;
+            {
+                const int tile_a = first % p.tiles_a, tile_b = first / p.tiles_a;
+                for (int i = 0; i < pre; ++i) {
+                    uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
+                    mbar_expect_tx(&full_bar[i], Smem<BN>::STAGE_BYTES);
+                    if (p.transposed) tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
+                    else tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
+                }
+                pdl_wait();
+                for (int i = 0; i < pre; ++i) {
+                    uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
+                    if (p.transposed) tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
+                    else tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
+                }
             }
-            pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
-                if (p.transposed) tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
-                else tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
-            }
-            int issued = pre;
-            for (int i = pre; i < n_kb; ++i) {
-                const int s = i % STAGES;
-                if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag, p.status)) break;
-                if (*abort_flag) break;
-                uint8_t *a_dst = tiles + (size_t)s * Smem<BN>::STAGE_BYTES;
-                uint8_t *b_dst = a_dst + Smem<BN>::A_BYTES;
-                mbar_expect_tx(&full_bar[s], Smem<BN>::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[s]);
-                tma_load_2d(b_dst, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[s]);
-                issued = i + 1;
+            int it = pre, issued = pre;       // k blocks issued so far, over all tiles of this CTA
+            bool ok = true;
+            for (int tile = first; tile < n_tiles && ok; tile += gridDim.x) {
+                const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+                for (int i = (tile == first ? pre : 0); i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, abort_flag, p.status) || *abort_flag) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *a_dst = tiles + (size_t)s * Smem<BN>::STAGE_BYTES;
+                    uint8_t *b_dst = a_dst + Smem<BN>::A_BYTES;
+                    mbar_expect_tx(&full_bar[s], Smem<BN>::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[s]);
+                    tma_load_2d(b_dst, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[s]);
+                    issued = it + 1;
+                }
             }
             // On an abort the consumer may never look at the last stages: let their copies land
             // before this CTA's shared memory can be given to another.
@@ -226,40 +245,53 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BM, BN);
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
-                ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abort_flag, p.status);
-                if (!ok) break;
+            int it = 0, j = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+                const int acc = j % NACC;
+                // the epilogue must have drained this accumulator (its use NACC tiles ago)
+                if (j >= NACC && !mbar_wait(&acc_empty[acc], ((j / NACC) - 1) & 1, abort_flag, p.status)) break;
                 tcgen05_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * Smem<BN>::STAGE_BYTES);
-                const uint32_t b_addr = a_addr + Smem<BN>::A_BYTES;
-                const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
+                const uint32_t tmem_acc = tmem_base + (uint32_t)acc * ACC_COLS;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag, p.status);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * Smem<BN>::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + Smem<BN>::A_BYTES;
+                    const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 elements = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+                        tcgen05_mma_bf16(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
                 }
-                tcgen05_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
+                tcgen05_commit(&acc_full[acc]);         // the accumulator is complete once all MMAs are done
             }
-            tcgen05_commit(&acc_bar);               // the accumulator is complete once all MMAs are done
         }
     } else {
         // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32 * (w % 4) .. + 31 ----------------
         pdl_wait();   // nothing is written before the earlier kernels are done (an empty K range gets here at once)
-        const bool ok = mbar_wait(&acc_bar, 0, abort_flag, p.status);
-        tcgen05_fence_after();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                   // row of the tile = TMEM lane
-        const int a_row = tile_a * BM + row;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         float *out_f = (float *)p.out + (size_t)split * p.split_stride;
         __nv_bfloat16 *out_h = (__nv_bfloat16 *)p.out;
         const bool f32 = p.out_f32 || p.split_stride != 0;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+        const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+        const int acc = j % NACC;
+        const uint32_t acc_col = (uint32_t)acc * ACC_COLS;
+        const int a_row = tile_a * BM + row;
+        const bool ok = mbar_wait(&acc_full[acc], (j / NACC) & 1, abort_flag, p.status);
+        tcgen05_fence_after();
         if (ok && n_kb > 0) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
-                tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                tcgen05_ld_16(lane_addr + acc_col + (uint32_t)c0, r);
                 tcgen05_wait_ld();
                 if (p.transposed) {
                     // tile row = feature (a_row), tile column = token: y[token][feature]
@@ -360,6 +392,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                 if (t < rows_t && f < rows_f) out_f[(size_t)t * p.ldo + f] = 0.f;
             }
         }
+        // this thread has read its part of the accumulator: hand it back to the MMA warp
+        tcgen05_fence_before();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -417,16 +453,16 @@ int make_map(CUtensorMap *map, const void *base, long long rows, long long K, lo
     return 0;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int NACC>
 int launch(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, dim3 grid, cudaStream_t stream) {
     const size_t smem = (size_t)STAGES * Smem<BN>::STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    lgml_launch(gemm_tcgen05_kernel<BN, STAGES>, grid, THREADS, smem, stream, ma, mb, p);
+    lgml_launch(gemm_tcgen05_kernel<BN, STAGES, NACC>, grid, THREADS, smem, stream, ma, mb, p);
     return lgml_launch_status("gemm_tcgen05");
 }
 
@@ -477,7 +513,9 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         p.rows_b = M;
         if ((rc = make_map(&ma, w, N, K, ldw, BM))) return rc;
         if ((rc = make_map(&mb, x, M, K, ldx, bn))) return rc;
-        grid = dim3((N + BM - 1) / BM, 1, n_splits);
+        p.tiles_a = (N + BM - 1) / BM;
+        p.tiles_b = 1;
+        grid = dim3(p.tiles_a, 1, n_splits);
     } else {
         bn = 256;
         p.transposed = 0;
@@ -485,15 +523,23 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         p.rows_b = N;
         if ((rc = make_map(&ma, x, M, K, ldx, BM))) return rc;
         if ((rc = make_map(&mb, w, N, K, ldw, bn))) return rc;
-        grid = dim3((M + BM - 1) / BM, (N + bn - 1) / bn, n_splits);
+        // a persistent grid: one CTA per SM walks the tiles, tile_a fastest, so that the CTAs
+        // running at one time share a few column blocks of the weights and all of the activations
+        p.tiles_a = (M + BM - 1) / BM;
+        p.tiles_b = (N + bn - 1) / bn;
+        const int n_tiles = p.tiles_a * p.tiles_b;
+        grid = dim3(n_tiles < 148 ? n_tiles : 148, 1, n_splits);
     }
-    LGML_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tcgen05: grid too large");
+    LGML_REQUIRE(grid.z <= 65535, "gemm_tcgen05: grid too large");
     switch (bn) {
-        case 16: rc = launch<16, 6>(ma, mb, p, grid, stream); break;
-        case 32: rc = launch<32, 5>(ma, mb, p, grid, stream); break;
-        case 64: rc = launch<64, 4>(ma, mb, p, grid, stream); break;
-        case 128: rc = launch<128, 6>(ma, mb, p, grid, stream); break;
-        default: rc = launch<256, 4>(ma, mb, p, grid, stream); break;
+        case 16: rc = launch<16, 6, 1>(ma, mb, p, grid, stream); break;
+        case 32: rc = launch<32, 5, 1>(ma, mb, p, grid, stream); break;
+        case 64: rc = launch<64, 4, 1>(ma, mb, p, grid, stream); break;
+        case 128: rc = launch<128, 6, 1>(ma, mb, p, grid, stream); break;
+        default:
+            if (swap) rc = launch<256, 4, 1>(ma, mb, p, grid, stream);
+            else rc = launch<256, 4, 2>(ma, mb, p, grid, stream);
+            break;
     }
     if (rc) return rc;
     if (n_splits > 1 && reduce) {
