@@ -65,6 +65,12 @@ class Engine:
         self.scheduler = Scheduler(self.runner.cache, max_position=min(max_pos, n_ctx), ubatch=ubatch,
                                    max_batch_tokens=max_batch_tokens, repeat_stop_tokens=repeat_stop_tokens)
         self.eos_ids = list(getattr(cfg, "eos_token_ids", []) or [])
+        # What exists now (modules, the model's objects) lives as long as the engine: keep the
+        # collector from walking it again and again.  A full collection over it takes tens of
+        # milliseconds, several decode steps, whenever it happens to trigger.
+        import gc
+        gc.collect()
+        gc.freeze()
         self._next_id = 0
         self.timings: Dict[str, float] = {}
         # one record per scheduler turn: wall seconds, prompt tokens, decoded tokens, bytes copied each way
