@@ -244,9 +244,9 @@ def main() -> int:
                            max_batch_tokens=2048)
     g = torch.Generator().manual_seed(2)
     prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(BATCH)]
-    e2e_steps = min(args.steps, 64) + warmup
-    eng.generate(prompts, max_tokens=e2e_steps, temperature=0.0, stop=[])
-    e2e = eng.decode_rate(skip=warmup)
+    eng.generate(prompts, max_tokens=warmup + 2, temperature=0.0, stop=[])      # warm-up: kernels loaded, graph captured
+    eng.generate(prompts, max_tokens=min(args.steps, 64) + 1, temperature=0.0, stop=[])
+    e2e = eng.decode_rate(skip=1)
 
     rec = {
         "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts, context 4,096)",
