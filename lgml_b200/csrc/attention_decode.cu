@@ -32,7 +32,6 @@ constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
 constexpr int MAX_D = 256;
 constexpr int NH = 8;                  // heads per CTA = the N of the tensor-core tile
-constexpr int PLD = PAGE + 8;          // padded row of P^T (bfloat16)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async_16(void *dst, const void *src, bool valid) {
@@ -55,25 +54,29 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// KS = D / 16.  G here is only the count of heads this CTA really has (<= 8).
+// KS = D / 16.  Each of the four warps is a pipeline of its own: of every page it copies,
+// scores and weighs only its quarter of the keys (16), keeping a running maximum, sum and
+// output of its own, so the loop over pages needs no barrier between warps; the four partial
+// results are merged once at the end.
 template <int KS, int STAGES>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo,
     float *__restrict__ part_o, float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks,
-    float scale, int window, int *__restrict__ status) {
+    float scale, int window, int newest, int *__restrict__ status) {
     pdl_trigger();
-    pdl_wait();
     constexpr int D = KS * 16;
     constexpr int LD = D + 8;                       // padded row of the K and V stages (elements)
-    constexpr int MT = (KS + WARPS - 1) / WARPS;    // output m tiles (16 dims) per warp
+    constexpr int WK = PAGE / WARPS;                // keys of a page per warp: 16
+    constexpr int PW = WK + 8;                      // padded row of a warp's P^T (bfloat16)
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16 *kv_s = reinterpret_cast<__nv_bfloat16 *>(smem_raw);       // [STAGES][K | V][PAGE][LD]
-    float *S = reinterpret_cast<float *>(kv_s + (size_t)STAGES * 2 * PAGE * LD);   // [PAGE][NH] scores
-    __nv_bfloat16 *Pt = reinterpret_cast<__nv_bfloat16 *>(S + PAGE * NH);    // [NH][PLD] probabilities, transposed
-    __shared__ float m_s[NH], l_s[NH], corr_s[NH];
-    __shared__ int stage_ok[STAGES];
+    // per warp: [STAGES][K | V][WK][LD] bfloat16, then P^T [NH][PW] bfloat16
+    constexpr size_t WARP_STAGE = (size_t)2 * WK * LD;                  // elements of one stage of one warp
+    constexpr size_t WARP_BYTES = (STAGES * WARP_STAGE + NH * PW) * 2;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __nv_bfloat16 *kv_w = reinterpret_cast<__nv_bfloat16 *>(smem_raw + (size_t)warp * WARP_BYTES);
+    __nv_bfloat16 *Pw = kv_w + STAGES * WARP_STAGE;
 
     const int t = blockIdx.x;
     const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
@@ -81,7 +84,6 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const int group = H / Hkv;
     const int h0 = kvh * group + chunk * heads_per_cta;                 // first query head of this CTA
     const int g_count = min(heads_per_cta, group - chunk * heads_per_cta);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int mat = lane >> 3, mrow = lane & 7;
 
     const int pos = positions[t];
@@ -95,7 +97,44 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     const int pb = first_page + split * pps;
     const int pe = min(pb + pps, n_pages_seq);
     const int n_iter = max(pe - pb, 0);
-    const float scale_log2 = scale * 1.4426950408889634f;
+    const float scale_log2 = scale * 1.4426950408889634f;   // scores in the base-2 domain: exp(x) = exp2(x log2 e)
+
+    // Copy this warp's 16 rows of the page of iteration `it` into its stage it % STAGES; rows past
+    // the last visible key, and a page the table does not hold, become zeros.
+    auto load_rows = [&](int it) {
+        const int pg = pb + it;
+        const int page = table[pg];
+        const bool have = page >= 0 && page < n_pages;
+        if (!have && lane == 0) atomicExch(status, 3);
+        const int valid_rows = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
+        const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D + (size_t)warp * WK * D;
+        __nv_bfloat16 *ks_ = kv_w + (size_t)(it % STAGES) * WARP_STAGE, *vs_ = ks_ + WK * LD;
+#pragma unroll
+        for (int c = lane; c < WK * (D / 8); c += 32) {
+            const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+            const bool ok = warp * WK + row < valid_rows;
+            cp_async_16(ks_ + row * LD + col, k_pages + off + (size_t)row * D + col, ok);
+            cp_async_16(vs_ + row * LD + col, v_pages + off + (size_t)row * D + col, ok);
+        }
+    };
+    // The positions and block tables come from the host, and pages that lie wholly before this
+    // step's new tokens were written by earlier steps: their copies can start before the
+    // kernels ahead of this one in the stream (which write this step's keys and the queries)
+    // have finished.  `newest` is the most tokens any request brings in this step.
+    const int old_pages = max(pos - newest + 1, 0) / PAGE;       // pages below this index hold old tokens only
+    bool waited = false;
+#pragma unroll
+    for (int it = 0; it < STAGES - 1; ++it) {
+        if (it < n_iter) {
+            if (!waited && pb + it >= old_pages) {
+                pdl_wait();
+                waited = true;
+            }
+            load_rows(it);
+        }
+        cp_async_commit();
+    }
+    if (!waited) pdl_wait();
 
     // Q^T as B fragments: b0 holds (d = 16 ks + 2 (lane % 4) + {0, 1}, head = lane / 4), b1 the same 8 dims on
     uint32_t qb[KS][2];
@@ -104,153 +143,128 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
         const __nv_bfloat16 *qrow = q + (size_t)t * ldq + (size_t)(h0 + head) * D + (lane & 3) * 2;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            qb[ks][0] = head < g_count ? *reinterpret_cast<const uint32_t *>(qrow + ks * 16) : 0u;
-            qb[ks][1] = head < g_count ? *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8) : 0u;
+            // the queries were written by the kernel just ahead, while this one may already have been
+            // running: read them through L2 (ld.global.cg), not through a cache that is only
+            // coherent at kernel boundaries
+            qb[ks][0] = head < g_count ? act_load(reinterpret_cast<const unsigned int *>(qrow + ks * 16)) : 0u;
+            qb[ks][1] = head < g_count ? act_load(reinterpret_cast<const unsigned int *>(qrow + ks * 16 + 8)) : 0u;
         }
-    }
-    for (int i = tid; i < NH * PLD; i += THREADS) Pt[i] = __float2bfloat16_rn(0.f);   // heads this CTA does not have stay zero
-    if (tid < NH) {
-        m_s[tid] = -INFINITY;
-        l_s[tid] = 0.f;
-        corr_s[tid] = 1.f;
     }
 
-    // Copy the page of iteration `it` into stage it % STAGES; rows past the last visible key are zero.
-    auto load_page = [&](int it) {
-        const int pg = pb + it;
-        const int stage = it % STAGES;
-        const int page = table[pg];
-        const bool have = page >= 0 && page < n_pages;
-        if (tid == 0) {
-            stage_ok[stage] = have ? 1 : 0;
-            if (!have) atomicExch(status, 3);
-        }
-        const int valid_rows = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
-        const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
-        __nv_bfloat16 *ks_ = kv_s + (size_t)stage * 2 * PAGE * LD, *vs_ = ks_ + PAGE * LD;
-        for (int c = tid; c < PAGE * (D / 8); c += THREADS) {
-            const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
-            const bool ok = row < valid_rows;
-            cp_async_16(ks_ + row * LD + col, k_pages + off + (size_t)row * D + col, ok);
-            cp_async_16(vs_ + row * LD + col, v_pages + off + (size_t)row * D + col, ok);
-        }
-    };
+    // this thread's two heads: columns (lane % 4) * 2 and + 1 of the S^T and O^T fragments
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[KS][4];
 #pragma unroll
-    for (int it = 0; it < STAGES - 1; ++it) {
-        if (it < n_iter) load_page(it);
-        cp_async_commit();
-    }
-
-    float oacc[MT][4];
-#pragma unroll
-    for (int i = 0; i < MT; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+    for (int i = 0; i < KS; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
     for (int it = 0; it < n_iter; ++it) {
-        if (it + STAGES - 1 < n_iter) load_page(it + STAGES - 1);
+        if (it + STAGES - 1 < n_iter) load_rows(it + STAGES - 1);
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
-        __syncthreads();
-        const int stage = it % STAGES;
+        __syncwarp();
         const int pg = pb + it;
-        const bool have = stage_ok[stage] != 0;
-        const int k_begin = max(lo - pg * PAGE, 0), k_end = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
-        const __nv_bfloat16 *ks_ = kv_s + (size_t)stage * 2 * PAGE * LD, *vs_ = ks_ + PAGE * LD;
+        const __nv_bfloat16 *ks_ = kv_w + (size_t)(it % STAGES) * WARP_STAGE, *vs_ = ks_ + WK * LD;
+        const int key_base = pg * PAGE + warp * WK;               // position of this warp's first key
 
-        // ---- (1) S^T = K Q^T: warp w takes keys 16w .. 16w + 15 ----------------------------------
-        {
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+        // ---- S^T = K Q^T for the warp's 16 keys ---------------------------------------------------
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                uint32_t a[4];
-                ldmatrix_x4(a, ks_ + (size_t)(warp * 16 + (mat & 1) * 8 + mrow) * LD + ks * 16 + (mat >> 1) * 8);
-                mma_bf16(c, a, qb[ks][0], qb[ks][1]);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int key = warp * 16 + (lane >> 2) + (i >> 1) * 8, head = (lane & 3) * 2 + (i & 1);
-                // scores in the base-2 domain: exp(x) = exp2(x log2 e), and exp2 is one instruction
-                S[key * NH + head] = (key >= k_begin && key < k_end) ? c[i] * scale_log2 : -INFINITY;
-            }
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(a, ks_ + (size_t)((mat & 1) * 8 + mrow) * LD + ks * 16 + (mat >> 1) * 8);
+            mma_bf16(c, a, qb[ks][0], qb[ks][1]);
         }
-        __syncthreads();
-
-        // ---- (2) online softmax, one warp per head -----------------------------------------------
-        for (int g = warp; g < g_count; g += WARPS) {
-            const float s0 = S[lane * NH + g], s1 = S[(lane + 32) * NH + g];
-            const float mx = warp_max(fmaxf(s0, s1));
-            const float m_old = m_s[g];
-            const float m_new = fmaxf(m_old, mx);
-            float p0 = 0.f, p1 = 0.f, corr = 1.f;
-            if (m_new != -INFINITY) {
-                corr = exp2f(m_old - m_new);
-                p0 = exp2f(s0 - m_new);
-                p1 = exp2f(s1 - m_new);
-            }
+        // rows of the fragment are keys (lane / 4, + 8), columns heads ((lane % 4) * 2, + 1)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int kpos = key_base + (lane >> 2) + (i >> 1) * 8;
+            c[i] = (kpos >= lo && kpos <= pos) ? c[i] * scale_log2 : -INFINITY;
+            mx[i & 1] = fmaxf(mx[i & 1], c[i]);
+        }
+        float corr[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 4));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 8));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 16));
+            const float m_new = fmaxf(m_run[hh], mx[hh]);
+            corr[hh] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[hh] - m_new);
+            m_run[hh] = m_new;
+        }
+        // P^T through the warp's own shared memory: written as (head, key), read as B fragments
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int hh = i & 1;
+            const float pf = (m_run[hh] == -INFINITY) ? 0.f : exp2f(c[i] - m_run[hh]);
+            const __nv_bfloat16 ph = __float2bfloat16_rn(pf);
             // the sum runs over the probabilities as the product will see them (rounded to bfloat16)
-            const __nv_bfloat16 h0_ = __float2bfloat16_rn(p0), h1_ = __float2bfloat16_rn(p1);
-            const float ls = warp_sum(__bfloat162float(h0_) + __bfloat162float(h1_));
-            Pt[g * PLD + lane] = h0_;
-            Pt[g * PLD + lane + 32] = h1_;
-            if (lane == 0) {
-                m_s[g] = m_new;
-                l_s[g] = l_s[g] * corr + ls;
-                corr_s[g] = corr;
-            }
+            l_run[hh] = (i < 2 ? l_run[hh] * corr[hh] : l_run[hh]) + __bfloat162float(ph);
+            Pw[((lane & 3) * 2 + hh) * PW + (lane >> 2) + (i >> 1) * 8] = ph;
         }
-        __syncthreads();
+        __syncwarp();
+        const uint32_t pb0 = *reinterpret_cast<const uint32_t *>(Pw + (lane >> 2) * PW + (lane & 3) * 2);
+        const uint32_t pb1 = *reinterpret_cast<const uint32_t *>(Pw + (lane >> 2) * PW + (lane & 3) * 2 + 8);
 
-        // ---- (3) O^T += V^T P^T: warp w takes the 16-dim tiles w, w + 4, ... -----------------------
-        {
-            const float ca = corr_s[(lane & 3) * 2], cb = corr_s[(lane & 3) * 2 + 1];
-            uint32_t pb_[4][2];
+        // ---- O^T += V^T P^T over the warp's 16 keys: one k step per 16-dim tile ---------------------
 #pragma unroll
-            for (int k2 = 0; k2 < 4; ++k2) {
-                const __nv_bfloat16 *pr = Pt + (lane >> 2) * PLD + k2 * 16 + (lane & 3) * 2;
-                pb_[k2][0] = *reinterpret_cast<const uint32_t *>(pr);
-                pb_[k2][1] = *reinterpret_cast<const uint32_t *>(pr + 8);
-            }
-#pragma unroll
-            for (int mi = 0; mi < MT; ++mi) {
-                const int mt = warp + mi * WARPS;
-                if (mt < KS) {
-                    oacc[mi][0] *= ca;
-                    oacc[mi][1] *= cb;
-                    oacc[mi][2] *= ca;
-                    oacc[mi][3] *= cb;
-#pragma unroll
-                    for (int k2 = 0; k2 < 4; ++k2) {
-                        uint32_t a[4];
-                        ldmatrix_x4_trans(a, vs_ + (size_t)(k2 * 16 + (mat >> 1) * 8 + mrow) * LD + mt * 16 + (mat & 1) * 8);
-                        mma_bf16(oacc[mi], a, pb_[k2][0], pb_[k2][1]);
-                    }
-                }
-            }
+        for (int mt = 0; mt < KS; ++mt) {
+            oacc[mt][0] *= corr[0];
+            oacc[mt][1] *= corr[1];
+            oacc[mt][2] *= corr[0];
+            oacc[mt][3] *= corr[1];
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, vs_ + (size_t)((mat >> 1) * 8 + mrow) * LD + mt * 16 + (mat & 1) * 8);
+            mma_bf16(oacc[mt], a, pb0, pb1);
         }
-        __syncthreads();   // S, P^T and the stage are free for the next iterations
     }
     cp_async_wait<0>();
 
-    // ---- write: O^T fragment rows are dims, columns heads ---------------------------------------------
+    // ---- merge the four warps -----------------------------------------------------------------------
+    // the sums: over the 8 lanes that share this thread's two heads
 #pragma unroll
-    for (int mi = 0; mi < MT; ++mi) {
-        const int mt = warp + mi * WARPS;
-        if (mt >= KS) continue;
+    for (int hh = 0; hh < 2; ++hh) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+    }
+    __syncthreads();                                             // every warp is done with its stages
+    float *mo = reinterpret_cast<float *>(smem_raw);             // [WARPS][D][NH] outputs, then [WARPS][NH] m and l
+    float *mm = mo + (size_t)WARPS * D * NH, *ml = mm + WARPS * NH;
+#pragma unroll
+    for (int mt = 0; mt < KS; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int d = mt * 16 + (lane >> 2) + (i >> 1) * 8, head = (lane & 3) * 2 + (i & 1);
-            if (head >= g_count) continue;
-            const int h = h0 + head;
-            const float o = oacc[mi][i];
-            if (n_splits == 1) {
-                const float l = l_s[head];
-                out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
-            } else {
-                part_o[(((size_t)t * H + h) * n_splits + split) * D + d] = o;
-            }
+            mo[((size_t)warp * D + d) * NH + head] = oacc[mt][i];
+        }
+    if (lane < 4) {
+        mm[warp * NH + lane * 2] = m_run[0];
+        mm[warp * NH + lane * 2 + 1] = m_run[1];
+        ml[warp * NH + lane * 2] = l_run[0];
+        ml[warp * NH + lane * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    for (int i = tid; i < D * NH; i += THREADS) {
+        const int d = i / NH, head = i - d * NH;
+        if (head >= g_count) continue;
+        float m = -INFINITY;
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, mm[w * NH + head]);
+        float o = 0.f, l = 0.f;
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = (mm[w * NH + head] == -INFINITY) ? 0.f : exp2f(mm[w * NH + head] - m);
+            o += mo[((size_t)w * D + d) * NH + head] * f;
+            l += ml[w * NH + head] * f;
+        }
+        const int h = h0 + head;
+        if (n_splits == 1) {
+            out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else {
+            part_o[(((size_t)t * H + h) * n_splits + split) * D + d] = o;
+            if (d == 0) part_ml[((size_t)t * H + h) * n_splits + split] = make_float2(m * 0.6931471805599453f, l);   // the maximum back in natural units
         }
     }
-    if (n_splits > 1 && tid < g_count)
-        part_ml[((size_t)t * H + h0 + tid) * n_splits + split] = make_float2(m_s[tid] * 0.6931471805599453f, l_s[tid]);   // the maximum back in natural units
 }
 
 // Merge the splits of one (token, head) in split order.
@@ -261,14 +275,19 @@ __global__ void decode_combine_kernel(const float *__restrict__ part_o, const fl
     const int t = blockIdx.x, h = blockIdx.y;
     const float2 *ml = part_ml + ((size_t)t * H + h) * n_splits;
     float mm = -INFINITY;
-    for (int i = 0; i < n_splits; ++i) mm = fmaxf(mm, ml[i].x);
+    for (int i = 0; i < n_splits; ++i) mm = fmaxf(mm, act_load(ml + i).x);
     float l = 0.f;
-    for (int i = 0; i < n_splits; ++i) l += ml[i].x == -INFINITY ? 0.f : ml[i].y * expf(ml[i].x - mm);
+    for (int i = 0; i < n_splits; ++i) {
+        const float2 v = act_load(ml + i);
+        l += v.x == -INFINITY ? 0.f : v.y * expf(v.x - mm);
+    }
     const float *po = part_o + ((size_t)t * H + h) * n_splits * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.f;
-        for (int i = 0; i < n_splits; ++i)
-            if (ml[i].x != -INFINITY) o += po[(size_t)i * D + d] * expf(ml[i].x - mm);
+        for (int i = 0; i < n_splits; ++i) {
+            const float mi = act_load(ml + i).x;
+            if (mi != -INFINITY) o += act_load(po + (size_t)i * D + d) * expf(mi - mm);
+        }
         out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
 }
@@ -277,19 +296,25 @@ template <int KS, int STAGES>
 int launch_ks(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
               int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo,
               float *part_o, float2 *part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks, float scale, int window,
-              int *status, cudaStream_t stream) {
+              int newest, int *status, cudaStream_t stream) {
     constexpr int D = KS * 16;
-    const size_t smem = (size_t)STAGES * 2 * PAGE * (D + 8) * 2 + sizeof(float) * PAGE * NH + 2 * NH * PLD;
+    // per warp: its quarter of the K and V stages and its P^T; at the end the same memory holds the warps' partial results
+    const size_t stages = (size_t)WARPS * ((size_t)STAGES * 2 * (PAGE / WARPS) * (D + 8) + NH * (PAGE / WARPS + 8)) * 2;
+    const size_t merge = sizeof(float) * ((size_t)WARPS * D * NH + 2 * WARPS * NH);
+    const size_t smem = stages > merge ? stages : merge;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<KS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("decode_attention: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     lgml_launch(decode_attention_kernel<KS, STAGES>, grid, THREADS, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks,
-                k_pages, v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, heads_per_cta, n_chunks, scale, window, status);
+                k_pages, v_pages, n_pages, out, ldo, part_o, part_ml, n_splits, H, Hkv, heads_per_cta, n_chunks, scale, window, newest, status);
     return 0;
 }
 }  // namespace
 
+// max_new_tokens: the most tokens one request brings in this step (1 when decoding).  Pages that
+// lie wholly before a token's last max_new_tokens positions are fetched while earlier kernels
+// of the stream may still be writing this step's keys and values.
 // Scratch the caller provides when n_splits > 1:
 //   part_o  float32 [n_tokens, H, n_splits, D],  part_ml float32 [n_tokens, H, n_splits, 2]
 LGML_API long long lgml_decode_attention_scratch_floats(int n_tokens, int H, int D, int n_splits) {
@@ -300,13 +325,22 @@ LGML_API long long lgml_decode_attention_scratch_floats(int n_tokens, int H, int
 LGML_API int lgml_decode_attention(const void *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
                                    int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size, void *out,
                                    int ldo, float *scratch, int n_splits, int n_tokens, int H, int Hkv, int D, float scale,
-                                   int window, int *status, cudaStream_t stream) {
+                                   int window, int max_new_tokens, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && max_blocks > 0, "decode_attention: bad sizes");
     LGML_REQUIRE(page_size == PAGE, "decode_attention: pages of %d tokens, this kernel takes %d", page_size, PAGE);
     LGML_REQUIRE(H % Hkv == 0, "decode_attention: %d heads are no multiple of %d KV heads", H, Hkv);
     LGML_REQUIRE(D >= 16 && D <= MAX_D && D % 16 == 0, "decode_attention: head_dim %d must be a multiple of 16 up to %d", D, MAX_D);
     LGML_REQUIRE(n_splits >= 1 && n_splits <= 65535, "decode_attention: bad split count %d", n_splits);
     LGML_REQUIRE(n_splits == 1 || scratch != nullptr, "decode_attention: %d splits need scratch memory", n_splits);
+    LGML_REQUIRE(max_new_tokens >= 1, "decode_attention: max_new_tokens (the most tokens a request brings in this step) must be at least 1");
+    {
+        static int early = -1;
+        if (early < 0) {
+            const char *e = getenv("LGML_ATTN_EARLY");
+            early = (e != nullptr && e[0] == '0') ? 0 : 1;
+        }
+        if (!early) max_new_tokens = 1 << 28;     // no page counts as old: every copy waits for the kernels ahead
+    }
     LGML_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0, "decode_attention: the cache must be 16-byte aligned");
     if (n_tokens == 0) return 0;
     const int group = H / Hkv;
@@ -321,7 +355,7 @@ LGML_API int lgml_decode_attention(const void *q, int ldq, const int *positions,
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
     int lrc = 0;
 #define LGML_ARGS grid, qq, ldq, positions, seq_of_token, block_table, max_blocks, kk, vv, n_pages, oo, ldo, part_o, part_ml, n_splits, H, Hkv, \
-                  heads_per_cta, n_chunks, scale, window, status, stream
+                  heads_per_cta, n_chunks, scale, window, max_new_tokens, status, stream
 #define LGML_CASE3(KK) case KK: lrc = launch_ks<KK, 3>(LGML_ARGS); break;
 #define LGML_CASE2(KK) case KK: lrc = launch_ks<KK, 2>(LGML_ARGS); break;
     switch (D / 16) {

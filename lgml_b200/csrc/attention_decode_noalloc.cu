@@ -42,7 +42,8 @@ LGML_API const char *lgml_attention_decode_noalloc_last_error(void) { return lgm
 LGML_API int lgml_decode_attention_noalloc(const void *q, int ldq, const int *positions, const int *seq_of_token,
                                            const int *block_table, int max_blocks, const void *k_pages, const void *v_pages,
                                            int n_pages, int page_size, void *out, int ldo, int n_splits, int n_tokens, int H,
-                                           int Hkv, int D, float scale, int window, int *status, cudaStream_t stream) {
+                                           int Hkv, int D, float scale, int window, int max_new_tokens, int *status,
+                                           cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && D > 0 && n_splits >= 1, "decode_attention_noalloc: bad sizes");
     const long long need = lgml_decode_attention_scratch_floats(n_tokens, H, D, n_splits);
     LGML_REQUIRE(need <= (long long)LGML_NOALLOC_SCRATCH_FLOATS,
@@ -52,5 +53,5 @@ LGML_API int lgml_decode_attention_noalloc(const void *q, int ldq, const int *po
     float *scratch = noalloc_scratch();
     if (scratch == nullptr) return -1;
     return lgml_decode_attention(q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages, v_pages, n_pages, page_size, out,
-                                 ldo, scratch, n_splits, n_tokens, H, Hkv, D, scale, window, status, stream);
+                                 ldo, scratch, n_splits, n_tokens, H, Hkv, D, scale, window, max_new_tokens, status, stream);
 }

@@ -10,7 +10,8 @@
  * a fixed array in the library's device image.
  *
  * What the caller still passes: every input and the output, exactly as for
- * lgml_decode_attention, minus the scratch pointer.
+ * lgml_decode_attention, minus the scratch pointer (max_new_tokens is the most tokens one
+ * request brings in this step: 1 when decoding).
  *
  * Limits and rules:
  *  - The scratch array holds LGML_NOALLOC_SCRATCH_FLOATS floats (16 MiB).  Every GPU
@@ -40,7 +41,7 @@ extern "C" {
 int lgml_decode_attention_noalloc(const void *q, int ldq, const int *positions, const int *seq_of_token,
                                   const int *block_table, int max_blocks, const void *k_pages, const void *v_pages,
                                   int n_pages, int page_size, void *out, int ldo, int n_splits, int n_tokens, int H,
-                                  int Hkv, int D, float scale, int window, int *status, cudaStream_t stream);
+                                  int Hkv, int D, float scale, int window, int max_new_tokens, int *status, cudaStream_t stream);
 
 const char *lgml_attention_decode_noalloc_last_error(void);
 

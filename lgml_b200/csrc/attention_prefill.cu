@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(
         for (int i = 0; i < 4; ++i) {
             const int r = r_in + (i & 1) * 8, d = ks * 16 + c_in + (i >> 1) * 8;
             uint32_t v = 0;
-            if (r < rows_valid) v = *reinterpret_cast<const uint32_t *>(q + (size_t)(row0 + wrow0 + r) * ldq + (size_t)h * D + d);
+            if (r < rows_valid) v = act_load(reinterpret_cast<const unsigned int *>(q + (size_t)(row0 + wrow0 + r) * ldq + (size_t)h * D + d));
             qf[ks][i] = v;
         }
     }

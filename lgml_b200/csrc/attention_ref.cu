@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
     const int *table = block_table + (size_t)seq * max_blocks;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
 
-    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = to_f32(q[(size_t)t * ldq + (size_t)h * D + d]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = to_f32(act_load(q + (size_t)t * ldq + (size_t)h * D + d));
     __syncthreads();
 
     float m = -INFINITY, l = 0.f;
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
         }
         const size_t cell = (((size_t)page * Hkv + g) * page_size + (size_t)(j % page_size)) * D;
         float dot = 0.f;
-        for (int d = lane; d < D; d += 32) dot = fmaf(qs[d], to_f32(k_pages[cell + d]), dot);
+        for (int d = lane; d < D; d += 32) dot = fmaf(qs[d], to_f32(act_load(k_pages + cell + d)), dot);
         const float s = warp_sum(dot) * scale;
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
 #pragma unroll
         for (int i = 0; i < MAX_D / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) acc[i] = acc[i] * corr + p * to_f32(v_pages[cell + d]);
+            if (d < D) acc[i] = acc[i] * corr + p * to_f32(act_load(v_pages + cell + d));
         }
         m = m_new;
     }

@@ -48,6 +48,16 @@ static inline int lgml_launch_status(const char *what) {
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// A kernel launched this way may already be running while the kernel ahead of it is still
+// writing its results.  Its reads of those results therefore go through L2 (ld.global.cg): the
+// read-only cache path that the compiler picks for const __restrict__ pointers (ld.global.nc) is
+// coherent only at kernel boundaries, and was seen to return the previous layer's values.
+// Weights, block tables and other data the stream does not write may still be read any way.
+__device__ __forceinline__ float act_load(const float *p) { return __ldcg(p); }
+__device__ __forceinline__ __nv_bfloat16 act_load(const __nv_bfloat16 *p) { return __ldcg(p); }
+__device__ __forceinline__ unsigned int act_load(const unsigned int *p) { return __ldcg(p); }
+__device__ __forceinline__ float2 act_load(const float2 *p) { return __ldcg(p); }
+
 static inline bool lgml_pdl_enabled() {
     static int enabled = -1;
     if (enabled < 0) {

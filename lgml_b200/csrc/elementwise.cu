@@ -84,7 +84,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
         for (int j = 0; j < PER; ++j) {
             const int i = base + j * blockDim.x + threadIdx.x;
             v[j] = i < c1 ? xr[i] : 0.f;
-            d[j] = (dr && i < c1) ? to_f32(dr[i]) : 0.f;
+            d[j] = (dr && i < c1) ? to_f32(act_load(dr + i)) : 0.f;
         }
         if (dr) {
             // the parts are the partial sums of a matrix product cut along K: four are fetched
@@ -97,7 +97,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
                     for (int j = 0; j < PER; ++j) {
                         const int i = base + j * blockDim.x + threadIdx.x;
-                        e[q][j] = i < c1 ? to_f32(dr[(size_t)(p + q) * part_stride + i]) : 0.f;
+                        e[q][j] = i < c1 ? to_f32(act_load(dr + (size_t)(p + q) * part_stride + i)) : 0.f;
                     }
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -109,7 +109,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int i = base + j * blockDim.x + threadIdx.x;
-                    e[j] = i < c1 ? to_f32(dr[(size_t)p * part_stride + i]) : 0.f;
+                    e[j] = i < c1 ? to_f32(act_load(dr + (size_t)p * part_stride + i)) : 0.f;
                 }
 #pragma unroll
                 for (int j = 0; j < PER; ++j) d[j] += e[j];
@@ -153,8 +153,8 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ del
             for (int j = 0; j < PER; ++j) {
                 const int i = base + j * blockDim.x + threadIdx.x;
                 if (i < c1) {
-                    float d = to_f32(dr[i]);
-                    for (int p = 1; p < n_parts; ++p) d += to_f32(dr[(size_t)p * part_stride + i]);
+                    float d = to_f32(act_load(dr + i));
+                    for (int p = 1; p < n_parts; ++p) d += to_f32(act_load(dr + (size_t)p * part_stride + i));
                     if (delta_bias) d += delta_bias[i];
                     v[j] += d;
                 }
@@ -214,8 +214,8 @@ __global__ void silu_mul_kernel(const T *__restrict__ gu, T *__restrict__ act, i
     const size_t total = (size_t)n_tokens * width;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / width, f = i - t * width;
-        const float g = to_f32(gu[t * 2 * width + (paired ? 2 * f : f)]);
-        const float u = to_f32(gu[t * 2 * width + (paired ? 2 * f + 1 : width + f)]);
+        const float g = to_f32(act_load(gu + t * 2 * width + (paired ? 2 * f : f)));
+        const float u = to_f32(act_load(gu + t * 2 * width + (paired ? 2 * f + 1 : width + f)));
         const float s = g / (1.0f + expf(-g));
         act[i] = from_f32<T>(s * u);
     }
@@ -245,7 +245,7 @@ __global__ void residual_add_kernel(float *__restrict__ x, const TD *__restrict_
     pdl_trigger();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
-        x[i] += to_f32(delta[i]);
+        x[i] += to_f32(act_load(delta + i));
 }
 
 LGML_API int lgml_residual_add(float *x, const void *delta, int delta_dtype, long long total, cudaStream_t stream) {

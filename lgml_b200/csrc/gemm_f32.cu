@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float *__restrict__
         for (int j = 0; j < 4; ++j) {
             const int k = k0 + lk + j;
             const int am = m0 + lr, wn = n0 + lr;
-            As[lk + j][lr] = (am < M && k < K) ? A[(size_t)am * lda + k] : 0.f;
+            As[lk + j][lr] = (am < M && k < K) ? act_load(A + (size_t)am * lda + k) : 0.f;
             Ws[lk + j][lr] = (wn < N && k < K) ? W[(size_t)wn * ldw + k] : 0.f;
         }
         __syncthreads();

@@ -415,7 +415,7 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ part, long long s
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
         float v = 0.f;
-        for (int s = 0; s < n_splits; ++s) v += part[(size_t)s * split_stride + i];
+        for (int s = 0; s < n_splits; ++s) v += act_load(part + (size_t)s * split_stride + i);
         if (bias) v += bias[c];
         out[(size_t)r * ldo + c] = from_f32<TO>(v);
     }

@@ -51,10 +51,10 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
     }
     const size_t col = (size_t)head * D;
     const TS *row = src + (size_t)t * lds + col;
-    float a = to_f32(row[d0]), b = to_f32(row[d1]);
+    float a = to_f32(act_load(row + d0)), b = to_f32(act_load(row + d1));
     for (int p = 1; p < n_parts; ++p) {
-        a += to_f32(row[(size_t)p * part_stride + d0]);
-        b += to_f32(row[(size_t)p * part_stride + d1]);
+        a += to_f32(act_load(row + (size_t)p * part_stride + d0));
+        b += to_f32(act_load(row + (size_t)p * part_stride + d1));
     }
     if (bias) {
         a += bias[col + d0];

@@ -26,7 +26,7 @@ __device__ __forceinline__ Best better(Best a, Best b) {  // larger value, then 
 __device__ Best block_argmax(const float *row, int V, Best *smem) {
     Best best{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
+        const float v = act_load(row + i);
         if (v > best.v || (v == best.v && i < best.i)) best = Best{v, i};  // NaN never wins
     }
 #pragma unroll
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(THREADS) sample_rows_kernel(const float *__res
     const int chunk = (V + THREADS - 1) / THREADS;
     const int b = threadIdx.x * chunk, e = min(V, b + chunk);
     double s = 0.0;
-    for (int i = b; i < e; ++i) s += (double)expf(row[i] / T - m);
+    for (int i = b; i < e; ++i) s += (double)expf(act_load(row + i) / T - m);
     part[threadIdx.x] = s;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(THREADS) sample_rows_kernel(const float *__res
         int pick = cb, last = -1;
         bool found = false;
         for (int i = cb; i < ce; ++i) {
-            const float w = expf(row[i] / T - m);
+            const float w = expf(act_load(row + i) / T - m);
             if (w <= 0.f) continue;
             run += (double)w;
             last = i;
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_partial_kernel(const float 
     Best best{-INFINITY, 0x7fffffff};
 #pragma unroll 4
     for (int i = b + threadIdx.x; i < e; i += AM_THREADS) {
-        const float v = row[i];
+        const float v = act_load(row + i);
         if (v > best.v || (v == best.v && i < best.i)) best = Best{v, i};
     }
 #pragma unroll
@@ -142,7 +142,7 @@ __global__ void argmax_final_kernel(const float *__restrict__ part_v, const int 
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x, lane = threadIdx.x;
-    Best best{part_v[r * AM_CHUNKS + lane], part_i[r * AM_CHUNKS + lane]};
+    Best best{act_load(part_v + r * AM_CHUNKS + lane), (int)act_load(reinterpret_cast<const unsigned int *>(part_i) + r * AM_CHUNKS + lane)};
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         Best other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};

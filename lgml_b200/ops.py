@@ -473,9 +473,11 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, p
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                      k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
-                     status: torch.Tensor, n_splits: int, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     status: torch.Tensor, n_splits: int, scratch: Optional[torch.Tensor] = None, max_new_tokens: int = 16) -> torch.Tensor:
     """bfloat16 split-KV attention: each token over its request's cells.  Scratch (float32,
-    ``decode_attention_scratch_floats`` elements) is needed when n_splits > 1."""
+    ``decode_attention_scratch_floats`` elements) is needed when n_splits > 1.
+    ``max_new_tokens``: the most tokens one request brings in this step (the kernel starts
+    fetching older pages before the kernels ahead of it have finished)."""
     _need(q, "queries", torch.bfloat16, 2)
     _need(out, "attention output", torch.bfloat16, 2)
     ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
@@ -498,10 +500,10 @@ def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: tor
         if scratch.numel() < need:
             raise KernelError(f"decode_attention: scratch of {scratch.numel()} floats, {need} needed")
     fn = _fn("attention_decode", "lgml_decode_attention", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                           c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+                                                           c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_decode", fn(_ptr(q), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_pages),
                                   _ptr(v_pages), n_pages, page, _ptr(out), ldo, _ptr(scratch if n_splits > 1 else None), n_splits, n, n_heads, hkv, d,
-                                  float(scale), int(window or 0), _ptr(status), _stream()), "decode_attention")
+                                  float(scale), int(window or 0), int(max_new_tokens), _ptr(status), _stream()), "decode_attention")
     return out
 
 
@@ -553,7 +555,7 @@ def paged_attention(q, batch, cache, out, n_heads: int, scale: float, window: in
         if batch.max_q_len <= DECODE_MAX_Q:
             n_splits = batch.decode_splits if getattr(batch, "decode_splits", None) else decode_splits(q.shape[0], hkv, n_heads // hkv, batch.max_kv_len)
             return decode_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
-                                    window, status, n_splits)
+                                    window, status, n_splits, max_new_tokens=batch.max_q_len)
         if d <= 128:
             tiles = batch.attention_tiles(prefill_tile_tokens(n_heads, hkv))
             return prefill_attention(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window, status)

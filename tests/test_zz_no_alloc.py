@@ -40,11 +40,11 @@ def call_noalloc(lib, q, positions, seq_of, table, k, v, H, n_splits, scale, win
     fn = lib.lgml_decode_attention_noalloc
     fn.restype = c_int
     fn.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
-                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
     out = torch.empty_like(q)
     n_pages, hkv, page, d = k.shape
     rc = fn(q.data_ptr(), q.stride(0), positions.data_ptr(), seq_of.data_ptr(), table.data_ptr(), table.shape[1], k.data_ptr(),
-            v.data_ptr(), n_pages, page, out.data_ptr(), out.stride(0), n_splits, q.shape[0], H, hkv, d, scale, window,
+            v.data_ptr(), n_pages, page, out.data_ptr(), out.stride(0), n_splits, q.shape[0], H, hkv, d, scale, window, 1,
             status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     err = lib.lgml_attention_decode_noalloc_last_error
     err.restype = ctypes.c_char_p
