@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_decode": ("attention_decode.cu", []),
     "gemm_tcgen05": ("gemm_tcgen05.cu", []),
     "attention_prefill": ("attention_prefill.cu", []),
+    "attention_prefill_tc": ("attention_prefill_tc.cu", []),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", []),
 }
 

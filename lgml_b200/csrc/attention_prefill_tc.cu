@@ -1,0 +1,433 @@
+// Paged attention for prompts and portions of prompts on the 5th-generation tensor cores
+// (tcgen05), bfloat16 operands, float32 scores, softmax and output.
+//
+// A CTA takes 128 query rows of one KV head: `tt` consecutive new tokens of one request times
+// the `hpc` query heads that share the KV head (row = token * hpc + head), and walks the
+// request's pages from the first one a query can see to the page of its last token.  Per page
+// of 64 keys:
+//     S[128, 64]  = Q[128, D] . K_page[64, D]^T      tcgen05.mma, accumulator in tensor memory
+//     softmax: one thread per row reads its 64 scores from TMEM, keeps the running maximum and
+//              sum in float32 (base-2 exponentials), writes P as bfloat16 to shared memory
+//     O_page[128, D] = P[128, 64] . V_page[64, D]    tcgen05.mma (V is the N-major B operand)
+//     O = O * correction + O_page                    in registers, 8 warps x 64 columns
+// Q, K, V and P sit in shared memory in the 128-byte-swizzled layout the tensor core reads;
+// pages are copied with cp.async (K two stages ahead, V one), so copies overlap the math, and
+// two CTAs share an SM so that one's products overlap the other's softmax.  Keys are taken
+// from the cache, so this step's own keys are seen at cache precision, as in mischief/lgml,
+// which writes the cache before attention reads it (lua/lgml/transformer.lua:1838-1839,
+// :2405-2407; formula :1805-1816, scale :1845).  Waits on mbarriers are bounded.
+#include <math.h>
+
+#include "common.cuh"
+
+LGML_DEFINE_LAST_ERROR(lgml_attention_prefill_tc)
+
+namespace {
+constexpr int PAGE = 64;
+constexpr int ROWS = 128;            // query rows per CTA = UMMA M
+constexpr int THREADS = 256;
+constexpr uint32_t SPIN_LIMIT = 4u << 20;
+constexpr int STATUS_TIMEOUT = 12;
+constexpr uint32_t TMEM_COLS = 256;  // S: columns 0..63, O_page: columns 64..64+DP-1
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// shared memory written by threads or cp.async becomes visible to the tensor core's reads
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, STATUS_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tcgen05_alloc(uint32_t *dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 2^x in one instruction; 2^(-inf) = 0
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1.  Offsets in units of 16 bytes.
+//   K-major operand (rows of 128 bytes, 8-row groups of 1024 bytes): leading 1 (unused), stride 1024.
+//   N-major operand (64 elements of N contiguous in 128 bytes, 8 rows of K per 1024 bytes):
+//   leading = distance between blocks of 64 along N, stride = distance between groups of 8 along K.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)((leading_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((stride_bytes >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: float32 accumulator, bfloat16 operands, A K-major; B K-major or N-major
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_n_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_n_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a swizzled block of 128-byte rows
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// DP: head size padded to a multiple of 64 (the tensor core reads 64-element, 128-byte rows);
+// the pad columns of Q, K and V are zero.
+template <int DP>
+__global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
+    const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ tiles,
+    const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
+    const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int D,
+    int hpc, float scale, int window, int *__restrict__ status) {
+    pdl_trigger();
+    constexpr int KB = DP / 64;                       // 64-element blocks along the head dimension
+    constexpr uint32_t Q_BYTES = KB * ROWS * 128;     // [KB][128 rows][128 B]
+    constexpr uint32_t K_BYTES = KB * PAGE * 128;     // [KB][64 keys][128 B]      (K-major: row = key)
+    constexpr uint32_t V_BYTES = KB * PAGE * 128;     // [KB][64 keys][128 B]      (N-major: 64 dims per row)
+    constexpr uint32_t P_BYTES = ROWS * 128;          // [128 rows][64 keys]
+    constexpr int HALF = DP / 2;                      // output columns per thread
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *Qs = base, *Ks = Qs + Q_BYTES, *Vs = Ks + 2 * K_BYTES, *Ps = Vs + V_BYTES;
+    float *corr_s = reinterpret_cast<float *>(Ps + P_BYTES);   // [128] this page's correction of the running output
+    float *l_s = corr_s + ROWS;                                 // [128] final sums
+    __shared__ uint64_t s_bar, o_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s, page_ok[2];
+    volatile int *abort_flag = &abort_s;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tile = blockIdx.x;
+    const int seq = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
+    const int group = H / Hkv;
+    const int chunks_per_kv = (group + hpc - 1) / hpc;
+    const int kvh = blockIdx.y / chunks_per_kv, hchunk = blockIdx.y - kvh * chunks_per_kv;
+    const int g0 = hchunk * hpc;                                  // first head of the group this CTA holds
+    const int g_count = min(hpc, group - g0);
+    const int *table = block_table + (size_t)seq * max_blocks;
+    const int pos_first = positions[row0], pos_last = pos_first + n_tok - 1;
+    const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int pg_lo = lo_first / PAGE, pg_hi = pos_last / PAGE;
+    const int n_iter = pg_hi - pg_lo + 1;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const int chunks_d = D / 8;                                   // 16-byte chunks of a real row
+
+    if (tid == 0) {
+        mbar_init(&s_bar, 1);
+        mbar_init(&o_bar, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc(&tmem_base_s, TMEM_COLS);
+    // zero everything once: pad columns, rows of absent tokens and of heads this CTA does not have
+    for (uint32_t i = tid * 16; i < Q_BYTES + 2 * K_BYTES + V_BYTES + P_BYTES; i += THREADS * 16)
+        *reinterpret_cast<uint4 *>(base + i) = make_uint4(0, 0, 0, 0);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    // ---- page copies ------------------------------------------------------------------------------
+    auto load_k = [&](int it) {
+        const int pg = pg_lo + it, stage = it & 1;
+        const int page = table[pg];
+        const bool have = page >= 0 && page < n_pages;
+        if (tid == 0) {
+            page_ok[stage] = have ? 1 : 0;
+            if (!have) atomicExch(status, 3);
+        }
+        const int valid_rows = have ? min(pos_last - pg * PAGE + 1, PAGE) : 0;   // rows past the last key become zero
+        const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
+        const uint32_t dst = smem_u32(Ks + stage * K_BYTES);
+        for (int c = tid; c < PAGE * chunks_d; c += THREADS) {
+            const int row = c / chunks_d, ch = c - row * chunks_d;
+            cp_async_16(dst + (ch >> 3) * (PAGE * 128) + swz(row, ch & 7), k_pages + off + (size_t)row * D + ch * 8, row < valid_rows);
+        }
+    };
+    auto load_v = [&](int it) {
+        const int pg = pg_lo + it;
+        const int page = table[pg];
+        const bool have = page >= 0 && page < n_pages;
+        const int valid_rows = have ? min(pos_last - pg * PAGE + 1, PAGE) : 0;
+        const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
+        const uint32_t dst = smem_u32(Vs);
+        for (int c = tid; c < PAGE * chunks_d; c += THREADS) {
+            const int row = c / chunks_d, ch = c - row * chunks_d;
+            cp_async_16(dst + (ch >> 3) * (PAGE * 128) + swz(row, ch & 7), v_pages + off + (size_t)row * D + ch * 8, row < valid_rows);
+        }
+    };
+    // The positions, tiles and block tables come from the host; everything else this kernel reads
+    // (queries, this step's keys and values) is written by the kernels ahead of it.
+    pdl_wait();
+    load_k(0);
+    cp_async_commit();
+    load_v(0);
+    cp_async_commit();
+    // queries: row r = token (r / hpc), head g0 + (r % hpc); through L2, they were just written
+    for (int c = tid; c < ROWS * chunks_d; c += THREADS) {
+        const int r = c / chunks_d, ch = c - r * chunks_d;
+        const int tok = r / hpc, g = r - tok * hpc;
+        if (tok < n_tok && g < g_count) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
+            *reinterpret_cast<uint4 *>(Qs + (ch >> 3) * (ROWS * 128) + swz(r, ch & 7)) = v;
+        }
+    }
+
+    // ---- per-thread state ---------------------------------------------------------------------------
+    const int quarter = warp & 3;                                 // TMEM lane quarter this warp may read
+    const int row = quarter * 32 + lane;                          // this thread's row
+    const int my_tok = row / hpc, my_g = row - my_tok * hpc;
+    const bool row_valid = my_tok < n_tok && my_g < g_count;
+    const int qpos = row_valid ? pos_first + my_tok : -1;
+    const int col0 = warp < 4 ? 0 : HALF;                         // the output columns this thread accumulates
+    float o_reg[HALF];
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) o_reg[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    constexpr uint32_t idesc_qk = make_idesc(ROWS, PAGE, 0);
+    constexpr uint32_t idesc_pv = make_idesc(ROWS, DP, 1);
+    bool alive = true;
+
+    for (int it = 0; it < n_iter; ++it) {
+        const int stage = it & 1, pg = pg_lo + it, key0 = pg * PAGE;
+        // K(it) has landed (V(it) may still be in flight)
+        cp_async_wait<1>();
+        fence_async_smem();
+        __syncthreads();
+        // ---- S = Q K^T -------------------------------------------------------------------------------
+        if (tid == 0) {
+            tcgen05_fence_after();
+            const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + stage * K_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < DP / 16; ++ks) {
+                const uint64_t da = make_desc(qa + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, 16, 1024);
+                const uint64_t db = make_desc(ka + (ks >> 2) * (PAGE * 128) + (ks & 3) * 32, 16, 1024);
+                tcgen05_mma_bf16(tmem_base, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+            }
+            tcgen05_commit(&s_bar);
+        }
+        // the next page of keys goes into the other stage while the tensor core works
+        if (it + 1 < n_iter) load_k(it + 1);
+        cp_async_commit();
+
+        // ---- softmax: warps 0-3, one thread per row -----------------------------------------------------
+        if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
+        tcgen05_fence_after();
+        if (warp < 4) {
+            const bool have = page_ok[stage] != 0;
+            // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A page that lies wholly
+            // inside every row's range takes the path without per-element tests.
+            const bool edge = !have || key0 + PAGE - 1 > pos_first || (window > 0 && key0 < pos_last - window + 1) || n_tok * hpc < ROWS || g_count < hpc;
+            const int c_hi = have ? qpos - key0 : -1;                                  // qpos = -1 for a row without a token
+            const int c_lo = (window > 0) ? qpos - window + 1 - key0 : -(1 << 30);
+            float mx = -INFINITY;
+            if (edge) {
+#pragma unroll
+                for (int c0 = 0; c0 < PAGE; c0 += 16) {
+                    uint32_t r[16];
+                    tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                    tcgen05_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j <= c_hi && c0 + j >= c_lo) mx = fmaxf(mx, __uint_as_float(r[j]));
+                }
+            } else {
+#pragma unroll
+                for (int c0 = 0; c0 < PAGE; c0 += 16) {
+                    uint32_t r[16];
+                    tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                    tcgen05_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+                }
+            }
+            // the scale is positive, so the maximum of the raw scores is the maximum of the scaled ones
+            const float m_new = fmaxf(m_run, mx * scale_log2);
+            const float corr = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
+            const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;      // keeps (-inf) - (-inf) out of the exponent
+            m_run = m_new;
+            float sum = 0.f;
+#pragma unroll
+            for (int c0 = 0; c0 < PAGE; c0 += 16) {
+                uint32_t r[16];
+                tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                tcgen05_wait_ld();
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    float p0 = ex2(fmaf(__uint_as_float(r[j]), scale_log2, -m_sub));
+                    float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_sub));
+                    if (edge) {
+                        if (c0 + j > c_hi || c0 + j < c_lo) p0 = 0.f;
+                        if (c0 + j + 1 > c_hi || c0 + j + 1 < c_lo) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                    packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                }
+                // 16 keys = two 16-byte chunks of this row of P
+                *reinterpret_cast<uint4 *>(Ps + swz(row, (c0 >> 3))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4 *>(Ps + swz(row, (c0 >> 3) + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+            l_run = l_run * corr + sum;
+            corr_s[row] = corr;
+        }
+        // V(it) has landed (K(it+1) may still be in flight); P is written
+        cp_async_wait<1>();
+        fence_async_smem();
+        tcgen05_fence_before();
+        __syncthreads();
+        // ---- O_page = P V ------------------------------------------------------------------------------
+        if (tid == 0) {
+            tcgen05_fence_after();
+            const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs);
+#pragma unroll
+            for (int k2 = 0; k2 < PAGE / 16; ++k2) {
+                const uint64_t da = make_desc(pa + k2 * 32, 16, 1024);
+                // 16 keys further = two groups of 8 rows; blocks of 64 dims are PAGE * 128 bytes apart
+                const uint64_t db = make_desc(va + k2 * 2048, PAGE * 128, 1024);
+                tcgen05_mma_bf16(tmem_base + 64, da, db, idesc_pv, k2 > 0 ? 1u : 0u);
+            }
+            tcgen05_commit(&o_bar);
+        }
+        if (alive && !mbar_wait(&o_bar, it & 1, abort_flag, status)) alive = false;
+        tcgen05_fence_after();
+        // the values' stage is free: the next page of values
+        if (it + 1 < n_iter) load_v(it + 1);
+        cp_async_commit();
+        // ---- O = O * correction + O_page, 8 warps x HALF columns -------------------------------------------
+        {
+            const float corr = corr_s[row];
+#pragma unroll
+            for (int c0 = 0; c0 < HALF; c0 += 16) {
+                uint32_t r[16];
+                tcgen05_ld_16(lane_addr + 64u + (uint32_t)(col0 + c0), r);
+                tcgen05_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) o_reg[c0 + j] = fmaf(o_reg[c0 + j], corr, __uint_as_float(r[j]));
+            }
+        }
+        tcgen05_fence_before();
+    }
+    cp_async_wait<0>();
+    // ---- normalise and write ----------------------------------------------------------------------------
+    if (warp < 4) l_s[row] = l_run;
+    __syncthreads();
+    if (row_valid && alive) {
+        const float l = l_s[row];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16 *dst = out + (size_t)(row0 + my_tok) * ldo + (size_t)(kvh * group + g0 + my_g) * D;
+#pragma unroll
+        for (int c0 = 0; c0 < HALF; c0 += 8) {
+            const int d = col0 + c0;
+            if (d + 8 <= D) {
+                uint32_t h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(o_reg[c0 + 2 * j] * inv, o_reg[c0 + 2 * j + 1] * inv);
+                    h[j] = *reinterpret_cast<uint32_t *>(&pr);
+                }
+                *reinterpret_cast<uint4 *>(dst + d) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tcgen05_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int DP>
+int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table, int max_blocks,
+           const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D,
+           int hpc, float scale, int window, int *status, cudaStream_t stream) {
+    constexpr int KB = DP / 64;
+    const size_t smem = (size_t)KB * ROWS * 128 + 3 * (size_t)KB * PAGE * 128 + ROWS * 128 + 2 * ROWS * sizeof(float) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) LGML_FAIL("prefill_attention_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    lgml_launch(prefill_attention_tc_kernel<DP>, grid, THREADS, smem, stream, q, ldq, positions, tiles, block_table, max_blocks, k_pages,
+                v_pages, n_pages, out, ldo, H, Hkv, D, hpc, scale, window, status);
+    return lgml_launch_status("prefill_attention_tc");
+}
+}  // namespace
+
+// Heads per CTA for a group of `group` query heads per KV head (at most 8) and the tokens of a
+// tile: 128 rows / heads per CTA.
+LGML_API void lgml_prefill_attention_tc_shape(int group, int *heads_per_cta, int *tile_tokens) {
+    const int hpc = group < 8 ? group : 8;
+    *heads_per_cta = hpc;
+    *tile_tokens = ROWS / hpc;
+}
+
+LGML_API int lgml_prefill_attention_tc(const void *q, int ldq, const int *positions, const int *tiles, int n_tiles, const int *block_table,
+                                       int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size, void *out,
+                                       int ldo, int H, int Hkv, int D, float scale, int window, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && max_blocks > 0, "prefill_attention_tc: bad sizes");
+    LGML_REQUIRE(page_size == PAGE, "prefill_attention_tc: pages of %d tokens, this kernel takes %d", page_size, PAGE);
+    LGML_REQUIRE(H % Hkv == 0, "prefill_attention_tc: %d heads are no multiple of %d KV heads", H, Hkv);
+    LGML_REQUIRE(D >= 16 && D <= 128 && D % 16 == 0, "prefill_attention_tc: head_dim %d must be a multiple of 16 up to 128", D);
+    LGML_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 && D % 8 == 0,
+                 "prefill_attention_tc: q and out must be 16-byte aligned with row strides that are multiples of 8");
+    LGML_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0, "prefill_attention_tc: the cache must be 16-byte aligned");
+    if (n_tiles == 0) return 0;
+    const int group = H / Hkv;
+    int hpc, tt;
+    lgml_prefill_attention_tc_shape(group, &hpc, &tt);
+    const int chunks = (group + hpc - 1) / hpc;
+    LGML_REQUIRE((long long)Hkv * chunks <= 65535, "prefill_attention_tc: too many heads");
+    dim3 grid(n_tiles, Hkv * chunks);
+    const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
+    __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
+    if (D <= 64)
+        return launch<64>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, D, hpc, scale, window, status, stream);
+    return launch<128>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, D, hpc, scale, window, status, stream);
+}

@@ -9,6 +9,7 @@ another device is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -541,6 +542,47 @@ def prefill_attention(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Ten
     return out
 
 
+def prefill_tc_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
+    """Tokens per tile of the tcgen05 prefill attention kernel: 128 rows / heads per CTA."""
+    return 128 // min(n_heads // n_kv_heads, 8)
+
+
+def prefill_attention_tc(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor,
+                         k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                         status: torch.Tensor) -> torch.Tensor:
+    """bfloat16 attention for prompts and portions on tcgen05 tensor cores (S and the page's
+    output in tensor memory).  ``tiles`` as for ``prefill_attention``, each at most
+    ``prefill_tc_tile_tokens`` long."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    _need(positions, "positions", torch.int32, 1)
+    _need(tiles, "tiles", torch.int32, 2)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4:
+        raise KernelError(f"prefill_attention_tc: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
+        raise KernelError("prefill_attention_tc: pages, block table and tiles must be contiguous")
+    fn = _fn("attention_prefill_tc", "lgml_prefill_attention_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                                   c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check("attention_prefill_tc", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
+                                      _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
+                                      int(window or 0), _ptr(status), _stream()), "prefill_attention_tc")
+    return out
+
+
+def prefill_tc_supports(q: torch.Tensor, out: torch.Tensor) -> bool:
+    """The tcgen05 kernel reads q and writes out in 16-byte pieces."""
+    return q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+
+
+# which kernel runs prompts and portions: "tcgen05" (default) or "mma" (the mma.sync kernel)
+PREFILL_ATTENTION = os.environ.get("LGML_PREFILL_ATTENTION", "tcgen05")
+
 # a portion of at most this many tokens per request is run by the decode kernel
 DECODE_MAX_Q = 8
 
@@ -556,6 +598,9 @@ def paged_attention(q, batch, cache, out, n_heads: int, scale: float, window: in
             n_splits = batch.decode_splits if getattr(batch, "decode_splits", None) else decode_splits(q.shape[0], hkv, n_heads // hkv, batch.max_kv_len)
             return decode_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
                                     window, status, n_splits, max_new_tokens=batch.max_q_len)
+        if d <= 128 and PREFILL_ATTENTION == "tcgen05" and prefill_tc_supports(q, out):
+            tiles = batch.attention_tiles(prefill_tc_tile_tokens(n_heads, hkv))
+            return prefill_attention_tc(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window, status)
         if d <= 128:
             tiles = batch.attention_tiles(prefill_tile_tokens(n_heads, hkv))
             return prefill_attention(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window, status)

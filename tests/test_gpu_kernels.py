@@ -347,6 +347,9 @@ def run_attention(kind, case, window, n_splits=None):
         ops.paged_attention_ref(q, b.positions, b.seq_of_token, tab, kp, vp, out, H, scale, window, st)
     elif kind == "decode":
         ops.decode_attention(q, b.positions, b.seq_of_token, tab, kp, vp, out, H, scale, window, st, n_splits)
+    elif kind == "prefill_tc":
+        tiles = b.attention_tiles(ops.prefill_tc_tile_tokens(H, case["G"]))
+        ops.prefill_attention_tc(q, b.positions, tiles, tab, kp, vp, out, H, scale, window, st)
     else:
         tiles = b.attention_tiles(ops.prefill_tile_tokens(H, case["G"]))
         ops.prefill_attention(q, b.positions, tiles, tab, kp, vp, out, H, scale, window, st)
@@ -371,11 +374,12 @@ def test_attention_decode_kernel(H, G, D, window, n_splits):
     assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("H,G,D", ATT_SHAPES + [(3, 3, 112)])
+@pytest.mark.parametrize("H,G,D", ATT_SHAPES + [(3, 3, 112), (16, 1, 64)])
 @pytest.mark.parametrize("window", [0, 90])
-def test_attention_prefill_kernel(H, G, D, window):
+@pytest.mark.parametrize("kind", ["prefill", "prefill_tc"])
+def test_attention_prefill_kernel(H, G, D, window, kind):
     case = make_attention_case(3, H, G, D, kv_lens=[300, 70, 1, 129, 64], q_lens=[300, 33, 1, 65, 2], dtype=torch.bfloat16)
-    got, want = run_attention("prefill", case, window)
+    got, want = run_attention(kind, case, window)
     assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
 
 
@@ -383,7 +387,7 @@ def test_attention_finds_the_far_key():
     """The aimed query's output is that key's value, in every kernel."""
     case = make_attention_case(4, 4, 2, 64, kv_lens=[500], q_lens=[1], dtype=torch.bfloat16)
     far = 500 - 67
-    for kind, splits in (("ref", None), ("decode", 4), ("prefill", None)):
+    for kind, splits in (("ref", None), ("decode", 4), ("prefill", None), ("prefill_tc", None)):
         got, _ = run_attention(kind, case, 0, splits)
         for h in range(4):
             v_far = case["vs"][0][far, h // 2]
