@@ -8,7 +8,8 @@ the pool larger than one request's context), ``slots`` (the most requests kept a
 ``lua/lgml/kvpool.lua:28``), ``ubatch`` (prompt tokens per request per step,
 default 512), ``max_tokens`` (default reply length: the free context),
 ``sampling`` (sampler defaults, a request's values replace them),
-``repeat_stop_tokens``.  ``generate.greedy`` of the reference
+``repeat_stop_tokens``.  ``run_ahead`` (not in the reference): launch a decode step before
+the host has seen the ids of the one before, when those are chosen on the device.  ``generate.greedy`` of the reference
 (``lua/lgml/generate.lua:19-34``) is ``Engine.greedy``.
 """
 from __future__ import annotations
@@ -21,6 +22,7 @@ import torch
 from .. import ops
 from ..sampling import Sampler, SamplingParams
 from .runner import ModelRunner
+from .runtime import MAX_RESULT
 from .scheduler import REPEAT_STOP, UBATCH, GenRequest, Scheduler
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
@@ -38,7 +40,8 @@ def parse_dtype(name) -> torch.dtype:
 class Engine:
     def __init__(self, model=None, *, config=None, random_weights: Optional[int] = None, dtype="bfloat16", n_ctx: Optional[int] = None,
                  kv_tokens: Optional[int] = None, slots: int = 4, ubatch: int = UBATCH, max_batch_tokens: Optional[int] = None, max_tokens: Optional[int] = None,
-                 sampling: Optional[dict] = None, repeat_stop_tokens: int = REPEAT_STOP, device="cuda:0"):
+                 sampling: Optional[dict] = None, repeat_stop_tokens: int = REPEAT_STOP, device="cuda:0",
+                 run_ahead: bool = True):
         dt = parse_dtype(dtype)
         if model is None and config is None:
             raise ValueError("give a model folder, or a config with random_weights=seed")
@@ -72,51 +75,103 @@ class Engine:
         gc.collect()
         gc.freeze()
         self._next_id = 0
+        self.run_ahead = run_ahead
+        self._ahead: Optional[dict] = None          # the step whose ids the host has not seen yet
+        self._host_ring = [torch.empty(MAX_RESULT + 1, dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._host_turn = 0
+        self._t_mark = time.perf_counter()
         self.timings: Dict[str, float] = {}
         # one record per scheduler turn: wall seconds, prompt tokens, decoded tokens, bytes copied each way
         self.turn_log: List[dict] = []
 
     # ---- one scheduler turn -------------------------------------------------------------
-    def _turn(self) -> List[GenRequest]:
-        sch = self.scheduler
-        t_start = time.perf_counter()
-        plan = sch.plan()
-        if not plan:
-            return []
-        entries = [(e.request.cache_req, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan]
-        logits = self.runner.step(entries)
-        sampled: Dict[Hashable, int] = {}
+    # A step whose tokens are chosen on the device is not waited for: its ids travel to the
+    # host in the background, and the next decode step, planned ahead of them, is launched
+    # with the ids still on the device.  The host's work of a turn then runs beside the GPU's.
+    def _launch(self, plan, device_tokens: Optional[torch.Tensor]) -> dict:
+        """Run the planned step and choose its tokens.  Returns the record that ``_resolve``
+        finishes: ``toks`` when the host already has the ids, else a pinned buffer and the
+        event after which it holds them, followed by the status word."""
+        if device_tokens is None:
+            entries = [(e.request.cache_req, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan]
+            logits = self.runner.step(entries)
+        else:
+            logits = self.runner.decode_step([e.request.cache_req for e in plan], device_tokens)
         rows = [e for e in plan if e.sample]
-        if rows:
-            neutral = all(e.request.params.on_device for e in rows)
-            if neutral and all(e.request.params.greedy for e in rows):
-                out = torch.empty(len(rows), dtype=torch.int32, device=logits.device)
-                toks = ops.argmax_rows(logits, out).cpu().tolist()
-            elif neutral:
+        rec = {"plan": plan, "rows": rows, "toks": None, "out": None, "h2d": self.runner.last_batch.h2d_bytes + 12 * len(rows)}
+        if not rows:
+            rec["toks"] = []
+            return rec
+        n = len(rows)
+        neutral = n <= MAX_RESULT and all(e.request.params.on_device for e in rows)
+        if neutral:
+            res = self.rt.result
+            out = res[MAX_RESULT - n:MAX_RESULT]
+            if all(e.request.params.greedy for e in rows):
+                ops.argmax_rows(logits, out)
+            else:
                 temps = torch.tensor([e.request.params.temperature for e in rows], dtype=torch.float32).pin_memory()
                 us = torch.tensor([0.0 if e.request.params.greedy else e.request.sampler.uniform() for e in rows],
                                   dtype=torch.float64).pin_memory()
-                out = torch.empty(len(rows), dtype=torch.int32, device=logits.device)
                 ops.sample_rows(logits, temps.to(logits.device, non_blocking=True), us.to(logits.device, non_blocking=True), out)
-                toks = out.cpu().tolist()
-            else:
-                host = logits.cpu().numpy()
-                toks = [e.request.sampler.sample(host[i]) for i, e in enumerate(rows)]
-            for e, t in zip(rows, toks):
-                sampled[e.request.id] = int(t)
-        self.rt.check_status()
-        done = sch.complete(plan, sampled)
-        n_decode = sum(1 for e in plan if len(e.tokens) == 1 and e.sample)
-        self.turn_log.append({"s": time.perf_counter() - t_start, "tokens": sum(len(e.tokens) for e in plan),
-                              "decode": n_decode, "pure_decode": n_decode == len(plan),
-                              "h2d": self.runner.last_batch.h2d_bytes + 12 * len(rows), "d2h": 4 * len(rows) + 4})
+            host = self._host_ring[self._host_turn % len(self._host_ring)]
+            self._host_turn += 1
+            host[:n + 1].copy_(res[MAX_RESULT - n:], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            rec.update(out=out, host=host, event=ev)
+        else:
+            host_logits = logits.cpu().numpy()
+            rec["toks"] = [int(e.request.sampler.sample(host_logits[i])) for i, e in enumerate(rows)]
+        return rec
+
+    def _resolve(self, rec: dict) -> List[GenRequest]:
+        """Wait for the step's ids, check the status word, and tell the scheduler."""
+        rows, plan = rec["rows"], rec["plan"]
+        if rec["toks"] is None:
+            rec["event"].synchronize()
+            got = rec["host"][:len(rows) + 1].tolist()
+            toks, code = got[:-1], got[-1]
+            if code:
+                self.rt.status.zero_()
+            self.rt.check_status(code)
+        else:
+            toks = rec["toks"]
+            self.rt.check_status()
+        # a request that an earlier step ended has a token too many in this one: not counted
+        n_decode = sum(1 for e in plan if len(e.tokens) == 1 and e.sample and e.request.finish_reason is None)
+        done = self.scheduler.complete(plan, {e.request.id: int(t) for e, t in zip(rows, toks)})
+        now = time.perf_counter()
+        self.turn_log.append({"s": now - self._t_mark, "tokens": sum(len(e.tokens) for e in plan),
+                              "decode": n_decode, "pure_decode": all(len(e.tokens) == 1 for e in plan),
+                              "h2d": rec["h2d"], "d2h": 4 * len(rows) + 4})
+        self._t_mark = now
         return done
 
-    def decode_rate(self, skip: int = 0) -> dict:
+    def _turn(self) -> List[GenRequest]:
+        sch = self.scheduler
+        prev, self._ahead = self._ahead, None
+        if prev is not None:
+            plan = sch.plan_ahead(prev["plan"]) if self.run_ahead else None
+            if plan is not None:
+                self._ahead = self._launch(plan, prev["out"])
+            return self._resolve(prev)
+        plan = sch.plan()
+        if not plan:
+            return []
+        rec = self._launch(plan, None)
+        if rec["out"] is not None:
+            self._ahead = rec          # its ids are on their way; the next turn takes them up
+            return []
+        return self._resolve(rec)
+
+    def decode_rate(self, skip: int = 0, rows: Optional[int] = None) -> dict:
         """Decoded tokens per second over the turns that held only decode tokens (the
         reference reports the same as ``predicted_per_second``, ``lua/lgml/engine.lua:3225-3239``),
-        leaving out the first ``skip`` of them."""
-        turns = [t for t in self.turn_log if t["pure_decode"]][skip:]
+        leaving out the first ``skip`` of them; with ``rows``, over the turns that decoded
+        exactly that many requests (the rate at one batch size, without the turns in which
+        requests that started later are still going on alone)."""
+        turns = [t for t in self.turn_log if t["pure_decode"] and (rows is None or t["decode"] == rows)][skip:]
         secs = sum(t["s"] for t in turns)
         toks = sum(t["decode"] for t in turns)
         n = max(len(turns), 1)
@@ -135,7 +190,7 @@ class Engine:
         stop_ids = list(stop) if stop is not None else self.eos_ids
         reqs = []
         self.turn_log = []
-        t0 = time.perf_counter()
+        t0 = self._t_mark = time.perf_counter()
         for i, p in enumerate(prompts):
             p = [int(t) for t in p]
             room = self.scheduler.max_position - len(p)
@@ -149,7 +204,7 @@ class Engine:
             else:
                 self.scheduler.add(req)
             reqs.append(req)
-        while not self.scheduler.idle:
+        while not self.scheduler.idle or self._ahead is not None:
             self._turn()
         torch.cuda.synchronize(self.rt.device)
         self.timings = {"total": time.perf_counter() - t0}

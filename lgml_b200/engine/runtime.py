@@ -22,6 +22,9 @@ _STATUS_TEXT = {
 }
 
 
+MAX_RESULT = 4096     # most sampled rows of a step whose ids travel with the status word
+
+
 class DeviceFault(RuntimeError):
     """A kernel flagged an input it refused to use (it skipped the access)."""
 
@@ -37,7 +40,10 @@ class Runtime:
             raise ValueError(f"compute type must be bfloat16 or float32, not {dtype}")
         self.dtype = dtype
         torch.cuda.set_device(self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # sampled token ids of a step end at result[MAX_RESULT], where the status word sits: one
+        # copy brings both to the host
+        self.result = torch.zeros(MAX_RESULT + 1, dtype=torch.int32, device=self.device)
+        self.status = self.result[MAX_RESULT:]
         self.gemm_backend = gemm
         self.attention_backend = "auto"
 
@@ -65,8 +71,11 @@ class Runtime:
         return ops.paged_attention(q, batch, cache, out, n_heads, scale, window, self.status)
 
     # ---- faults ------------------------------------------------------------------------
-    def check_status(self) -> None:
-        code = int(self.status.item())
+    def check_status(self, code: Optional[int] = None) -> None:
+        """Raise if a kernel flagged a fault; ``code`` is the status word when the caller
+        already has it on the host."""
+        if code is None:
+            code = int(self.status.item())
         if code:
             self.status.zero_()
             raise DeviceFault(f"kernel status {code}: {_STATUS_TEXT.get(code, 'unknown')}")

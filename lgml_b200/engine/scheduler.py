@@ -29,6 +29,7 @@ from ..cache import CacheManager, NoSlot
 from ..sampling import Sampler, SamplingParams
 
 UBATCH = 512          # prompt tokens per request per step (lua/lgml/engine.lua:57)
+UNKNOWN_TOKEN = -1    # stands for an id that is still on the device (a step planned ahead)
 REPEAT_STOP = 256     # equal tokens in a row that end a reply (lua/lgml/engine.lua:61, :2679-2689)
 
 
@@ -189,6 +190,33 @@ class Scheduler:
             self.stats["tokens"] += sum(len(e.tokens) for e in plan)
         return plan
 
+    def plan_ahead(self, inflight: List[PlannedEntry]) -> Optional[List[PlannedEntry]]:
+        """The decode step after ``inflight``, planned before the tokens that ``inflight``
+        samples are known: the same requests, one token each, the ids still on the device.
+        None when the outcome of ``inflight`` could change the plan in any way but an end
+        token: a request waits, a token limit or the repeat guard may strike, a portion of a
+        prompt is under way, or a page is missing.  A request that ``inflight`` ends with an
+        end token runs one token too many; ``complete`` drops it."""
+        if self.waiting or not inflight or len(inflight) != len(self.running) or len(inflight) > self.max_batch_tokens:
+            return None
+        for e in inflight:
+            r = e.request
+            if not e.sample or r.finish_reason is not None or r.cache_req is None:
+                return None
+            after = len(r.generated) + 1
+            if after >= r.max_new_tokens or len(r.prompt) + after >= self.max_position:
+                return None
+            if self.repeat_stop_tokens and r.repeat_run + 1 >= self.repeat_stop_tokens:
+                return None
+        for e in inflight:
+            if not self.cache.reserve(e.request.cache_req, 1):
+                return None
+        plan = [PlannedEntry(e.request, [UNKNOWN_TOKEN], True) for e in inflight]
+        self.stats["steps"] += 1
+        self.stats["rows"] += len(plan)
+        self.stats["tokens"] += len(plan)
+        return plan
+
     # ---- after the step --------------------------------------------------------------------
     def complete(self, plan: List[PlannedEntry], sampled: Dict[Hashable, int]) -> List[GenRequest]:
         """Record that the planned tokens ran; ``sampled`` maps the id of each entry with
@@ -196,6 +224,8 @@ class Scheduler:
         done = []
         for e in plan:
             req = e.request
+            if req.finish_reason is not None:
+                continue                     # planned ahead of the end token that finished it
             req.n_cached += len(e.tokens)
             if not e.sample:
                 continue

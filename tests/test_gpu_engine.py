@@ -96,6 +96,41 @@ def test_preemption_keeps_every_reply_whole(folders):
     assert tight.runner.cache.n_free_pages == 5
 
 
+@pytest.mark.parametrize("key", [("B", "float32"), ("B", "bfloat16")])
+def test_launching_ahead_of_the_host_changes_no_reply(folders, key):
+    """Decode steps launched before the host has seen the ids of the step before: replies,
+    end tokens and reasons equal those of an engine that waits for every step; six requests
+    on three slots, end tokens that strike in mid-flight, greedy and seeded draws."""
+    import lgml_b200
+
+    folder = folders[key]
+    prompts = [H.random_ids(n, 320, 300 + n) for n in (9, 33, 70, 21, 64, 5)]
+    for opts in (dict(temperature=0.0), dict(temperature=0.9, seed=5)):
+        waits = lgml_b200.Engine(str(folder), dtype=key[1], slots=3, kv_tokens=64 * 9, run_ahead=False)
+        base = waits.generate(prompts, max_tokens=48, **opts)
+        # end tokens: ids that some replies produce part-way
+        stop = [base[0][10], base[2][30], base[4][3]]
+        want = waits.generate(prompts, max_tokens=48, stop=stop, return_details=True, **opts)
+        ahead = lgml_b200.Engine(str(folder), dtype=key[1], slots=3, kv_tokens=64 * 9)
+        got = ahead.generate(prompts, max_tokens=48, stop=stop, return_details=True, **opts)
+        if key[1] == "float32":
+            # 32-bit results do not depend on what else is in the batch: the replies are equal
+            assert [r.generated for r in got] == [r.generated for r in want]
+            assert [r.finish_reason for r in got] == [r.finish_reason for r in want]
+            assert any(r.finish_reason == "stop" for r in got)
+        for r in got:
+            # in bfloat16 a batch of another size may round a near tie the other way, so
+            # only what must hold of any reply: it ends at its first end token, or at the limit
+            hits = [i for i, t in enumerate(r.generated) if t in stop]
+            if hits:
+                assert r.finish_reason == "stop" and hits[0] == len(r.generated) - 1
+            else:
+                assert r.finish_reason == "length" and len(r.generated) == 48
+        ahead.runner.cache.check()
+        assert not ahead.runner.cache.live and ahead.runner.cache.n_free_pages == 9
+        assert sum(t["decode"] for t in ahead.turn_log) == sum(len(r.generated) - 1 for r in got)
+
+
 def test_full_sampler_chain_runs_on_host_logits(folders):
     import lgml_b200
 

@@ -166,3 +166,123 @@ def test_prompts_that_can_never_fit_are_refused():
         s.add(req("long", 1000, 1))
     with pytest.raises(ValueError, match="empty"):
         s.add(GenRequest(id="e", prompt=[], max_new_tokens=1))
+
+
+def drive_ahead(s, cm, log=None, limit=10000):
+    """As an engine that launches a decode step before it has seen the ids of the step before:
+    the step after ``inflight`` is planned (and 'launched': committed) first, then ``inflight``
+    is completed."""
+    inflight = None
+    for _ in range(limit):
+        if inflight is None:
+            if s.idle:
+                return
+            inflight = s.plan()
+            for e in inflight:
+                cm.commit(e.request.cache_req, len(e.tokens))
+            if log is not None:
+                log.append(("plan", [(e.request.id, len(e.tokens)) for e in inflight]))
+            continue
+        nxt = s.plan_ahead(inflight)
+        if nxt is not None:
+            for e in nxt:
+                cm.commit(e.request.cache_req, 1)
+            if log is not None:
+                log.append(("ahead", [(e.request.id, len(e.tokens)) for e in nxt]))
+        cm.check()
+        s.complete(inflight, {e.request.id: stub_token(e.request) for e in inflight if e.sample and e.request.finish_reason is None})
+        cm.check()
+        inflight = nxt
+    raise AssertionError("the scheduler did not finish")
+
+
+def test_planning_ahead_gives_the_same_replies():
+    outs = []
+    for ahead in (False, True):
+        s, cm = make(ubatch=64, budget=128, n_pages=12, slots=3)
+        rs = [req("a", 70, 40), req("b", 130, 25), req("c", 5, 60), req("d", 64, 64)]
+        for r in rs:
+            s.add(r)
+        (drive_ahead if ahead else drive)(s, cm)
+        assert cm.n_free_pages == 12 and not cm.live
+        outs.append([(r.generated, r.finish_reason) for r in rs])
+    assert outs[0] == outs[1]
+
+
+def test_planning_ahead_only_when_nothing_but_an_end_token_can_change_the_plan():
+    s, cm = make(ubatch=64, n_pages=8, slots=2)
+    a = req("a", 10, 5)
+    s.add(a)
+    p0 = s.plan()
+    cm.commit(a.cache_req, 10)
+    # one request, decoding, tokens left: the next step can be planned before the id is known
+    p1 = s.plan_ahead(p0)
+    assert p1 is not None and [(e.request.id, len(e.tokens), e.sample) for e in p1] == [("a", 1, True)]
+    cm.commit(a.cache_req, 1)
+    s.complete(p0, {"a": 7})
+    # a request waits: admission comes first
+    s.add(req("b", 10, 5))
+    assert s.plan_ahead(p1) is None
+    s.complete(p1, {"a": 8})
+    p2 = s.plan()                       # a decodes, b's prompt is admitted
+    assert sorted((e.request.id, len(e.tokens)) for e in p2) == [("a", 1), ("b", 10)]
+    for e in p2:
+        cm.commit(e.request.cache_req, len(e.tokens))
+    p3 = s.plan_ahead(p2)               # both sample in p2: both can go on
+    assert p3 is not None and len(p3) == 2
+    for e in p3:
+        cm.commit(e.request.cache_req, 1)
+    s.complete(p2, {"a": 9, "b": 9})
+    # a has 3 of 5; after p3 it has 4, after the next 5: that step can still be planned ahead,
+    # the one after it cannot (the limit ends a there)
+    p4 = s.plan_ahead(p3)
+    assert p4 is not None
+    for e in p4:
+        cm.commit(e.request.cache_req, 1)
+    s.complete(p3, {"a": 9, "b": 9})
+    assert s.plan_ahead(p4) is None
+    s.complete(p4, {"a": 9, "b": 9})
+    assert a.finish_reason == "length" and len(a.generated) == 5
+    cm.check()
+
+
+def test_an_end_token_drops_the_step_planned_ahead():
+    s, cm = make(n_pages=8, slots=2)
+    a, b = req("a", 10, 50, stop=(77,)), req("b", 20, 50)
+    s.add(a)
+    s.add(b)
+    p0 = s.plan()
+    for e in p0:
+        cm.commit(e.request.cache_req, len(e.tokens))
+    p1 = s.plan_ahead(p0)
+    for e in p1:
+        cm.commit(e.request.cache_req, 1)
+    done = s.complete(p0, {"a": 77, "b": 5})          # a ends while its next token is under way
+    assert done == [a] and a.finish_reason == "stop" and a.generated == [77]
+    cm.check()
+    assert s.plan_ahead(p1) is None                   # the batch changed
+    s.complete(p1, {"a": 123, "b": 6})                # a's extra token is dropped
+    assert a.generated == [77] and b.generated == [5, 6] and b.n_cached == 21
+    cm.check()
+    assert len(cm.live) == 1
+
+
+def test_planning_ahead_stops_when_a_page_is_missing():
+    s, cm = make(n_pages=2, slots=1)
+    a = req("a", 120, 50)
+    s.add(a)
+    inflight = s.plan()
+    cm.commit(a.cache_req, 120)
+    n = 0
+    while True:
+        nxt = s.plan_ahead(inflight)
+        if nxt is None:
+            break
+        cm.commit(a.cache_req, 1)
+        s.complete(inflight, {"a": 3})
+        inflight = nxt
+        n += 1
+    assert a.cache_req.n_tokens == 128 and n == 8    # both pages full: the next token needs a third
+    s.complete(inflight, {"a": 3})
+    assert s.plan() == [] and a.finish_reason == "length"   # alone and out of pages
+    cm.check()
