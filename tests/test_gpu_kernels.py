@@ -367,7 +367,7 @@ def test_attention_ref_kernel(H, G, D, dtype, window):
 
 
 @pytest.mark.parametrize("H,G,D", ATT_SHAPES + [(16, 1, 32), (4, 2, 256)])
-@pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 5), (100, 3)])
+@pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 5), (100, 3), (0, 8), (0, 11), (100, 9)])
 def test_attention_decode_kernel(H, G, D, window, n_splits):
     case = make_attention_case(2, H, G, D, kv_lens=[700, 64, 1, 333, 129, 65], q_lens=[1, 1, 1, 3, 1, 2], dtype=torch.bfloat16)
     got, want = run_attention("decode", case, window, n_splits)

@@ -57,7 +57,7 @@ def test_noalloc_entry_point_matches_the_regular_one_twice_in_a_row():
     lib = csrc.load("attention_decode_noalloc")
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     cases = [
-        dict(seed=1, n_seqs=5, H=8, Hkv=2, D=64, lens=[700, 64, 1, 333, 129], n_splits=6, window=0),
+        dict(seed=1, n_seqs=5, H=8, Hkv=2, D=64, lens=[700, 64, 1, 333, 129], n_splits=11, window=0),
         dict(seed=2, n_seqs=3, H=6, Hkv=6, D=48, lens=[200, 450, 65], n_splits=3, window=100),
     ]
     for c in cases:
