@@ -68,11 +68,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_kernel(
     __nv_bfloat16 *kv_s = reinterpret_cast<__nv_bfloat16 *>(smem_raw);   // [2 stages][K | V][PAGE][LD]
     __shared__ int page_ok[2];
 
-    const int tile = blockIdx.x;
+    const int tile = blockIdx.y;                  // heads run fastest: the CTAs of one tile start together, tiles in the order given
     const int seq = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
     const int group = H / Hkv;
     const int chunks_per_kv = (group + hpc - 1) / hpc;
-    const int kvh = blockIdx.y / chunks_per_kv, hchunk = blockIdx.y - kvh * chunks_per_kv;
+    const int kvh = blockIdx.x / chunks_per_kv, hchunk = blockIdx.x - kvh * chunks_per_kv;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head_local = warp % hpc, tb = warp / hpc;
     const int g = hchunk * hpc + head_local;                      // head within the group
@@ -279,7 +279,8 @@ LGML_API int lgml_prefill_attention(const void *q, int ldq, const int *positions
     lgml_prefill_attention_shape(group, &hpc, &n_tb);
     const int chunks = (group + hpc - 1) / hpc;
     LGML_REQUIRE((long long)Hkv * chunks <= 65535, "prefill_attention: too many heads");
-    dim3 grid(n_tiles, Hkv * chunks);
+    LGML_REQUIRE(n_tiles <= 65535, "prefill_attention: %d tiles in one launch (at most 65535)", n_tiles);
+    dim3 grid(Hkv * chunks, n_tiles);
     const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
 #define LGML_CASE(DD)                                                                                                                 \

@@ -143,11 +143,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     volatile int *abort_flag = &abort_s;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tile = blockIdx.x;
+    const int tile = blockIdx.y;                  // heads run fastest: the CTAs of one tile start together, tiles in the order given
     const int seq = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
     const int group = H / Hkv;
     const int chunks_per_kv = (group + hpc - 1) / hpc;
-    const int kvh = blockIdx.y / chunks_per_kv, hchunk = blockIdx.y - kvh * chunks_per_kv;
+    const int kvh = blockIdx.x / chunks_per_kv, hchunk = blockIdx.x - kvh * chunks_per_kv;
     const int g0 = hchunk * hpc;                                  // first head of the group this CTA holds
     const int g_count = min(hpc, group - g0);
     const int *table = block_table + (size_t)seq * max_blocks;
@@ -424,7 +424,8 @@ LGML_API int lgml_prefill_attention_tc(const void *q, int ldq, const int *positi
     lgml_prefill_attention_tc_shape(group, &hpc, &tt);
     const int chunks = (group + hpc - 1) / hpc;
     LGML_REQUIRE((long long)Hkv * chunks <= 65535, "prefill_attention_tc: too many heads");
-    dim3 grid(n_tiles, Hkv * chunks);
+    LGML_REQUIRE(n_tiles <= 65535, "prefill_attention_tc: %d tiles in one launch (at most 65535)", n_tiles);
+    dim3 grid(Hkv * chunks, n_tiles);
     const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
     if (D <= 64)

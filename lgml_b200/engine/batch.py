@@ -124,15 +124,19 @@ class StepBatch:
     def attention_tiles(self, tile_tokens: int) -> torch.Tensor:
         """The new tokens cut into tiles of at most ``tile_tokens`` consecutive tokens of one
         request, for the prefill attention kernel: int32 [n_tiles, 4] on the device, rows
-        (request row, first token row, tokens, 0).  Made once per tile size."""
+        (request row, first token row, tokens, 0), the tile with the most keys to visit first:
+        the kernel starts its CTAs in this order, and a long tile that starts last would run on
+        alone at the end.  Made once per tile size."""
         cached = self._tiles.get(tile_tokens)
         if cached is None:
             rows = []
             start = 0
             for s, n in enumerate(self.seq_lens):
                 for t0 in range(0, n, tile_tokens):
-                    rows.append((s, start + t0, min(tile_tokens, n - t0), 0))
+                    rows.append((s, start + t0, min(tile_tokens, n - t0), self.pos0[s] + min(t0 + tile_tokens, n)))
                 start += n
+            rows.sort(key=lambda r: -r[3])
+            rows = [(s, r0, nt, 0) for s, r0, nt, _ in rows]
             cached = torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(self.token_ids.device)
             self._tiles[tile_tokens] = cached
         return cached

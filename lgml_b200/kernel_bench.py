@@ -117,7 +117,7 @@ def case_prefill_attention(a) -> None:
     positions = torch.arange(T, dtype=torch.int32, device=DEV)
     table = torch.randperm(n_pages).to(torch.int32).reshape(1, n_pages).to(DEV)
     tt = ops.prefill_tile_tokens(H, G) if a.mma else ops.prefill_tc_tile_tokens(H, G)
-    tiles = torch.tensor([(0, t0, min(tt, T - t0), 0) for t0 in range(0, T, tt)], dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([(0, t0, min(tt, T - t0), 0) for t0 in reversed(range(0, T, tt))], dtype=torch.int32, device=DEV)   # longest first
     fn = ops.prefill_attention if a.mma else ops.prefill_attention_tc
     us = timed(lambda i: fn(q, positions, tiles, table, k, v, out, H, D ** -0.5, 0, status), 1, a.warmup, a.iters)
     flops = 4.0 * H * D * T * (T + 1) / 2
