@@ -11,8 +11,10 @@
 //     O_page[128, D] = P[128, 64] . V_page[64, D]    tcgen05.mma (V is the N-major B operand)
 //     O = O * correction + O_page                    in registers, 8 warps x 64 columns
 // Q, K, V and P sit in shared memory in the 128-byte-swizzled layout the tensor core reads;
-// pages are copied with cp.async (K two stages ahead, V one), so copies overlap the math, and
-// two CTAs share an SM so that one's products overlap the other's softmax.  Keys are taken
+// pages are copied with cp.async (K two pages ahead, V one), so copies overlap the math.  The
+// scores of page i+1 are issued right behind the P V product of page i, into a second S
+// buffer, so they are ready when the output of page i has been added up; and two CTAs share
+// an SM so that one's products overlap the other's softmax.  Keys are taken
 // from the cache, so this step's own keys are seen at cache precision, as in mischief/lgml,
 // which writes the cache before attention reads it (lua/lgml/transformer.lua:1838-1839,
 // :2405-2407; formula :1805-1816, scale :1845).  Waits on mbarriers are bounded.
@@ -28,7 +30,8 @@ constexpr int ROWS = 128;            // query rows per CTA = UMMA M
 constexpr int THREADS = 256;
 constexpr uint32_t SPIN_LIMIT = 4u << 20;
 constexpr int STATUS_TIMEOUT = 12;
-constexpr uint32_t TMEM_COLS = 256;  // S: columns 0..63, O_page: columns 64..64+DP-1
+constexpr uint32_t TMEM_COLS = 256;  // S of even pages: columns 0..63, O_page: 64..64+DP-1, S of odd pages: 192..255
+constexpr uint32_t O_COL = 64, S1_COL = 192;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool valid) {
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     float *l_s = corr_s + ROWS;                                 // [128] final sums
     __shared__ uint64_t s_bar, o_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s, page_ok[2];
+    __shared__ int abort_s;
     volatile int *abort_flag = &abort_s;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -178,10 +181,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         const int pg = pg_lo + it, stage = it & 1;
         const int page = table[pg];
         const bool have = page >= 0 && page < n_pages;
-        if (tid == 0) {
-            page_ok[stage] = have ? 1 : 0;
-            if (!have) atomicExch(status, 3);
-        }
+        if (tid == 0 && !have) atomicExch(status, 3);
         const int valid_rows = have ? min(pos_last - pg * PAGE + 1, PAGE) : 0;   // rows past the last key become zero
         const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
         const uint32_t dst = smem_u32(Ks + stage * K_BYTES);
@@ -209,6 +209,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     cp_async_commit();
     load_v(0);
     cp_async_commit();
+    if (n_iter > 1) load_k(1);
+    cp_async_commit();
     // queries: row r = token (r / hpc), head g0 + (r % hpc); through L2, they were just written
     for (int c = tid; c < ROWS * chunks_d; c += THREADS) {
         const int r = c / chunks_d, ch = c - r * chunks_d;
@@ -235,33 +237,43 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     constexpr uint32_t idesc_pv = make_idesc(ROWS, DP, 1);
     bool alive = true;
 
+    // S = Q K^T of page `it` into the S buffer of its parity (one thread issues)
+    auto issue_qk = [&](int it) {
+        const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + (it & 1) * K_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < DP / 16; ++ks) {
+            const uint64_t da = make_desc(qa + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, 16, 1024);
+            const uint64_t db = make_desc(ka + (ks >> 2) * (PAGE * 128) + (ks & 3) * 32, 16, 1024);
+            tcgen05_mma_bf16(tmem_base + ((it & 1) ? S1_COL : 0u), da, db, idesc_qk, ks > 0 ? 1u : 0u);
+        }
+        tcgen05_commit(&s_bar);
+    };
+    // Q and K(0) have landed: the first scores; later ones are issued a page ahead, behind the
+    // P V product of the page before, so that the tensor core has them ready when the softmax
+    // of that page is done.
+    cp_async_wait<2>();
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+        tcgen05_fence_after();
+        issue_qk(0);
+    }
+
     for (int it = 0; it < n_iter; ++it) {
         const int stage = it & 1, pg = pg_lo + it, key0 = pg * PAGE;
-        // K(it) has landed (V(it) may still be in flight)
-        cp_async_wait<1>();
-        fence_async_smem();
-        __syncthreads();
-        // ---- S = Q K^T -------------------------------------------------------------------------------
-        if (tid == 0) {
-            tcgen05_fence_after();
-            const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + stage * K_BYTES);
-#pragma unroll
-            for (int ks = 0; ks < DP / 16; ++ks) {
-                const uint64_t da = make_desc(qa + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, 16, 1024);
-                const uint64_t db = make_desc(ka + (ks >> 2) * (PAGE * 128) + (ks & 3) * 32, 16, 1024);
-                tcgen05_mma_bf16(tmem_base, da, db, idesc_qk, ks > 0 ? 1u : 0u);
-            }
-            tcgen05_commit(&s_bar);
-        }
-        // the next page of keys goes into the other stage while the tensor core works
-        if (it + 1 < n_iter) load_k(it + 1);
+        const uint32_t s_col = stage ? S1_COL : 0u;
+        if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
+        tcgen05_fence_after();
+        // the scores of this page are done, so its keys' stage is free: the keys of the page after the next
+        if (it + 2 < n_iter) load_k(it + 2);
         cp_async_commit();
 
         // ---- softmax: warps 0-3, one thread per row -----------------------------------------------------
         if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
         tcgen05_fence_after();
         if (warp < 4) {
-            const bool have = page_ok[stage] != 0;
+            const int page_id = table[pg];
+            const bool have = page_id >= 0 && page_id < n_pages;
             // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A page that lies wholly
             // inside every row's range takes the path without per-element tests.
             const bool edge = !have || key0 + PAGE - 1 > pos_first || (window > 0 && key0 < pos_last - window + 1) || n_tok * hpc < ROWS || g_count < hpc;
@@ -272,7 +284,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 #pragma unroll
                 for (int c0 = 0; c0 < PAGE; c0 += 16) {
                     uint32_t r[16];
-                    tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
                     tcgen05_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
@@ -282,7 +294,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 #pragma unroll
                 for (int c0 = 0; c0 < PAGE; c0 += 16) {
                     uint32_t r[16];
-                    tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
                     tcgen05_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
@@ -297,7 +309,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 #pragma unroll
             for (int c0 = 0; c0 < PAGE; c0 += 16) {
                 uint32_t r[16];
-                tcgen05_ld_16(lane_addr + (uint32_t)c0, r);
+                tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
                 tcgen05_wait_ld();
                 uint32_t packed[8];
 #pragma unroll
@@ -319,7 +331,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             l_run = l_run * corr + sum;
             corr_s[row] = corr;
         }
-        // V(it) has landed (K(it+1) may still be in flight); P is written
+        // V(it) and K(it+1) have landed (K(it+2) may still be in flight); P is written
         cp_async_wait<1>();
         fence_async_smem();
         tcgen05_fence_before();
@@ -333,9 +345,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
                 const uint64_t da = make_desc(pa + k2 * 32, 16, 1024);
                 // 16 keys further = two groups of 8 rows; blocks of 64 dims are PAGE * 128 bytes apart
                 const uint64_t db = make_desc(va + k2 * 2048, PAGE * 128, 1024);
-                tcgen05_mma_bf16(tmem_base + 64, da, db, idesc_pv, k2 > 0 ? 1u : 0u);
+                tcgen05_mma_bf16(tmem_base + O_COL, da, db, idesc_pv, k2 > 0 ? 1u : 0u);
             }
             tcgen05_commit(&o_bar);
+            if (it + 1 < n_iter) issue_qk(it + 1);
         }
         if (alive && !mbar_wait(&o_bar, it & 1, abort_flag, status)) alive = false;
         tcgen05_fence_after();
@@ -348,7 +361,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 #pragma unroll
             for (int c0 = 0; c0 < HALF; c0 += 16) {
                 uint32_t r[16];
-                tcgen05_ld_16(lane_addr + 64u + (uint32_t)(col0 + c0), r);
+                tcgen05_ld_16(lane_addr + O_COL + (uint32_t)(col0 + c0), r);
                 tcgen05_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) o_reg[c0 + j] = fmaf(o_reg[c0 + j], corr, __uint_as_float(r[j]));

@@ -57,6 +57,8 @@ __device__ __forceinline__ float act_load(const float *p) { return __ldcg(p); }
 __device__ __forceinline__ __nv_bfloat16 act_load(const __nv_bfloat16 *p) { return __ldcg(p); }
 __device__ __forceinline__ unsigned int act_load(const unsigned int *p) { return __ldcg(p); }
 __device__ __forceinline__ float2 act_load(const float2 *p) { return __ldcg(p); }
+__device__ __forceinline__ float4 act_load(const float4 *p) { return __ldcg(p); }
+__device__ __forceinline__ uint4 act_load(const uint4 *p) { return __ldcg(p); }
 
 static inline bool lgml_pdl_enabled() {
     static int enabled = -1;

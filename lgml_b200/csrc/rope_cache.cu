@@ -89,6 +89,127 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
     dst[d1] = from_f32<T>(b);
 }
 
+
+// The same for many tokens at once (prompts), bfloat16 in and out, one part: a block per token.
+// The token's cosines and sines are computed once and shared by all its heads, and a work unit
+// is 16 bytes (8 elements) of one head, or for the "half" pairing the two 16-byte runs that
+// hold 8 pairs, so that loads and stores are as wide as the hardware takes.  The arithmetic of
+// one pair is that of the kernel above.
+constexpr int WIDE_THREADS = 128;
+constexpr int WIDE_MAX_ROT = 512;
+__global__ void __launch_bounds__(WIDE_THREADS) rope_kv_write_wide_kernel(
+    const __nv_bfloat16 *__restrict__ src, int lds, const float *__restrict__ bias, __nv_bfloat16 *__restrict__ q_out, int ldq,
+    const int *__restrict__ positions, const int *__restrict__ seq_of_token, const int *__restrict__ block_table, int max_blocks,
+    const float *__restrict__ inv_freq, int n_rot, int pairing, __nv_bfloat16 *__restrict__ k_pages,
+    __nv_bfloat16 *__restrict__ v_pages, int n_pages, int page_size, int H, int Hkv, int D, int write_kv, int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float2 cs[WIDE_MAX_ROT / 2];      // (cos, sin) of pair i
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int pos = positions[t];
+    const int half_rot = n_rot / 2;
+    for (int i = tid; i < half_rot; i += WIDE_THREADS) {
+        float sn, c;
+        sincosf((float)pos * inv_freq[i], &sn, &c);
+        cs[i] = make_float2(c, sn);
+    }
+    // where this token's k and v go
+    int page = -1;
+    if (write_kv) {
+        const int seq = seq_of_token[t];
+        const int blk = pos / page_size;
+        if (pos >= 0 && blk < max_blocks) page = block_table[(size_t)seq * max_blocks + blk];
+        if (page < 0 || page >= n_pages) {   // the host reserves pages first; never write outside the pool
+            if (tid == 0) atomicExch(status, 2);
+            page = -1;
+        }
+    }
+    __syncthreads();
+    const int rot_units = pairing ? n_rot / 8 : n_rot / 16;     // units of a rotated head that turn
+    const int copy_units = (D - n_rot) / 8;                     // and those that pass through
+    const int units_qk = rot_units + copy_units, units_v = D / 8;
+    const int n_qk = write_kv ? H + Hkv : H;
+    const int total = n_qk * units_qk + (write_kv ? Hkv * units_v : 0);
+    const __nv_bfloat16 *row = src + (size_t)t * lds;
+    for (int u = tid; u < total; u += WIDE_THREADS) {
+        int head, unit;
+        bool is_v = false;
+        if (u < n_qk * units_qk) {
+            head = u / units_qk;
+            unit = u - head * units_qk;
+        } else {
+            const int w = u - n_qk * units_qk;
+            head = H + Hkv + w / units_v;
+            unit = w - (w / units_v) * units_v;
+            is_v = true;
+        }
+        const size_t col = (size_t)head * D;
+        __nv_bfloat16 *dst;
+        if (head < H) {
+            dst = q_out + (size_t)t * ldq + col;
+        } else {
+            if (page < 0) continue;
+            const int g = is_v ? head - H - Hkv : head - H;
+            dst = (is_v ? v_pages : k_pages) + (((size_t)page * Hkv + g) * page_size + (size_t)(pos % page_size)) * D;
+        }
+        if (is_v || unit >= rot_units) {
+            // 8 elements that do not turn
+            const int d = is_v ? unit * 8 : n_rot + (unit - rot_units) * 8;
+            uint4 raw = act_load(reinterpret_cast<const uint4 *>(row + col + d));
+            if (bias) {
+                __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16_rn(__bfloat162float(e[j]) + bias[col + d + j]);
+            }
+            *reinterpret_cast<uint4 *>(dst + d) = raw;
+        } else if (pairing) {
+            // adjacent pairs: 8 elements = pairs 4 unit .. 4 unit + 3
+            const int d = unit * 8;
+            uint4 raw = act_load(reinterpret_cast<const uint4 *>(row + col + d));
+            __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float a = __bfloat162float(e[2 * j]), b = __bfloat162float(e[2 * j + 1]);
+                if (bias) {
+                    a += bias[col + d + 2 * j];
+                    b += bias[col + d + 2 * j + 1];
+                }
+                const float2 f = cs[unit * 4 + j];
+                e[2 * j] = __float2bfloat16_rn(a * f.x - b * f.y);
+                e[2 * j + 1] = __float2bfloat16_rn(a * f.y + b * f.x);
+            }
+            *reinterpret_cast<uint4 *>(dst + d) = raw;
+        } else {
+            // half pairs: elements 8 unit .. 8 unit + 7 with their partners n_rot / 2 further
+            const int d0 = unit * 8, d1 = d0 + half_rot;
+            uint4 ra = act_load(reinterpret_cast<const uint4 *>(row + col + d0));
+            uint4 rb = act_load(reinterpret_cast<const uint4 *>(row + col + d1));
+            __nv_bfloat16 *ea = reinterpret_cast<__nv_bfloat16 *>(&ra), *eb = reinterpret_cast<__nv_bfloat16 *>(&rb);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float a = __bfloat162float(ea[j]), b = __bfloat162float(eb[j]);
+                if (bias) {
+                    a += bias[col + d0 + j];
+                    b += bias[col + d1 + j];
+                }
+                const float2 f = cs[d0 + j];
+                ea[j] = __float2bfloat16_rn(a * f.x - b * f.y);
+                eb[j] = __float2bfloat16_rn(a * f.y + b * f.x);
+            }
+            *reinterpret_cast<uint4 *>(dst + d0) = ra;
+            *reinterpret_cast<uint4 *>(dst + d1) = rb;
+        }
+    }
+}
+
+// Whether the wide kernel can take this call: 16-byte runs everywhere.
+inline bool wide_ok(const void *src, int lds, const void *q_out, int ldq, const void *k_pages, const void *v_pages, int n_rot, int pairing,
+                    int D, int n_tokens) {
+    if (n_tokens < 32 || n_rot > WIDE_MAX_ROT) return false;
+    if (D % 8 || lds % 8 || ldq % 8 || n_rot % (pairing ? 8 : 16)) return false;
+    return (((uintptr_t)src | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+}
+
 template <typename TS, typename T>
 int launch(const void *src, int lds, int n_parts, long long part_stride, const float *bias, void *q_out, int ldq, const int *positions,
            const int *seq_of_token, const int *block_table, int max_blocks, const float *inv_freq, int n_rot, int pairing, void *k_pages,
@@ -122,7 +243,15 @@ LGML_API int lgml_rope_kv_write(const void *src, int src_dtype, int lds, int n_p
              k_pages, v_pages, n_pages, page_size, n_tokens, H, Hkv, D, write_kv, status, stream
     if (src_dtype == LGML_F32 && dtype == LGML_F32) return launch<float, float>(ARGS);
     if (src_dtype == LGML_F32 && dtype == LGML_BF16) return launch<float, __nv_bfloat16>(ARGS);
-    if (src_dtype == LGML_BF16 && dtype == LGML_BF16) return launch<__nv_bfloat16, __nv_bfloat16>(ARGS);
+    if (src_dtype == LGML_BF16 && dtype == LGML_BF16) {
+        if (n_parts == 1 && wide_ok(src, lds, q_out, ldq, k_pages, v_pages, n_rot, pairing, D, n_tokens)) {
+            lgml_launch(rope_kv_write_wide_kernel, dim3(n_tokens), WIDE_THREADS, 0, stream, (const __nv_bfloat16 *)src, lds, bias,
+                        (__nv_bfloat16 *)q_out, ldq, positions, seq_of_token, block_table, max_blocks, inv_freq, n_rot, pairing,
+                        (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, n_pages, page_size, H, Hkv, D, write_kv, status);
+            return lgml_launch_status("rope_kv_write");
+        }
+        return launch<__nv_bfloat16, __nv_bfloat16>(ARGS);
+    }
 #undef ARGS
     LGML_FAIL("rope_kv_write: unsupported types (source %d, output %d)", src_dtype, dtype);
 }

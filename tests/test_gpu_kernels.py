@@ -217,12 +217,13 @@ def ref_rope(x, pos, inv_freq, pairing, n_rot):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("pairing,n_rot,from_parts", [("half", 48, False), ("adjacent", 48, False), ("half", 32, False), ("half", 48, True), ("half", 0, False)])
-def test_rope_kv_write(dtype, pairing, n_rot, from_parts):
+@pytest.mark.parametrize("lens", [[3, 70, 1], [3, 5, 1]])     # many tokens take the kernel with 16-byte accesses, few the other
+def test_rope_kv_write(dtype, pairing, n_rot, from_parts, lens):
     from lgml_b200 import ops
 
     torch.manual_seed(3)
     H, G, D, page = 5, 5 if n_rot == 32 else 1, 48, 64
-    lens, pos0 = [3, 70, 1], [62, 0, 127]              # the first request crosses a page edge
+    pos0 = [62, 0, 127]                                # the first request crosses a page edge
     n = sum(lens)
     positions = torch.tensor([p + i for p, ln in zip(pos0, lens) for i in range(ln)], dtype=torch.int32)
     seq_of = torch.tensor([s for s, ln in enumerate(lens) for _ in range(ln)], dtype=torch.int32)
