@@ -47,144 +47,307 @@ LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids,
 //   delta != null : x[row] += delta[row] first, and the sum is written back (the residual add)
 //   rows  != null : output row r reads x[rows[r]] (the logits' row selection, :2349-2350);
 //                   delta is then added for the gathered rows only and x is not written.
-// One block per output row; the mean square is summed in a fixed order.
+//
+// One order of arithmetic for every way of launching it, so that a row's result has the same
+// bits whatever else is in the batch.  A row is cut into `cs` slices (8 for wide rows, the
+// width alone decides).  A slice belongs to a group of 128 threads; in round rd thread g of the
+// group holds the four consecutive elements  slice start + 512 rd + 4 g ...+3  (one 16-byte
+// access when the row allows it), adds their squares in that order, the group adds its threads'
+// sums by warp trees and then the four warps' sums by index, and the slices' sums are added by
+// index.  Three kernels share this:
+//   - few rows (decoding): the slices of a row are the CTAs of a thread-block cluster, so the
+//     row's bytes come through several SMs' memory paths; the sums cross through distributed
+//     shared memory;
+//   - many rows (prompts): one block of 128 threads takes all slices of its row one after the
+//     other, with every load of the row issued before any is used;
+//   - rows too wide for the registers of those two: one block per row that walks the row twice.
 // ---------------------------------------------------------------------------------------
-// A row is spread over a thread-block cluster of CS CTAs (CS = 1 for narrow rows): with few
-// rows (decoding) one CTA per row would leave the row's bytes to a single SM's memory path.
-// Each CTA sums the squares of its slice; the slices' sums are exchanged through distributed
-// shared memory and added in rank order.
-template <typename TD, typename TO>
-__global__ void rmsnorm_kernel(float *__restrict__ x, const TD *__restrict__ delta, int n_parts, long long part_stride,
-                               const float *__restrict__ delta_bias, const float *__restrict__ weight,
-                               const int *__restrict__ rows, TO *__restrict__ out, int width, float eps, int cs,
-                               int clustered) {
+namespace rms {
+constexpr int PER = 4, GROUP = 128, WARPS = GROUP / 32, MAX_CS = 8;
+
+__device__ __forceinline__ void load_quad(const float *p, int i, int c1, bool vec, float (&o)[PER]) {
+    if (vec && i + PER <= c1) {
+        const float4 t = act_load(reinterpret_cast<const float4 *>(p + i));
+        o[0] = t.x, o[1] = t.y, o[2] = t.z, o[3] = t.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) o[e] = i + e < c1 ? act_load(p + i + e) : 0.f;
+    }
+}
+__device__ __forceinline__ void load_quad(const __nv_bfloat16 *p, int i, int c1, bool vec, float (&o)[PER]) {
+    if (vec && i + PER <= c1) {
+        const float2 raw = act_load(reinterpret_cast<const float2 *>(p + i));       // 8 bytes = 4 bfloat16
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+        o[0] = __bfloat162float(lo.x), o[1] = __bfloat162float(lo.y), o[2] = __bfloat162float(hi.x), o[3] = __bfloat162float(hi.y);
+    } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) o[e] = i + e < c1 ? __bfloat162float(act_load(p + i + e)) : 0.f;
+    }
+}
+// weights and biases: not written by any kernel of the stream
+__device__ __forceinline__ void load_quad_const(const float *p, int i, int c1, bool vec, float (&o)[PER]) {
+    if (vec && i + PER <= c1) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p + i));
+        o[0] = t.x, o[1] = t.y, o[2] = t.z, o[3] = t.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) o[e] = i + e < c1 ? __ldg(p + i + e) : 0.f;
+    }
+}
+__device__ __forceinline__ void store_quad(float *p, int i, int c1, bool vec, const float (&v)[PER]) {
+    if (vec && i + PER <= c1) {
+        *reinterpret_cast<float4 *>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e)
+            if (i + e < c1) p[i + e] = v[e];
+    }
+}
+__device__ __forceinline__ void store_quad(__nv_bfloat16 *p, int i, int c1, bool vec, const float (&v)[PER]) {
+    if (vec && i + PER <= c1) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        float2 raw;
+        raw.x = *reinterpret_cast<float *>(&lo), raw.y = *reinterpret_cast<float *>(&hi);
+        *reinterpret_cast<float2 *>(p + i) = raw;
+    } else {
+#pragma unroll
+        for (int e = 0; e < PER; ++e)
+            if (i + e < c1) p[i + e] = __float2bfloat16_rn(v[e]);
+    }
+}
+
+struct Args {
+    float *x;
+    const void *delta;
+    int n_parts;
+    long long part_stride;
+    const float *delta_bias, *weight;
+    const int *rows;
+    void *out;
+    int width;
+    float eps;
+    int cs;
+    int vec;      // rows, parts and vectors allow 16-byte accesses (8-byte for bfloat16)
+};
+
+// x + delta of one quad: the parts in order, then the bias; written back unless rows are gathered
+template <typename TD>
+__device__ __forceinline__ void add_delta(const Args &a, float *xr, const TD *dr, int i, int c1, float (&v)[PER]) {
+    float d[PER];
+    load_quad(dr, i, c1, a.vec, d);
+    for (int p = 1; p < a.n_parts; ++p) {
+        float e[PER];
+        load_quad(dr + (size_t)p * a.part_stride, i, c1, a.vec, e);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) d[q] += e[q];
+    }
+    if (a.delta_bias) {
+        float bq[PER];
+        load_quad_const(a.delta_bias, i, c1, a.vec, bq);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) d[q] += bq[q];
+    }
+#pragma unroll
+    for (int q = 0; q < PER; ++q) v[q] += d[q];
+    if (!a.rows) store_quad(xr, i, c1, a.vec, v);
+}
+
+// SLICES = 1: this block holds one slice (its cluster rank, or the whole of a narrow row);
+// SLICES = MAX_CS: it holds all slices of its row.  ROUNDS rounds of a slice stay in registers.
+template <typename TD, typename TO, int ROUNDS, int SLICES, bool CLUSTERED>
+__global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
     pdl_trigger();
     pdl_wait();
     namespace cg = cooperative_groups;
-    __shared__ float red[32];
+    __shared__ float red[SLICES][WARPS];
     __shared__ float slice_ss;
-    constexpr int PER = 4;            // elements a thread keeps in registers per round
-    // A row is cut into cs slices whose sums of squares are added in slice order.  With few rows
-    // the slices run on the CTAs of a cluster; with many rows one CTA walks the slices itself.
-    // The arithmetic, and so the result, is the same either way.
-    const int r = clustered ? blockIdx.x / cs : blockIdx.x;
-    const int rank0 = clustered ? blockIdx.x - r * cs : 0, rank1 = clustered ? rank0 + 1 : cs;
+    const int gt = threadIdx.x, cs = a.cs, width = a.width;
+    const int r = CLUSTERED ? blockIdx.x / cs : blockIdx.x;
+    const int rank0 = CLUSTERED ? blockIdx.x - r * cs : 0;
     const int per_cta = ((width + cs - 1) / cs + 3) & ~3;
-    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
-    float *xr = x + src * width;
-    const TD *dr = delta ? delta + src * width : nullptr;
+    const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
+    float *xr = a.x + src * width;
+    const TD *dr = a.delta ? reinterpret_cast<const TD *>(a.delta) + src * width : nullptr;
+    const int n_slices = CLUSTERED ? 1 : cs;
+    float v[SLICES][ROUNDS][PER];
+    // every load of x first
+#pragma unroll
+    for (int k = 0; k < SLICES; ++k)
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+            const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
+            load_quad(xr, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec, v[k][rd]);
+        }
+    if (dr) {
+        // every load of the delta's first part next (no store lies between them), then the
+        // other parts in order, the bias, and the sums back to x
+        float d[SLICES][ROUNDS][PER];
+#pragma unroll
+        for (int k = 0; k < SLICES; ++k)
+#pragma unroll
+            for (int rd = 0; rd < ROUNDS; ++rd) {
+                const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
+                load_quad(dr, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec, d[k][rd]);
+            }
+        for (int p = 1; p < a.n_parts; ++p) {
+#pragma unroll
+            for (int k = 0; k < SLICES; ++k)
+#pragma unroll
+                for (int rd = 0; rd < ROUNDS; ++rd) {
+                    const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
+                    float e[PER];
+                    load_quad(dr + (size_t)p * a.part_stride, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec, e);
+#pragma unroll
+                    for (int q = 0; q < PER; ++q) d[k][rd][q] += e[q];
+                }
+        }
+#pragma unroll
+        for (int k = 0; k < SLICES; ++k)
+#pragma unroll
+            for (int rd = 0; rd < ROUNDS; ++rd) {
+                const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
+                const int i = (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt;
+                if (a.delta_bias) {
+                    float bq[PER];
+                    load_quad_const(a.delta_bias, i, c1, a.vec, bq);
+#pragma unroll
+                    for (int q = 0; q < PER; ++q) d[k][rd][q] += bq[q];
+                }
+#pragma unroll
+                for (int q = 0; q < PER; ++q) v[k][rd][q] += d[k][rd][q];
+                if (!a.rows) store_quad(xr, i, c1, a.vec, v[k][rd]);
+            }
+    }
+#pragma unroll
+    for (int k = 0; k < SLICES; ++k) {
+        float ss = 0.f;
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd)
+#pragma unroll
+            for (int q = 0; q < PER; ++q) ss = fmaf(v[k][rd][q], v[k][rd][q], ss);
+        ss = warp_sum(ss);
+        if ((gt & 31) == 0) red[k][gt >> 5] = ss;
+    }
+    __syncthreads();
     float total = 0.f;
-    for (int rank = rank0; rank < rank1; ++rank) {
-    const int c0 = rank * per_cta, c1 = min(width, c0 + per_cta);
-    float ss = 0.f;
-    for (int base = c0; base < c1; base += PER * blockDim.x) {
-        // all loads of this round first, so that they are in flight together
-        float v[PER], d[PER];
-#pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int i = base + j * blockDim.x + threadIdx.x;
-            v[j] = i < c1 ? xr[i] : 0.f;
-            d[j] = (dr && i < c1) ? to_f32(act_load(dr + i)) : 0.f;
-        }
-        if (dr) {
-            // the parts are the partial sums of a matrix product cut along K: four are fetched
-            // together (their loads overlap), then added in order
-            int p = 1;
-            for (; p + 4 <= n_parts; p += 4) {
-                float e[4][PER];
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-#pragma unroll
-                    for (int j = 0; j < PER; ++j) {
-                        const int i = base + j * blockDim.x + threadIdx.x;
-                        e[q][j] = i < c1 ? to_f32(act_load(dr + (size_t)(p + q) * part_stride + i)) : 0.f;
-                    }
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-#pragma unroll
-                    for (int j = 0; j < PER; ++j) d[j] += e[q][j];
-            }
-            for (; p < n_parts; ++p) {
-                float e[PER];
-#pragma unroll
-                for (int j = 0; j < PER; ++j) {
-                    const int i = base + j * blockDim.x + threadIdx.x;
-                    e[j] = i < c1 ? to_f32(act_load(dr + (size_t)p * part_stride + i)) : 0.f;
-                }
-#pragma unroll
-                for (int j = 0; j < PER; ++j) d[j] += e[j];
-            }
-#pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                const int i = base + j * blockDim.x + threadIdx.x;
-                if (i < c1) {
-                    if (delta_bias) d[j] += delta_bias[i];
-                    v[j] += d[j];
-                    if (!rows) xr[i] = v[j];
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < PER; ++j) ss = fmaf(v[j], v[j], ss);
+    for (int k = 0; k < n_slices; ++k) {
+        float slice = 0.f;
+        for (int w = 0; w < WARPS; ++w) slice += red[k][w];
+        total += slice;
     }
-    total += block_sum(ss, red);
-    }
-    if (clustered && cs > 1) {
+    if (CLUSTERED) {
         cg::cluster_group cluster = cg::this_cluster();
-        if (threadIdx.x == 0) slice_ss = total;
+        if (gt == 0) slice_ss = total;
         cluster.sync();
         total = 0.f;
         for (int k = 0; k < cs; ++k) total += *cluster.map_shared_rank(&slice_ss, k);
-        cluster.sync();               // no CTA leaves while another may still read its slice's sum
     }
-    const float inv = 1.0f / sqrtf(total / (float)width + eps);
-    // second pass: with a delta the row was just written (or, with a row list, is summed again the same way)
-    const int c0 = rank0 * per_cta, c1 = min(width, rank1 * per_cta);
-    for (int base = c0; base < c1; base += PER * blockDim.x) {
-        float v[PER], w[PER];
+    const float inv = 1.0f / sqrtf(total / (float)width + a.eps);
+    TO *orow = reinterpret_cast<TO *>(a.out) + (size_t)r * width;
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int i = base + j * blockDim.x + threadIdx.x;
-            w[j] = i < c1 ? weight[i] : 0.f;
-            v[j] = i < c1 ? xr[i] : 0.f;
-        }
-        if (dr && rows) {
+    for (int k = 0; k < SLICES; ++k)
 #pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                const int i = base + j * blockDim.x + threadIdx.x;
-                if (i < c1) {
-                    float d = to_f32(act_load(dr + i));
-                    for (int p = 1; p < n_parts; ++p) d += to_f32(act_load(dr + (size_t)p * part_stride + i));
-                    if (delta_bias) d += delta_bias[i];
-                    v[j] += d;
-                }
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+            const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
+            const int i = (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt;
+            if (i < c1) {
+                float w[PER], y[PER];
+                load_quad_const(a.weight, i, c1, a.vec, w);
+#pragma unroll
+                for (int q = 0; q < PER; ++q) y[q] = v[k][rd][q] * inv * w[q];
+                store_quad(orow, i, c1, a.vec, y);
             }
         }
+    if (CLUSTERED) cg::this_cluster().sync();     // no CTA leaves while another may still read its slice's sum
+}
+
+// Any width: one block per row walks the slices and their rounds, then the row again.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(GROUP) rmsnorm_any_kernel(const Args a) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    const int gt = threadIdx.x, cs = a.cs, width = a.width;
+    const int r = blockIdx.x;
+    const int per_cta = ((width + cs - 1) / cs + 3) & ~3;
+    const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
+    float *xr = a.x + src * width;
+    const TD *dr = a.delta ? reinterpret_cast<const TD *>(a.delta) + src * width : nullptr;
+    float total = 0.f;
+    for (int k = 0; k < cs; ++k) {
+        const int c0 = k * per_cta, c1 = min(width, c0 + per_cta);
+        float ss = 0.f;
+        for (int i = c0 + PER * gt; i < c1; i += PER * GROUP) {
+            float v[PER];
+            load_quad(xr, i, c1, a.vec, v);
+            if (dr) add_delta<TD>(a, xr, dr, i, c1, v);
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int i = base + j * blockDim.x + threadIdx.x;
-            if (i < c1) out[(size_t)r * width + i] = from_f32<TO>(v[j] * inv * w[j]);
+            for (int q = 0; q < PER; ++q) ss = fmaf(v[q], v[q], ss);
+        }
+        total += block_sum(ss, red);
+    }
+    const float inv = 1.0f / sqrtf(total / (float)width + a.eps);
+    TO *orow = reinterpret_cast<TO *>(a.out) + (size_t)r * width;
+    Args b = a;
+    b.rows = a.rows ? a.rows : reinterpret_cast<const int *>(1);      // second walk: never write x again
+    for (int k = 0; k < cs; ++k) {
+        const int c0 = k * per_cta, c1 = min(width, c0 + per_cta);
+        for (int i = c0 + PER * gt; i < c1; i += PER * GROUP) {
+            float v[PER], w[PER], y[PER];
+            load_quad(xr, i, c1, a.vec, v);            // with a delta and no row list this is the sum just written
+            if (dr && a.rows) add_delta<TD>(b, xr, dr, i, c1, v);
+            load_quad_const(a.weight, i, c1, a.vec, w);
+#pragma unroll
+            for (int q = 0; q < PER; ++q) y[q] = v[q] * inv * w[q];
+            store_quad(orow, i, c1, a.vec, y);
         }
     }
+}
+}  // namespace rms
+
+template <typename TD, typename TO>
+static int rmsnorm_launch(const rms::Args &a, int n_rows, cudaStream_t stream) {
+    using namespace rms;
+    // The number of slices depends on the width only, so a row's sum is formed in the same
+    // order whatever else is in the batch.
+    const int cs = a.cs;
+    const int per_cta = ((a.width + cs - 1) / cs + 3) & ~3;
+    const int rounds = (per_cta + PER * GROUP - 1) / (PER * GROUP);
+    const bool clustered = cs > 1 && n_rows <= 64;              // many rows fill the GPU without clusters
+    cudaError_t e = cudaSuccess;
+    if (clustered && rounds <= 4) {
+        const int blocks = n_rows * cs;
+        switch (rounds) {
+            case 1: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
+            case 2: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
+            case 3: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 3, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
+            default: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 4, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
+        }
+    } else if (cs == 1 && rounds <= 2) {
+        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, false>, n_rows, GROUP, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, 1, false>, n_rows, GROUP, 0, stream, a);
+    } else if (cs > 1 && rounds <= 2) {
+        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, false>, n_rows, GROUP, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, MAX_CS, false>, n_rows, GROUP, 0, stream, a);
+    } else {
+        e = lgml_launch(rmsnorm_any_kernel<TD, TO>, n_rows, GROUP, 0, stream, a);
+    }
+    (void)e;
+    return lgml_launch_status("rmsnorm");
 }
 
 template <typename TD>
 static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long part_stride, const float *delta_bias,
                             const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
                             cudaStream_t stream) {
-    // The cluster and block sizes depend on the width only, so a row's sum is formed in the
-    // same order whatever else is in the batch.
-    const int cs = width >= 2048 ? 8 : (width >= 1024 ? 4 : 1);
-    const int clustered = (cs > 1 && n_rows <= 64) ? 1 : 0;     // many rows fill the GPU without clusters
-    const int blocks = clustered ? n_rows * cs : n_rows;
-    const int threads = 128;
-    cudaError_t e;
-    if (out_dtype == LGML_F32)
-        e = lgml_launch_cluster(rmsnorm_kernel<TD, float>, blocks, threads, 0, stream, clustered ? cs : 1, x, delta, n_parts, part_stride, delta_bias, weight, rows, (float *)out, width, eps, cs, clustered);
-    else
-        e = lgml_launch_cluster(rmsnorm_kernel<TD, __nv_bfloat16>, blocks, threads, 0, stream, clustered ? cs : 1, x, delta, n_parts, part_stride, delta_bias, weight, rows, (__nv_bfloat16 *)out, width, eps, cs, clustered);
-    (void)e;
-    return lgml_launch_status("rmsnorm");
+    rms::Args a;
+    a.x = x, a.delta = delta, a.n_parts = n_parts, a.part_stride = part_stride, a.delta_bias = delta_bias, a.weight = weight;
+    a.rows = rows, a.out = out, a.width = width, a.eps = eps;
+    a.cs = width >= 2048 ? 8 : (width >= 1024 ? 4 : 1);
+    const uintptr_t ptrs = (uintptr_t)x | (uintptr_t)delta | (uintptr_t)delta_bias | (uintptr_t)weight | (uintptr_t)out;
+    a.vec = (width % 4 == 0 && part_stride % 4 == 0 && (ptrs & 15) == 0) ? 1 : 0;
+    if (out_dtype == LGML_F32) return rmsnorm_launch<TD, float>(a, n_rows, stream);
+    return rmsnorm_launch<TD, __nv_bfloat16>(a, n_rows, stream);
 }
 
 // delta: null, or [n_parts][rows of x][width] (part_stride elements between parts) whose parts

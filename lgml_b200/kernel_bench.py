@@ -126,12 +126,19 @@ def case_prefill_attention(a) -> None:
 
 def case_rmsnorm(a) -> None:
     rows, width, parts = a.rows, a.width, a.parts
-    x = torch.randn(rows, width, device=DEV)
+    nb = min(ring(rows * width * 4), 16)
+    xs = [torch.randn(rows, width, device=DEV) for _ in range(nb)]
     w = torch.ones(width, device=DEV)
     out = torch.empty(rows, width, dtype=torch.bfloat16, device=DEV)
-    delta = ops.Partials(torch.randn(parts, rows, width, device=DEV)) if parts > 0 else None
-    us = timed(lambda i: ops.rmsnorm(x, w, 1e-5, out, delta=delta), 1, a.warmup, a.iters)
-    print(f"rmsnorm rows={rows} width={width} parts={parts}: {us:.2f} us")
+    if a.bf16_delta:
+        deltas = [torch.randn(rows, width, device=DEV).to(torch.bfloat16) for _ in range(nb)]
+    elif parts > 0:
+        deltas = [ops.Partials(torch.randn(parts, rows, width, device=DEV)) for _ in range(min(nb, 4))]
+    else:
+        deltas = [None]
+    us = timed(lambda i: ops.rmsnorm(xs[i], w, 1e-5, out, delta=deltas[i % len(deltas)]), nb, a.warmup, a.iters)
+    byts = rows * width * (4 + 2) + (rows * width * (4 + (2 if a.bf16_delta else 4 * parts)) if deltas[0] is not None else 0)
+    print(f"rmsnorm rows={rows} width={width} parts={parts} bf16_delta={a.bf16_delta}: {us:.2f} us, {byts / us / 1e3:.0f} GB/s")
 
 
 def main(argv=None) -> int:
@@ -166,6 +173,7 @@ def main(argv=None) -> int:
     r.add_argument("--rows", type=int, default=8)
     r.add_argument("--width", type=int, default=4096)
     r.add_argument("--parts", type=int, default=9)
+    r.add_argument("--bf16-delta", action="store_true", help="add a bfloat16 delta (a product's output) instead of float32 partial sums")
     a = ap.parse_args(argv)
     global USE_GRAPH
     USE_GRAPH = not a.no_graph

@@ -61,17 +61,26 @@ def test_rmsnorm_plain_delta_parts_rows(width, out_dtype):
     assert torch.allclose(x.double().cpu(), want_x, atol=1e-5, rtol=1e-6)
 
 
-def test_rmsnorm_row_does_not_depend_on_the_batch():
+@pytest.mark.parametrize("width", [777, 1500, 4096, 5000, 9000, 20000])
+def test_rmsnorm_row_does_not_depend_on_the_batch(width):
+    """A row among many (a block per row) and the same row alone (spread over a cluster when it
+    is wide) come out with the same bits, with and without partial sums added first."""
     from lgml_b200 import ops
 
     torch.manual_seed(0)
-    w = torch.rand(777, device=DEV) + 0.5
-    x = torch.randn(9, 777, device=DEV)
-    a = torch.empty(9, 777, device=DEV)
-    b = torch.empty(1, 777, device=DEV)
+    w = torch.rand(width, device=DEV) + 0.5
+    x = torch.randn(100, width, device=DEV)
+    a = torch.empty(100, width, device=DEV)
+    b = torch.empty(1, width, device=DEV)
     ops.rmsnorm(x.clone(), w, 1e-5, a)
-    ops.rmsnorm(x[4:5].clone(), w, 1e-5, b)
-    assert torch.equal(a[4], b[0])
+    ops.rmsnorm(x[41:42].clone(), w, 1e-5, b)
+    assert torch.equal(a[41], b[0])
+    parts = torch.randn(5, 100, width, device=DEV)
+    bias = torch.randn(width, device=DEV)
+    xa, xb = x.clone(), x[41:42].clone()
+    ops.rmsnorm(xa, w, 1e-5, a, delta=ops.Partials(parts, bias))
+    ops.rmsnorm(xb, w, 1e-5, b, delta=ops.Partials(parts[:, 41:42].contiguous(), bias))
+    assert torch.equal(a[41], b[0]) and torch.equal(xa[41], xb[0])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
