@@ -116,6 +116,34 @@ __device__ __forceinline__ void store_quad(__nv_bfloat16 *p, int i, int c1, bool
     }
 }
 
+// Four elements as they lie in memory, for loads that are all issued before any is used: a
+// bfloat16 quad then waits in two registers, not four.
+template <typename T> struct RawQuad;
+template <> struct RawQuad<float> {
+    float v[PER];
+    __device__ __forceinline__ void load(const float *p, int i, int c1, bool vec) { load_quad(p, i, c1, vec, v); }
+    __device__ __forceinline__ void get(float (&o)[PER]) const {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) o[e] = v[e];
+    }
+};
+template <> struct RawQuad<__nv_bfloat16> {
+    __nv_bfloat162 lo, hi;
+    __device__ __forceinline__ void load(const __nv_bfloat16 *p, int i, int c1, bool vec) {
+        if (vec && i + PER <= c1) {
+            const float2 raw = act_load(reinterpret_cast<const float2 *>(p + i));
+            lo = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+        } else {
+            const __nv_bfloat16 z = __float2bfloat16_rn(0.f);
+            lo.x = i < c1 ? act_load(p + i) : z, lo.y = i + 1 < c1 ? act_load(p + i + 1) : z;
+            hi.x = i + 2 < c1 ? act_load(p + i + 2) : z, hi.y = i + 3 < c1 ? act_load(p + i + 3) : z;
+        }
+    }
+    __device__ __forceinline__ void get(float (&o)[PER]) const {
+        o[0] = __bfloat162float(lo.x), o[1] = __bfloat162float(lo.y), o[2] = __bfloat162float(hi.x), o[3] = __bfloat162float(hi.y);
+    }
+};
+
 struct Args {
     float *x;
     const void *delta;
@@ -181,40 +209,36 @@ __global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
     if (dr) {
         // every load of the delta's first part next (no store lies between them), then the
         // other parts in order, the bias, and the sums back to x
-        float d[SLICES][ROUNDS][PER];
+        RawQuad<TD> d0[SLICES][ROUNDS];
 #pragma unroll
         for (int k = 0; k < SLICES; ++k)
 #pragma unroll
             for (int rd = 0; rd < ROUNDS; ++rd) {
                 const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
-                load_quad(dr, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec, d[k][rd]);
+                d0[k][rd].load(dr, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec);
             }
-        for (int p = 1; p < a.n_parts; ++p) {
-#pragma unroll
-            for (int k = 0; k < SLICES; ++k)
-#pragma unroll
-                for (int rd = 0; rd < ROUNDS; ++rd) {
-                    const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
-                    float e[PER];
-                    load_quad(dr + (size_t)p * a.part_stride, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec, e);
-#pragma unroll
-                    for (int q = 0; q < PER; ++q) d[k][rd][q] += e[q];
-                }
-        }
 #pragma unroll
         for (int k = 0; k < SLICES; ++k)
 #pragma unroll
             for (int rd = 0; rd < ROUNDS; ++rd) {
                 const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
                 const int i = (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt;
+                float d[PER];
+                d0[k][rd].get(d);
+                for (int p = 1; p < a.n_parts; ++p) {
+                    float e[PER];
+                    load_quad(dr + (size_t)p * a.part_stride, i, c1, a.vec, e);
+#pragma unroll
+                    for (int q = 0; q < PER; ++q) d[q] += e[q];
+                }
                 if (a.delta_bias) {
                     float bq[PER];
                     load_quad_const(a.delta_bias, i, c1, a.vec, bq);
 #pragma unroll
-                    for (int q = 0; q < PER; ++q) d[k][rd][q] += bq[q];
+                    for (int q = 0; q < PER; ++q) d[q] += bq[q];
                 }
 #pragma unroll
-                for (int q = 0; q < PER; ++q) v[k][rd][q] += d[k][rd][q];
+                for (int q = 0; q < PER; ++q) v[k][rd][q] += d[q];
                 if (!a.rows) store_quad(xr, i, c1, a.vec, v[k][rd]);
             }
     }
