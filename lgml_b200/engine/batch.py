@@ -19,6 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -58,17 +59,14 @@ class StepBatch:
         self.max_kv_len = max(self.kv_lens) if lens else 0
         self.decode_splits = None       # a fixed split count (set by a captured graph)
         self._tiles = {}
+        self.after_staged_copy = None   # called after a later copy out of the pinned buffer (its owner marks the buffer busy again)
 
-        flat: List[int] = []
-        for t in tokens:
-            flat.extend(int(v) for v in t)
-        positions: List[int] = []
-        seq_of: List[int] = []
-        starts = [0]
-        for s, (p0, n) in enumerate(zip(self.pos0, lens)):
-            positions.extend(range(p0, p0 + n))
-            seq_of.extend([s] * n)
-            starts.append(starts[-1] + n)
+        # Everything below is array arithmetic: a prompt portion brings thousands of tokens, and a
+        # Python loop over them would cost as much as the step's first layers.
+        tok_arrays = [np.asarray(t, dtype=np.int64).reshape(-1) for t in tokens]
+        lens_a = np.asarray(lens, dtype=np.int64)
+        starts = np.zeros(S + 1, dtype=np.int64)
+        np.cumsum(lens_a, out=starts[1:])
         rows: List[int] = []
         self.rows_of_seq: List[List[int]] = []
         for s, w in enumerate(want):
@@ -77,7 +75,7 @@ class StepBatch:
                 if not 0 <= i < lens[s]:
                     raise IndexError(f"wanted place {i} is outside the {lens[s]} tokens request {self.requests[s].id!r} brings")
                 mine.append(len(rows))
-                rows.append(starts[s] + int(i))
+                rows.append(int(starts[s]) + int(i))
             self.rows_of_seq.append(mine)
         self.n_rows = len(rows)
 
@@ -85,14 +83,38 @@ class StepBatch:
         for g in range(len(cm.groups)):
             tables.append(cm.block_table_rows(self.requests, g, table_widths[g] if table_widths else None))
         self.table_width = [len(t[0]) if t else 1 for t in tables]
-        parts = [flat, positions, seq_of, starts, self.pos0, [r.slot for r in self.requests], self.kv_lens, rows or [0]]
-        for t in tables:
-            parts.append([p for row in t for p in row])
-        total = sum(len(p) for p in parts)
-        host = torch.tensor([v for p in parts for v in p], dtype=torch.int32)
+        n_rows_field = max(len(rows), 1)
+        total = 3 * N + (S + 1) + 3 * S + n_rows_field + S * sum(self.table_width)
         if pinned is not None and pinned.numel() >= total:
-            pinned[:total].copy_(host)
             host = pinned[:total]
+            self._pinned, self._pinned_used = pinned, total
+        else:
+            host = torch.empty(total, dtype=torch.int32)
+            self._pinned, self._pinned_used = None, 0
+        h = host.numpy()
+        seq_of = np.repeat(np.arange(S, dtype=np.int64), lens_a)
+        off = 0
+        h[off:off + N] = np.concatenate(tok_arrays) if S else 0
+        off += N
+        # position of token j of request s: its first position + j
+        h[off:off + N] = np.asarray(self.pos0, dtype=np.int64)[seq_of] + (np.arange(N, dtype=np.int64) - starts[seq_of]) if N else 0
+        off += N
+        h[off:off + N] = seq_of
+        off += N
+        h[off:off + S + 1] = starts
+        off += S + 1
+        h[off:off + S] = self.pos0
+        off += S
+        h[off:off + S] = [r.slot for r in self.requests]
+        off += S
+        h[off:off + S] = self.kv_lens
+        off += S
+        h[off:off + n_rows_field] = rows or [0]
+        off += n_rows_field
+        for t, w in zip(tables, self.table_width):
+            if S:
+                h[off:off + S * w] = np.asarray(t, dtype=np.int64).reshape(-1)
+            off += S * w
         if device_buffer is not None:
             if device_buffer.numel() < total:
                 raise ValueError("the step's description does not fit the buffer kept for it")
@@ -136,8 +158,22 @@ class StepBatch:
                     rows.append((s, start + t0, min(tile_tokens, n - t0), self.pos0[s] + min(t0 + tile_tokens, n)))
                 start += n
             rows.sort(key=lambda r: -r[3])
-            rows = [(s, r0, nt, 0) for s, r0, nt, _ in rows]
-            cached = torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(self.token_ids.device)
+            arr = np.asarray(rows, dtype=np.int32).reshape(-1, 4)
+            arr[:, 3] = 0
+            n_ints = arr.size
+            dev = self.token_ids.device
+            if self._pinned is not None and self._pinned.numel() >= self._pinned_used + n_ints:
+                # the rest of the step's staging buffer: no copy has to wait for pageable memory
+                stage = self._pinned[self._pinned_used:self._pinned_used + n_ints]
+                self._pinned_used += n_ints
+                stage.numpy()[:] = arr.reshape(-1)
+                cached = torch.empty(n_ints, dtype=torch.int32, device=dev)
+                cached.copy_(stage, non_blocking=True)
+                cached = cached.view(-1, 4)
+                if self.after_staged_copy is not None:
+                    self.after_staged_copy()
+            else:
+                cached = torch.from_numpy(arr).to(dev)
             self._tiles[tile_tokens] = cached
         return cached
 

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 from typing import Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager, PoolFull, Request
@@ -83,6 +84,12 @@ class ModelRunner:
         model.bind(tensors, rt)
         return cls(model, rt, **kw)
 
+    @staticmethod
+    def _mark_busy(stage) -> None:
+        """The copies out of this staging buffer queued so far must run before it is written again."""
+        stage[1] = torch.cuda.Event()
+        stage[1].record()
+
     # ---- requests ----------------------------------------------------------------------
     def open(self, rid: Hashable) -> Request:
         return self.cache.open(rid)
@@ -105,9 +112,15 @@ class ModelRunner:
             seen.add(id(req))
             if len(tokens) == 0:
                 raise StepError(f"request {req.id!r} brings no tokens")
-            for t in tokens:
-                if not 0 <= int(t) < vocab:
-                    raise StepError(f"request {req.id!r}: token id {t} is outside the vocabulary of {vocab}")
+            if len(tokens) > 16:
+                arr = np.asarray(tokens, dtype=np.int64)
+                bad = np.nonzero((arr < 0) | (arr >= vocab))[0]
+                if bad.size:
+                    raise StepError(f"request {req.id!r}: token id {int(arr[bad[0]])} is outside the vocabulary of {vocab}")
+            else:
+                for t in tokens:
+                    if not 0 <= int(t) < vocab:
+                        raise StepError(f"request {req.id!r}: token id {t} is outside the vocabulary of {vocab}")
             for i in want:
                 if not 0 <= int(i) < len(tokens):
                     raise StepError(f"request {req.id!r}: wanted place {i} is outside the {len(tokens)} tokens it brings")
@@ -131,8 +144,8 @@ class ModelRunner:
         else:
             batch = StepBatch(self.cache, [e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries],
                               self.rt.device, stage[0])
-            stage[1] = torch.cuda.Event()
-            stage[1].record()
+            self._mark_busy(stage)
+            batch.after_staged_copy = lambda: self._mark_busy(stage)
             self.last_batch = batch
             logits = self.model.forward(self.rt, batch)
         for req, tokens, _ in entries:
