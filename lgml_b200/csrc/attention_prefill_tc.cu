@@ -10,14 +10,17 @@
 //              sum in float32 (base-2 exponentials), writes P as bfloat16 to shared memory
 //     O_page[128, D] = P[128, 64] . V_page[64, D]    tcgen05.mma (V is the N-major B operand)
 //     O = O * correction + O_page                    in registers, 8 warps x 64 columns
-// Q, K, V and P sit in shared memory in the 128-byte-swizzled layout the tensor core reads;
-// pages are copied with cp.async (K two pages ahead, V one), so copies overlap the math.  The
-// scores of page i+1 are issued right behind the P V product of page i, into a second S
-// buffer, so they are ready when the output of page i has been added up; and two CTAs share
-// an SM so that one's products overlap the other's softmax.  Keys are taken
-// from the cache, so this step's own keys are seen at cache precision, as in mischief/lgml,
-// which writes the cache before attention reads it (lua/lgml/transformer.lua:1838-1839,
-// :2405-2407; formula :1805-1816, scale :1845).  Waits on mbarriers are bounded.
+// Q, K, V and P sit in shared memory in the 128-byte-swizzled layout the tensor core reads.
+// The 8 warps have two roles.  Warps 0-3 do the softmax (one thread per row).  Warps 4-7 copy
+// the pages with cp.async (K two pages ahead, V one) and their first thread issues the
+// products: the scores of page i+1 go right behind the P V product of page i, into a second S
+// buffer, so they are ready when the output of page i has been added up.  All 8 warps add the
+// page's output to the running one (each thread half the columns of its row).  Two CTAs share
+// an SM, so that one's products overlap the other's softmax.  CTAs are started with the longest
+// tiles first (the caller orders them).  Keys are taken from the cache, so this step's own
+// keys are seen at cache precision, as in mischief/lgml, which writes the cache before
+// attention reads it (lua/lgml/transformer.lua:1838-1839, :2405-2407; formula :1805-1816,
+// scale :1845).  Waits on mbarriers are bounded.
 #include <math.h>
 
 #include "common.cuh"
@@ -29,14 +32,20 @@ constexpr int PAGE = 64;
 constexpr int ROWS = 128;            // query rows per CTA = UMMA M
 constexpr int THREADS = 256;
 constexpr uint32_t SPIN_LIMIT = 4u << 20;
+constexpr uint32_t WAIT_HINT_NS = 2000;
 constexpr int STATUS_TIMEOUT = 12;
 constexpr uint32_t TMEM_COLS = 256;  // S of even pages: columns 0..63, O_page: 64..64+DP-1, S of odd pages: 192..255
 constexpr uint32_t O_COL = 64, S1_COL = 192;
+constexpr int LOADERS = 128;         // threads of warps 4-7, which copy the pages
+constexpr int ISSUER = 128;          // the thread that issues the tensor-core products (first of warp 4)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool valid) {
     const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void st_shared_16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -50,9 +59,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS) : "memory");   // the thread may sleep up to the hint; it wakes when the phase completes
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
@@ -138,8 +147,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     extern __shared__ uint8_t smem_raw[];
     uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *Qs = base, *Ks = Qs + Q_BYTES, *Vs = Ks + 2 * K_BYTES, *Ps = Vs + V_BYTES;
-    float *corr_s = reinterpret_cast<float *>(Ps + P_BYTES);   // [128] this page's correction of the running output
-    float *l_s = corr_s + ROWS;                                 // [128] final sums
+    // [2][128] the page's correction of the running output, by the page's parity: a softmax warp
+    // may be a page ahead of the warp that still adds up the page before
+    float *corr_s = reinterpret_cast<float *>(Ps + P_BYTES);
+    float *l_s = corr_s + 2 * ROWS;                             // [128] final sums
     __shared__ uint64_t s_bar, o_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
@@ -177,18 +188,51 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     const uint32_t tmem_base = tmem_base_s;
 
     // ---- page copies ------------------------------------------------------------------------------
+    // A page of one head is PAGE rows of chunks_d 16-byte chunks; loader thread l copies chunks l,
+    // l + LOADERS, ...  Row and chunk of its first one are worked out once, the later ones
+    // follow by addition (no division in the loop over pages).
+    const int ltid = tid - LOADERS;                               // index among the loader threads (warps 4-7)
+    const int row_first = ltid / chunks_d, ch_first = ltid - row_first * chunks_d;
+    const int row_step = LOADERS / chunks_d, ch_step = LOADERS - row_step * chunks_d;
+    // When the chunks of a row divide the loader threads, a thread keeps its chunk and moves down
+    // row_step rows (a multiple of 8) each time: both addresses advance by constants.
+    const bool linear = ch_step == 0;
+    const uint32_t dst_first = (uint32_t)(ch_first >> 3) * (PAGE * 128) + swz(row_first, ch_first & 7);
+    const int src_first = row_first * D + ch_first * 8;
+    auto copy_page = [&](uint32_t dst, const __nv_bfloat16 *src, int valid_rows) {
+        if (linear) {
+            uint32_t d = dst + dst_first;
+            const __nv_bfloat16 *sp = src + src_first;
+            const uint32_t d_step = (uint32_t)row_step * 128;
+            const int s_step = row_step * D;
+#pragma unroll 4
+            for (int row = row_first; row < PAGE; row += row_step) {
+                cp_async_16(d, sp, row < valid_rows);
+                d += d_step;
+                sp += s_step;
+            }
+            return;
+        }
+        int row = row_first, ch = ch_first;
+        while (row < PAGE) {
+            cp_async_16(dst + (ch >> 3) * (PAGE * 128) + swz(row, ch & 7), src + row * D + ch * 8, row < valid_rows);
+            row += row_step;
+            ch += ch_step;
+            if (ch >= chunks_d) {
+                ch -= chunks_d;
+                ++row;
+            }
+        }
+    };
     auto load_k = [&](int it) {
         const int pg = pg_lo + it, stage = it & 1;
         const int page = table[pg];
         const bool have = page >= 0 && page < n_pages;
-        if (tid == 0 && !have) atomicExch(status, 3);
+        if (ltid == 0 && !have) atomicExch(status, 3);
         const int valid_rows = have ? min(pos_last - pg * PAGE + 1, PAGE) : 0;   // rows past the last key become zero
         const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
         const uint32_t dst = smem_u32(Ks + stage * K_BYTES);
-        for (int c = tid; c < PAGE * chunks_d; c += THREADS) {
-            const int row = c / chunks_d, ch = c - row * chunks_d;
-            cp_async_16(dst + (ch >> 3) * (PAGE * 128) + swz(row, ch & 7), k_pages + off + (size_t)row * D + ch * 8, row < valid_rows);
-        }
+        copy_page(dst, k_pages + off, valid_rows);
     };
     auto load_v = [&](int it) {
         const int pg = pg_lo + it;
@@ -197,20 +241,18 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         const int valid_rows = have ? min(pos_last - pg * PAGE + 1, PAGE) : 0;
         const size_t off = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE * D;
         const uint32_t dst = smem_u32(Vs);
-        for (int c = tid; c < PAGE * chunks_d; c += THREADS) {
-            const int row = c / chunks_d, ch = c - row * chunks_d;
-            cp_async_16(dst + (ch >> 3) * (PAGE * 128) + swz(row, ch & 7), v_pages + off + (size_t)row * D + ch * 8, row < valid_rows);
-        }
+        copy_page(dst, v_pages + off, valid_rows);
     };
     // The positions, tiles and block tables come from the host; everything else this kernel reads
     // (queries, this step's keys and values) is written by the kernels ahead of it.
     pdl_wait();
-    load_k(0);
-    cp_async_commit();
-    load_v(0);
-    cp_async_commit();
-    if (n_iter > 1) load_k(1);
-    cp_async_commit();
+    const bool loader = warp >= 4;            // warps 4-7 copy the pages; warps 0-3 do the softmax
+    if (loader) {
+        load_k(0);
+        load_v(0);
+        if (n_iter > 1) load_k(1);
+        cp_async_commit();
+    }
     // queries: row r = token (r / hpc), head g0 + (r % hpc); through L2, they were just written
     for (int c = tid; c < ROWS * chunks_d; c += THREADS) {
         const int r = c / chunks_d, ch = c - r * chunks_d;
@@ -251,10 +293,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     // Q and K(0) have landed: the first scores; later ones are issued a page ahead, behind the
     // P V product of the page before, so that the tensor core has them ready when the softmax
     // of that page is done.
-    cp_async_wait<2>();
+    cp_async_wait<0>();
     fence_async_smem();
     __syncthreads();
-    if (tid == 0) {
+    if (tid == ISSUER) {
         tcgen05_fence_after();
         issue_qk(0);
     }
@@ -262,16 +304,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     for (int it = 0; it < n_iter; ++it) {
         const int stage = it & 1, pg = pg_lo + it, key0 = pg * PAGE;
         const uint32_t s_col = stage ? S1_COL : 0u;
-        if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
-        tcgen05_fence_after();
-        // the scores of this page are done, so its keys' stage is free: the keys of the page after the next
-        if (it + 2 < n_iter) load_k(it + 2);
-        cp_async_commit();
 
         // ---- softmax: warps 0-3, one thread per row -----------------------------------------------------
-        if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
-        tcgen05_fence_after();
         if (warp < 4) {
+            if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
+            tcgen05_fence_after();
             const int page_id = table[pg];
             const bool have = page_id >= 0 && page_id < n_pages;
             // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A page that lies wholly
@@ -306,38 +343,59 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;      // keeps (-inf) - (-inf) out of the exponent
             m_run = m_new;
             float sum = 0.f;
+            const uint32_t p_row = smem_u32(Ps) + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);   // this row of P
+            const uint32_t p_xor = (uint32_t)(row & 7);
+            if (edge) {
 #pragma unroll
-            for (int c0 = 0; c0 < PAGE; c0 += 16) {
-                uint32_t r[16];
-                tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
-                tcgen05_wait_ld();
-                uint32_t packed[8];
+                for (int c0 = 0; c0 < PAGE; c0 += 16) {
+                    uint32_t r[16];
+                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
+                    tcgen05_wait_ld();
+                    uint32_t packed[8];
 #pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    float p0 = ex2(fmaf(__uint_as_float(r[j]), scale_log2, -m_sub));
-                    float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_sub));
-                    if (edge) {
+                    for (int j = 0; j < 16; j += 2) {
+                        float p0 = ex2(fmaf(__uint_as_float(r[j]), scale_log2, -m_sub));
+                        float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_sub));
                         if (c0 + j > c_hi || c0 + j < c_lo) p0 = 0.f;
                         if (c0 + j + 1 > c_hi || c0 + j + 1 < c_lo) p1 = 0.f;
+                        sum += p0 + p1;
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
-                    sum += p0 + p1;
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                    packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                    // 16 keys = two 16-byte chunks of this row of P
+                    st_shared_16(p_row + ((((uint32_t)(c0 >> 3)) ^ p_xor) << 4), packed[0], packed[1], packed[2], packed[3]);
+                    st_shared_16(p_row + ((((uint32_t)(c0 >> 3) + 1) ^ p_xor) << 4), packed[4], packed[5], packed[6], packed[7]);
                 }
-                // 16 keys = two 16-byte chunks of this row of P
-                *reinterpret_cast<uint4 *>(Ps + swz(row, (c0 >> 3))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                *reinterpret_cast<uint4 *>(Ps + swz(row, (c0 >> 3) + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+                const float neg_m = -m_sub;
+#pragma unroll
+                for (int c0 = 0; c0 < PAGE; c0 += 16) {
+                    uint32_t r[16];
+                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
+                    tcgen05_wait_ld();
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(r[j]), scale_log2, neg_m));
+                        const float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale_log2, neg_m));
+                        sum += p0 + p1;
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                    }
+                    st_shared_16(p_row + ((((uint32_t)(c0 >> 3)) ^ p_xor) << 4), packed[0], packed[1], packed[2], packed[3]);
+                    st_shared_16(p_row + ((((uint32_t)(c0 >> 3) + 1) ^ p_xor) << 4), packed[4], packed[5], packed[6], packed[7]);
+                }
             }
             l_run = l_run * corr + sum;
-            corr_s[row] = corr;
+            corr_s[stage * ROWS + row] = corr;
         }
-        // V(it) and K(it+1) have landed (K(it+2) may still be in flight); P is written
-        cp_async_wait<1>();
+        // V(it) and K(it+1) have landed (the loaders wait for their copies); P is written
+        cp_async_wait<0>();
         fence_async_smem();
         tcgen05_fence_before();
         __syncthreads();
-        // ---- O_page = P V ------------------------------------------------------------------------------
-        if (tid == 0) {
+        // ---- O_page = P V, and the scores of the next page behind it ------------------------------------
+        if (tid == ISSUER) {
             tcgen05_fence_after();
             const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs);
 #pragma unroll
@@ -350,14 +408,19 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             tcgen05_commit(&o_bar);
             if (it + 1 < n_iter) issue_qk(it + 1);
         }
+        // The softmax warps saw the scores of this page before the barrier above, so its keys' stage
+        // is free: the keys of the page after the next.
+        if (loader && it + 2 < n_iter) load_k(it + 2);
         if (alive && !mbar_wait(&o_bar, it & 1, abort_flag, status)) alive = false;
         tcgen05_fence_after();
         // the values' stage is free: the next page of values
-        if (it + 1 < n_iter) load_v(it + 1);
-        cp_async_commit();
+        if (loader) {
+            if (it + 1 < n_iter) load_v(it + 1);
+            cp_async_commit();
+        }
         // ---- O = O * correction + O_page, 8 warps x HALF columns -------------------------------------------
         {
-            const float corr = corr_s[row];
+            const float corr = corr_s[stage * ROWS + row];
 #pragma unroll
             for (int c0 = 0; c0 < HALF; c0 += 16) {
                 uint32_t r[16];
@@ -404,7 +467,7 @@ int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, con
            const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D,
            int hpc, float scale, int window, int *status, cudaStream_t stream) {
     constexpr int KB = DP / 64;
-    const size_t smem = (size_t)KB * ROWS * 128 + 3 * (size_t)KB * PAGE * 128 + ROWS * 128 + 2 * ROWS * sizeof(float) + 1024;
+    const size_t smem = (size_t)KB * ROWS * 128 + 3 * (size_t)KB * PAGE * 128 + ROWS * 128 + 3 * ROWS * sizeof(float) + 1024;
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) LGML_FAIL("prefill_attention_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     lgml_launch(prefill_attention_tc_kernel<DP>, grid, THREADS, smem, stream, q, ldq, positions, tiles, block_table, max_blocks, k_pages,
