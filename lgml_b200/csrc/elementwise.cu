@@ -182,7 +182,9 @@ __device__ __forceinline__ void add_delta(const Args &a, float *xr, const TD *dr
 
 // SLICES = 1: this block holds one slice (its cluster rank, or the whole of a narrow row);
 // SLICES = MAX_CS: it holds all slices of its row.  ROUNDS rounds of a slice stay in registers.
-template <typename TD, typename TO, int ROUNDS, int SLICES, bool CLUSTERED>
+// FULL: every slice is exactly ROUNDS rounds of whole quads and 16-byte accesses are allowed, so
+// no access needs a test (the usual case: widths that are multiples of 512 x slices).
+template <typename TD, typename TO, int ROUNDS, int SLICES, bool CLUSTERED, bool FULL>
 __global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
     pdl_trigger();
     pdl_wait();
@@ -192,20 +194,21 @@ __global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
     const int gt = threadIdx.x, cs = a.cs, width = a.width;
     const int r = CLUSTERED ? blockIdx.x / cs : blockIdx.x;
     const int rank0 = CLUSTERED ? blockIdx.x - r * cs : 0;
-    const int per_cta = ((width + cs - 1) / cs + 3) & ~3;
+    const int per_cta = FULL ? ROUNDS * PER * GROUP : (((width + cs - 1) / cs + 3) & ~3);
     const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
     float *xr = a.x + src * width;
     const TD *dr = a.delta ? reinterpret_cast<const TD *>(a.delta) + src * width : nullptr;
-    const int n_slices = CLUSTERED ? 1 : cs;
+    const int n_slices = (CLUSTERED || FULL) ? SLICES : cs;
+    const bool vec = FULL ? true : (a.vec != 0);
+    // first element of (slice k, round rd) of this thread, and the end of slice k
+    auto first = [&](int k, int rd) { return (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt; };
+    auto end = [&](int k) { return FULL ? (1 << 30) : (k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0); };
     float v[SLICES][ROUNDS][PER];
     // every load of x first
 #pragma unroll
     for (int k = 0; k < SLICES; ++k)
 #pragma unroll
-        for (int rd = 0; rd < ROUNDS; ++rd) {
-            const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
-            load_quad(xr, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec, v[k][rd]);
-        }
+        for (int rd = 0; rd < ROUNDS; ++rd) load_quad(xr, first(k, rd), end(k), vec, v[k][rd]);
     if (dr) {
         // every load of the delta's first part next (no store lies between them), then the
         // other parts in order, the bias, and the sums back to x
@@ -213,33 +216,29 @@ __global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
 #pragma unroll
         for (int k = 0; k < SLICES; ++k)
 #pragma unroll
-            for (int rd = 0; rd < ROUNDS; ++rd) {
-                const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
-                d0[k][rd].load(dr, (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt, c1, a.vec);
-            }
+            for (int rd = 0; rd < ROUNDS; ++rd) d0[k][rd].load(dr, first(k, rd), end(k), vec);
 #pragma unroll
         for (int k = 0; k < SLICES; ++k)
 #pragma unroll
             for (int rd = 0; rd < ROUNDS; ++rd) {
-                const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
-                const int i = (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt;
+                const int c1 = end(k), i = first(k, rd);
                 float d[PER];
                 d0[k][rd].get(d);
                 for (int p = 1; p < a.n_parts; ++p) {
                     float e[PER];
-                    load_quad(dr + (size_t)p * a.part_stride, i, c1, a.vec, e);
+                    load_quad(dr + (size_t)p * a.part_stride, i, c1, vec, e);
 #pragma unroll
                     for (int q = 0; q < PER; ++q) d[q] += e[q];
                 }
                 if (a.delta_bias) {
                     float bq[PER];
-                    load_quad_const(a.delta_bias, i, c1, a.vec, bq);
+                    load_quad_const(a.delta_bias, i, c1, vec, bq);
 #pragma unroll
                     for (int q = 0; q < PER; ++q) d[q] += bq[q];
                 }
 #pragma unroll
                 for (int q = 0; q < PER; ++q) v[k][rd][q] += d[q];
-                if (!a.rows) store_quad(xr, i, c1, a.vec, v[k][rd]);
+                if (!a.rows) store_quad(xr, i, c1, vec, v[k][rd]);
             }
     }
 #pragma unroll
@@ -272,14 +271,13 @@ __global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
     for (int k = 0; k < SLICES; ++k)
 #pragma unroll
         for (int rd = 0; rd < ROUNDS; ++rd) {
-            const int c1 = k < n_slices ? min(width, (rank0 + k + 1) * per_cta) : 0;
-            const int i = (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt;
+            const int c1 = end(k), i = first(k, rd);
             if (i < c1) {
                 float w[PER], y[PER];
-                load_quad_const(a.weight, i, c1, a.vec, w);
+                load_quad_const(a.weight, i, c1, vec, w);
 #pragma unroll
                 for (int q = 0; q < PER; ++q) y[q] = v[k][rd][q] * inv * w[q];
-                store_quad(orow, i, c1, a.vec, y);
+                store_quad(orow, i, c1, vec, y);
             }
         }
     if (CLUSTERED) cg::this_cluster().sync();     // no CTA leaves while another may still read its slice's sum
@@ -339,20 +337,26 @@ static int rmsnorm_launch(const rms::Args &a, int n_rows, cudaStream_t stream) {
     const int rounds = (per_cta + PER * GROUP - 1) / (PER * GROUP);
     const bool clustered = cs > 1 && n_rows <= 64;              // many rows fill the GPU without clusters
     cudaError_t e = cudaSuccess;
+    // whole quads everywhere: each slice is exactly `rounds` rounds, 16-byte accesses allowed
+    const bool full = a.vec && per_cta * cs == a.width && per_cta == rounds * PER * GROUP;
     if (clustered && rounds <= 4) {
         const int blocks = n_rows * cs;
-        switch (rounds) {
-            case 1: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
-            case 2: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
-            case 3: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 3, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
-            default: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 4, 1, true>, blocks, GROUP, 0, stream, cs, a); break;
+        if (full && rounds == 1) e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, true, true>, blocks, GROUP, 0, stream, cs, a);
+        else if (full && rounds == 2) e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, true, true>, blocks, GROUP, 0, stream, cs, a);
+        else switch (rounds) {
+            case 1: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
+            case 2: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
+            case 3: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 3, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
+            default: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 4, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
         }
     } else if (cs == 1 && rounds <= 2) {
-        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, false>, n_rows, GROUP, 0, stream, a);
-        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, 1, false>, n_rows, GROUP, 0, stream, a);
+        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, false, false>, n_rows, GROUP, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, 1, false, false>, n_rows, GROUP, 0, stream, a);
+    } else if (cs == MAX_CS && full && rounds == 1) {
+        e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, false, true>, n_rows, GROUP, 0, stream, a);
     } else if (cs > 1 && rounds <= 2) {
-        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, false>, n_rows, GROUP, 0, stream, a);
-        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, MAX_CS, false>, n_rows, GROUP, 0, stream, a);
+        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, false, false>, n_rows, GROUP, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, MAX_CS, false, false>, n_rows, GROUP, 0, stream, a);
     } else {
         e = lgml_launch(rmsnorm_any_kernel<TD, TO>, n_rows, GROUP, 0, stream, a);
     }
