@@ -3,7 +3,8 @@
 //
 // Both operands are row-major with K contiguous ("K-major"), which is how activations
 // x[tokens, K] and weights w[features, K] lie in memory, so y = x . w^T needs no transpose:
-//   * many tokens (prefill):  A = x (128 tokens per tile), B = w (BN features per tile);
+//   * many tokens (prefill):  A = x (128 tokens per tile), B = w (BN features per tile); from
+//     512 tokens on, two CTAs share a 256 x 256 tile (tcgen05.mma.cta_group::2, below);
 //   * few tokens (decode):    A = w (128 features per tile), B = x (all tokens, padded to
 //     BN), and the tile in TMEM is y^T, which the epilogue writes transposed.  The product
 //     is then a stream of weights through the tensor core at HBM speed; to fill all SMs the
@@ -137,6 +138,69 @@ struct Params {
     const float *bias;        // per feature, or null (only when there is no split)
     int *status;
 };
+
+// One thread's 16 consecutive features f0 .. f0 + 15 of token row a_row (tile row = token,
+// tile column = feature): bias, the gated activation if asked for, and the store.
+__device__ __forceinline__ void store_run(const Params &p, int a_row, int f0, const uint32_t (&r)[16], float *out_f, __nv_bfloat16 *out_h,
+                                          bool f32) {
+    if (a_row < p.rows_a) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + ((p.bias && f0 + j < p.rows_b) ? p.bias[f0 + j] : 0.f);
+        if (p.swiglu) {
+            // columns 2j and 2j+1 are the gate and the up of feature (f0 / 2) + j
+            const size_t o = (size_t)a_row * p.ldo + (f0 >> 1);
+            float act[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) act[j] = v[2 * j] / (1.0f + expf(-v[2 * j])) * v[2 * j + 1];
+            if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0 && !f32) {
+                uint32_t h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
+                    h[j] = *reinterpret_cast<uint32_t *>(&pr);
+                }
+                *reinterpret_cast<uint4 *>(out_h + o) = make_uint4(h[0], h[1], h[2], h[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (f0 + 2 * j + 1 < p.rows_b) {
+                        if (f32) out_f[o + j] = act[j];
+                        else out_h[o + j] = __float2bfloat16_rn(act[j]);
+                    }
+                }
+            }
+        } else {
+            const size_t o = (size_t)a_row * p.ldo + f0;
+            if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0) {
+                // whole run in range and 16-byte aligned (f0 is a multiple of 16): vector stores
+                if (f32) {
+                    float4 *dst = reinterpret_cast<float4 *>(out_f + o);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    uint32_t h[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        __nv_bfloat162 pr = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                        h[j] = *reinterpret_cast<uint32_t *>(&pr);
+                    }
+                    uint4 *dst = reinterpret_cast<uint4 *>(out_h + o);
+                    dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                    dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (f0 + j < p.rows_b) {
+                        if (f32) out_f[o + j] = v[j];
+                        else out_h[o + j] = __float2bfloat16_rn(v[j]);
+                    }
+                }
+            }
+        }
+    }
+}
 
 template <int BN>
 struct Smem {
@@ -323,65 +387,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                         }
                     }
                 } else {
-                    // tile row = token (a_row), tile column = feature: 16 consecutive features per thread
-                    if (a_row < p.rows_a) {
-                        const int f0 = tile_b * BN + c0;
-                        float v[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + ((p.bias && f0 + j < p.rows_b) ? p.bias[f0 + j] : 0.f);
-                        if (p.swiglu) {
-                            // columns 2j and 2j+1 are the gate and the up of feature (f0 / 2) + j
-                            const size_t o = (size_t)a_row * p.ldo + (f0 >> 1);
-                            float act[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) act[j] = v[2 * j] / (1.0f + expf(-v[2 * j])) * v[2 * j + 1];
-                            if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0 && !f32) {
-                                uint32_t h[4];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    __nv_bfloat162 pr = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
-                                    h[j] = *reinterpret_cast<uint32_t *>(&pr);
-                                }
-                                *reinterpret_cast<uint4 *>(out_h + o) = make_uint4(h[0], h[1], h[2], h[3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    if (f0 + 2 * j + 1 < p.rows_b) {
-                                        if (f32) out_f[o + j] = act[j];
-                                        else out_h[o + j] = __float2bfloat16_rn(act[j]);
-                                    }
-                                }
-                            }
-                        } else {
-                            const size_t o = (size_t)a_row * p.ldo + f0;
-                            if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0) {
-                                // whole run in range and 16-byte aligned (f0 is a multiple of 16): vector stores
-                                if (f32) {
-                                    float4 *dst = reinterpret_cast<float4 *>(out_f + o);
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                                } else {
-                                    uint32_t h[8];
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) {
-                                        __nv_bfloat162 pr = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                        h[j] = *reinterpret_cast<uint32_t *>(&pr);
-                                    }
-                                    uint4 *dst = reinterpret_cast<uint4 *>(out_h + o);
-                                    dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
-                                    dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 16; ++j) {
-                                    if (f0 + j < p.rows_b) {
-                                        if (f32) out_f[o + j] = v[j];
-                                        else out_h[o + j] = __float2bfloat16_rn(v[j]);
-                                    }
-                                }
-                            }
-                        }
-                    }
+                    store_run(p, a_row, tile_b * BN + c0, r, out_f, out_h, f32);
                 }
             }
         } else if (ok && p.split_stride != 0) {
@@ -402,6 +408,289 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     if (warp == 1) {
         tcgen05_fence_after();
         tcgen05_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+
+// ---- two CTAs on one tile -------------------------------------------------------------------------
+// For many tokens: a cluster of two CTAs (two SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA holds half of the rows of A (128 tokens) and half of the
+// rows of B (128 features), so per 64 elements of K it stages 32 KB instead of the 48 KB a lone
+// CTA moves for a 128 x 256 tile; shared-memory traffic per flop, which bounds the single-CTA
+// kernel, drops by a third.  A stage holds 128 elements of K (64 KB, three stages): the cost of
+// a stage's barriers and commits, not their latency, was what held the pairs back with 64.
+// The even CTA of the pair (the leader) issues the products; the accumulator of each CTA's 128
+// rows lands in that CTA's tensor memory, and each CTA's epilogue warps store their own rows.
+// Measured at 2,048 tokens against the single-CTA kernel: 1.38 against 1.26 PFLOP/s (N 6144,
+// K 4096), 1.50 against 1.37 (N 28672 with the gated epilogue), 1.44 against 1.30 (K 14336).
+//   full_bar[s]   (leader)    both CTAs' TMA copies of stage s have landed (the other CTA's copies
+//                             count their bytes on the leader's barrier)
+//   empty_bar[s]  (each CTA)  the products have read stage s (tcgen05.commit, multicast to both)
+//   acc_full[a]   (each CTA)  accumulator a is complete (commit, multicast to both)
+//   acc_empty[a]  (leader)    both CTAs' epilogue threads have read accumulator a (256 arrivals)
+constexpr int PAIR_BN = 256;               // columns of the pair's tile
+constexpr int PAIR_HALF = PAIR_BN / 2;     // rows of B each CTA loads
+constexpr int PAIR_KSUB = 2;               // 64-element k blocks per stage
+constexpr int PAIR_A_BYTES = BM * BK * 2, PAIR_B_BYTES = PAIR_HALF * BK * 2;     // one k block of each operand
+constexpr int PAIR_STAGE_BYTES = PAIR_KSUB * (PAIR_A_BYTES + PAIR_B_BYTES);       // [A k0][A k1]..[B k0][B k1]..
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t *bar, uint32_t rank) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\t"
+        "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(smem_u32(bar)), "r"(rank) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, STATUS_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tcgen05_alloc_pair(uint32_t *dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair once the products issued so far are done
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t *bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// What tcgen05.alloc returned in the leader and in the other CTA of pair 0 (a check of the set-up).
+__device__ unsigned int lgml_pair_tmem_seen[2];
+
+// A TMA copy into this CTA's shared memory whose bytes are counted on a barrier of the pair's
+// leader (`bar_cluster`: a shared::cluster address from mapa).
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t mapa_u32(const void *p, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(p)), "r"(rank));
+    return ra;
+}
+
+template <int STAGES, int PAIR_NACC>
+__global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b, const Params p) {
+    pdl_trigger();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[PAIR_NACC], acc_empty[PAIR_NACC];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    volatile int *abort_flag = &abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();            // 0: the leader, which issues the products
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_kb = (p.k_blocks + PAIR_KSUB - 1) / PAIR_KSUB;      // stages per tile
+    const int n_tiles = p.tiles_a * p.tiles_b;          // tiles of 256 x 256
+    constexpr uint32_t ACC_COLS = PAIR_BN;
+    constexpr uint32_t TMEM_COLS = ACC_COLS * PAIR_NACC;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < PAIR_NACC; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 256);      // the epilogue threads of both CTAs arrive
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) tcgen05_alloc_pair(&tmem_base_s, TMEM_COLS);
+    tcgen05_fence_before();
+    cluster_sync_all();             // both CTAs' barriers exist before anything arrives on them from the other side
+    tcgen05_fence_after();
+    // The products name one accumulator address for both CTAs: the leader's.  (Both CTAs take
+    // part in one allocation and get the same address; reading the leader's keeps this right
+    // even if they did not.)
+    uint32_t tmem_base;
+    {
+        uint32_t ra;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(&tmem_base_s)), "r"(0u));
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(tmem_base) : "r"(ra) : "memory");
+    }
+    if (threadIdx.x == 0 && pair == 0) lgml_pair_tmem_seen[rank] = tmem_base_s;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (each CTA loads its halves) ----------------
+        if (lane == 0) {
+            // This pair's work is a list of (tile, k block) items; item q goes to stage q % STAGES.
+            // Weights do not depend on the kernels before this one: those of the first STAGES items
+            // go out at once, then the wait for the earlier kernels, then the activations.  The bytes
+            // of both CTAs' copies of a stage are counted on the leader's barrier of that stage,
+            // which the leader arms for both.
+            uint32_t bar_of[STAGES];
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) bar_of[s] = mapa_u32(&full_bar[s], 0);
+            int q = 0;
+            bool waited = false, ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                const int row_a = (tile % p.tiles_a) * 2 * BM + (int)rank * BM;
+                const int row_b = (tile / p.tiles_a) * PAIR_BN + (int)rank * PAIR_HALF;
+                for (int kb = 0; kb < n_kb; ++kb, ++q) {
+                    const int s = q % STAGES;
+                    if (q == STAGES && !waited) {
+                        // the activations of the first STAGES items, whose weights are under way
+                        pdl_wait();
+                        waited = true;
+                        int t2 = pair, k2 = 0;
+                        for (int q2 = 0; q2 < STAGES; ++q2) {
+#pragma unroll
+                            for (int u = 0; u < PAIR_KSUB; ++u)
+                                tma_load_2d_pair(tiles + (size_t)q2 * PAIR_STAGE_BYTES + u * PAIR_A_BYTES, &map_a, (k2 * PAIR_KSUB + u) * BK,
+                                                 (t2 % p.tiles_a) * 2 * BM + (int)rank * BM, bar_of[q2]);
+                            if (++k2 == n_kb) {
+                                k2 = 0;
+                                t2 += n_pairs;
+                            }
+                        }
+                    }
+                    if (q >= STAGES && (!mbar_wait(&empty_bar[s], ((q / STAGES) - 1) & 1, abort_flag, p.status) || *abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *a_dst = tiles + (size_t)s * PAIR_STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);
+#pragma unroll
+                    for (int u = 0; u < PAIR_KSUB; ++u) {
+                        if (waited) tma_load_2d_pair(a_dst + u * PAIR_A_BYTES, &map_a, (kb * PAIR_KSUB + u) * BK, row_a, bar_of[s]);
+                        tma_load_2d_pair(a_dst + PAIR_KSUB * PAIR_A_BYTES + u * PAIR_B_BYTES, &map_b, (kb * PAIR_KSUB + u) * BK, row_b, bar_of[s]);
+                    }
+                }
+            }
+            if (!waited) {
+                // fewer items than stages: their activations are still to come
+                pdl_wait();
+                int t2 = pair, k2 = 0;
+                for (int q2 = 0; q2 < q; ++q2) {
+#pragma unroll
+                    for (int u = 0; u < PAIR_KSUB; ++u)
+                        tma_load_2d_pair(tiles + (size_t)q2 * PAIR_STAGE_BYTES + u * PAIR_A_BYTES, &map_a, (k2 * PAIR_KSUB + u) * BK,
+                                         (t2 % p.tiles_a) * 2 * BM + (int)rank * BM, bar_of[q2]);
+                    if (++k2 == n_kb) {
+                        k2 = 0;
+                        t2 += n_pairs;
+                    }
+                }
+            }
+            // (On an abort copies may still be in flight; the cluster barrier at the end of the
+            // kernel keeps both CTAs, and so their shared memory, until the leader has gone through
+            // its bounded waits.)
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---------------- MMA issuer (leader) ----------------
+            constexpr uint32_t idesc = make_idesc(2 * BM, PAIR_BN);
+            bool ok = true;
+            int it = 0, j = 0;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++j) {
+                const int acc = j % PAIR_NACC;
+                if (j >= PAIR_NACC && !mbar_wait_cluster(&acc_empty[acc], ((j / PAIR_NACC) - 1) & 1, abort_flag, p.status)) break;
+                tcgen05_fence_after();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)acc * ACC_COLS;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag, p.status);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * PAIR_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + PAIR_KSUB * PAIR_A_BYTES;
+#pragma unroll
+                    for (int u = 0; u < PAIR_KSUB; ++u) {
+                        const uint64_t da = make_smem_desc(a_addr + u * PAIR_A_BYTES), db = make_smem_desc(b_addr + u * PAIR_B_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            tcgen05_mma_bf16_pair(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || u > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit_pair(&empty_bar[s]);
+                }
+                tcgen05_commit_pair(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: 4 warps per CTA, each CTA its own 128 rows ----------------
+        pdl_wait();
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float *out_f = (float *)p.out;
+        __nv_bfloat16 *out_h = (__nv_bfloat16 *)p.out;
+        const bool f32 = p.out_f32 != 0;
+        int j = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
+            const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+            const int acc = j % PAIR_NACC;
+            const uint32_t acc_col = (uint32_t)acc * ACC_COLS;
+            const int a_row = tile_a * 2 * BM + (int)rank * BM + row;
+            const bool ok = mbar_wait(&acc_full[acc], (j / PAIR_NACC) & 1, abort_flag, p.status);
+            tcgen05_fence_after();
+            if (ok) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
+                    uint32_t r[16];
+                    tcgen05_ld_16(lane_addr + acc_col + (uint32_t)c0, r);
+                    tcgen05_wait_ld();
+                    store_run(p, a_row, tile_b * PAIR_BN + c0, r, out_f, out_h, f32);
+                }
+            }
+            // this thread has read its part of the accumulator: tell the leader's MMA warp
+            tcgen05_fence_before();
+            if (rank == 0) asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+            else mbar_arrive_remote(&acc_empty[acc], 0);
+        }
+    }
+    // nobody leaves, and no tensor memory is given back, while the other CTA may still arrive on
+    // this one's barriers or the leader's products may still use this one's memory
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tcgen05_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -466,7 +755,86 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, dim3 g
     return lgml_launch_status("gemm_tcgen05");
 }
 
+// How many pairs of CTAs the device runs at one time (pairs need both SMs of a TPC, and not
+// every TPC of a part has two): the persistent grid is this many pairs, never more, or the
+// rest would wait for a second round.  0 if the query fails.
+template <int STAGES, int NACC>
+int pairs_at_once(size_t smem) {
+    static int n = -1;
+    if (n < 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 74);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<STAGES, NACC>, &cfg);
+        n = (e == cudaSuccess && clusters > 0) ? clusters : 0;
+        if (e != cudaSuccess) cudaGetLastError();
+    }
+    return n;
+}
+
+template <int STAGES, int NACC>
+int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, int n_tiles, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * PAIR_STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<STAGES, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int at_once = pairs_at_once<STAGES, NACC>(smem);
+    if (at_once <= 0) LGML_FAIL("gemm_tcgen05: the device runs no pair of CTAs of this kernel");
+    int n_pairs = n_tiles < at_once ? n_tiles : at_once;
+    {
+        static int forced = -1;
+        if (forced < 0) {
+            const char *e = getenv("LGML_GEMM_PAIRS");
+            forced = e ? atoi(e) : 0;
+        }
+        if (forced > 0 && forced < n_pairs) n_pairs = forced;
+    }
+    cudaError_t e = lgml_launch_cluster(gemm_pair_kernel<STAGES, NACC>, dim3(2 * n_pairs), dim3(THREADS), smem, stream, 2, ma, mb, p);
+    if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: launch of CTA pairs failed: %s", cudaGetErrorString(e));
+    return lgml_launch_status("gemm_tcgen05 pairs");
+}
+
+// LGML_GEMM_PAIR=0: never use CTA pairs (every product of many tokens on single CTAs).
+bool pairs_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("LGML_GEMM_PAIR");
+        on = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
 }  // namespace
+
+// Pairs of CTAs of the product for many tokens that the device runs at one time.
+LGML_API int lgml_gemm_pairs_at_once(void) {
+    const size_t smem = (size_t)3 * PAIR_STAGE_BYTES + 1024;
+    cudaFuncSetAttribute(gemm_pair_kernel<3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return pairs_at_once<3, 2>(smem);
+}
+
+// The tensor-memory addresses that the two CTAs of pair 0 got from their allocation in the last
+// launch on pairs of CTAs (they should agree).
+LGML_API int lgml_gemm_pair_tmem_seen(unsigned int *leader, unsigned int *other) {
+    unsigned int v[2] = {0, 0};
+    cudaError_t e = cudaMemcpyFromSymbol(v, lgml_pair_tmem_seen, sizeof(v));
+    if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot read the set-up record: %s", cudaGetErrorString(e));
+    *leader = v[0];
+    *other = v[1];
+    return 0;
+}
 
 // Floats of scratch that `n_splits` > 1 needs.
 LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) {
@@ -516,6 +884,18 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         p.tiles_a = (N + BM - 1) / BM;
         p.tiles_b = 1;
         grid = dim3(p.tiles_a, 1, n_splits);
+    } else if (n_splits == 1 && M >= 512 && pairs_enabled()) {
+        // many tokens: pairs of CTAs on 256 x 256 tiles, tile_a fastest
+        p.transposed = 0;
+        p.rows_a = M;
+        p.rows_b = N;
+        p.kb_per_split = k_blocks;
+        if ((rc = make_map(&ma, x, M, K, ldx, BM))) return rc;
+        if ((rc = make_map(&mb, w, N, K, ldw, PAIR_HALF))) return rc;
+        p.tiles_a = (M + 2 * BM - 1) / (2 * BM);
+        p.tiles_b = (N + PAIR_BN - 1) / PAIR_BN;
+        const int n_tiles = p.tiles_a * p.tiles_b;
+        return launch_pair<3, 2>(ma, mb, p, n_tiles, stream);
     } else {
         bn = 256;
         p.transposed = 0;

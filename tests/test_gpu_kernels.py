@@ -152,6 +152,8 @@ def test_gemm_f32_is_exact_and_batch_invariant(M, N, K):
     (1, 128, 64, False, False, None), (8, 331 * 8, 120, True, True, None), (5, 200, 192, True, False, 3),
     (64, 1000, 1096, True, True, 4), (100, 320, 96, False, False, None), (129, 520, 264, True, False, None),
     (300, 648, 200, True, True, None), (700, 1200, 520, False, False, None),
+    # 512 rows and more: pairs of CTAs on 256 x 256 tiles (edges in every direction, several tiles per pair)
+    (512, 256, 64, False, False, None), (777, 1000, 328, True, True, None), (1500, 40 * 256 + 8, 136, True, False, None),
 ])
 def test_gemm_tcgen05(M, N, K, bias, f32, splits):
     from lgml_b200 import ops
@@ -175,7 +177,7 @@ def test_gemm_tcgen05_gated_epilogue_and_partials():
 
     torch.manual_seed(5)
     st = status()
-    for M, F, K in [(6, 100, 96), (300, 176, 120)]:
+    for M, F, K in [(6, 100, 96), (300, 176, 120), (640, 300, 200)]:
         x = torch.randn(M, K).to(torch.bfloat16)
         wg, wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16), (torch.randn(F, K) * 0.1).to(torch.bfloat16)
         bg, bu = torch.randn(F), torch.randn(F)
