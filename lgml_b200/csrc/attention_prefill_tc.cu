@@ -8,15 +8,19 @@
 //     S[128, 64]  = Q[128, D] . K_page[64, D]^T      tcgen05.mma, accumulator in tensor memory
 //     softmax: one thread per row reads its 64 scores from TMEM, keeps the running maximum and
 //              sum in float32 (base-2 exponentials), writes P as bfloat16 to shared memory
-//     O_page[128, D] = P[128, 64] . V_page[64, D]    tcgen05.mma (V is the N-major B operand)
-//     O = O * correction + O_page                    in registers, 8 warps x 64 columns
+//     O[128, D] += P[128, 64] . V_page[64, D]        tcgen05.mma, accumulated in tensor memory (V is the
+//                                                    N-major B operand)
+// The running output O is corrected (read, scaled, written back) only when a row's maximum has
+// grown by more than 8 (base-2 units) since the value its sums are relative to; until then the
+// exponentials are taken against that older maximum and stay below 2^8, which bfloat16 and the
+// float32 sums hold without loss.  So a page costs one read of its scores from tensor memory
+// and nothing for the output; O is read once, at the end, and divided by the row's sum.
 // Q, K, V and P sit in shared memory in the 128-byte-swizzled layout the tensor core reads.
 // The 8 warps have two roles.  Warps 0-3 do the softmax (one thread per row).  Warps 4-7 copy
 // the pages with cp.async (K two pages ahead, V one) and their first thread issues the
 // products: the scores of page i+1 go right behind the P V product of page i, into a second S
-// buffer, so they are ready when the output of page i has been added up.  All 8 warps add the
-// page's output to the running one (each thread half the columns of its row).  Two CTAs share
-// an SM, so that one's products overlap the other's softmax.  CTAs are started with the longest
+// buffer; they also do the rare corrections of O.  Two CTAs share an SM, so that one's
+// products overlap the other's softmax.  CTAs are started with the longest
 // tiles first (the caller orders them).  Keys are taken from the cache, so this step's own
 // keys are seen at cache precision, as in mischief/lgml, which writes the cache before
 // attention reads it (lua/lgml/transformer.lua:1838-1839, :2405-2407; formula :1805-1816,
@@ -31,11 +35,15 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int ROWS = 128;            // query rows per CTA = UMMA M
 constexpr int THREADS = 256;
-constexpr uint32_t SPIN_LIMIT = 4u << 20;
-constexpr uint32_t WAIT_HINT_NS = 2000;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;   // polls of up to WAIT_HINT_NS each: about a second
+constexpr uint32_t WAIT_HINT_NS = 1000;
+#ifndef POLL_SLEEP_NS
+#define POLL_SLEEP_NS 100
+#endif
 constexpr int STATUS_TIMEOUT = 12;
-constexpr uint32_t TMEM_COLS = 256;  // S of even pages: columns 0..63, O_page: 64..64+DP-1, S of odd pages: 192..255
-constexpr uint32_t O_COL = 64, S1_COL = 192;
+constexpr uint32_t TMEM_COLS = 256;  // S of even pages: columns 0..63, of odd pages: 64..127; the output O: 128..128+DP-1
+constexpr uint32_t S1_COL = 64, O_COL = 128;
+constexpr float RESCALE_STEP = 8.f;  // the output is corrected only when a row's maximum has grown by more than this (base-2 units)
 constexpr int LOADERS = 128;         // threads of warps 4-7, which copy the pages
 constexpr int ISSUER = 128;          // the thread that issues the tensor-core products (first of warp 4)
 
@@ -68,6 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
+        __nanosleep(POLL_SLEEP_NS);      // a polling warp takes issue slots from the other CTA's working warps
     }
     *abort_flag = 1;
     atomicExch(status, STATUS_TIMEOUT);
@@ -100,6 +109,14 @@ __device__ __forceinline__ void tcgen05_ld_16(uint32_t taddr, uint32_t (&r)[16])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_st_16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 2^x in one instruction; 2^(-inf) = 0
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -269,30 +286,33 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     const int my_tok = row / hpc, my_g = row - my_tok * hpc;
     const bool row_valid = my_tok < n_tok && my_g < g_count;
     const int qpos = row_valid ? pos_first + my_tok : -1;
-    const int col0 = warp < 4 ? 0 : HALF;                         // the output columns this thread accumulates
-    float o_reg[HALF];
-#pragma unroll
-    for (int i = 0; i < HALF; ++i) o_reg[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // m_ref: the maximum (base-2 units) that this row's sum l_run and its output in tensor memory
+    // are relative to.  It follows the row's running maximum only when that has grown by more
+    // than RESCALE_STEP since: until then the exponentials are taken against the older maximum
+    // (they stay below 2^RESCALE_STEP) and the output needs no correction.
+    float m_ref = -INFINITY, l_run = 0.f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     constexpr uint32_t idesc_qk = make_idesc(ROWS, PAGE, 0);
     constexpr uint32_t idesc_pv = make_idesc(ROWS, DP, 1);
     bool alive = true;
 
-    // S = Q K^T of page `it` into the S buffer of its parity (one thread issues)
+    // S = Q K^T of page `it` into the S buffer of its parity (one thread issues).  The descriptors
+    // differ from their first one only in the address field (units of 16 bytes), so they are made
+    // once and advanced by additions.
+    const uint64_t desc_q0 = make_desc(smem_u32(Qs), 16, 1024), desc_k0 = make_desc(smem_u32(Ks), 16, 1024);
+    const uint64_t desc_p0 = make_desc(smem_u32(Ps), 16, 1024), desc_v0 = make_desc(smem_u32(Vs), PAGE * 128, 1024);
     auto issue_qk = [&](int it) {
-        const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + (it & 1) * K_BYTES);
+        const uint64_t dk = desc_k0 + (uint64_t)(((it & 1) * K_BYTES) >> 4);
 #pragma unroll
         for (int ks = 0; ks < DP / 16; ++ks) {
-            const uint64_t da = make_desc(qa + (ks >> 2) * (ROWS * 128) + (ks & 3) * 32, 16, 1024);
-            const uint64_t db = make_desc(ka + (ks >> 2) * (PAGE * 128) + (ks & 3) * 32, 16, 1024);
+            const uint64_t da = desc_q0 + (uint64_t)(((ks >> 2) * (ROWS * 128) + (ks & 3) * 32) >> 4);
+            const uint64_t db = dk + (uint64_t)(((ks >> 2) * (PAGE * 128) + (ks & 3) * 32) >> 4);
             tcgen05_mma_bf16(tmem_base + ((it & 1) ? S1_COL : 0u), da, db, idesc_qk, ks > 0 ? 1u : 0u);
         }
         tcgen05_commit(&s_bar);
     };
     // Q and K(0) have landed: the first scores; later ones are issued a page ahead, behind the
-    // P V product of the page before, so that the tensor core has them ready when the softmax
-    // of that page is done.
+    // P V product of the page before.
     cp_async_wait<0>();
     fence_async_smem();
     __syncthreads();
@@ -304,9 +324,12 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     for (int it = 0; it < n_iter; ++it) {
         const int stage = it & 1, pg = pg_lo + it, key0 = pg * PAGE;
         const uint32_t s_col = stage ? S1_COL : 0u;
+        int need = 0;
 
-        // ---- softmax: warps 0-3, one thread per row -----------------------------------------------------
+        // ---- softmax: warps 0-3, one thread per row, the page's scores in registers ---------------------
         if (warp < 4) {
+            // (the scores of page it were issued behind P V of page it-1: once they are here, that
+            //  product is done too and P may be written again)
             if (alive && !mbar_wait(&s_bar, it & 1, abort_flag, status)) alive = false;
             tcgen05_fence_after();
             const int page_id = table[pg];
@@ -316,141 +339,157 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             const bool edge = !have || key0 + PAGE - 1 > pos_first || (window > 0 && key0 < pos_last - window + 1) || n_tok * hpc < ROWS || g_count < hpc;
             const int c_hi = have ? qpos - key0 : -1;                                  // qpos = -1 for a row without a token
             const int c_lo = (window > 0) ? qpos - window + 1 - key0 : -(1 << 30);
-            float mx = -INFINITY;
+            uint32_t r[PAGE];
+#pragma unroll
+            for (int c0 = 0; c0 < PAGE; c0 += 16) tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, *reinterpret_cast<uint32_t(*)[16]>(&r[c0]));
+            tcgen05_wait_ld();
+            // (four chains each: the order of a maximum or of these float32 partial sums is a
+            //  function of the column only, so a row's result does not depend on the batch)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (edge) {
 #pragma unroll
-                for (int c0 = 0; c0 < PAGE; c0 += 16) {
-                    uint32_t r[16];
-                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
-                    tcgen05_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c0 + j <= c_hi && c0 + j >= c_lo) mx = fmaxf(mx, __uint_as_float(r[j]));
-                }
+                for (int c = 0; c < PAGE; ++c)
+                    if (c <= c_hi && c >= c_lo) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(r[c]));
             } else {
 #pragma unroll
-                for (int c0 = 0; c0 < PAGE; c0 += 16) {
-                    uint32_t r[16];
-                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
-                    tcgen05_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
-                }
+                for (int c = 0; c < PAGE; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(r[c]));
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the scale is positive, so the maximum of the raw scores is the maximum of the scaled ones
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            const float corr = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
-            const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;      // keeps (-inf) - (-inf) out of the exponent
-            m_run = m_new;
-            float sum = 0.f;
+            const float m_new = mx * scale_log2;
+            float corr = 1.f;
+            if (m_ref == -INFINITY) {
+                m_ref = m_new;                       // nothing summed yet: nothing to correct
+            } else if (m_new > m_ref + RESCALE_STEP) {
+                corr = ex2(m_ref - m_new);
+                m_ref = m_new;
+                l_run *= corr;
+                need = 1;
+            }
+            corr_s[row] = corr;
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;    // keeps (-inf) - (-inf) out of the exponent
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t p_row = smem_u32(Ps) + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);   // this row of P
             const uint32_t p_xor = (uint32_t)(row & 7);
             if (edge) {
 #pragma unroll
-                for (int c0 = 0; c0 < PAGE; c0 += 16) {
-                    uint32_t r[16];
-                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
-                    tcgen05_wait_ld();
-                    uint32_t packed[8];
+                for (int c0 = 0; c0 < PAGE; c0 += 8) {
+                    uint32_t packed[4];
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        float p0 = ex2(fmaf(__uint_as_float(r[j]), scale_log2, -m_sub));
-                        float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale_log2, -m_sub));
+                    for (int j = 0; j < 8; j += 2) {
+                        float p0 = ex2(fmaf(__uint_as_float(r[c0 + j]), scale_log2, neg_m));
+                        float p1 = ex2(fmaf(__uint_as_float(r[c0 + j + 1]), scale_log2, neg_m));
                         if (c0 + j > c_hi || c0 + j < c_lo) p0 = 0.f;
                         if (c0 + j + 1 > c_hi || c0 + j + 1 < c_lo) p1 = 0.f;
-                        sum += p0 + p1;
+                        sum4[(j >> 1) & 3] += p0 + p1;
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                         packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
-                    // 16 keys = two 16-byte chunks of this row of P
                     st_shared_16(p_row + ((((uint32_t)(c0 >> 3)) ^ p_xor) << 4), packed[0], packed[1], packed[2], packed[3]);
-                    st_shared_16(p_row + ((((uint32_t)(c0 >> 3) + 1) ^ p_xor) << 4), packed[4], packed[5], packed[6], packed[7]);
                 }
             } else {
-                const float neg_m = -m_sub;
+                // every row sees the whole page: no tests
 #pragma unroll
-                for (int c0 = 0; c0 < PAGE; c0 += 16) {
-                    uint32_t r[16];
-                    tcgen05_ld_16(lane_addr + s_col + (uint32_t)c0, r);
-                    tcgen05_wait_ld();
-                    uint32_t packed[8];
+                for (int c0 = 0; c0 < PAGE; c0 += 8) {
+                    uint32_t packed[4];
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(r[j]), scale_log2, neg_m));
-                        const float p1 = ex2(fmaf(__uint_as_float(r[j + 1]), scale_log2, neg_m));
-                        sum += p0 + p1;
+                    for (int j = 0; j < 8; j += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(r[c0 + j]), scale_log2, neg_m));
+                        const float p1 = ex2(fmaf(__uint_as_float(r[c0 + j + 1]), scale_log2, neg_m));
+                        sum4[(j >> 1) & 3] += p0 + p1;
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                         packed[j >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
                     st_shared_16(p_row + ((((uint32_t)(c0 >> 3)) ^ p_xor) << 4), packed[0], packed[1], packed[2], packed[3]);
-                    st_shared_16(p_row + ((((uint32_t)(c0 >> 3) + 1) ^ p_xor) << 4), packed[4], packed[5], packed[6], packed[7]);
                 }
             }
-            l_run = l_run * corr + sum;
-            corr_s[stage * ROWS + row] = corr;
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         }
-        // V(it) and K(it+1) have landed (the loaders wait for their copies); P is written
+        // V(it) and K(it+1) have landed (the loaders wait for their copies); P is written.  The
+        // barrier also tells everyone whether any row's output has to be corrected first.
         cp_async_wait<0>();
         fence_async_smem();
         tcgen05_fence_before();
-        __syncthreads();
-        // ---- O_page = P V, and the scores of the next page behind it ------------------------------------
-        if (tid == ISSUER) {
-            tcgen05_fence_after();
-            const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs);
+        const int any_need = __syncthreads_or(need);
+        if (warp >= 4) {
+            if (any_need) {
+                // ---- correct the running output in tensor memory (rare): row by row, warps 4-7 ------------
+                // (a correction implies an earlier page: its product into O must be done)
+                if (alive && !mbar_wait(&o_bar, (it - 1) & 1, abort_flag, status)) alive = false;
+                tcgen05_fence_after();
+                const float corr = corr_s[row];
+                // (tensor-memory loads and stores are for whole warps: a warp goes in if any of its rows needs it)
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-            for (int k2 = 0; k2 < PAGE / 16; ++k2) {
-                const uint64_t da = make_desc(pa + k2 * 32, 16, 1024);
-                // 16 keys further = two groups of 8 rows; blocks of 64 dims are PAGE * 128 bytes apart
-                const uint64_t db = make_desc(va + k2 * 2048, PAGE * 128, 1024);
-                tcgen05_mma_bf16(tmem_base + O_COL, da, db, idesc_pv, k2 > 0 ? 1u : 0u);
+                    for (int c0 = 0; c0 < DP; c0 += 16) {
+                        uint32_t r[16];
+                        tcgen05_ld_16(lane_addr + O_COL + (uint32_t)c0, r);
+                        tcgen05_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
+                        tcgen05_st_16(lane_addr + O_COL + (uint32_t)c0, r);
+                    }
+                    tcgen05_wait_st();
+                }
+                tcgen05_fence_before();
+                asm volatile("bar.sync 1, 128;" ::: "memory");      // warps 4-7: all rows corrected before the product
             }
-            tcgen05_commit(&o_bar);
-            if (it + 1 < n_iter) issue_qk(it + 1);
-        }
-        // The softmax warps saw the scores of this page before the barrier above, so its keys' stage
-        // is free: the keys of the page after the next.
-        if (loader && it + 2 < n_iter) load_k(it + 2);
-        if (alive && !mbar_wait(&o_bar, it & 1, abort_flag, status)) alive = false;
-        tcgen05_fence_after();
-        // the values' stage is free: the next page of values
-        if (loader) {
+            // ---- O += P V, and the scores of the next page behind it ---------------------------------------
+            if (tid == ISSUER) {
+                tcgen05_fence_after();
+#pragma unroll
+                for (int k2 = 0; k2 < PAGE / 16; ++k2) {
+                    // 16 keys further: 32 bytes along a row of P; two groups of 8 rows of V (blocks of 64
+                    // dims are PAGE * 128 bytes apart: the leading offset of the V descriptor)
+                    tcgen05_mma_bf16(tmem_base + O_COL, desc_p0 + (uint64_t)((k2 * 32) >> 4), desc_v0 + (uint64_t)((k2 * 2048) >> 4), idesc_pv,
+                                     (it > 0 || k2 > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(&o_bar);
+                if (it + 1 < n_iter) issue_qk(it + 1);
+            }
+            // The softmax warps saw the scores of this page before the barrier above, so its keys' stage
+            // is free: the keys of the page after the next.
+            if (it + 2 < n_iter) load_k(it + 2);
+            // the values' stage is free once the product has read it: the next page of values
+            if (alive && !mbar_wait(&o_bar, it & 1, abort_flag, status)) alive = false;
             if (it + 1 < n_iter) load_v(it + 1);
             cp_async_commit();
         }
-        // ---- O = O * correction + O_page, 8 warps x HALF columns -------------------------------------------
-        {
-            const float corr = corr_s[stage * ROWS + row];
-#pragma unroll
-            for (int c0 = 0; c0 < HALF; c0 += 16) {
-                uint32_t r[16];
-                tcgen05_ld_16(lane_addr + O_COL + (uint32_t)(col0 + c0), r);
-                tcgen05_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) o_reg[c0 + j] = fmaf(o_reg[c0 + j], corr, __uint_as_float(r[j]));
-            }
-        }
-        tcgen05_fence_before();
     }
     cp_async_wait<0>();
-    // ---- normalise and write ----------------------------------------------------------------------------
-    if (warp < 4) l_s[row] = l_run;
+    // ---- normalise and write: every thread half the columns of its row -------------------------------------
+    if (warp < 4) {
+        l_s[row] = l_run;
+        // the loaders waited for the last product; the softmax warps have not yet
+        if (alive && n_iter > 0 && !mbar_wait(&o_bar, (n_iter - 1) & 1, abort_flag, status)) alive = false;
+    }
+    tcgen05_fence_after();
     __syncthreads();
-    if (row_valid && alive) {
+    {
+        // (every lane takes part in the loads from tensor memory, which are for whole warps; rows
+        //  without a token only skip the stores)
         const float l = l_s[row];
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16 *dst = out + (size_t)(row0 + my_tok) * ldo + (size_t)(kvh * group + g0 + my_g) * D;
+        const int col0 = warp < 4 ? 0 : HALF;
+        const bool store = row_valid && alive;
+        __nv_bfloat16 *dst = out + (size_t)(row0 + (store ? my_tok : 0)) * ldo + (size_t)(kvh * group + g0 + (store ? my_g : 0)) * D;
 #pragma unroll
-        for (int c0 = 0; c0 < HALF; c0 += 8) {
-            const int d = col0 + c0;
-            if (d + 8 <= D) {
-                uint32_t h[4];
+        for (int c0 = 0; c0 < HALF; c0 += 16) {
+            uint32_t r[16];
+            tcgen05_ld_16(lane_addr + O_COL + (uint32_t)(col0 + c0), r);
+            tcgen05_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(o_reg[c0 + 2 * j] * inv, o_reg[c0 + 2 * j + 1] * inv);
-                    h[j] = *reinterpret_cast<uint32_t *>(&pr);
+            for (int c8 = 0; c8 < 16; c8 += 8) {
+                const int d = col0 + c0 + c8;
+                if (store && d + 8 <= D) {
+                    uint32_t h[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(r[c8 + 2 * j]) * inv, __uint_as_float(r[c8 + 2 * j + 1]) * inv);
+                        h[j] = *reinterpret_cast<uint32_t *>(&pr);
+                    }
+                    *reinterpret_cast<uint4 *>(dst + d) = make_uint4(h[0], h[1], h[2], h[3]);
                 }
-                *reinterpret_cast<uint4 *>(dst + d) = make_uint4(h[0], h[1], h[2], h[3]);
             }
         }
     }
