@@ -363,13 +363,16 @@ def tcgen05_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def tcgen05_splits(M: int, N: int, K: int) -> int:
-    """K ranges for a product with few tokens: enough CTAs to cover the SMs about twice,
-    each with at least four 64-wide K blocks."""
+    """K ranges for a product with few tokens: enough CTAs to cover the SMs about twice (once
+    from 17 tokens on: every range writes and the next kernel reads M x N float32 partial sums,
+    which with many tokens is no longer small beside the weights), each with at least four
+    64-wide K blocks."""
     if M > 256:
         return 1
     tiles = -(-N // 128)
     k_blocks = -(-K // 64)
-    return max(1, min((2 * SM_COUNT) // tiles, k_blocks // 4, 16))
+    cover = (2 * SM_COUNT) // tiles if M <= 16 else -(-SM_COUNT // tiles)
+    return max(1, min(cover, k_blocks // 4, 16))
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor], status: torch.Tensor,
