@@ -1,0 +1,90 @@
+"""The kernels at the sizes of a full model (Llama-3.1-8B layer sizes, two layers): the
+bfloat16 path against the 32-bit path of the same engine on the same (bfloat16-valued)
+weights.  The tiny configurations of the other tests never reach the tensor-core paths for
+many tokens (pairs of CTAs on 256 x 256 tiles, the tcgen05 attention at head size 128, the
+many-rows norm and rotary kernels); here a 640-token prompt does, a second request runs beside
+it in portions, and both go on token by token.  What separates the two paths is bfloat16
+rounding of activations and of the cache (2^-9 relative per value, about a dozen rounded
+stages over two layers): on a logit that is a standard deviation of about 2e-3 of the logits'
+range, and the largest of the 1.3 million compared logits lies five to six of those out.  The
+bounds are 2 % of the range for the largest and 0.3 % for the mean difference (measured: 1.2 %
+and 0.18 %; the logits' range is about 6.5, their standard deviation 1.3)."""
+import zlib
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False,
+    "max_position_embeddings": 4096, "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+
+
+def two_runners():
+    """The same random model twice: bfloat16, and float32 holding the bfloat16 values."""
+    from lgml_b200 import ops
+    from lgml_b200.config import config_from_dict
+    from lgml_b200.engine.runner import ModelRunner
+    from lgml_b200.engine.runtime import Runtime
+    from lgml_b200.models import build_model
+    from lgml_b200.weights.loader import target_dtype
+
+    cfg = config_from_dict(SHAPE)
+    runners = {}
+    half = {}
+    for dtype in (torch.bfloat16, torch.float32):
+        rt = Runtime("cuda:0", dtype)
+        model = build_model(cfg)
+        tensors = {}
+        for s in model.tensor_specs():
+            if s.optional:
+                continue
+            if dtype == torch.bfloat16:
+                t = torch.empty(s.shape, dtype=target_dtype(s.kind, dtype), device=rt.device)
+                ops.fill_normal(t, s.init[0], s.init[1] * 0.02, (7 << 32) ^ zlib.crc32(s.name.encode()))
+                half[s.name] = t
+            else:
+                t = half[s.name].to(target_dtype(s.kind, dtype))
+            tensors[s.name] = t
+        model.bind(tensors, rt)
+        runners[dtype] = ModelRunner(model, rt, n_pages=24, max_slots=2, max_step_tokens=1024)
+    return cfg, runners
+
+
+def test_bfloat16_against_32_bit_at_full_layer_sizes():
+    cfg, runners = two_runners()
+    g = torch.Generator().manual_seed(11)
+    a = torch.randint(0, cfg.vocab_size, (640 + 3,), generator=g).tolist()
+    b = torch.randint(0, cfg.vocab_size, (300 + 3,), generator=g).tolist()
+    out = {}
+    for dtype, r in runners.items():
+        ra, rb = r.open("a"), r.open("b")
+        rows = []
+        # a whole (640 tokens: the paths for many tokens), b's first portion beside it
+        rows.append(r.step([(ra, a[:640], [0, 63, 64, 639]), (rb, b[:100], [99])]).float().cpu())
+        # b's second portion (200 tokens: the single-CTA tiles) beside one decoded token of a
+        rows.append(r.step([(ra, a[640:641], [0]), (rb, b[100:300], [0, 199])]).float().cpu())
+        # both token by token (captured graph from the second such step on)
+        for i in range(2):
+            rows.append(r.step([(ra, a[641 + i:642 + i], [0]), (rb, b[300 + i:301 + i], [0])]).float().cpu())
+        r.rt.check_status()
+        r.close(ra)
+        r.close(rb)
+        out[dtype] = torch.cat(rows)
+    ref, got = out[torch.float32], out[torch.bfloat16]
+    assert torch.isfinite(got).all() and torch.isfinite(ref).all()
+    scale = float(ref.abs().max())
+    diff = (got - ref).abs()
+    assert scale > 1.0                                   # the logits spread, so a bound relative to their range means something
+    assert float(diff.max()) <= 2e-2 * scale, (float(diff.max()), scale)
+    assert float(diff.mean()) <= 3e-3 * scale, (float(diff.mean()), scale)
+    # the two paths rank the vocabulary alike: the 32-bit path's first choice is within bfloat16's error of the other's best
+    top = ref.argmax(dim=1)
+    assert bool(((got.max(dim=1).values - got[torch.arange(got.shape[0]), top]) <= 2e-2 * scale).all())
