@@ -150,6 +150,151 @@ __global__ void argmax_final_kernel(const float *__restrict__ part_v, const int 
     }
     if (lane == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;   // a row of NaN or -inf: index 0
 }
+
+// ---------------------------------------------------------------------------------------------
+// The k best candidates of every row, ordered by (logit descending, id ascending): the first
+// step of the sampler's chain after bias and penalties (top_k, src/sample.c:769-790; the order of
+// sorted candidates :680-688).  The rest of the chain works on these k values, so with top_k on
+// the host needs k pairs per row, not the row.
+// One block per row.  A candidate's key is 64 bits: the logit's bits made monotonic, then the
+// complement of the id, so keys are distinct and a larger key is a better candidate.  The k-th
+// largest key is found by radix selection, 11 bits a pass from the top, stopping as soon as
+// the keys that still tie on the bits seen fit shared memory, where they are sorted; then the
+// keys at or above the k-th are gathered and sorted.  NaN sorts last.
+// ---------------------------------------------------------------------------------------------
+constexpr int TK_THREADS = 1024;
+constexpr int TK_BITS = 11, TK_BINS = 1 << TK_BITS;
+constexpr int TK_CAP = 1024;          // keys sorted in shared memory at once
+constexpr int TK_MAX_K = 128;
+
+__device__ __forceinline__ unsigned long long topk_key(float v, int id) {
+    unsigned int u = __float_as_uint(v);
+    if (v != v) u = 0u;                                            // NaN: below everything
+    else u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);          // monotonic in v
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned int)id);
+}
+
+// sort keys[0 .. n) descending; n a power of two up to TK_CAP; all threads of the block call it
+__device__ void topk_sort_desc(unsigned long long *keys, int n) {
+    for (int size = 2; size <= n; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n / 2; i += blockDim.x) {
+                const int lo = 2 * i - (i & (stride - 1)), hi = lo + stride;
+                const bool desc = (lo & size) == 0;
+                const unsigned long long a = keys[lo], b = keys[hi];
+                if ((a < b) == desc) {
+                    keys[lo] = b;
+                    keys[hi] = a;
+                }
+            }
+        }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(TK_THREADS) topk_rows_kernel(const float *__restrict__ logits, int ld, int V, int k, float *__restrict__ out_vals,
+                                                               int *__restrict__ out_ids) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ unsigned int hist[TK_BINS];
+    __shared__ unsigned int warp_tot[32];
+    __shared__ unsigned long long keys[TK_CAP];
+    __shared__ unsigned long long s_prefix, s_threshold;
+    __shared__ unsigned int s_need, s_count, s_bin_count;
+    const float *row = logits + (size_t)blockIdx.x * ld;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    unsigned long long prefix = 0, mask = 0;       // the bits decided so far and where they are
+    unsigned int need = (unsigned int)k;           // how many of the keys that match the prefix are wanted
+    int shift = 64 - TK_BITS;
+    while (true) {
+        const int bits = shift >= 0 ? TK_BITS : TK_BITS + shift;     // the last pass may be narrower
+        const int sh = shift >= 0 ? shift : 0;
+        const unsigned int digit_mask = (1u << bits) - 1u;
+        for (int i = tid; i < TK_BINS; i += TK_THREADS) hist[i] = 0;
+        __syncthreads();
+        for (int i = tid; i < V; i += TK_THREADS) {
+            const unsigned long long key = topk_key(act_load(row + i), i);
+            if ((key & mask) == prefix) atomicAdd(&hist[(unsigned int)(key >> sh) & digit_mask], 1u);
+        }
+        __syncthreads();
+        // suffix sums over the bins (two bins a thread): S(t) = keys with a digit >= 2t
+        const unsigned int h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
+        unsigned int suf = h0 + h1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int other = __shfl_down_sync(0xffffffffu, suf, o);
+            if (lane + o < 32) suf += other;
+        }
+        if (lane == 0) warp_tot[warp] = suf;
+        __syncthreads();
+        unsigned int after = 0;                                       // keys in the warps above this one
+        for (int w = warp + 1; w < 32; ++w) after += warp_tot[w];
+        const unsigned int s_here = suf + after;                      // digits >= 2 tid
+        const unsigned int s_next = s_here - (h0 + h1);               // digits >= 2 tid + 2
+        if (s_here >= need && s_next < need) {
+            // the k-th key has its digit in this thread's pair of bins
+            unsigned int digit, above;
+            if (s_next + h1 >= need) {
+                digit = 2 * tid + 1;
+                above = s_next;
+            } else {
+                digit = 2 * tid;
+                above = s_next + h1;
+            }
+            s_prefix = prefix | ((unsigned long long)digit << sh);
+            s_need = need - above;
+            s_bin_count = digit == 2 * (unsigned int)tid + 1 ? h1 : h0;
+        }
+        __syncthreads();
+        prefix = s_prefix;
+        mask |= (unsigned long long)digit_mask << sh;
+        need = s_need;
+        const unsigned int in_bin = s_bin_count;
+        __syncthreads();
+        if (in_bin <= TK_CAP || sh == 0) break;                       // (at sh == 0 all bits are decided: one key is left)
+        shift -= TK_BITS;
+    }
+    // the keys that match the prefix, sorted: the need-th of them is the k-th key of the row
+    if (tid == 0) s_count = 0;
+    for (int i = tid; i < TK_CAP; i += TK_THREADS) keys[i] = 0ull;
+    __syncthreads();
+    for (int i = tid; i < V; i += TK_THREADS) {
+        const unsigned long long key = topk_key(act_load(row + i), i);
+        if ((key & mask) == prefix) {
+            const unsigned int at = atomicAdd(&s_count, 1u);
+            if (at < TK_CAP) keys[at] = key;
+        }
+    }
+    __syncthreads();
+    int n = 2;
+    while (n < (int)min(s_count, (unsigned int)TK_CAP)) n <<= 1;
+    topk_sort_desc(keys, n);
+    if (tid == 0) s_threshold = keys[need - 1];
+    __syncthreads();
+    const unsigned long long threshold = s_threshold;
+    __syncthreads();
+    // gather the k keys at or above the k-th, sort them, write values and ids
+    if (tid == 0) s_count = 0;
+    for (int i = tid; i < TK_MAX_K; i += TK_THREADS) keys[i] = 0ull;
+    __syncthreads();
+    for (int i = tid; i < V; i += TK_THREADS) {
+        const float v = act_load(row + i);
+        const unsigned long long key = topk_key(v, i);
+        if (key >= threshold) {
+            const unsigned int at = atomicAdd(&s_count, 1u);
+            if (at < TK_MAX_K) keys[at] = key;
+        }
+    }
+    __syncthreads();
+    topk_sort_desc(keys, TK_MAX_K);
+    for (int j = tid; j < k; j += TK_THREADS) {
+        const unsigned long long key = keys[j];
+        const int id = (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+        out_ids[(size_t)blockIdx.x * k + j] = id;
+        out_vals[(size_t)blockIdx.x * k + j] = act_load(row + id);
+    }
+}
 }  // namespace
 
 // scratch: n_rows * 32 floats and n_rows * 32 ints (lgml_argmax_scratch_words words in all).
@@ -175,4 +320,14 @@ LGML_API int lgml_sample_rows(const float *logits, int ld, int n_rows, int V, co
     if (n_rows == 0) return 0;
     lgml_launch(sample_rows_kernel, n_rows, THREADS, 0, stream, logits, ld, V, temperature, uniform, out);
     return lgml_launch_status("sample_rows");
+}
+
+// out_vals, out_ids: [n_rows, k], the k best candidates of each row by (logit descending, id
+// ascending); 1 <= k <= min(V, 128).
+LGML_API int lgml_topk_rows(const float *logits, int ld, int n_rows, int V, int k, float *out_vals, int *out_ids, cudaStream_t stream) {
+    LGML_REQUIRE(n_rows >= 0 && V > 0 && ld >= V, "topk_rows: bad sizes");
+    LGML_REQUIRE(k >= 1 && k <= TK_MAX_K && k <= V, "topk_rows: k = %d must be between 1 and min(vocabulary %d, %d)", k, V, TK_MAX_K);
+    if (n_rows == 0) return 0;
+    lgml_launch(topk_rows_kernel, n_rows, TK_THREADS, 0, stream, logits, ld, V, k, out_vals, out_ids);
+    return lgml_launch_status("topk_rows");
 }

@@ -120,6 +120,12 @@ class Engine:
             ev = torch.cuda.Event()
             ev.record()
             rec.update(out=out, host=host, event=ev)
+        elif all(e.request.params.top_k_on_device and e.request.params.top_k == rows[0].request.params.top_k for e in rows) \
+                and rows[0].request.params.top_k < logits.shape[1]:
+            # top_k on the device; the host runs the rest of the chain on k candidates per row, not on the row
+            vals, ids = ops.topk_rows(logits, rows[0].request.params.top_k)
+            vals, ids = vals.cpu().numpy(), ids.cpu().numpy()
+            rec["toks"] = [int(e.request.sampler.sample_candidates(ids[i], vals[i])) for i, e in enumerate(rows)]
         else:
             host_logits = logits.cpu().numpy()
             rec["toks"] = [int(e.request.sampler.sample(host_logits[i])) for i, e in enumerate(rows)]

@@ -336,6 +336,30 @@ def argmax_rows(logits: torch.Tensor, out: torch.Tensor, scratch: Optional[torch
     return out
 
 
+TOPK_MAX = 128
+
+
+def topk_rows(logits: torch.Tensor, k: int, out_vals: Optional[torch.Tensor] = None, out_ids: Optional[torch.Tensor] = None):
+    """The k best candidates of every row, ordered by (logit descending, id ascending), as the
+    sampler's top_k leaves them: (values float32 [rows, k], ids int32 [rows, k])."""
+    _need(logits, "logits", torch.float32, 2)
+    ld = _rows_contiguous(logits, "logits")
+    n, v = logits.shape
+    if not 1 <= k <= min(v, TOPK_MAX):
+        raise KernelError(f"topk_rows: k = {k} must be between 1 and min(vocabulary {v}, {TOPK_MAX})")
+    if out_vals is None:
+        out_vals = torch.empty((n, k), dtype=torch.float32, device=logits.device)
+    if out_ids is None:
+        out_ids = torch.empty((n, k), dtype=torch.int32, device=logits.device)
+    _need(out_vals, "top-k values", torch.float32, 2)
+    _need(out_ids, "top-k ids", torch.int32, 2)
+    if tuple(out_vals.shape) != (n, k) or tuple(out_ids.shape) != (n, k) or not out_vals.is_contiguous() or not out_ids.is_contiguous():
+        raise KernelError("topk_rows: outputs must be contiguous [rows, k]")
+    fn = _fn("sampling", "lgml_topk_rows", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check("sampling", fn(_ptr(logits), ld, n, v, int(k), _ptr(out_vals), _ptr(out_ids), _stream()), "topk_rows")
+    return out_vals, out_ids
+
+
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """Row r: argmax if temperature[r] <= 0, else the inverse-CDF draw of
     softmax(logits[r] / temperature[r]) at uniform[r]."""

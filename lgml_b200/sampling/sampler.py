@@ -111,6 +111,14 @@ class SamplingParams:
         return plain and (self.greedy or self.is_neutral)
 
     @property
+    def top_k_on_device(self) -> bool:
+        """top_k can be taken on the device and the rest of the chain run on its k candidates:
+        nothing alters the logits first, a draw follows, and k is within the kernel's reach."""
+        plain = (not self.logit_bias and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0
+                 and self.presence_penalty == 0.0)
+        return plain and self.temperature > 0.0 and 0 < self.top_k <= 128
+
+    @property
     def is_neutral(self) -> bool:
         """No step of the chain but temperature and the draw changes the logits."""
         return (not self.logit_bias and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0
@@ -178,6 +186,19 @@ class Sampler:
         if 0 < p.top_k < n:
             order = np.lexsort((ids, -vals.astype(np.float64)))[: p.top_k]   # logit descending, then id ascending
             ids, vals, is_sorted = ids[order], vals[order], True
+        return self._after_top_k(ids, vals, is_sorted)
+
+    def sample_candidates(self, ids: Sequence[int], vals: Sequence[float]) -> int:
+        """The chain from top_p on, for candidates that top_k has already chosen on the device
+        (``ops.topk_rows``: the top_k best, logit descending, id ascending).  The same id as
+        ``sample`` on the whole row when no bias and no penalty is set and temperature > 0."""
+        if not self.p.temperature > 0.0:
+            raise ValueError("sample_candidates is for temperature > 0 (the argmax needs no candidates)")
+        self.last_logits = None
+        return self._after_top_k(np.asarray(ids, dtype=np.int64), np.asarray(vals, dtype=np.float32), True)
+
+    def _after_top_k(self, ids: np.ndarray, vals: np.ndarray, is_sorted: bool) -> int:
+        p = self.p
         if p.top_p < 1.0:
             if not is_sorted:
                 order = np.lexsort((ids, -vals.astype(np.float64)))

@@ -145,6 +145,26 @@ def test_full_sampler_chain_runs_on_host_logits(folders):
     assert c[0] == a[0][: a[0].index(stop) + 1]
 
 
+def test_default_chain_takes_top_k_on_the_device(folders, monkeypatch):
+    """The reference's default chain (top_k 40, top_p 0.95, min_p 0.05, temperature 0.8): top_k
+    runs on the device and the host finishes on 40 candidates per row; the replies equal those
+    of the chain run on whole rows of logits."""
+    import lgml_b200
+    from lgml_b200 import ops
+
+    folder = folders[("B", "float32")]
+    prompts = [H.random_ids(n, 320, 500 + n) for n in (12, 31, 70)]
+    eng = lgml_b200.Engine(str(folder), dtype="float32", slots=3)
+    calls = []
+    real = ops.topk_rows
+    monkeypatch.setattr(ops, "topk_rows", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    got = eng.generate(prompts, max_tokens=24, seed=21)                     # every option at its default
+    assert calls, "the default chain did not take the device path"
+    # the whole-row path: a bias of zero on one id changes no logit but keeps the chain on the host
+    want = eng.generate(prompts, max_tokens=24, seed=21, logit_bias={0: 0.0})
+    assert got == want and all(len(x) == 24 for x in got)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_as_a_process(folders, dtype, tmp_path):
     """bin/trace_run in a separate process: a mixed trace with page reuse, logits files and

@@ -440,3 +440,30 @@ def test_sample_rows_matches_the_host_sampler():
     ops.sample_rows(logits.to(DEV), torch.tensor(temps, device=DEV), torch.tensor(us, dtype=torch.float64, device=DEV), out)
     host = [tw.sample(logits[i].numpy()) for i, tw in enumerate(twins)]
     assert out.cpu().tolist() == host
+
+
+@pytest.mark.parametrize("V,k", [(300, 1), (300, 40), (5000, 128), (128256, 40), (1024, 7)])
+def test_topk_rows(V, k):
+    """The k best of each row in the sampler's order (logit descending, id ascending), with
+    ties, rows of one value, infinities and NaN."""
+    import numpy as np
+    from lgml_b200 import ops
+
+    g = torch.Generator().manual_seed(V + k)
+    rows = [torch.randn(V, generator=g) * 3,
+            torch.randint(-3, 4, (V,), generator=g).float(),            # many ties
+            torch.full((V,), 1.25),                                      # one value: the lowest ids win
+            torch.randn(V, generator=g)]
+    rows[3][::7] = float("-inf")
+    rows[3][5] = float("nan")
+    rows[3][11] = float("inf")
+    x = torch.stack(rows)
+    vals, ids = ops.topk_rows(x.to(DEV), k)
+    vals, ids = vals.cpu().numpy(), ids.cpu().numpy()
+    for r in range(x.shape[0]):
+        l = x[r].numpy().astype(np.float64)
+        l[np.isnan(l)] = -np.inf                                         # NaN sorts last (with -inf, by id)
+        order = np.lexsort((np.arange(V), -l))[:k]
+        nan_free = ~np.isnan(x[r].numpy()[order])
+        assert np.array_equal(ids[r][nan_free], order[nan_free]), (r, ids[r][:8], order[:8])
+        assert np.array_equal(vals[r][nan_free], x[r].numpy()[order][nan_free])

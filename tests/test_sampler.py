@@ -103,3 +103,27 @@ def test_draw_frequencies_fit_the_softmax():
     for i in range(5):
         sigma = math.sqrt(n * p[i] * (1 - p[i]))
         assert abs(counts[i] - n * p[i]) < 4 * sigma
+
+
+def test_candidates_from_top_k_give_the_same_draws_as_the_whole_row():
+    """The chain run on the top_k candidates (as the device hands them over: logit descending,
+    id ascending) picks what the chain on the whole row picks, draw after draw."""
+    import numpy as np
+    from lgml_b200.sampling import Sampler, SamplingParams
+
+    rng = np.random.default_rng(4)
+    for kw in (dict(), dict(top_k=7, top_p=0.8, min_p=0.1, temperature=1.3), dict(top_k=50, top_p=1.0, min_p=0.0, temperature=0.5)):
+        a, b = Sampler(SamplingParams(seed=9, **kw)), Sampler(SamplingParams(seed=9, **kw))
+        assert a.p.top_k_on_device
+        for _ in range(40):
+            row = (rng.standard_normal(500) * 2).astype(np.float32)
+            row[rng.integers(0, 500, 30)] = row[3]                       # ties
+            k = a.p.top_k
+            order = np.lexsort((np.arange(500), -row.astype(np.float64)))[:k]
+            got = b.sample_candidates(order, row[order])
+            want = a.sample(row)
+            assert got == want
+            a.accept(want), b.accept(got)
+    assert not SamplingParams(repeat_penalty=1.1).top_k_on_device
+    assert not SamplingParams(temperature=0.0).top_k_on_device and not SamplingParams(top_k=0).top_k_on_device
+    assert not SamplingParams(logit_bias={3: 1.0}).top_k_on_device
