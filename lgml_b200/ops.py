@@ -492,11 +492,13 @@ SM_COUNT = 148  # B200
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, page: int = 64) -> int:
-    """How many ranges the keys of a token are cut into, so that the grid fills the SMs
-    a few times over; at most one range per page."""
+    """How many ranges the keys of a token are cut into, so that the grid fills the SMs about
+    twice over, with at least four pages a range: a range costs its CTA's start and its share
+    of the merge whatever its length (one request at 2,176 tokens: 15.7 us with a range per
+    page, 10.0 us with 12 ranges)."""
     ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
     pages = max(1, -(-max_kv_len // page))
-    return max(1, min(pages, (2 * SM_COUNT) // max(ctas, 1)))
+    return max(1, min(-(-pages // 4), (2 * SM_COUNT) // max(ctas, 1)))
 
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
