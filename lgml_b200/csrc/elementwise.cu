@@ -54,10 +54,10 @@ LGML_API int lgml_embed_rows(const void *table, int table_dtype, const int *ids,
 // group holds the four consecutive elements  slice start + 512 rd + 4 g ...+3  (one 16-byte
 // access when the row allows it), adds their squares in that order, the group adds its threads'
 // sums by warp trees and then the four warps' sums by index, and the slices' sums are added by
-// index.  Three kernels share this:
-//   - few rows (decoding): the slices of a row are the CTAs of a thread-block cluster, so the
-//     row's bytes come through several SMs' memory paths; the sums cross through distributed
-//     shared memory;
+// index.  Four ways of launching share this:
+//   - few rows (decoding): the slices of a row are the groups of 128 threads of one block (a
+//     slice then has at most 1,024 elements); for wider rows they are the CTAs of a thread-block
+//     cluster, whose sums cross through distributed shared memory;
 //   - many rows (prompts): one block of 128 threads takes all slices of its row one after the
 //     other, with every load of the row issued before any is used;
 //   - rows too wide for the registers of those two: one block per row that walks the row twice.
@@ -184,21 +184,25 @@ __device__ __forceinline__ void add_delta(const Args &a, float *xr, const TD *dr
 // SLICES = MAX_CS: it holds all slices of its row.  ROUNDS rounds of a slice stay in registers.
 // FULL: every slice is exactly ROUNDS rounds of whole quads and 16-byte accesses are allowed, so
 // no access needs a test (the usual case: widths that are multiples of 512 x slices).
-template <typename TD, typename TO, int ROUNDS, int SLICES, bool CLUSTERED, bool FULL>
-__global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
+// MODE 0: one block of 128 threads takes SLICES slices of its row; 1: the slices of a row are the
+// CTAs of a cluster; 2: the slices of a row are the groups of 128 threads of one block.
+template <typename TD, typename TO, int ROUNDS, int SLICES, int MODE, bool FULL>
+__global__ void __launch_bounds__(MODE == 2 ? GROUP * MAX_CS : GROUP) rmsnorm_kernel(const Args a) {
+    constexpr bool CLUSTERED = MODE == 1;
+    constexpr bool GROUPED = MODE == 2;
     pdl_trigger();
     pdl_wait();
     namespace cg = cooperative_groups;
-    __shared__ float red[SLICES][WARPS];
+    __shared__ float red[GROUPED ? MAX_CS : SLICES][WARPS];
     __shared__ float slice_ss;
-    const int gt = threadIdx.x, cs = a.cs, width = a.width;
+    const int gt = GROUPED ? (threadIdx.x & (GROUP - 1)) : threadIdx.x, cs = a.cs, width = a.width;
     const int r = CLUSTERED ? blockIdx.x / cs : blockIdx.x;
-    const int rank0 = CLUSTERED ? blockIdx.x - r * cs : 0;
+    const int rank0 = CLUSTERED ? blockIdx.x - r * cs : (GROUPED ? threadIdx.x / GROUP : 0);
     const int per_cta = FULL ? ROUNDS * PER * GROUP : (((width + cs - 1) / cs + 3) & ~3);
     const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
     float *xr = a.x + src * width;
     const TD *dr = a.delta ? reinterpret_cast<const TD *>(a.delta) + src * width : nullptr;
-    const int n_slices = (CLUSTERED || FULL) ? SLICES : cs;
+    const int n_slices = (CLUSTERED || GROUPED || FULL) ? SLICES : cs;
     const bool vec = FULL ? true : (a.vec != 0);
     // first element of (slice k, round rd) of this thread, and the end of slice k
     auto first = [&](int k, int rd) { return (rank0 + k) * per_cta + rd * PER * GROUP + PER * gt; };
@@ -249,11 +253,11 @@ __global__ void __launch_bounds__(GROUP) rmsnorm_kernel(const Args a) {
 #pragma unroll
             for (int q = 0; q < PER; ++q) ss = fmaf(v[k][rd][q], v[k][rd][q], ss);
         ss = warp_sum(ss);
-        if ((gt & 31) == 0) red[k][gt >> 5] = ss;
+        if ((gt & 31) == 0) red[GROUPED ? rank0 : k][gt >> 5] = ss;
     }
     __syncthreads();
     float total = 0.f;
-    for (int k = 0; k < n_slices; ++k) {
+    for (int k = 0; k < (GROUPED ? cs : n_slices); ++k) {
         float slice = 0.f;
         for (int w = 0; w < WARPS; ++w) slice += red[k][w];
         total += slice;
@@ -339,24 +343,36 @@ static int rmsnorm_launch(const rms::Args &a, int n_rows, cudaStream_t stream) {
     cudaError_t e = cudaSuccess;
     // whole quads everywhere: each slice is exactly `rounds` rounds, 16-byte accesses allowed
     const bool full = a.vec && per_cta * cs == a.width && per_cta == rounds * PER * GROUP;
-    if (clustered && rounds <= 4) {
+    // LGML_NORM_GROUPED=0: few rows always go to clusters of CTAs (the groups of one block are faster
+    // where they fit: 3.3 us against 3.9 us for 8 rows of 4,096 with 9 partial sums)
+    static int grouped = -1;
+    if (grouped < 0) {
+        const char *e = getenv("LGML_NORM_GROUPED");
+        grouped = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    if (grouped && clustered && rounds <= 2) {
+        const int threads = GROUP * cs;
+        if (full && rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, 2, true>, n_rows, threads, 0, stream, a);
+        else if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, 2, false>, n_rows, threads, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, 1, 2, false>, n_rows, threads, 0, stream, a);
+    } else if (clustered && rounds <= 4) {
         const int blocks = n_rows * cs;
-        if (full && rounds == 1) e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, true, true>, blocks, GROUP, 0, stream, cs, a);
-        else if (full && rounds == 2) e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, true, true>, blocks, GROUP, 0, stream, cs, a);
+        if (full && rounds == 1) e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, 1, true>, blocks, GROUP, 0, stream, cs, a);
+        else if (full && rounds == 2) e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, 1, true>, blocks, GROUP, 0, stream, cs, a);
         else switch (rounds) {
-            case 1: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
-            case 2: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
-            case 3: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 3, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
-            default: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 4, 1, true, false>, blocks, GROUP, 0, stream, cs, a); break;
+            case 1: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 1, 1, 1, false>, blocks, GROUP, 0, stream, cs, a); break;
+            case 2: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 2, 1, 1, false>, blocks, GROUP, 0, stream, cs, a); break;
+            case 3: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 3, 1, 1, false>, blocks, GROUP, 0, stream, cs, a); break;
+            default: e = lgml_launch_cluster(rmsnorm_kernel<TD, TO, 4, 1, 1, false>, blocks, GROUP, 0, stream, cs, a); break;
         }
     } else if (cs == 1 && rounds <= 2) {
-        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, false, false>, n_rows, GROUP, 0, stream, a);
-        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, 1, false, false>, n_rows, GROUP, 0, stream, a);
+        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, 1, 0, false>, n_rows, GROUP, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, 1, 0, false>, n_rows, GROUP, 0, stream, a);
     } else if (cs == MAX_CS && full && rounds == 1) {
-        e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, false, true>, n_rows, GROUP, 0, stream, a);
+        e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, 0, true>, n_rows, GROUP, 0, stream, a);
     } else if (cs > 1 && rounds <= 2) {
-        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, false, false>, n_rows, GROUP, 0, stream, a);
-        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, MAX_CS, false, false>, n_rows, GROUP, 0, stream, a);
+        if (rounds == 1) e = lgml_launch(rmsnorm_kernel<TD, TO, 1, MAX_CS, 0, false>, n_rows, GROUP, 0, stream, a);
+        else e = lgml_launch(rmsnorm_kernel<TD, TO, 2, MAX_CS, 0, false>, n_rows, GROUP, 0, stream, a);
     } else {
         e = lgml_launch(rmsnorm_any_kernel<TD, TO>, n_rows, GROUP, 0, stream, a);
     }
