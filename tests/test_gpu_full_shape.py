@@ -27,7 +27,7 @@ SHAPE = {
 }
 
 
-def two_runners():
+def two_runners(n_pages=24, max_position=None):
     """The same random model twice: bfloat16, and float32 holding the bfloat16 values."""
     from lgml_b200 import ops
     from lgml_b200.config import config_from_dict
@@ -36,7 +36,7 @@ def two_runners():
     from lgml_b200.models import build_model
     from lgml_b200.weights.loader import target_dtype
 
-    cfg = config_from_dict(SHAPE)
+    cfg = config_from_dict({**SHAPE, **({"max_position_embeddings": max_position} if max_position else {})})
     runners = {}
     half = {}
     for dtype in (torch.bfloat16, torch.float32):
@@ -54,7 +54,7 @@ def two_runners():
                 t = half[s.name].to(target_dtype(s.kind, dtype))
             tensors[s.name] = t
         model.bind(tensors, rt)
-        runners[dtype] = ModelRunner(model, rt, n_pages=24, max_slots=2, max_step_tokens=1024)
+        runners[dtype] = ModelRunner(model, rt, n_pages=n_pages, max_slots=2, max_step_tokens=1024)
     return cfg, runners
 
 
@@ -88,3 +88,33 @@ def test_bfloat16_against_32_bit_at_full_layer_sizes():
     # the two paths rank the vocabulary alike: the 32-bit path's first choice is within bfloat16's error of the other's best
     top = ref.argmax(dim=1)
     assert bool(((got.max(dim=1).values - got[torch.arange(got.shape[0]), top]) <= 2e-2 * scale).all())
+
+
+def test_long_context_then_decoding_across_a_page_edge():
+    """4,100 tokens in portions of 1,024 (the keys of 65 pages, split over key ranges when
+    decoding), then 70 tokens one by one through the captured step, across the edge of a page
+    (position 4,160): the bfloat16 path stays with the 32-bit path all the way."""
+    cfg, runners = two_runners(n_pages=70, max_position=8192)
+    g = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, cfg.vocab_size, (4100 + 70,), generator=g).tolist()
+    out = {}
+    for dtype, r in runners.items():
+        req = r.open("long")
+        rows = []
+        for p in range(0, 4100, 1024):
+            part = ids[p:min(p + 1024, 4100)]
+            rows.append(r.step([(req, part, [len(part) - 1])]).float().cpu())
+        for i in range(70):
+            lg = r.step([(req, ids[4100 + i:4101 + i], [0])])
+            if i in (0, 1, 2, 58, 59, 60, 61, 69):              # around the first steps and the page's edge
+                rows.append(lg.float().cpu())
+        r.rt.check_status()
+        assert req.n_tokens == 4170
+        r.close(req)
+        out[dtype] = torch.cat(rows)
+    ref, got = out[torch.float32], out[torch.bfloat16]
+    assert torch.isfinite(got).all() and torch.isfinite(ref).all()
+    scale = float(ref.abs().max())
+    diff = (got - ref).abs()
+    assert float(diff.max()) <= 2e-2 * scale, (float(diff.max()), scale)
+    assert float(diff.mean()) <= 3e-3 * scale, (float(diff.mean()), scale)
