@@ -428,11 +428,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
 //   empty_bar[s]  (each CTA)  the products have read stage s (tcgen05.commit, multicast to both)
 //   acc_full[a]   (each CTA)  accumulator a is complete (commit, multicast to both)
 //   acc_empty[a]  (leader)    both CTAs' epilogue threads have read accumulator a (256 arrivals)
-constexpr int PAIR_BN = 256;               // columns of the pair's tile
-constexpr int PAIR_HALF = PAIR_BN / 2;     // rows of B each CTA loads
+// PBN: columns of the pair's tile (256, or 192 or 128 when 256 would leave pairs idle); each CTA
+// loads PBN / 2 rows of B.
 constexpr int PAIR_KSUB = 2;               // 64-element k blocks per stage
-constexpr int PAIR_A_BYTES = BM * BK * 2, PAIR_B_BYTES = PAIR_HALF * BK * 2;     // one k block of each operand
-constexpr int PAIR_STAGE_BYTES = PAIR_KSUB * (PAIR_A_BYTES + PAIR_B_BYTES);       // [A k0][A k1]..[B k0][B k1]..
+constexpr int PAIR_A_BYTES = BM * BK * 2;                                          // one k block of A
+__host__ __device__ constexpr int pair_stage_bytes(int pbn) { return PAIR_KSUB * (PAIR_A_BYTES + (pbn / 2) * BK * 2); }   // [A k0][A k1]..[B k0][B k1]..
+constexpr int PAIR_ACC_COLS = 256;          // tensor-memory columns between the two accumulators
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -508,7 +509,7 @@ __device__ __forceinline__ uint32_t mapa_u32(const void *p, uint32_t rank) {
     return ra;
 }
 
-template <int STAGES, int PAIR_NACC>
+template <int PAIR_BN, int STAGES, int PAIR_NACC>
 __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b, const Params p) {
     pdl_trigger();
@@ -524,8 +525,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int n_kb = (p.k_blocks + PAIR_KSUB - 1) / PAIR_KSUB;      // stages per tile
     const int n_tiles = p.tiles_a * p.tiles_b;          // tiles of 256 x 256
-    constexpr uint32_t ACC_COLS = PAIR_BN;
+    constexpr int PAIR_HALF = PAIR_BN / 2, PAIR_B_BYTES = PAIR_HALF * BK * 2, PAIR_STAGE_BYTES = pair_stage_bytes(PAIR_BN);
+    constexpr uint32_t ACC_COLS = PAIR_ACC_COLS;
     constexpr uint32_t TMEM_COLS = ACC_COLS * PAIR_NACC;
+    static_assert(PAIR_BN % 32 == 0 && PAIR_BN <= 256 && PAIR_STAGE_BYTES % 1024 == 0, "tile width");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -758,7 +761,7 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, dim3 g
 // How many pairs of CTAs the device runs at one time (pairs need both SMs of a TPC, and not
 // every TPC of a part has two): the persistent grid is this many pairs, never more, or the
 // rest would wait for a second round.  0 if the query fails.
-template <int STAGES, int NACC>
+template <int PBN, int STAGES, int NACC>
 int pairs_at_once(size_t smem) {
     static int n = -1;
     if (n < 0) {
@@ -774,36 +777,47 @@ int pairs_at_once(size_t smem) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<STAGES, NACC>, &cfg);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<PBN, STAGES, NACC>, &cfg);
         n = (e == cudaSuccess && clusters > 0) ? clusters : 0;
         if (e != cudaSuccess) cudaGetLastError();
     }
     return n;
 }
 
-template <int STAGES, int NACC>
+template <int PBN, int STAGES, int NACC>
 int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, int n_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)STAGES * PAIR_STAGE_BYTES + 1024;
+    const size_t smem = (size_t)STAGES * pair_stage_bytes(PBN) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<STAGES, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<PBN, STAGES, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    const int at_once = pairs_at_once<STAGES, NACC>(smem);
+    const int at_once = pairs_at_once<PBN, STAGES, NACC>(smem);
     if (at_once <= 0) LGML_FAIL("gemm_tcgen05: the device runs no pair of CTAs of this kernel");
-    int n_pairs = n_tiles < at_once ? n_tiles : at_once;
-    {
-        static int forced = -1;
-        if (forced < 0) {
-            const char *e = getenv("LGML_GEMM_PAIRS");
-            forced = e ? atoi(e) : 0;
-        }
-        if (forced > 0 && forced < n_pairs) n_pairs = forced;
-    }
-    cudaError_t e = lgml_launch_cluster(gemm_pair_kernel<STAGES, NACC>, dim3(2 * n_pairs), dim3(THREADS), smem, stream, 2, ma, mb, p);
+    const int n_pairs = n_tiles < at_once ? n_tiles : at_once;
+    cudaError_t e = lgml_launch_cluster(gemm_pair_kernel<PBN, STAGES, NACC>, dim3(2 * n_pairs), dim3(THREADS), smem, stream, 2, ma, mb, p);
     if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: launch of CTA pairs failed: %s", cudaGetErrorString(e));
     return lgml_launch_status("gemm_tcgen05 pairs");
+}
+
+// The width of the pairs' tiles for an M x N product: 256 unless a narrower tile fills the 74
+// pairs better (few tokens: 512 x 4096 is 32 tiles of 256 columns but 64 of 128).  The cost of a
+// tile is taken as its width plus a fixed part; a narrower tile must win by more than 5 %.
+int pair_tile_width(int M, int N) {
+    const int widths[3] = {256, 192, 128};
+    int best = 256;
+    double best_cost = 0;
+    for (int i = 0; i < 3; ++i) {
+        const int w = widths[i];
+        const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + w - 1) / w);
+        const double cost = (double)((tiles + 73) / 74) * (w + 40);
+        if (i == 0 || cost < 0.95 * best_cost) {
+            best = w;
+            best_cost = cost;
+        }
+    }
+    return best;
 }
 
 // LGML_GEMM_PAIR=0: never use CTA pairs (every product of many tokens on single CTAs).
@@ -820,9 +834,9 @@ bool pairs_enabled() {
 
 // Pairs of CTAs of the product for many tokens that the device runs at one time.
 LGML_API int lgml_gemm_pairs_at_once(void) {
-    const size_t smem = (size_t)3 * PAIR_STAGE_BYTES + 1024;
-    cudaFuncSetAttribute(gemm_pair_kernel<3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return pairs_at_once<3, 2>(smem);
+    const size_t smem = (size_t)3 * pair_stage_bytes(256) + 1024;
+    cudaFuncSetAttribute(gemm_pair_kernel<256, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return pairs_at_once<256, 3, 2>(smem);
 }
 
 // The tensor-memory addresses that the two CTAs of pair 0 got from their allocation in the last
@@ -890,12 +904,15 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         p.rows_a = M;
         p.rows_b = N;
         p.kb_per_split = k_blocks;
+        const int pbn = pair_tile_width(M, N);
         if ((rc = make_map(&ma, x, M, K, ldx, BM))) return rc;
-        if ((rc = make_map(&mb, w, N, K, ldw, PAIR_HALF))) return rc;
+        if ((rc = make_map(&mb, w, N, K, ldw, pbn / 2))) return rc;
         p.tiles_a = (M + 2 * BM - 1) / (2 * BM);
-        p.tiles_b = (N + PAIR_BN - 1) / PAIR_BN;
+        p.tiles_b = (N + pbn - 1) / pbn;
         const int n_tiles = p.tiles_a * p.tiles_b;
-        return launch_pair<3, 2>(ma, mb, p, n_tiles, stream);
+        if (pbn == 128) return launch_pair<128, 4, 2>(ma, mb, p, n_tiles, stream);
+        if (pbn == 192) return launch_pair<192, 4, 2>(ma, mb, p, n_tiles, stream);
+        return launch_pair<256, 3, 2>(ma, mb, p, n_tiles, stream);
     } else {
         bn = 256;
         p.transposed = 0;

@@ -154,6 +154,8 @@ def test_gemm_f32_is_exact_and_batch_invariant(M, N, K):
     (300, 648, 200, True, True, None), (700, 1200, 520, False, False, None),
     # 512 rows and more: pairs of CTAs on 256 x 256 tiles (edges in every direction, several tiles per pair)
     (512, 256, 64, False, False, None), (777, 1000, 328, True, True, None), (1500, 40 * 256 + 8, 136, True, False, None),
+    # narrower tiles where 256 columns would leave pairs idle: 192 (512 x 6144: 64 tiles) and 128 (512 x 4096)
+    (512, 6144 - 16, 200, True, False, None), (500, 4000, 136, False, True, None),
 ])
 def test_gemm_tcgen05(M, N, K, bias, f32, splits):
     from lgml_b200 import ops
