@@ -16,16 +16,24 @@
 // float32 sums hold without loss.  So a page costs one read of its scores from tensor memory
 // and nothing for the output; O is read once, at the end, and divided by the row's sum.
 // Q, K, V and P sit in shared memory in the 128-byte-swizzled layout the tensor core reads.
-// The 8 warps have two roles.  Warps 0-3 do the softmax (one thread per row).  Warps 4-7 copy
-// the pages with cp.async (K two pages ahead, V one) and their first thread issues the
-// products: the scores of page i+1 go right behind the P V product of page i, into a second S
-// buffer; they also do the rare corrections of O.  Two CTAs share an SM, so that one's
-// products overlap the other's softmax.  CTAs are started with the longest
-// tiles first (the caller orders them).  Keys are taken from the cache, so this step's own
-// keys are seen at cache precision, as in mischief/lgml, which writes the cache before
-// attention reads it (lua/lgml/transformer.lua:1838-1839, :2405-2407; formula :1805-1816,
-// scale :1845).  Waits on mbarriers are bounded.
+// Warps 0-3 do the softmax (one thread per row).  For head sizes that are multiples of 64 the
+// pages come by TMA (a page of one head is then whole 64 x 64 boxes of the cache tensor): one
+// thread of warp 5 issues the copies (K two pages ahead, V one), one thread of warp 4 the
+// products, the scores of page i+1 ahead of the P V product of page i, into a second S
+// buffer.  For other head sizes warps 4-7 copy the pages with cp.async and their first thread
+// issues the products.  Warps 4-7 also do the rare corrections of O, and all 8 warps write
+// the output.  Two CTAs share an SM, so that one's products overlap the other's softmax.  CTAs
+// are started with the longest tiles first (the caller orders them).  Keys are taken from the
+// cache, so this step's own keys are seen at cache precision, as in mischief/lgml, which writes
+// the cache before attention reads it (lua/lgml/transformer.lua:1838-1839, :2405-2407; formula
+// :1805-1816, scale :1845).  Waits on mbarriers are bounded.
+// A page takes this kernel about 3,400 cycles per CTA, of which the tensor core works 560: what
+// bounds it is the chain scores -> softmax (1,000 cycles) -> barrier -> issue of 12 small
+// products by one thread (1,200 cycles: about 80 a product, whatever its size) -> scores.
+#include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -45,6 +53,7 @@ constexpr uint32_t TMEM_COLS = 256;  // S of even pages: columns 0..63, of odd p
 constexpr uint32_t S1_COL = 64, O_COL = 128;
 constexpr float RESCALE_STEP = 8.f;  // the output is corrected only when a row's maximum has grown by more than this (base-2 units)
 constexpr int LOADERS = 128;         // threads of warps 4-7, which copy the pages
+constexpr int COPIER = 160;          // with TMA: the thread that issues the copies of the pages (first of warp 5)
 constexpr int ISSUER = 128;          // the thread that issues the tensor-core products (first of warp 4)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -62,6 +71,16 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// one 64 x 64 box (columns x0.., all 64 rows of (page, KV head) z) of a cache tensor into swizzled shared memory
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap *map, int x0, int z, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x0), "r"(0), "r"(z), "r"(smem_u32(bar))
+        : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -148,9 +167,13 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 
 // DP: head size padded to a multiple of 64 (the tensor core reads 64-element, 128-byte rows);
 // the pad columns of Q, K and V are zero.
-template <int DP>
+// TMA: the pages come by TMA (head sizes that are multiples of 64: a page of one head is then whole
+// 64 x 64 boxes), issued by the thread that issues the products; otherwise warps 4-7 copy them
+// with cp.async, 16 bytes a thread, which at this kernel's rate of pages is bound by the number
+// of requests L2 takes.
+template <int DP, bool TMA>
 __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
-    const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ tiles,
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ tiles,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int D,
     int hpc, float scale, int window, int *__restrict__ status) {
@@ -168,7 +191,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     // may be a page ahead of the warp that still adds up the page before
     float *corr_s = reinterpret_cast<float *>(Ps + P_BYTES);
     float *l_s = corr_s + 2 * ROWS;                             // [128] final sums
-    __shared__ uint64_t s_bar, o_bar;
+    __shared__ uint64_t s_bar, o_bar, k_full[2], v_full;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     volatile int *abort_flag = &abort_s;
@@ -192,6 +215,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     if (tid == 0) {
         mbar_init(&s_bar, 1);
         mbar_init(&o_bar, 1);
+        mbar_init(&k_full[0], 1);
+        mbar_init(&k_full[1], 1);
+        mbar_init(&v_full, 1);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -260,15 +286,36 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         const uint32_t dst = smem_u32(Vs);
         copy_page(dst, v_pages + off, valid_rows);
     };
+    // The same by TMA (one thread): the page's 64 x 64 boxes; what it reads of rows past the last
+    // key is dealt with where it matters (see the values below).
+    auto tma_k = [&](int it) {
+        const int page = table[pg_lo + it];
+        const bool have = page >= 0 && page < n_pages;
+        if (!have) atomicExch(status, 3);
+        uint64_t *bar = &k_full[it & 1];
+        mbar_expect_tx(bar, K_BYTES);
+        for (int b = 0; b < KB; ++b) tma_load_box(smem_u32(Ks + (it & 1) * K_BYTES) + b * (PAGE * 128), &map_k, b * 64, (have ? page : 0) * Hkv + kvh, bar);
+    };
+    auto tma_v = [&](int it) {
+        const int page = table[pg_lo + it];
+        const bool have = page >= 0 && page < n_pages;
+        mbar_expect_tx(&v_full, V_BYTES);
+        for (int b = 0; b < KB; ++b) tma_load_box(smem_u32(Vs) + b * (PAGE * 128), &map_v, b * 64, (have ? page : 0) * Hkv + kvh, &v_full);
+    };
     // The positions, tiles and block tables come from the host; everything else this kernel reads
     // (queries, this step's keys and values) is written by the kernels ahead of it.
     pdl_wait();
-    const bool loader = warp >= 4;            // warps 4-7 copy the pages; warps 0-3 do the softmax
+    const bool loader = !TMA && warp >= 4;    // without TMA warps 4-7 copy the pages; warps 0-3 do the softmax
     if (loader) {
         load_k(0);
         load_v(0);
         if (n_iter > 1) load_k(1);
         cp_async_commit();
+    }
+    if (TMA && tid == COPIER) {
+        tma_k(0);
+        tma_v(0);
+        if (n_iter > 1) tma_k(1);
     }
     // queries: row r = token (r / hpc), head g0 + (r % hpc); through L2, they were just written
     for (int c = tid; c < ROWS * chunks_d; c += THREADS) {
@@ -317,6 +364,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     fence_async_smem();
     __syncthreads();
     if (tid == ISSUER) {
+        if (TMA && alive && !mbar_wait(&k_full[0], 0, abort_flag, status)) alive = false;
         tcgen05_fence_after();
         issue_qk(0);
     }
@@ -368,6 +416,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             }
             corr_s[row] = corr;
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;    // keeps (-inf) - (-inf) out of the exponent
+            // With TMA the next page's scores are issued ahead of P V, so their arrival says nothing
+            // about that product: it must be done before P is written again (it mostly is by now).
+            if (TMA && it > 0 && alive && !mbar_wait(&o_bar, (it - 1) & 1, abort_flag, status)) alive = false;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t p_row = smem_u32(Ps) + (uint32_t)((row >> 3) * 1024 + (row & 7) * 128);   // this row of P
             const uint32_t p_xor = (uint32_t)(row & 7);
@@ -433,6 +484,52 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
                 }
                 tcgen05_fence_before();
                 asm volatile("bar.sync 1, 128;" ::: "memory");      // warps 4-7: all rows corrected before the product
+            }
+            if (TMA) {
+                // ---- the scores of the next page, then O += P V, then the next copies: warp 4 ---------------
+                // (the scores first: the next softmax waits for them and they need nothing of this one)
+                if (warp == 4) {
+                    if (lane == 0) {
+                        tcgen05_fence_after();
+                        if (it + 1 < n_iter) {
+                            if (alive && !mbar_wait(&k_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag, status)) alive = false;
+                            issue_qk(it + 1);
+                        }
+                        if (alive && !mbar_wait(&v_full, it & 1, abort_flag, status)) alive = false;
+                    }
+                    __syncwarp();
+                    // The values of rows past the tile's last key (the rest of its last page, or a
+                    // page the table does not hold) may be anything, NaN included, and 0 x NaN is NaN:
+                    // they become zeros.  (Keys there give scores that the softmax masks.)
+                    const int page = table[pg];
+                    const int valid_rows = (page >= 0 && page < n_pages) ? min(pos_last - pg * PAGE + 1, PAGE) : 0;
+                    if (valid_rows < PAGE) {
+                        for (int i = lane; i < (PAGE - valid_rows) * chunks_d; i += 32) {
+                            const int zr = valid_rows + i / chunks_d, ch = i % chunks_d;
+                            st_shared_16(smem_u32(Vs) + (ch >> 3) * (PAGE * 128) + swz(zr, ch & 7), 0u, 0u, 0u, 0u);
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                    }
+                    if (lane == 0) {
+#pragma unroll
+                        for (int k2 = 0; k2 < PAGE / 16; ++k2)
+                            tcgen05_mma_bf16(tmem_base + O_COL, desc_p0 + (uint64_t)((k2 * 32) >> 4), desc_v0 + (uint64_t)((k2 * 2048) >> 4), idesc_pv,
+                                             (it > 0 || k2 > 0) ? 1u : 0u);
+                        tcgen05_commit(&o_bar);
+                    }
+                    __syncwarp();
+                } else if (tid == COPIER) {
+                    // ---- the next copies, by a thread of their own (issuing a product or a copy
+                    // takes the issuing thread tens of cycles each: one thread for both was the
+                    // slowest part of a page) ----
+                    // the keys' stage of this page is free (its scores were seen before the barrier)
+                    if (it + 2 < n_iter) tma_k(it + 2);
+                    // the values' stage is free once the product has read it
+                    if (alive && !mbar_wait(&o_bar, it & 1, abort_flag, status)) alive = false;
+                    if (it + 1 < n_iter) tma_v(it + 1);
+                }
+                continue;
             }
             // ---- O += P V, and the scores of the next page behind it ---------------------------------------
             if (tid == ISSUER) {
@@ -501,16 +598,65 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     }
 }
 
-template <int DP>
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// The cache of one layer, [pages][KV heads][64][D] bfloat16, as a 3-dimensional tensor
+// (D, 64, pages x KV heads) read in boxes of 64 columns x 64 rows with the 128-byte swizzle.
+int make_page_map(CUtensorMap *map, const void *base, int n_pages, int Hkv, int D) {
+    EncodeTiledFn enc = encode_tiled();
+    if (enc == nullptr) LGML_FAIL("prefill_attention_tc: the driver has no cuTensorMapEncodeTiled");
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)PAGE, (cuuint64_t)n_pages * (cuuint64_t)Hkv};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)PAGE * D * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)PAGE, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) LGML_FAIL("prefill_attention_tc: cuTensorMapEncodeTiled failed with %d (pages %d, KV heads %d, head_dim %d)", (int)r, n_pages, Hkv, D);
+    return 0;
+}
+
+// LGML_ATTN_TMA=0: the pages are always copied with cp.async.
+bool tma_pages_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("LGML_ATTN_TMA");
+        on = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
+template <int DP, bool TMA>
 int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table, int max_blocks,
            const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D,
            int hpc, float scale, int window, int *status, cudaStream_t stream) {
     constexpr int KB = DP / 64;
     const size_t smem = (size_t)KB * ROWS * 128 + 3 * (size_t)KB * PAGE * 128 + ROWS * 128 + 3 * ROWS * sizeof(float) + 1024;
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<DP, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) LGML_FAIL("prefill_attention_tc: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    lgml_launch(prefill_attention_tc_kernel<DP>, grid, THREADS, smem, stream, q, ldq, positions, tiles, block_table, max_blocks, k_pages,
-                v_pages, n_pages, out, ldo, H, Hkv, D, hpc, scale, window, status);
+    CUtensorMap mk, mv;
+    memset(&mk, 0, sizeof(mk));
+    memset(&mv, 0, sizeof(mv));
+    if (TMA) {
+        int rc;
+        if ((rc = make_page_map(&mk, k_pages, n_pages, Hkv, D))) return rc;
+        if ((rc = make_page_map(&mv, v_pages, n_pages, Hkv, D))) return rc;
+    }
+    lgml_launch(prefill_attention_tc_kernel<DP, TMA>, grid, THREADS, smem, stream, mk, mv, q, ldq, positions, tiles, block_table, max_blocks,
+                k_pages, v_pages, n_pages, out, ldo, H, Hkv, D, hpc, scale, window, status);
     return lgml_launch_status("prefill_attention_tc");
 }
 }  // namespace
@@ -543,7 +689,9 @@ LGML_API int lgml_prefill_attention_tc(const void *q, int ldq, const int *positi
     dim3 grid(Hkv * chunks, n_tiles);
     const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
-    if (D <= 64)
-        return launch<64>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, D, hpc, scale, window, status, stream);
-    return launch<128>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, D, hpc, scale, window, status, stream);
+#define LGML_ARGS grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, D, hpc, scale, window, status, stream
+    const bool tma = tma_pages_enabled() && D % 64 == 0;     // a page of one head is then whole 64 x 64 boxes
+    if (D <= 64) return tma ? launch<64, true>(LGML_ARGS) : launch<64, false>(LGML_ARGS);
+    return tma ? launch<128, true>(LGML_ARGS) : launch<128, false>(LGML_ARGS);
+#undef LGML_ARGS
 }
