@@ -295,6 +295,39 @@ __global__ void __launch_bounds__(TK_THREADS) topk_rows_kernel(const float *__re
         out_vals[(size_t)blockIdx.x * k + j] = act_load(row + id);
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// The first two steps of the sampler's chain, in place on the rows of logits: the logit bias
+// (l[id] += b) and then the history penalties over the distinct ids of a request's recent
+// tokens (src/sample.c:1051-1053, apply_penalties :652-677): v = l[id]; v = v * repeat if
+// v <= 0 else v / repeat; l[id] = v - (count * frequency + presence), every step rounded to
+// float32.  One warp per row; the ids within a step are distinct, so its lanes do not collide.
+// edits: per row  [n_bias, n_hist, then n_bias x (id, value bits), then n_hist x (id, count)]
+// at offset row * stride (int32 words); params: per row (repeat, frequency, presence).
+// ---------------------------------------------------------------------------------------------
+__global__ void sampler_edits_kernel(float *__restrict__ logits, int ld, int V, const int *__restrict__ edits, int stride,
+                                     const float *__restrict__ params) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, lane = threadIdx.x;
+    float *row = logits + (size_t)r * ld;
+    const int *e = edits + (size_t)r * stride;
+    const int n_bias = e[0], n_hist = e[1];
+    for (int i = lane; i < n_bias; i += 32) {
+        const int id = e[2 + 2 * i];
+        if (id >= 0 && id < V) row[id] = __fadd_rn(row[id], __int_as_float(e[3 + 2 * i]));
+    }
+    __syncwarp();
+    const float rep = params[3 * r], freq = params[3 * r + 1], pres = params[3 * r + 2];
+    const int *h = e + 2 + 2 * n_bias;
+    for (int i = lane; i < n_hist; i += 32) {
+        const int id = h[2 * i];
+        if (id < 0 || id >= V) continue;
+        float v = row[id];
+        v = v <= 0.f ? __fmul_rn(v, rep) : __fdiv_rn(v, rep);
+        row[id] = __fsub_rn(v, __fadd_rn(__fmul_rn((float)h[2 * i + 1], freq), pres));
+    }
+}
 }  // namespace
 
 // scratch: n_rows * 32 floats and n_rows * 32 ints (lgml_argmax_scratch_words words in all).
@@ -330,4 +363,14 @@ LGML_API int lgml_topk_rows(const float *logits, int ld, int n_rows, int V, int 
     if (n_rows == 0) return 0;
     lgml_launch(topk_rows_kernel, n_rows, TK_THREADS, 0, stream, logits, ld, V, k, out_vals, out_ids);
     return lgml_launch_status("topk_rows");
+}
+
+// Bias and history penalties of the sampler's chain, in place (see sampler_edits_kernel for the
+// layout of `edits` and `params`).
+LGML_API int lgml_sampler_edits(float *logits, int ld, int n_rows, int V, const int *edits, int stride, const float *params,
+                                cudaStream_t stream) {
+    LGML_REQUIRE(n_rows >= 0 && V > 0 && ld >= V && stride >= 2, "sampler_edits: bad sizes");
+    if (n_rows == 0) return 0;
+    lgml_launch(sampler_edits_kernel, n_rows, 32, 0, stream, logits, ld, V, edits, stride, params);
+    return lgml_launch_status("sampler_edits");
 }

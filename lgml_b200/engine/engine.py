@@ -122,7 +122,10 @@ class Engine:
             rec.update(out=out, host=host, event=ev)
         elif all(e.request.params.top_k_on_device and e.request.params.top_k == rows[0].request.params.top_k for e in rows) \
                 and rows[0].request.params.top_k < logits.shape[1]:
-            # top_k on the device; the host runs the rest of the chain on k candidates per row, not on the row
+            # bias, penalties and top_k on the device; the host runs the rest of the chain on k
+            # candidates per row, not on the row
+            if any(e.request.params.edits_logits for e in rows):
+                logits = self._apply_edits(logits, rows)
             vals, ids = ops.topk_rows(logits, rows[0].request.params.top_k)
             vals, ids = vals.cpu().numpy(), ids.cpu().numpy()
             rec["toks"] = [int(e.request.sampler.sample_candidates(ids[i], vals[i])) for i, e in enumerate(rows)]
@@ -130,6 +133,25 @@ class Engine:
             host_logits = logits.cpu().numpy()
             rec["toks"] = [int(e.request.sampler.sample(host_logits[i])) for i, e in enumerate(rows)]
         return rec
+
+    def _apply_edits(self, logits: torch.Tensor, rows) -> torch.Tensor:
+        """The requests' logit biases and history penalties, applied to their rows on the device."""
+        import struct
+
+        per_row = [e.request.sampler.device_edits() for e in rows]
+        stride = 2 + 2 * max(len(b) + len(h) for b, h, _ in per_row)
+        edits = torch.zeros((len(rows), stride), dtype=torch.int32)
+        params = torch.empty((len(rows), 3), dtype=torch.float32)
+        for i, (bias, hist, pen) in enumerate(per_row):
+            flat = [len(bias), len(hist)]
+            for t, b in bias:
+                flat += [t, struct.unpack("<i", struct.pack("<f", b))[0]]
+            for t, c in hist:
+                flat += [t, c]
+            edits[i, :len(flat)] = torch.tensor(flat, dtype=torch.int32)
+            params[i] = torch.tensor(pen, dtype=torch.float32)
+        # in place: a row of logits belongs to one request and is not read again after its token is chosen
+        return ops.sampler_edits(logits, edits.to(logits.device), params.to(logits.device))
 
     def _resolve(self, rec: dict) -> List[GenRequest]:
         """Wait for the step's ids, check the status word, and tell the scheduler."""

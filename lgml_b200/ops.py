@@ -360,6 +360,22 @@ def topk_rows(logits: torch.Tensor, k: int, out_vals: Optional[torch.Tensor] = N
     return out_vals, out_ids
 
 
+def sampler_edits(logits: torch.Tensor, edits: torch.Tensor, params: torch.Tensor) -> torch.Tensor:
+    """In place on the rows of ``logits``: the sampler's logit bias, then its history penalties.
+    ``edits`` int32 [rows, stride]: per row (n_bias, n_hist, n_bias x (id, float bits of the
+    bias), n_hist x (id, count)); ``params`` float32 [rows, 3]: repeat, frequency, presence."""
+    _need(logits, "logits", torch.float32, 2)
+    _need(edits, "sampler edits", torch.int32, 2)
+    _need(params, "penalty parameters", torch.float32, 2)
+    ld = _rows_contiguous(logits, "logits")
+    n, v = logits.shape
+    if edits.shape[0] != n or tuple(params.shape) != (n, 3) or not edits.is_contiguous() or not params.is_contiguous():
+        raise KernelError("sampler_edits: one row of edits and of parameters per row of logits")
+    fn = _fn("sampling", "lgml_sampler_edits", [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p])
+    _check("sampling", fn(_ptr(logits), ld, n, v, _ptr(edits), edits.shape[1], _ptr(params), _stream()), "sampler_edits")
+    return logits
+
+
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """Row r: argmax if temperature[r] <= 0, else the inverse-CDF draw of
     softmax(logits[r] / temperature[r]) at uniform[r]."""

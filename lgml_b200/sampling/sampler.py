@@ -12,7 +12,9 @@ draw uses one double ``(next() >> 11) * 2^-53`` (``:126-130``).
 When the chain is *neutral* (no bias, no penalties, top_k 0, top_p 1, min_p 0) a draw
 is exactly "softmax(logits / T), inverse CDF in id order"; the engine then samples on
 the device with the uniform number this sampler supplies, and the host chain below is
-its plain twin.
+its plain twin.  With top_k set (the default chain) the device applies bias and penalties to
+the rows, picks the k best in this chain's order, and ``sample_candidates`` finishes the chain
+on those k pairs; a chain without top_k that sorts the whole row stays on the host.
 """
 from __future__ import annotations
 
@@ -112,11 +114,14 @@ class SamplingParams:
 
     @property
     def top_k_on_device(self) -> bool:
-        """top_k can be taken on the device and the rest of the chain run on its k candidates:
-        nothing alters the logits first, a draw follows, and k is within the kernel's reach."""
-        plain = (not self.logit_bias and self.repeat_penalty == 1.0 and self.frequency_penalty == 0.0
-                 and self.presence_penalty == 0.0)
-        return plain and self.temperature > 0.0 and 0 < self.top_k <= 128
+        """Bias, penalties and top_k can run on the device and the rest of the chain on the k
+        candidates: a draw follows, and k is within the kernel's reach."""
+        return self.temperature > 0.0 and 0 < self.top_k <= 128
+
+    @property
+    def edits_logits(self) -> bool:
+        """A bias or a penalty alters logits before top_k."""
+        return bool(self.logit_bias) or self.repeat_penalty != 1.0 or self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
 
     @property
     def is_neutral(self) -> bool:
@@ -146,6 +151,18 @@ class Sampler:
 
     def reset(self) -> None:
         self.hist.clear()
+
+    def device_edits(self):
+        """What the device needs to apply this sampler's bias and penalties to a row of logits:
+        ([(id, bias)], [(id, count)] over the distinct ids of the history, (repeat, frequency,
+        presence))."""
+        p = self.p
+        bias = [(int(t), float(b)) for t, b in (p.logit_bias or {}).items()]
+        counts: Dict[int, int] = {}
+        if p.repeat_penalty != 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0:
+            for t in self.hist:
+                counts[t] = counts.get(t, 0) + 1
+        return bias, list(counts.items()), (float(p.repeat_penalty), float(p.frequency_penalty), float(p.presence_penalty))
 
     def uniform(self) -> float:
         """The next uniform double of this request's stream (for the device draw)."""

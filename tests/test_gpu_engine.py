@@ -131,7 +131,7 @@ def test_launching_ahead_of_the_host_changes_no_reply(folders, key):
         assert sum(t["decode"] for t in ahead.turn_log) == sum(len(r.generated) - 1 for r in got)
 
 
-def test_full_sampler_chain_runs_on_host_logits(folders):
+def test_full_sampler_chain_is_reproducible_and_stops(folders):
     import lgml_b200
 
     folder = folders[("B", "bfloat16")]
@@ -145,24 +145,33 @@ def test_full_sampler_chain_runs_on_host_logits(folders):
     assert c[0] == a[0][: a[0].index(stop) + 1]
 
 
-def test_default_chain_takes_top_k_on_the_device(folders, monkeypatch):
-    """The reference's default chain (top_k 40, top_p 0.95, min_p 0.05, temperature 0.8): top_k
-    runs on the device and the host finishes on 40 candidates per row; the replies equal those
-    of the chain run on whole rows of logits."""
+def test_chains_with_top_k_run_on_the_device(folders, monkeypatch):
+    """The reference's default chain (top_k 40, top_p 0.95, min_p 0.05, temperature 0.8), and a
+    chain with a logit bias and all three history penalties: bias, penalties and top_k run on
+    the device and the host finishes on k candidates per row; the replies equal those of the
+    chain run on whole rows of logits on the host."""
     import lgml_b200
     from lgml_b200 import ops
+    from lgml_b200.sampling import SamplingParams
 
     folder = folders[("B", "float32")]
     prompts = [H.random_ids(n, 320, 500 + n) for n in (12, 31, 70)]
     eng = lgml_b200.Engine(str(folder), dtype="float32", slots=3)
-    calls = []
-    real = ops.topk_rows
-    monkeypatch.setattr(ops, "topk_rows", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
-    got = eng.generate(prompts, max_tokens=24, seed=21)                     # every option at its default
-    assert calls, "the default chain did not take the device path"
-    # the whole-row path: a bias of zero on one id changes no logit but keeps the chain on the host
-    want = eng.generate(prompts, max_tokens=24, seed=21, logit_bias={0: 0.0})
-    assert got == want and all(len(x) == 24 for x in got)
+    chains = [dict(), dict(top_k=25, temperature=1.1, repeat_penalty=1.3, frequency_penalty=0.2, presence_penalty=0.1, repeat_last_n=16,
+                           logit_bias={7: 2.5, 300: -4.0, 11: 0.75})]
+    for opts in chains:
+        calls = []
+        real_topk, real_edits = ops.topk_rows, ops.sampler_edits
+        monkeypatch.setattr(ops, "topk_rows", lambda *a, **k: (calls.append("topk"), real_topk(*a, **k))[1])
+        monkeypatch.setattr(ops, "sampler_edits", lambda *a, **k: (calls.append("edits"), real_edits(*a, **k))[1])
+        got = eng.generate(prompts, max_tokens=24, seed=21, **opts)
+        assert "topk" in calls and (("edits" in calls) == bool(opts)), calls
+        # the same chain on whole rows on the host
+        with monkeypatch.context() as m:
+            m.setattr(SamplingParams, "top_k_on_device", property(lambda self: False))
+            want = eng.generate(prompts, max_tokens=24, seed=21, **opts)
+        assert got == want and all(len(x) == 24 for x in got)
+        monkeypatch.undo()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -469,3 +469,39 @@ def test_topk_rows(V, k):
         nan_free = ~np.isnan(x[r].numpy()[order])
         assert np.array_equal(ids[r][nan_free], order[nan_free]), (r, ids[r][:8], order[:8])
         assert np.array_equal(vals[r][nan_free], x[r].numpy()[order][nan_free])
+
+
+def test_sampler_edits_match_the_host_sampler():
+    """Bias and history penalties on the device give, bit for bit, the logits the host sampler
+    works on."""
+    import numpy as np
+    from lgml_b200 import ops
+    from lgml_b200.sampling import Sampler, SamplingParams
+
+    g = torch.Generator().manual_seed(8)
+    V = 777
+    x = (torch.randn(3, V, generator=g) * 4)
+    samplers = [Sampler(SamplingParams(seed=1, repeat_penalty=1.3, frequency_penalty=0.25, presence_penalty=0.5, repeat_last_n=8, logit_bias={4: 1.5, 700: -3.0})),
+                Sampler(SamplingParams(seed=2)),
+                Sampler(SamplingParams(seed=3, repeat_penalty=0.8, logit_bias={0: 0.125}))]
+    for s, hist in zip(samplers, ([5, 4, 5, 5, 9, 700, 3, 3, 3, 12], [1, 2, 3], [0, 0, 776])):
+        for t in hist:
+            s.accept(t)
+    import struct
+    per_row = [s.device_edits() for s in samplers]
+    stride = 2 + 2 * max(len(b) + len(h) for b, h, _ in per_row)
+    edits = torch.zeros((3, stride), dtype=torch.int32)
+    params = torch.empty((3, 3), dtype=torch.float32)
+    for i, (bias, hist, pen) in enumerate(per_row):
+        flat = [len(bias), len(hist)]
+        for t, b in bias:
+            flat += [t, struct.unpack("<i", struct.pack("<f", b))[0]]
+        for t, c in hist:
+            flat += [t, c]
+        edits[i, :len(flat)] = torch.tensor(flat, dtype=torch.int32)
+        params[i] = torch.tensor(pen, dtype=torch.float32)
+    got = ops.sampler_edits(x.clone().to(DEV), edits.to(DEV), params.to(DEV)).cpu().numpy()
+    for i, s in enumerate(samplers):
+        s.p.temperature = 0.0                      # sample() then stops after bias and penalties
+        s.sample(x[i].numpy())
+        assert np.array_equal(got[i], s.last_logits), i

@@ -124,6 +124,11 @@ def test_candidates_from_top_k_give_the_same_draws_as_the_whole_row():
             want = a.sample(row)
             assert got == want
             a.accept(want), b.accept(got)
-    assert not SamplingParams(repeat_penalty=1.1).top_k_on_device
     assert not SamplingParams(temperature=0.0).top_k_on_device and not SamplingParams(top_k=0).top_k_on_device
-    assert not SamplingParams(logit_bias={3: 1.0}).top_k_on_device
+    assert SamplingParams(repeat_penalty=1.1).top_k_on_device and SamplingParams(repeat_penalty=1.1).edits_logits
+    assert SamplingParams(logit_bias={3: 1.0}).edits_logits and not SamplingParams().edits_logits
+    s = Sampler(SamplingParams(seed=1, repeat_penalty=1.2, repeat_last_n=4, logit_bias={5: 0.5}))
+    for t in (9, 3, 9, 9, 2):
+        s.accept(t)
+    bias, hist, pen = s.device_edits()
+    assert bias == [(5, 0.5)] and sorted(hist) == [(2, 1), (3, 1), (9, 2)] and pen == (1.2, 0.0, 0.0)
