@@ -221,15 +221,11 @@ class Sampler:
                 order = np.lexsort((ids, -vals.astype(np.float64)))
                 ids, vals, is_sorted = ids[order], vals[order], True
             w = np.exp((vals - vals[0]).astype(np.float32)).astype(np.float32)
-            total = np.float32(0)
-            for x in w:                                    # float32 running sums, as apply_top_p (:808-831)
-                total = np.float32(total + x)
-            cum, keep = np.float32(0), len(w)
-            for i, x in enumerate(w):
-                cum = np.float32(cum + np.float32(x / total))
-                if cum >= np.float32(p.top_p):
-                    keep = i + 1
-                    break
+            # float32 running sums, as apply_top_p (:808-831); cumsum adds in order in the array's type
+            total = np.cumsum(w, dtype=np.float32)[-1]
+            cum = np.cumsum((w / total).astype(np.float32), dtype=np.float32)
+            reached = np.flatnonzero(cum >= np.float32(p.top_p))
+            keep = int(reached[0]) + 1 if reached.size else len(w)
             ids, vals = ids[:keep], vals[:keep]
         if p.min_p > 0.0:
             thr = np.float32(vals.max() + np.float32(math.log(p.min_p)))   # apply_min_p (:834-852)
