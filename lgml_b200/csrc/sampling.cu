@@ -328,6 +328,71 @@ __global__ void sampler_edits_kernel(float *__restrict__ logits, int ld, int V, 
         row[id] = __fsub_rn(v, __fadd_rn(__fmul_rn((float)h[2 * i + 1], freq), pres));
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// The rest of the chain on the k candidates that top_k left (sorted: logit descending, id
+// ascending): top_p, min_p, temperature and the draw, one thread per row, every step in the
+// arithmetic of the host sampler (src/sample.c:808-877): top_p keeps the shortest prefix whose
+// float32 running sum of exp(l - l0) / total reaches p; min_p keeps logits >= l0 + ln(p);
+// the logits are divided by T in float32; the draw takes float32 weights exp(l / T - max),
+// sums them in float64 and picks the first candidate whose running sum reaches sum * u.
+// params per row: top_p, ln(min_p) (or -inf), T;  uniform per row: u in [0, 1).
+// ---------------------------------------------------------------------------------------------
+__global__ void sample_candidates_kernel(const float *__restrict__ vals, const int *__restrict__ ids, int k, const float *__restrict__ params,
+                                         const double *__restrict__ uniform, int *__restrict__ out, int n_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    const float *v = vals + (size_t)r * k;
+    const int *id = ids + (size_t)r * k;
+    const float top_p = params[3 * r], log_min_p = params[3 * r + 1], T = params[3 * r + 2];
+    if (!(T > 0.f)) {             // the argmax: the first candidate (ties went to the lowest id)
+        out[r] = __ldcg(id);
+        return;
+    }
+    const float v0 = act_load(v);
+    int keep = k;
+    if (top_p < 1.0f) {
+        float total = 0.f;
+        for (int i = 0; i < k; ++i) total = __fadd_rn(total, expf(__fsub_rn(act_load(v + i), v0)));
+        float cum = 0.f;
+        for (int i = 0; i < k; ++i) {
+            cum = __fadd_rn(cum, __fdiv_rn(expf(__fsub_rn(act_load(v + i), v0)), total));
+            if (cum >= top_p) {
+                keep = i + 1;
+                break;
+            }
+        }
+    }
+    if (log_min_p > -INFINITY) {
+        const float thr = __fadd_rn(v0, log_min_p);
+        int n = 0;
+        while (n < keep && act_load(v + n) >= thr) ++n;       // sorted: the kept ones are a prefix
+        keep = n > 0 ? n : 1;
+    }
+    const float m = T != 1.0f ? __fdiv_rn(v0, T) : v0;
+    double sum = 0.0;
+    for (int i = 0; i < keep; ++i) {
+        const float l = T != 1.0f ? __fdiv_rn(act_load(v + i), T) : act_load(v + i);
+        sum += (double)expf(__fsub_rn(l, m));
+    }
+    const double tgt = sum * uniform[r];
+    double run = 0.0;
+    int pick = -1, last = 0;
+    for (int i = 0; i < keep; ++i) {
+        const float l = T != 1.0f ? __fdiv_rn(act_load(v + i), T) : act_load(v + i);
+        const float w = expf(__fsub_rn(l, m));
+        if (w <= 0.f) continue;
+        run += (double)w;
+        last = i;
+        if (run >= tgt) {
+            pick = i;
+            break;
+        }
+    }
+    out[r] = __ldcg(id + (pick >= 0 ? pick : last));
+}
 }  // namespace
 
 // scratch: n_rows * 32 floats and n_rows * 32 ints (lgml_argmax_scratch_words words in all).
@@ -373,4 +438,14 @@ LGML_API int lgml_sampler_edits(float *logits, int ld, int n_rows, int V, const 
     if (n_rows == 0) return 0;
     lgml_launch(sampler_edits_kernel, n_rows, 32, 0, stream, logits, ld, V, edits, stride, params);
     return lgml_launch_status("sampler_edits");
+}
+
+// vals, ids: [n_rows, k] from lgml_topk_rows; params float32 [n_rows, 3] = top_p, ln(min_p) or
+// -inf, temperature (<= 0: the first candidate); uniform float64 [n_rows]; out int32 [n_rows].
+LGML_API int lgml_sample_candidates(const float *vals, const int *ids, int n_rows, int k, const float *params, const double *uniform,
+                                    int *out, cudaStream_t stream) {
+    LGML_REQUIRE(n_rows >= 0 && k >= 1, "sample_candidates: bad sizes");
+    if (n_rows == 0) return 0;
+    lgml_launch(sample_candidates_kernel, (n_rows + 31) / 32, 32, 0, stream, vals, ids, k, params, uniform, out, n_rows);
+    return lgml_launch_status("sample_candidates");
 }

@@ -14,6 +14,7 @@ the host has seen the ids of the one before, when those are chosen on the device
 """
 from __future__ import annotations
 
+import math
 import time
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -114,16 +115,23 @@ class Engine:
                 us = torch.tensor([0.0 if e.request.params.greedy else e.request.sampler.uniform() for e in rows],
                                   dtype=torch.float64).pin_memory()
                 ops.sample_rows(logits, temps.to(logits.device, non_blocking=True), us.to(logits.device, non_blocking=True), out)
-            host = self._host_ring[self._host_turn % len(self._host_ring)]
-            self._host_turn += 1
-            host[:n + 1].copy_(res[MAX_RESULT - n:], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record()
-            rec.update(out=out, host=host, event=ev)
+            self._ids_to_host(rec, out)
+        elif n <= MAX_RESULT and self._candidates_on_device(rows, logits.shape[1]):
+            # top_k, then the rest of the chain on its candidates, all on the device: the ids stay
+            # there for the next step, as with the argmax
+            k = next(e.request.params.top_k for e in rows if not e.request.params.greedy)
+            vals, ids = ops.topk_rows(logits, k)
+            params = torch.tensor([[p.top_p, math.log(p.min_p) if p.min_p > 0.0 else -math.inf, p.temperature]
+                                   for p in (e.request.params for e in rows)], dtype=torch.float32).pin_memory()
+            us = torch.tensor([0.0 if e.request.params.greedy else e.request.sampler.uniform() for e in rows], dtype=torch.float64).pin_memory()
+            res = self.rt.result
+            out = res[MAX_RESULT - n:MAX_RESULT]
+            ops.sample_candidates(vals, ids, params.to(logits.device, non_blocking=True), us.to(logits.device, non_blocking=True), out)
+            self._ids_to_host(rec, out)
         elif all(e.request.params.top_k_on_device and e.request.params.top_k == rows[0].request.params.top_k for e in rows) \
                 and rows[0].request.params.top_k < logits.shape[1]:
             # bias, penalties and top_k on the device; the host runs the rest of the chain on k
-            # candidates per row, not on the row
+            # candidates per row, not on the row (the penalties need the ids the host has seen)
             if any(e.request.params.edits_logits for e in rows):
                 logits = self._apply_edits(logits, rows)
             vals, ids = ops.topk_rows(logits, rows[0].request.params.top_k)
@@ -133,6 +141,32 @@ class Engine:
             host_logits = logits.cpu().numpy()
             rec["toks"] = [int(e.request.sampler.sample(host_logits[i])) for i, e in enumerate(rows)]
         return rec
+
+    def _ids_to_host(self, rec: dict, out: torch.Tensor) -> None:
+        """Start the copy of the chosen ids and the status word after them to pinned memory."""
+        n = out.shape[0]
+        host = self._host_ring[self._host_turn % len(self._host_ring)]
+        self._host_turn += 1
+        host[:n + 1].copy_(self.rt.result[MAX_RESULT - n:], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        rec.update(out=out, host=host, event=ev)
+
+    @staticmethod
+    def _candidates_on_device(rows, vocab: int) -> bool:
+        """Every row's chain is top_k and what follows it (or the argmax), with one k for all and
+        nothing that alters the logits first."""
+        ks = set()
+        for e in rows:
+            p = e.request.params
+            if p.edits_logits:
+                return False
+            if p.greedy:
+                continue
+            if not p.top_k_on_device:
+                return False
+            ks.add(p.top_k)
+        return len(ks) == 1 and next(iter(ks)) < vocab
 
     def _apply_edits(self, logits: torch.Tensor, rows) -> torch.Tensor:
         """The requests' logit biases and history penalties, applied to their rows on the device."""
@@ -208,11 +242,12 @@ class Engine:
 
     # ---- public --------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None, stop: Optional[Sequence[int]] = None,
-                 seed: Optional[int] = None, return_details: bool = False, **sampling):
+                 seed: Optional[int] = None, return_details: bool = False, per_prompt: Optional[Sequence[dict]] = None, **sampling):
         """Token ids in, token ids out.  ``prompts``: lists of token ids.  Sampler options
         (``temperature``, ``top_k``, ``top_p``, ``min_p``, ``repeat_penalty``,
         ``frequency_penalty``, ``presence_penalty``, ``repeat_last_n``, ``logit_bias``) and
         ``seed`` as in the sampler; request i draws from the stream of ``seed + i``.
+        ``per_prompt``: one dict of sampler options per prompt that override the common ones.
         Returns one list of new ids per prompt (with the stop id when one ends it)."""
         opts = {**self.sampling_defaults, **sampling}
         stop_ids = list(stop) if stop is not None else self.eos_ids
@@ -223,7 +258,7 @@ class Engine:
             p = [int(t) for t in p]
             room = self.scheduler.max_position - len(p)
             limit = max_tokens if max_tokens is not None else (self.default_max_tokens or room)
-            params = SamplingParams(seed=None if seed is None else seed + i, **opts)
+            params = SamplingParams(seed=None if seed is None else seed + i, **({**opts, **per_prompt[i]} if per_prompt else opts))
             req = GenRequest(id=("gen", self._next_id), prompt=p, max_new_tokens=max(min(limit, room), 0), params=params,
                              stop_ids=stop_ids)
             self._next_id += 1

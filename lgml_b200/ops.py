@@ -360,6 +360,24 @@ def topk_rows(logits: torch.Tensor, k: int, out_vals: Optional[torch.Tensor] = N
     return out_vals, out_ids
 
 
+def sample_candidates(vals: torch.Tensor, ids: torch.Tensor, params: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The chain after top_k on its candidates (``topk_rows``): top_p, min_p, temperature, draw.
+    ``params`` float32 [rows, 3]: top_p, ln(min_p) or -inf, temperature > 0; ``uniform`` float64
+    [rows]; ``out`` int32 [rows]."""
+    _need(vals, "candidate values", torch.float32, 2)
+    _need(ids, "candidate ids", torch.int32, 2)
+    _need(params, "chain parameters", torch.float32, 2)
+    _need(uniform, "uniform numbers", torch.float64, 1)
+    _need(out, "token output", torch.int32, 1)
+    n, k = vals.shape
+    if tuple(ids.shape) != (n, k) or tuple(params.shape) != (n, 3) or uniform.numel() != n or out.numel() != n \
+            or not (vals.is_contiguous() and ids.is_contiguous() and params.is_contiguous()):
+        raise KernelError("sample_candidates: shapes disagree")
+    fn = _fn("sampling", "lgml_sample_candidates", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check("sampling", fn(_ptr(vals), _ptr(ids), n, k, _ptr(params), _ptr(uniform), _ptr(out), _stream()), "sample_candidates")
+    return out
+
+
 def sampler_edits(logits: torch.Tensor, edits: torch.Tensor, params: torch.Tensor) -> torch.Tensor:
     """In place on the rows of ``logits``: the sampler's logit bias, then its history penalties.
     ``edits`` int32 [rows, stride]: per row (n_bias, n_hist, n_bias x (id, float bits of the

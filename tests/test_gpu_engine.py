@@ -147,9 +147,10 @@ def test_full_sampler_chain_is_reproducible_and_stops(folders):
 
 def test_chains_with_top_k_run_on_the_device(folders, monkeypatch):
     """The reference's default chain (top_k 40, top_p 0.95, min_p 0.05, temperature 0.8), and a
-    chain with a logit bias and all three history penalties: bias, penalties and top_k run on
-    the device and the host finishes on k candidates per row; the replies equal those of the
-    chain run on whole rows of logits on the host."""
+    chain with a logit bias and all three history penalties.  The first runs on the device to
+    the chosen id (top_k, then the rest on its candidates), also beside a greedy request; for the
+    second, bias, penalties and top_k run on the device and the host finishes on k candidates
+    per row.  The replies equal those of the chain run on whole rows of logits on the host."""
     import lgml_b200
     from lgml_b200 import ops
     from lgml_b200.sampling import SamplingParams
@@ -161,17 +162,28 @@ def test_chains_with_top_k_run_on_the_device(folders, monkeypatch):
                            logit_bias={7: 2.5, 300: -4.0, 11: 0.75})]
     for opts in chains:
         calls = []
-        real_topk, real_edits = ops.topk_rows, ops.sampler_edits
+        real_topk, real_edits, real_rest = ops.topk_rows, ops.sampler_edits, ops.sample_candidates
         monkeypatch.setattr(ops, "topk_rows", lambda *a, **k: (calls.append("topk"), real_topk(*a, **k))[1])
         monkeypatch.setattr(ops, "sampler_edits", lambda *a, **k: (calls.append("edits"), real_edits(*a, **k))[1])
+        monkeypatch.setattr(ops, "sample_candidates", lambda *a, **k: (calls.append("rest"), real_rest(*a, **k))[1])
         got = eng.generate(prompts, max_tokens=24, seed=21, **opts)
-        assert "topk" in calls and (("edits" in calls) == bool(opts)), calls
+        assert "topk" in calls and (("edits" in calls) == bool(opts)) and (("rest" in calls) == (not opts)), calls
         # the same chain on whole rows on the host
         with monkeypatch.context() as m:
             m.setattr(SamplingParams, "top_k_on_device", property(lambda self: False))
             want = eng.generate(prompts, max_tokens=24, seed=21, **opts)
         assert got == want and all(len(x) == 24 for x in got)
         monkeypatch.undo()
+    # a greedy request beside two with the default chain: one batch, all chosen on the device
+    own = [{}, dict(temperature=0.0), {}]
+    calls = []
+    real_rest = ops.sample_candidates
+    monkeypatch.setattr(ops, "sample_candidates", lambda *a, **k: (calls.append("rest"), real_rest(*a, **k))[1])
+    got = eng.generate(prompts, max_tokens=12, seed=5, per_prompt=own)
+    assert calls
+    monkeypatch.undo()
+    alone = [eng.generate([p], max_tokens=12, seed=5 + i, **own[i])[0] for i, p in enumerate(prompts)]
+    assert got == alone
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -505,3 +505,34 @@ def test_sampler_edits_match_the_host_sampler():
         s.p.temperature = 0.0                      # sample() then stops after bias and penalties
         s.sample(x[i].numpy())
         assert np.array_equal(got[i], s.last_logits), i
+
+
+@pytest.mark.parametrize("k", [1, 40, 128])
+def test_sample_candidates_matches_the_host_sampler(k):
+    """top_p, min_p, temperature and the draw on top_k's candidates, on the device: the ids of
+    the host sampler given the same uniform numbers, over flat and peaked rows and every
+    combination of the three options being on or off; temperature 0 takes the first candidate."""
+    import math
+
+    import numpy as np
+    from lgml_b200 import ops
+    from lgml_b200.sampling import Sampler, SamplingParams
+
+    V, n = 5000, 96
+    g = torch.Generator().manual_seed(k)
+    scale = torch.tensor([0.3, 1.0, 4.0, 12.0]).repeat(n // 4)[:, None]
+    x = torch.randn(n, V, generator=g) * scale
+    x[5, :] = 0.5                                                       # one value everywhere
+    opts = [dict(top_p=tp, min_p=mp, temperature=T) for tp in (1.0, 0.95, 0.3) for mp in (0.0, 0.05, 0.6) for T in (1.0, 0.8, 2.5)]
+    chains = [SamplingParams(seed=100 + r, top_k=k, **opts[r % len(opts)]) for r in range(n)]
+    chains[7] = SamplingParams(seed=7, temperature=0.0)
+    vals, ids = ops.topk_rows(x.to(DEV), k)
+    params = torch.tensor([[c.top_p, math.log(c.min_p) if c.min_p > 0 else -math.inf, c.temperature] for c in chains], dtype=torch.float32)
+    us = torch.tensor([0.0 if c.greedy else Sampler(c).uniform() for c in chains], dtype=torch.float64)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample_candidates(vals, ids, params.to(DEV), us.to(DEV), out)
+    got = out.cpu().tolist()
+    vals, ids = vals.cpu().numpy(), ids.cpu().numpy()
+    want = [int(ids[r][0]) if c.greedy else Sampler(c).sample_candidates(ids[r], vals[r]) for r, c in enumerate(chains)]
+    assert got == want, [(r, a, b) for r, (a, b) in enumerate(zip(got, want)) if a != b]
+    assert len(set(got)) > 1 if k > 1 else True
