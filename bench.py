@@ -37,9 +37,19 @@ LLAMA31_8B = {
     "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False,
     "max_position_embeddings": 4096, "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
+# Two further shapes for --shape (the default run and its record are the first one's): their
+# batch, prompt length and context follow the workloads they are quoted with.
+LLAMA32_3B = {**LLAMA31_8B, "num_hidden_layers": 28, "hidden_size": 3072, "num_attention_heads": 24, "intermediate_size": 8192,
+              "tie_word_embeddings": True, "rope_scaling": {**LLAMA31_8B["rope_scaling"], "factor": 32.0}}
+LLAMA2_13B = {**LLAMA31_8B, "num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 40,
+              "intermediate_size": 13824, "vocab_size": 32000, "rope_theta": 10000.0, "rope_scaling": None}
+SHAPES = {"llama31_8b": ("Llama-3.1-8B shape", LLAMA31_8B, 8, 2048, 4096),
+          "llama32_3b": ("Llama-3.2-3B shape", LLAMA32_3B, 32, 2048, 4096),
+          "llama2_13b": ("Llama-2-13B shape", LLAMA2_13B, 16, 3584, 4096)}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 BATCH = 8
+PREFILL_TOKENS = 2048
 
 
 def peaks():
@@ -166,13 +176,13 @@ def run_prefill(runner, cfg, reps: int = 3, seed: int = 1):
     g = torch.Generator().manual_seed(seed)
     best = None
     for i in range(reps + 1):
-        ids = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist()
+        ids = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
         r = runner.open(("prefill", i))
         try:
             torch.cuda.synchronize()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            runner.step([(r, ids, [PROMPT_LEN - 1])])
+            runner.step([(r, ids, [PREFILL_TOKENS - 1])])
             end.record()
             torch.cuda.synchronize()
             ms = start.elapsed_time(end)
@@ -191,6 +201,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in the record)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--shape", default="llama31_8b", choices=list(SHAPES), help="layer sizes and workload (the default is the headline's)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -209,14 +220,17 @@ def main() -> int:
     from lgml_b200.config import config_from_dict
     from lgml_b200.engine.runner import ModelRunner
 
-    d = dict(LLAMA31_8B)
+    global BATCH, PROMPT_LEN, CONTEXT
+    shape_name, shape, BATCH, PROMPT_LEN, CONTEXT = SHAPES[args.shape]
+    d = dict(shape)
     full_layers = d["num_hidden_layers"]
     if args.layers:
         d["num_hidden_layers"] = args.layers
     cfg = config_from_dict(d)
     hbm_gbs, bf16_tflops, peak_src = peaks()
-    n_pages = 64 * (CONTEXT // 64) + 8           # room for 64 requests of the benchmark context
-    runner = ModelRunner.from_config(cfg, seed=0, dtype=torch.bfloat16, n_pages=n_pages, max_slots=64, max_step_tokens=PROMPT_LEN)
+    points_too = args.shape == "llama31_8b" and not args.skip_points
+    n_pages = (64 if points_too else BATCH) * (CONTEXT // 64) + 8     # room for 64 requests of the benchmark context
+    runner = ModelRunner.from_config(cfg, seed=0, dtype=torch.bfloat16, n_pages=n_pages, max_slots=max(64, BATCH), max_step_tokens=2048)
 
     prefill_ms = run_prefill(runner, cfg)
     clocks = ClockSampler()
@@ -224,7 +238,7 @@ def main() -> int:
     ms_step, kv_tokens, launches = run_decode(runner, cfg, BATCH, args.steps, warmup)
     clock_rec = clocks.stop()
     points = {}
-    if not args.skip_points:
+    if points_too:
         for b, k in ((1, min(args.steps, 64)), (64, min(args.steps, 32))):
             ms_b, _, _ = run_decode(runner, cfg, b, k, warmup)
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
@@ -233,8 +247,8 @@ def main() -> int:
     kv_bytes = kv_tokens * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * cfg.num_hidden_layers
     step_bytes = weight_bytes(cfg) + kv_bytes
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
-    pf_flops = step_flops(cfg, PROMPT_LEN, [PROMPT_LEN])
-    prefill = {"value": round(PROMPT_LEN * 1000.0 / prefill_ms, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 3),
+    pf_flops = step_flops(cfg, PREFILL_TOKENS, [PREFILL_TOKENS])
+    prefill = {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
                "frac": round(pf_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12), 4)}
 
     # end to end through the Python entry point, on the same weights
@@ -257,11 +271,11 @@ def main() -> int:
             e2e = r
 
     rec = {
-        "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, 2,048-token prompts, context 4,096)",
+        "metric": f"decode tok/s at batch {BATCH} ({shape_name}, {PROMPT_LEN:,}-token prompts, context {CONTEXT:,})",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform-random token ids",
-        "config": {"model": "Llama-3.1-8B shape", "layers": cfg.num_hidden_layers, "layers_of_model": full_layers,
+        "config": {"model": shape_name, "layers": cfg.num_hidden_layers, "layers_of_model": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page": 64, "parallelism": "single GPU",

@@ -27,7 +27,18 @@ SHAPE = {
 }
 
 
-def two_runners(n_pages=24, max_position=None):
+# The other two full shapes that the engine is measured at: 24 heads in 8 groups on a width of
+# 3,072 with tied embeddings; 40 heads with keys of their own (no groups), a width of 5,120 and
+# an intermediate size of 13,824 (neither a power of two nor a multiple of 4,096), plain rotary
+# angles and a small vocabulary.
+SHAPE_3B = {**SHAPE, "hidden_size": 3072, "num_attention_heads": 24, "intermediate_size": 8192, "tie_word_embeddings": True,
+            "rope_scaling": {**SHAPE["rope_scaling"], "factor": 32.0}}
+SHAPE_13B = {**SHAPE, "num_hidden_layers": 1, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 40,
+             "intermediate_size": 13824, "vocab_size": 32000, "rope_theta": 10000.0, "rope_scaling": None}
+SHAPES = {"8b": SHAPE, "3b": SHAPE_3B, "13b": SHAPE_13B}
+
+
+def two_runners(n_pages=24, max_position=None, shape=SHAPE):
     """The same random model twice: bfloat16, and float32 holding the bfloat16 values."""
     from lgml_b200 import ops
     from lgml_b200.config import config_from_dict
@@ -36,7 +47,7 @@ def two_runners(n_pages=24, max_position=None):
     from lgml_b200.models import build_model
     from lgml_b200.weights.loader import target_dtype
 
-    cfg = config_from_dict({**SHAPE, **({"max_position_embeddings": max_position} if max_position else {})})
+    cfg = config_from_dict({**shape, **({"max_position_embeddings": max_position} if max_position else {})})
     runners = {}
     half = {}
     for dtype in (torch.bfloat16, torch.float32):
@@ -58,8 +69,9 @@ def two_runners(n_pages=24, max_position=None):
     return cfg, runners
 
 
-def test_bfloat16_against_32_bit_at_full_layer_sizes():
-    cfg, runners = two_runners()
+@pytest.mark.parametrize("shape", list(SHAPES))
+def test_bfloat16_against_32_bit_at_full_layer_sizes(shape):
+    cfg, runners = two_runners(shape=SHAPES[shape])
     g = torch.Generator().manual_seed(11)
     a = torch.randint(0, cfg.vocab_size, (640 + 3,), generator=g).tolist()
     b = torch.randint(0, cfg.vocab_size, (300 + 3,), generator=g).tolist()
