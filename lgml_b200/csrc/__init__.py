@@ -42,10 +42,11 @@ LIBRARIES: Dict[str, tuple] = {
     "gemm_tcgen05": ("gemm_tcgen05.cu", []),
     "attention_prefill": ("attention_prefill.cu", []),
     "attention_prefill_tc": ("attention_prefill_tc.cu", []),
+    "attention_prefill_twin": ("attention_prefill_twin.cu", []),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", []),
 }
 
-_HEADERS = ["common.cuh"]
+_HEADERS = ["common.cuh", "page_map.cuh"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 

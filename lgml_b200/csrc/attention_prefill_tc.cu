@@ -36,6 +36,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "page_map.cuh"
 
 LGML_DEFINE_LAST_ERROR(lgml_attention_prefill_tc)
 
@@ -599,36 +600,6 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
-// The cache of one layer, [pages][KV heads][64][D] bfloat16, as a 3-dimensional tensor
-// (D, 64, pages x KV heads) read in boxes of 64 columns x 64 rows with the 128-byte swizzle.
-int make_page_map(CUtensorMap *map, const void *base, int n_pages, int Hkv, int D) {
-    EncodeTiledFn enc = encode_tiled();
-    if (enc == nullptr) LGML_FAIL("prefill_attention_tc: the driver has no cuTensorMapEncodeTiled");
-    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)PAGE, (cuuint64_t)n_pages * (cuuint64_t)Hkv};
-    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)PAGE * D * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)PAGE, 1};
-    cuuint32_t elem[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) LGML_FAIL("prefill_attention_tc: cuTensorMapEncodeTiled failed with %d (pages %d, KV heads %d, head_dim %d)", (int)r, n_pages, Hkv, D);
-    return 0;
-}
-
 // LGML_ATTN_TMA=0: the pages are always copied with cp.async.
 bool tma_pages_enabled() {
     static int on = -1;
@@ -652,8 +623,8 @@ int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, con
     memset(&mv, 0, sizeof(mv));
     if (TMA) {
         int rc;
-        if ((rc = make_page_map(&mk, k_pages, n_pages, Hkv, D))) return rc;
-        if ((rc = make_page_map(&mv, v_pages, n_pages, Hkv, D))) return rc;
+        if ((rc = lgml_make_page_map(&mk, k_pages, n_pages, Hkv, D, "prefill_attention_tc"))) return rc;
+        if ((rc = lgml_make_page_map(&mv, v_pages, n_pages, Hkv, D, "prefill_attention_tc"))) return rc;
     }
     lgml_launch(prefill_attention_tc_kernel<DP, TMA>, grid, THREADS, smem, stream, mk, mv, q, ldq, positions, tiles, block_table, max_blocks,
                 k_pages, v_pages, n_pages, out, ldo, H, Hkv, D, hpc, scale, window, status);

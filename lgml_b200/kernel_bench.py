@@ -116,9 +116,9 @@ def case_prefill_attention(a) -> None:
     out = torch.empty_like(q)
     positions = torch.arange(T, dtype=torch.int32, device=DEV)
     table = torch.randperm(n_pages).to(torch.int32).reshape(1, n_pages).to(DEV)
-    tt = ops.prefill_tile_tokens(H, G) if a.mma else ops.prefill_tc_tile_tokens(H, G)
+    tt = ops.prefill_tile_tokens(H, G) if a.mma else (ops.prefill_tc_tile_tokens(H, G) if a.single else ops.prefill_twin_tile_tokens(H, G))
     tiles = torch.tensor([(0, t0, min(tt, T - t0), 0) for t0 in reversed(range(0, T, tt))], dtype=torch.int32, device=DEV)   # longest first
-    fn = ops.prefill_attention if a.mma else ops.prefill_attention_tc
+    fn = ops.prefill_attention if a.mma else (ops.prefill_attention_tc if a.single else ops.prefill_attention_twin)
     us = timed(lambda i: fn(q, positions, tiles, table, k, v, out, H, D ** -0.5, 0, status), 1, a.warmup, a.iters)
     flops = 4.0 * H * D * T * (T + 1) / 2
     print(f"prefill_attention ({'mma.sync' if a.mma else 'tcgen05'}) tokens={T} heads={H}/{G} head_dim={D}: {us:.2f} us, {flops / us / 1e6:.1f} TFLOP/s (causal), status {int(status.item())}")
@@ -169,6 +169,7 @@ def main(argv=None) -> int:
     p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--head-dim", type=int, default=128)
     p.add_argument("--mma", action="store_true", help="the mma.sync kernel instead of the tcgen05 one")
+    p.add_argument("--single", action="store_true", help="the tcgen05 kernel with one tile per CTA and one page per step")
     r = sub.add_parser("rmsnorm")
     r.add_argument("--rows", type=int, default=8)
     r.add_argument("--width", type=int, default=4096)

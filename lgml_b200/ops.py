@@ -638,12 +638,48 @@ def prefill_attention_tc(q: torch.Tensor, positions: torch.Tensor, tiles: torch.
     return out
 
 
+def prefill_twin_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
+    """Tokens per CTA of the two-tile tcgen05 prefill attention kernel: 2 x (128 rows / heads per CTA)."""
+    return 2 * (128 // min(n_heads // n_kv_heads, 8))
+
+
+def prefill_attention_twin(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor,
+                           k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                           status: torch.Tensor) -> torch.Tensor:
+    """bfloat16 attention for prompts and portions on tcgen05 tensor cores, two tiles of 128
+    rows per CTA and two pages per step (scores, P and the output in tensor memory), for head
+    sizes 64 and 128.  ``tiles`` as for ``prefill_attention``, each at most
+    ``prefill_twin_tile_tokens`` long."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    _need(positions, "positions", torch.int32, 1)
+    _need(tiles, "tiles", torch.int32, 2)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4:
+        raise KernelError(f"prefill_attention_twin: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
+        raise KernelError("prefill_attention_twin: pages, block table and tiles must be contiguous")
+    fn = _fn("attention_prefill_twin", "lgml_prefill_attention_twin", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                                       c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check("attention_prefill_twin", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
+                                        _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
+                                        int(window or 0), _ptr(status), _stream()), "prefill_attention_twin")
+    return out
+
+
 def prefill_tc_supports(q: torch.Tensor, out: torch.Tensor) -> bool:
     """The tcgen05 kernel reads q and writes out in 16-byte pieces."""
     return q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
 
 
-# which kernel runs prompts and portions: "tcgen05" (default) or "mma" (the mma.sync kernel)
+# which kernel runs prompts and portions: "tcgen05" (default: two tiles per CTA for head sizes 64
+# and 128, one tile otherwise), "single" (one tile per CTA for every head size) or "mma" (the
+# mma.sync kernel)
 PREFILL_ATTENTION = os.environ.get("LGML_PREFILL_ATTENTION", "tcgen05")
 
 # a portion of at most this many tokens per request is run by the decode kernel
@@ -661,7 +697,10 @@ def paged_attention(q, batch, cache, out, n_heads: int, scale: float, window: in
             n_splits = batch.decode_splits if getattr(batch, "decode_splits", None) else decode_splits(q.shape[0], hkv, n_heads // hkv, batch.max_kv_len)
             return decode_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
                                     window, status, n_splits, max_new_tokens=batch.max_q_len)
-        if d <= 128 and PREFILL_ATTENTION == "tcgen05" and prefill_tc_supports(q, out):
+        if d in (64, 128) and PREFILL_ATTENTION == "tcgen05" and prefill_tc_supports(q, out):
+            tiles = batch.attention_tiles(prefill_twin_tile_tokens(n_heads, hkv))
+            return prefill_attention_twin(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window, status)
+        if d <= 128 and PREFILL_ATTENTION in ("tcgen05", "single") and prefill_tc_supports(q, out):
             tiles = batch.attention_tiles(prefill_tc_tile_tokens(n_heads, hkv))
             return prefill_attention_tc(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window, status)
         if d <= 128:

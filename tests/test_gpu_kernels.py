@@ -364,6 +364,9 @@ def run_attention(kind, case, window, n_splits=None):
     elif kind == "prefill_tc":
         tiles = b.attention_tiles(ops.prefill_tc_tile_tokens(H, case["G"]))
         ops.prefill_attention_tc(q, b.positions, tiles, tab, kp, vp, out, H, scale, window, st)
+    elif kind == "prefill_twin":
+        tiles = b.attention_tiles(ops.prefill_twin_tile_tokens(H, case["G"]))
+        ops.prefill_attention_twin(q, b.positions, tiles, tab, kp, vp, out, H, scale, window, st)
     else:
         tiles = b.attention_tiles(ops.prefill_tile_tokens(H, case["G"]))
         ops.prefill_attention(q, b.positions, tiles, tab, kp, vp, out, H, scale, window, st)
@@ -397,11 +400,21 @@ def test_attention_prefill_kernel(H, G, D, window, kind):
     assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("H,G,D", [(8, 1, 64), (12, 4, 128), (16, 1, 64), (6, 2, 128), (3, 3, 64), (5, 5, 128), (32, 2, 64)])
+@pytest.mark.parametrize("window", [0, 90, 200])
+def test_attention_prefill_twin_kernel(H, G, D, window):
+    """Two tiles per CTA, two pages per step: full and partly filled tiles, a second tile with
+    one token, steps with one page, portions that start inside a page and far from it."""
+    case = make_attention_case(3, H, G, D, kv_lens=[300, 70, 1, 129, 64, 515, 260], q_lens=[300, 33, 1, 65, 2, 130, 257], dtype=torch.bfloat16)
+    got, want = run_attention("prefill_twin", case, window)
+    assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
+
+
 def test_attention_finds_the_far_key():
     """The aimed query's output is that key's value, in every kernel."""
     case = make_attention_case(4, 4, 2, 64, kv_lens=[500], q_lens=[1], dtype=torch.bfloat16)
     far = 500 - 67
-    for kind, splits in (("ref", None), ("decode", 4), ("prefill", None), ("prefill_tc", None)):
+    for kind, splits in (("ref", None), ("decode", 4), ("prefill", None), ("prefill_tc", None), ("prefill_twin", None)):
         got, _ = run_attention(kind, case, 0, splits)
         for h in range(4):
             v_far = case["vs"][0][far, h // 2]
