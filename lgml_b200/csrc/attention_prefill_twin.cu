@@ -46,16 +46,16 @@ LGML_DEFINE_LAST_ERROR(lgml_attention_prefill_twin)
 
 namespace {
 constexpr int PAGE = 64;
-constexpr int STEP_KEYS = 2 * PAGE;  // keys per step
+constexpr int STAGES = 4;            // pages of keys, and of values, in shared memory
 constexpr int ROWS = 128;            // query rows per tile = UMMA M
-constexpr int THREADS = 384;         // warps 0-3: softmax of tile 0; 4-7: of tile 1; 8: products; 9: copies; 10, 11: help with the queries
-constexpr int ISSUE_WARP = 8, COPY_WARP = 9;
+constexpr int THREADS = 384;         // warps 0-3: softmax of tile 0; 4-7: of tile 1; 8, 9: the products of tile 0, 1; 10: copies; 11: zeros behind the last value
+constexpr int ISSUE_WARP = 8, COPY_WARP = 10, HELP_WARP = 11, HELPERS = 32;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;   // polls of up to WAIT_HINT_NS each: about a second
 constexpr uint32_t WAIT_HINT_NS = 1000;
 constexpr uint32_t POLL_SLEEP_NS = 64;
 constexpr int STATUS_TIMEOUT = 13;
-constexpr uint32_t TMEM_COLS = 512;  // S (and P) of tile t: columns 128 t ..; the output O of tile t: 256 + 128 t ..
-constexpr uint32_t O_COL = 256;
+constexpr uint32_t TMEM_COLS = 512;  // tile t: columns 256 t ..: two buffers of scores (and P) of 64 columns, then the output O
+constexpr uint32_t TILE_COLS = 256, O_COL = 128;
 constexpr float RESCALE_STEP = 8.f;  // the output is corrected only when a row's maximum has grown by more than this (base-2 units)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -92,6 +92,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // false: the wait ran out (the status word says so) or another thread's did
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
+    {
+        // most phases waited for here are over already: a test that cannot suspend the thread
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u && *abort_flag) return false;
@@ -145,6 +155,12 @@ __device__ __forceinline__ void tcgen05_st_16(uint32_t taddr, const uint32_t (&r
         : "memory");
 }
 __device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// the largest of three in one instruction (NaN operands are passed over, as by fmaxf)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 // 2^x in one instruction; 2^(-inf) = 0
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -174,20 +190,22 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-// A wait of a whole warp: every lane waits, and the warp goes on only if all lanes got through
+// A wait of a whole warp: its first lane waits (32 lanes polling one mbarrier take turns, some
+// 300 cycles even when the phase is long over) and tells the others, so the warp goes on as one
 // (loads and stores of tensor memory behind it are instructions of the whole warp).
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status) {
-    const bool ok = mbar_wait(bar, parity, abort_flag, status);
-    return __all_sync(0xffffffffu, ok);
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // P = 2^(S scale - m) of one row as bfloat16 over the columns S came from: two a column, key 2 c
 // in the low half.  EDGE: keys outside c_lo..c_hi give 0 (whatever their score, NaN included).
 template <bool EDGE>
-__device__ __forceinline__ void write_p(const uint32_t (&r)[STEP_KEYS], uint32_t s_addr, float scale_log2, float neg_m, int c_lo, int c_hi,
+__device__ __forceinline__ void write_p(const uint32_t (&r)[PAGE], uint32_t s_addr, float scale_log2, float neg_m, int c_lo, int c_hi,
                                         float (&sum4)[4]) {
 #pragma unroll
-    for (int c0 = 0; c0 < STEP_KEYS; c0 += 32) {
+    for (int c0 = 0; c0 < PAGE; c0 += 32) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -215,14 +233,16 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     pdl_trigger();
     constexpr int KB = D / 64;                              // 64-element blocks along the head dimension
     constexpr uint32_t TILE_BYTES = KB * ROWS * 128;        // the queries of one tile: [KB][128 rows][128 B]
-    constexpr uint32_t K_STAGE = KB * STEP_KEYS * 128;      // [KB][128 keys][128 B]          (K-major: row = key)
-    constexpr uint32_t V_PAGE = KB * PAGE * 128;            // [KB][64 keys][128 B]           (N-major: 64 dims per row)
-    constexpr uint32_t V_STAGE = 2 * V_PAGE;                // [2 pages] of those
+    constexpr uint32_t PAGE_BYTES = KB * PAGE * 128;        // a page of keys [KB][64 keys][128 B] (K-major: row = key), or of values (N-major: 64 dims per row)
     constexpr int CHUNKS_D = D / 8;                         // 16-byte chunks of a row
     extern __shared__ uint8_t smem_raw[];
     uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *Qs = base, *Ks = Qs + 2 * TILE_BYTES, *Vs = Ks + 2 * K_STAGE;
-    __shared__ uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done[2];
+    uint8_t *Qs = base, *Ks = Qs + 2 * TILE_BYTES, *Vs = Ks + STAGES * PAGE_BYTES;
+    // k_full / v_full: a stage's copy has landed; k_empty / v_empty: the products that read it are
+    // done; s_full[t][b]: the scores in buffer b of tile t are there; p_full[t][b]: P is written
+    // over them; o_done[t]: one of the last two P V products of tile t is done; v_landed: the last page of
+    // values is there; v_fixed: zeros stand behind its last key.
+    __shared__ uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2][2], p_full[2][2], o_done[2], v_landed, v_fixed;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     volatile int *abort_flag = &abort_s;
@@ -239,20 +259,30 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     const int pos_first = positions[row0], pos_last = pos_first + n_tok - 1;
     const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     const int pg_lo = lo_first / PAGE, pg_hi = pos_last / PAGE;
-    const int n_steps = (pg_hi - pg_lo + 2) / 2;                  // two pages a step; the last step may hold one
+    const int n_steps = pg_hi - pg_lo + 1;                        // a page a step
     const int n_act = n_tok > tt ? 2 : 1;                         // tiles that hold tokens
     const float scale_log2 = scale * 1.4426950408889634f;
+    // The last page's values behind the last key may be anything, NaN included, and 0 x NaN is
+    // NaN: they become zeros before the product reads them.  (Keys there give scores that the
+    // softmax masks.)
+    const int last_rows = pos_last - pg_hi * PAGE + 1;            // rows of the last page that hold keys
+    const bool fix_last = last_rows < PAGE;
 
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < STAGES; ++i) {
             mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
+            mbar_init(&k_empty[i], n_act);        // a commit of each tile's issuing thread
             mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], ROWS);
-            mbar_init(&o_done[i], 1);
+            mbar_init(&v_empty[i], n_act);
         }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&s_full[i >> 1][i & 1], 1);
+            mbar_init(&p_full[i >> 1][i & 1], ROWS);
+        }
+        mbar_init(&o_done[0], 1);
+        mbar_init(&o_done[1], 1);
+        mbar_init(&v_landed, 1);
+        mbar_init(&v_fixed, HELPERS);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -262,51 +292,35 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    // The pages of step j: table entries pg_lo + 2 j and, if the range still holds it, the next.
-    // A page the table does not name is an error of the caller (status 3); page 0 is read in its
-    // place and all its keys are masked.
-    auto page_of = [&](int pg, bool &have) -> int {
-        if (pg > pg_hi) {
-            have = false;
-            return -1;
-        }
-        const int page = table[pg];
-        have = page >= 0 && page < n_pages;
-        return have ? page : 0;
+    // A page the table does not name is an error of the caller: the status word says so (3), the
+    // host raises, and page 0 is read in its place.
+    auto page_of = [&](int j) -> int {
+        const int page = table[pg_lo + j];
+        if (page >= 0 && page < n_pages) return page;
+        atomicExch(status, 3);
+        return 0;
     };
     auto copy_keys = [&](int j) {
-        const int s = j & 1, pg = pg_lo + 2 * j;
-        bool have0, have1;
-        const int page0 = page_of(pg, have0), page1 = page_of(pg + 1, have1);
-        if (!have0 || (!have1 && page1 == 0)) atomicExch(status, 3);
-        mbar_expect_tx(&k_full[s], (page1 >= 0 ? 2u : 1u) * (uint32_t)(KB * PAGE * 128));
-        const uint32_t dst = smem_u32(Ks + s * K_STAGE);
-        for (int b = 0; b < KB; ++b) {
-            tma_load_box(dst + b * (STEP_KEYS * 128), &map_k, b * 64, page0 * Hkv + kvh, &k_full[s]);
-            if (page1 >= 0) tma_load_box(dst + b * (STEP_KEYS * 128) + PAGE * 128, &map_k, b * 64, page1 * Hkv + kvh, &k_full[s]);
-        }
+        const int s = j % STAGES, z = page_of(j) * Hkv + kvh;
+        mbar_expect_tx(&k_full[s], PAGE_BYTES);
+        for (int b = 0; b < KB; ++b) tma_load_box(smem_u32(Ks + s * PAGE_BYTES) + b * (PAGE * 128), &map_k, b * 64, z, &k_full[s]);
     };
     auto copy_values = [&](int j) {
-        const int s = j & 1, pg = pg_lo + 2 * j;
-        bool have0, have1;
-        const int page0 = page_of(pg, have0), page1 = page_of(pg + 1, have1);
-        mbar_expect_tx(&v_full[s], (page1 >= 0 ? 2u : 1u) * V_PAGE);
-        const uint32_t dst = smem_u32(Vs + s * V_STAGE);
-        for (int b = 0; b < KB; ++b) {
-            tma_load_box(dst + b * (PAGE * 128), &map_v, b * 64, page0 * Hkv + kvh, &v_full[s]);
-            if (page1 >= 0) tma_load_box(dst + V_PAGE + b * (PAGE * 128), &map_v, b * 64, page1 * Hkv + kvh, &v_full[s]);
-        }
+        const int s = j % STAGES, z = page_of(j) * Hkv + kvh;
+        mbar_expect_tx(&v_full[s], PAGE_BYTES);
+        for (int b = 0; b < KB; ++b) tma_load_box(smem_u32(Vs + s * PAGE_BYTES) + b * (PAGE * 128), &map_v, b * 64, z, &v_full[s]);
     };
 
     // The positions, tiles and block tables come from the host; everything else this kernel reads
     // (queries, this step's keys and values) is written by the kernels ahead of it.
     pdl_wait();
     if (warp == COPY_WARP && lane == 0) {
+        // in the order the products want them: K(0), K(1), then V(j), K(j + 2)
         copy_keys(0);
-        copy_values(0);
-        if (n_steps > 1) {
-            copy_keys(1);
-            copy_values(1);
+        if (n_steps > 1) copy_keys(1);
+        for (int j = 0; j + 2 < STAGES && j < n_steps; ++j) {
+            copy_values(j);
+            if (j + 2 < n_steps) copy_keys(j + 2);
         }
     }
     // queries: row r of tile t = token (t tt + r / hpc), head g0 + (r % hpc); through L2, they were just written
@@ -323,7 +337,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     fence_async_smem();
     __syncthreads();
 
-    constexpr uint32_t idesc_qk = make_idesc(ROWS, STEP_KEYS, 0);
+    constexpr uint32_t idesc_qk = make_idesc(ROWS, PAGE, 0);
     constexpr uint32_t idesc_pv = make_idesc(ROWS, D, 1);
 
     if (warp < 8) {
@@ -337,44 +351,45 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         const int pos_first_t = pos_first + t * tt, pos_last_t = pos_first_t + n_tok_t - 1;
         const int qpos = row_valid ? pos_first_t + my_tok : -1;
         const bool full_rows = n_tok_t * hpc == ROWS && g_count == hpc;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t s_addr = lane_addr + (uint32_t)t * STEP_KEYS, o_addr = lane_addr + O_COL + (uint32_t)t * 128u;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)t * TILE_COLS;
+        const uint32_t o_addr = lane_addr + O_COL;
         // m_ref: the maximum (base-2 units) that this row's sum l_run and its output in tensor memory
         // are relative to.  It follows the row's running maximum only when that has grown by more
         // than RESCALE_STEP since.
         float m_ref = -INFINITY, l_run = 0.f;
         bool alive = t < n_act;
         for (int j = 0; alive && j < n_steps; ++j) {
-            const int pg = pg_lo + 2 * j, key0 = pg * PAGE;
-            if (!warp_wait(&s_full[t], j & 1, abort_flag, status)) {
+            const int key0 = (pg_lo + j) * PAGE, b = j & 1;
+            const uint32_t s_addr = lane_addr + (uint32_t)b * PAGE;
+            if (!warp_wait(&s_full[t][b], (j >> 1) & 1, abort_flag, status)) {
                 alive = false;
                 break;
             }
             tcgen05_fence_after();
-            bool have0, have1;
-            page_of(pg, have0);
-            page_of(pg + 1, have1);
-            // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A step that lies wholly
+            // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A page that lies wholly
             // inside every row's range takes the path without per-element tests.
-            const bool edge = !(have0 && have1) || key0 + STEP_KEYS - 1 > pos_first_t || (window > 0 && key0 < pos_last_t - window + 1) || !full_rows;
-            int c_hi = qpos - key0;                                                    // qpos = -1 for a row without a token
-            int c_lo = (window > 0) ? qpos - window + 1 - key0 : -(1 << 30);
-            if (!have1) c_hi = min(c_hi, PAGE - 1);
-            if (!have0) c_lo = max(c_lo, PAGE);
-            uint32_t r[STEP_KEYS];
+            const bool edge = key0 + PAGE - 1 > pos_first_t || (window > 0 && key0 < pos_last_t - window + 1) || !full_rows;
+            const int c_hi = qpos - key0;                                              // qpos = -1 for a row without a token
+            const int c_lo = (window > 0) ? qpos - window + 1 - key0 : -(1 << 30);
+            uint32_t r[PAGE];
 #pragma unroll
-            for (int c0 = 0; c0 < STEP_KEYS; c0 += 16) tcgen05_ld_16(s_addr + (uint32_t)c0, *reinterpret_cast<uint32_t(*)[16]>(&r[c0]));
+            for (int c0 = 0; c0 < PAGE; c0 += 16) tcgen05_ld_16(s_addr + (uint32_t)c0, *reinterpret_cast<uint32_t(*)[16]>(&r[c0]));
             tcgen05_wait_ld();
             // (four chains each: the order of a maximum or of these float32 partial sums is a
             //  function of the column only, so a row's result does not depend on the batch)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (edge) {
 #pragma unroll
-                for (int c = 0; c < STEP_KEYS; ++c)
+                for (int c = 0; c < PAGE; ++c)
                     if (c <= c_hi && c >= c_lo) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(r[c]));
             } else {
 #pragma unroll
-                for (int c = 0; c < STEP_KEYS; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(r[c]));
+                for (int c = 0; c < PAGE; c += 8) {
+                    mx4[0] = fmax3(mx4[0], __uint_as_float(r[c]), __uint_as_float(r[c + 1]));
+                    mx4[1] = fmax3(mx4[1], __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+                    mx4[2] = fmax3(mx4[2], __uint_as_float(r[c + 4]), __uint_as_float(r[c + 5]));
+                    mx4[3] = fmax3(mx4[3], __uint_as_float(r[c + 6]), __uint_as_float(r[c + 7]));
+                }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the scale is positive, so the maximum of the raw scores is the maximum of the scaled ones
@@ -389,8 +404,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             }
             if (__any_sync(0xffffffffu, corr != 1.f)) {
                 // ---- correct the running output in tensor memory (rare) ----
-                // (a correction implies an earlier step: its product into O must be done)
-                if (!warp_wait(&o_done[t], (j - 1) & 1, abort_flag, status)) {
+                // (a correction implies an earlier step: its product into O must be done.  The
+                //  scores of step j+1 were issued behind it, so their arrival says so; the last
+                //  step has o_done's first phase for it.)
+                if (!(j + 1 < n_steps ? warp_wait(&s_full[t][b ^ 1], ((j + 1) >> 1) & 1, abort_flag, status) : warp_wait(&o_done[t], 0, abort_flag, status))) {
                     alive = false;
                     break;
                 }
@@ -412,11 +429,13 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             tcgen05_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(&p_full[t]);
+            mbar_arrive(&p_full[t][b]);
         }
         // ---- normalise and write this row ----
         if (t < n_act) {
-            if (alive && !warp_wait(&o_done[t], (n_steps - 1) & 1, abort_flag, status)) alive = false;
+            // o_done's phases are the last two products, one after the other
+            if (alive && n_steps > 1 && !warp_wait(&o_done[t], 0, abort_flag, status)) alive = false;
+            if (alive && !warp_wait(&o_done[t], n_steps > 1 ? 1 : 0, abort_flag, status)) alive = false;
             tcgen05_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const bool store = row_valid && alive;
@@ -442,102 +461,95 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
                 }
             }
         }
-    } else if (warp == ISSUE_WARP) {
-        // ---- the products: issued by lane 0, the whole warp walks the steps ---------------------------
+    } else if ((warp == ISSUE_WARP || warp == ISSUE_WARP + 1) && lane == 0 && warp - ISSUE_WARP < n_act) {
+        // ---- the products of tile t: one thread issues them all ----------------------------------------
+        // (a thread of its own for each tile: issuing a product and its commits takes the thread
+        //  some 50 to 100 cycles each, and 12 products a page and tile are more than one thread
+        //  could issue for both tiles in the time the softmax takes)
+        const int t = warp - ISSUE_WARP;
         // The descriptors differ from their first one only in the address field (units of 16
         // bytes), so they are made once and advanced by additions.
-        const uint64_t desc_q0 = make_desc(smem_u32(Qs), 16, 1024), desc_k0 = make_desc(smem_u32(Ks), 16, 1024);
+        const uint64_t desc_q0 = make_desc(smem_u32(Qs + t * TILE_BYTES), 16, 1024), desc_k0 = make_desc(smem_u32(Ks), 16, 1024);
         const uint64_t desc_v0 = make_desc(smem_u32(Vs), PAGE * 128, 1024);
-        auto issue_scores = [&](int t, int j) {          // S_t = Q_t K(j)^T
-            const uint64_t dq = desc_q0 + (uint64_t)((t * TILE_BYTES) >> 4), dk = desc_k0 + (uint64_t)(((j & 1) * K_STAGE) >> 4);
+        const uint32_t tile_addr = tmem_base + (uint32_t)t * TILE_COLS;
+        auto issue_scores = [&](int j) {          // S_t[j & 1] = Q_t K(j)^T
+            const uint64_t dk = desc_k0 + (uint64_t)(((j % STAGES) * PAGE_BYTES) >> 4);
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
-                const uint64_t da = dq + (uint64_t)(((ks >> 2) * (ROWS * 128) + (ks & 3) * 32) >> 4);
-                const uint64_t db = dk + (uint64_t)(((ks >> 2) * (STEP_KEYS * 128) + (ks & 3) * 32) >> 4);
-                tcgen05_mma_ss(tmem_base + (uint32_t)t * STEP_KEYS, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                const uint64_t da = desc_q0 + (uint64_t)(((ks >> 2) * (ROWS * 128) + (ks & 3) * 32) >> 4);
+                const uint64_t db = dk + (uint64_t)(((ks >> 2) * (PAGE * 128) + (ks & 3) * 32) >> 4);
+                tcgen05_mma_ss(tile_addr + (uint32_t)(j & 1) * PAGE, da, db, idesc_qk, ks > 0 ? 1u : 0u);
             }
-            tcgen05_commit(&s_full[t]);
+            tcgen05_commit(&s_full[t][j & 1]);
+            tcgen05_commit(&k_empty[j % STAGES]);
         };
-        auto issue_output = [&](int t, int j) {          // O_t (+)= P_t V(j)
-            const uint64_t dv = desc_v0 + (uint64_t)(((j & 1) * V_STAGE) >> 4);
+        auto issue_output = [&](int j) {          // O_t (+)= P_t[j & 1] V(j)
+            const uint64_t dv = desc_v0 + (uint64_t)(((j % STAGES) * PAGE_BYTES) >> 4);
 #pragma unroll
-            for (int k2 = 0; k2 < STEP_KEYS / 16; ++k2) {
-                // 16 keys further: 8 columns of P; two groups of 8 rows of V, the second page behind the first
-                const uint64_t db = dv + (uint64_t)(((k2 >> 2) * V_PAGE + (k2 & 3) * 2048) >> 4);
-                tcgen05_mma_ts(tmem_base + O_COL + (uint32_t)t * 128u, tmem_base + (uint32_t)t * STEP_KEYS + (uint32_t)k2 * 8u, db, idesc_pv,
+            for (int k2 = 0; k2 < PAGE / 16; ++k2) {
+                // 16 keys further: 8 columns of P; two groups of 8 rows of V (blocks of 64 dims are
+                // PAGE * 128 bytes apart: the leading offset of the descriptor)
+                tcgen05_mma_ts(tile_addr + O_COL, tile_addr + (uint32_t)(j & 1) * PAGE + (uint32_t)k2 * 8u, dv + (uint64_t)((k2 * 2048) >> 4), idesc_pv,
                                (j > 0 || k2 > 0) ? 1u : 0u);
             }
-            tcgen05_commit(&o_done[t]);
+            if (j + 2 >= n_steps) tcgen05_commit(&o_done[t]);
+            tcgen05_commit(&v_empty[j % STAGES]);
         };
-        bool alive = warp_wait(&k_full[0], 0, abort_flag, status);
-        if (alive) {
-            tcgen05_fence_after();
-            if (lane == 0) {
-                for (int t = 0; t < n_act; ++t) issue_scores(t, 0);
-                tcgen05_commit(&k_empty[0]);
+        // the scores of the first two pages; later ones are issued two pages ahead, behind the
+        // P V product that read the buffer they go to
+        bool alive = true;
+        for (int j = 0; alive && j < 2 && j < n_steps; ++j) {
+            if (!mbar_wait(&k_full[j], 0, abort_flag, status)) {
+                alive = false;
+                break;
             }
-            __syncwarp();
+            tcgen05_fence_after();
+            issue_scores(j);
         }
         for (int j = 0; alive && j < n_steps; ++j) {
-            const int s = j & 1;
-            if (!warp_wait(&v_full[s], (j >> 1) & 1, abort_flag, status)) break;
-            // The values of rows past the last key (the rest of the last page, a page that the step
-            // no longer holds, or one the table does not name) may be anything, NaN included, and
-            // 0 x NaN is NaN: they become zeros.  (Keys there give scores that the softmax masks.)
-            for (int h = 0; h < 2; ++h) {
-                const int pg = pg_lo + 2 * j + h;
-                bool have;
-                page_of(pg, have);
-                const int valid_rows = have ? min(pos_last - pg * PAGE + 1, PAGE) : 0;
-                if (valid_rows < PAGE) {
-                    const uint32_t dst = smem_u32(Vs + s * V_STAGE) + h * V_PAGE;
-                    for (int i = lane; i < (PAGE - valid_rows) * CHUNKS_D; i += 32) {
-                        const int zr = valid_rows + i / CHUNKS_D, ch = i % CHUNKS_D;
-                        st_shared_16(dst + (ch >> 3) * (PAGE * 128) + swz(zr, ch & 7), 0u, 0u, 0u, 0u);
-                    }
-                    fence_async_smem();
-                }
-            }
-            __syncwarp();
-            for (int t = 0; alive && t < n_act; ++t) {
-                if (!warp_wait(&p_full[t], j & 1, abort_flag, status)) {
-                    alive = false;
-                    break;
-                }
+            if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, abort_flag, status)) break;
+            if (fix_last && j == n_steps - 1 && !mbar_wait(&v_fixed, 0, abort_flag, status)) break;
+            if (!mbar_wait(&p_full[t][j & 1], (j >> 1) & 1, abort_flag, status)) break;
+            tcgen05_fence_after();
+            issue_output(j);
+            if (j + 2 < n_steps) {
+                if (!mbar_wait(&k_full[(j + 2) % STAGES], ((j + 2) / STAGES) & 1, abort_flag, status)) break;
                 tcgen05_fence_after();
-                if (lane == 0) {
-                    issue_output(t, j);
-                    if (t == n_act - 1) tcgen05_commit(&v_empty[s]);
-                }
-                if (j + 1 < n_steps) {
-                    if (t == 0 && !warp_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, status)) {
-                        alive = false;
-                        break;
-                    }
-                    tcgen05_fence_after();
-                    if (lane == 0) {
-                        issue_scores(t, j + 1);
-                        if (t == n_act - 1) tcgen05_commit(&k_empty[(j + 1) & 1]);
-                    }
-                }
-                __syncwarp();
+                issue_scores(j + 2);
             }
         }
     } else if (warp == COPY_WARP && lane == 0) {
-        // ---- the copies of steps 2.. : a stage is free once the products that read it are done ----
+        // ---- the later copies: a stage is free once the products that read it are done -----------------
+        // (V(0 .. STAGES-3) and K(0 .. STAGES-1) went out above)
         bool alive = true;
-        for (int j = 2; alive && j < n_steps; ++j) {
-            const int s = j & 1;
-            const uint32_t parity = ((j >> 1) - 1) & 1;
-            if (!mbar_wait(&k_empty[s], parity, abort_flag, status)) break;
-            copy_keys(j);
-            if (!mbar_wait(&v_empty[s], parity, abort_flag, status)) break;
+        for (int j = STAGES - 2; alive && j < n_steps; ++j) {
+            if (j >= STAGES && !mbar_wait(&v_empty[j % STAGES], ((j / STAGES) - 1) & 1, abort_flag, status)) break;
             copy_values(j);
+            const int j2 = j + 2;
+            if (j2 < n_steps) {
+                if (!mbar_wait(&k_empty[j2 % STAGES], ((j2 / STAGES) - 1) & 1, abort_flag, status)) break;
+                copy_keys(j2);
+            }
         }
+        // the last page of values is there: the zeros behind its last key may be written
+        // (this thread armed that phase of the barrier itself, so it cannot take an older one for it)
+        if (fix_last && mbar_wait(&v_full[(n_steps - 1) % STAGES], ((n_steps - 1) / STAGES) & 1, abort_flag, status)) mbar_arrive(&v_landed);
         // no copy of this CTA is in flight when it ends (all have landed long ago unless a wait ran out)
-        for (int j = max(n_steps - 2, 0); j < n_steps; ++j) {
-            mbar_wait(&k_full[j & 1], (j >> 1) & 1, abort_flag, status);
-            mbar_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag, status);
+        for (int j = max(n_steps - STAGES, 0); j < n_steps; ++j) {
+            mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1, abort_flag, status);
+            mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, abort_flag, status);
+        }
+    } else if (warp == HELP_WARP && fix_last) {
+        // ---- zeros behind the last key of the last page's values: warp 11 ------------------------------
+        const int htid = lane, j = n_steps - 1;
+        if (warp_wait(&v_landed, 0, abort_flag, status)) {
+            const uint32_t dst = smem_u32(Vs + (j % STAGES) * PAGE_BYTES);
+            for (int i = htid; i < (PAGE - last_rows) * CHUNKS_D; i += HELPERS) {
+                const int zr = last_rows + i / CHUNKS_D, ch = i % CHUNKS_D;
+                st_shared_16(dst + (ch >> 3) * (PAGE * 128) + swz(zr, ch & 7), 0u, 0u, 0u, 0u);
+            }
+            fence_async_smem();
+            mbar_arrive(&v_fixed);
         }
     }
     tcgen05_fence_before();
@@ -554,7 +566,7 @@ int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, con
            const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo, int H, int Hkv, int hpc, int tt,
            float scale, int window, int *status, cudaStream_t stream) {
     constexpr int KB = D / 64;
-    const size_t smem = 2 * (size_t)KB * ROWS * 128 + 4 * (size_t)KB * STEP_KEYS * 128 + 1024;
+    const size_t smem = 2 * (size_t)KB * ROWS * 128 + 2 * STAGES * (size_t)KB * PAGE * 128 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_attention_twin_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
