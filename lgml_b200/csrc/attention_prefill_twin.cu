@@ -1,31 +1,40 @@
 // Paged attention for prompts and portions of prompts on the 5th-generation tensor cores
-// (tcgen05), two tiles of 128 query rows per CTA and 128 keys (two pages) per step, for head
-// sizes 64 and 128.  bfloat16 operands, float32 scores, softmax and output.
+// (tcgen05), two tiles of 128 query rows per CTA, for head sizes 64 and 128.  bfloat16 operands,
+// float32 scores, softmax and output.
 //
 // A CTA takes up to 256 query rows of one KV head: two tiles, each `tt` consecutive new tokens of
 // one request times the `hpc` query heads that share the KV head (row = token * hpc + head), and
-// walks the request's pages two at a time, from the first one a query can see to the page of
-// its last token.  Per step of 128 keys and per tile:
-//     S[128, 128] = Q[128, D] . K[128, D]^T          tcgen05.mma, accumulator in tensor memory
-//     softmax: one thread per row reads its 128 scores from tensor memory, keeps the running
+// walks the request's pages from the first one a query can see to the page of its last token.
+// Per page of 64 keys and per tile:
+//     S[128, 64]  = Q[128, D] . K[64, D]^T           tcgen05.mma, accumulator in tensor memory
+//     softmax: one thread per row reads its 64 scores from tensor memory, keeps the running
 //              maximum and sum in float32 (base-2 exponentials) and writes P as bfloat16 back
 //              into tensor memory, over the first half of the columns S came from
-//     O[128, D] += P[128, 128] . V[128, D]           tcgen05.mma with P read from tensor memory
+//     O[128, D] += P[128, 64] . V[64, D]             tcgen05.mma with P read from tensor memory
 //                                                    (V is the N-major B operand)
-// The two tiles take turns on the tensor core: while the four warps of one tile do their
-// softmax, the products of the other tile run.  What bounds the kernel is then the rate of
-// exponentials (16 a clock and SM), not the chain scores -> softmax -> product of one tile.
+// Each tile has two buffers of scores, and the scores of page j+2 are issued right behind the
+// P V product of page j, which read the buffer they go to.  So the scores of the next page are
+// there long before a tile's softmax has finished the current one, and the only chain left in
+// a tile is softmax after softmax; the products of both tiles run beside it.
 // Warps 0-3 are the softmax of tile 0, warps 4-7 of tile 1 (a warp reads the quarter of tensor
-// memory's lanes that its index modulo 4 names), one thread of warp 8 issues all products, one
-// thread of warp 9 all TMA copies of pages (keys and values in rings of two steps each).
+// memory's lanes that its index modulo 4 names); one thread of warp 8 issues the products of
+// tile 0, one of warp 9 those of tile 1 (a product of 128 rows takes the tensor core at least
+// 48 cycles whatever its width, 64 at 128 columns, and the thread that issues it as long: one
+// thread for both tiles was the slowest part of a page); one thread of warp 10 issues all TMA
+// copies of pages (keys and values in rings of four pages each); warp 11 writes zeros behind
+// the last key of the last page of values.
 // The running output O is corrected (read, scaled, written back, by the softmax threads) only
 // when a row's maximum has grown by more than 8 (base-2 units) since the value its sums are
 // relative to; until then the exponentials are taken against that older maximum and stay below
 // 2^8, which bfloat16 and the float32 sums hold without loss.
 // Products issued by one thread complete in the order of issue.  The kernel leans on that twice:
-// the scores of step j+1 of a tile are issued behind the P V product of its step j, so they
+// the scores of page j+2 of a tile are issued behind the P V product of its page j, so they
 // cannot overwrite P before it has been read; and their arrival tells the softmax threads that
 // this product is done.
+// A wait on an mbarrier names a phase by its parity.  A thread that comes to a barrier two
+// phases late would wait for a third, and one that comes a phase early passes at once; every
+// barrier here is either waited on phase after phase by its one kind of consumer, which the
+// producer cannot overtake, or is used once.
 // The CTA takes all 512 columns of the SM's tensor memory.  With its 193 KB of shared memory no
 // other kernel of this package that allocates tensor memory (each needs more than 34 KB of
 // shared memory) can be resident on the same SM, so the allocation never waits for a CTA that
@@ -161,6 +170,17 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
     return y;
 }
+// two float32 products-and-sums, or sums, in one instruction
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)), "l"(*reinterpret_cast<uint64_t *>(&c)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)));
+    return *reinterpret_cast<float2 *>(&d);
+}
 // 2^x in one instruction; 2^(-inf) = 0
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -201,22 +221,25 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volati
 
 // P = 2^(S scale - m) of one row as bfloat16 over the columns S came from: two a column, key 2 c
 // in the low half.  EDGE: keys outside c_lo..c_hi give 0 (whatever their score, NaN included).
+// The sums are kept as pairs (even keys, odd keys) in four chains; their order is a function of
+// the column only.
 template <bool EDGE>
 __device__ __forceinline__ void write_p(const uint32_t (&r)[PAGE], uint32_t s_addr, float scale_log2, float neg_m, int c_lo, int c_hi,
-                                        float (&sum4)[4]) {
+                                        float2 (&sum4)[4]) {
+    const float2 scale2 = make_float2(scale_log2, scale_log2), neg_m2 = make_float2(neg_m, neg_m);
 #pragma unroll
     for (int c0 = 0; c0 < PAGE; c0 += 32) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2(fmaf(__uint_as_float(r[c0 + i]), scale_log2, neg_m));
-            float p1 = ex2(fmaf(__uint_as_float(r[c0 + i + 1]), scale_log2, neg_m));
+            const float2 x = fma2(make_float2(__uint_as_float(r[c0 + i]), __uint_as_float(r[c0 + i + 1])), scale2, neg_m2);
+            float2 p = make_float2(ex2(x.x), ex2(x.y));
             if (EDGE) {
-                if (c0 + i > c_hi || c0 + i < c_lo) p0 = 0.f;
-                if (c0 + i + 1 > c_hi || c0 + i + 1 < c_lo) p1 = 0.f;
+                if (c0 + i > c_hi || c0 + i < c_lo) p.x = 0.f;
+                if (c0 + i + 1 > c_hi || c0 + i + 1 < c_lo) p.y = 0.f;
             }
-            sum4[(i >> 1) & 3] += p0 + p1;
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+            sum4[(i >> 1) & 3] = add2(sum4[(i >> 1) & 3], p);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(p.x, p.y);
             packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
         }
         tcgen05_st_16(s_addr + (uint32_t)(c0 >> 1), packed);
@@ -240,9 +263,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     uint8_t *Qs = base, *Ks = Qs + 2 * TILE_BYTES, *Vs = Ks + STAGES * PAGE_BYTES;
     // k_full / v_full: a stage's copy has landed; k_empty / v_empty: the products that read it are
     // done; s_full[t][b]: the scores in buffer b of tile t are there; p_full[t][b]: P is written
-    // over them; o_done[t]: one of the last two P V products of tile t is done; v_landed: the last page of
+    // over them; o_prev[t], o_last[t]: the last but one and the last P V product of tile t are done (a barrier
+    // each, used once: a thread that comes late to a barrier of two phases would wait for a third); v_landed: the last page of
     // values is there; v_fixed: zeros stand behind its last key.
-    __shared__ uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2][2], p_full[2][2], o_done[2], v_landed, v_fixed;
+    __shared__ uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2][2], p_full[2][2], o_prev[2], o_last[2], v_landed, v_fixed;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     volatile int *abort_flag = &abort_s;
@@ -279,8 +303,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             mbar_init(&s_full[i >> 1][i & 1], 1);
             mbar_init(&p_full[i >> 1][i & 1], ROWS);
         }
-        mbar_init(&o_done[0], 1);
-        mbar_init(&o_done[1], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&o_prev[i], 1);
+            mbar_init(&o_last[i], 1);
+        }
         mbar_init(&v_landed, 1);
         mbar_init(&v_fixed, HELPERS);
         abort_s = 0;
@@ -324,15 +350,25 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         }
     }
     // queries: row r of tile t = token (t tt + r / hpc), head g0 + (r % hpc); through L2, they were just written
-    for (int c = tid; c < 2 * ROWS * CHUNKS_D; c += THREADS) {
-        const int r2 = c / CHUNKS_D, ch = c - r2 * CHUNKS_D;
-        const int t = r2 >> 7, r = r2 & (ROWS - 1);
-        const int tok_in = r / hpc, g = r - tok_in * hpc;
-        const int tok = t * tt + tok_in;
-        if (tok_in < tt && tok < n_tok && g < g_count) {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
-            *reinterpret_cast<uint4 *>(Qs + t * TILE_BYTES + (ch >> 3) * (ROWS * 128) + swz(r, ch & 7)) = v;
+    // (a thread's loads all go out before its first store: the CTA waits here for one trip to L2, not for eleven)
+    {
+        constexpr int PER_THREAD = (2 * ROWS * CHUNKS_D + THREADS - 1) / THREADS;
+        uint4 v[PER_THREAD];
+        uint32_t dst[PER_THREAD];
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int c = tid + i * THREADS;
+            const int r2 = c / CHUNKS_D, ch = c - r2 * CHUNKS_D;
+            const int t = r2 >> 7, r = r2 & (ROWS - 1);
+            const int tok_in = r / hpc, g = r - tok_in * hpc;
+            const int tok = t * tt + tok_in;
+            const bool have = c < 2 * ROWS * CHUNKS_D && tok_in < tt && tok < n_tok && g < g_count;
+            dst[i] = have ? smem_u32(Qs + t * TILE_BYTES + (ch >> 3) * (ROWS * 128)) + swz(r, ch & 7) : 0u;
+            if (have) v[i] = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
         }
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i)
+            if (dst[i]) st_shared_16(dst[i], v[i].x, v[i].y, v[i].z, v[i].w);
     }
     fence_async_smem();
     __syncthreads();
@@ -406,8 +442,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
                 // ---- correct the running output in tensor memory (rare) ----
                 // (a correction implies an earlier step: its product into O must be done.  The
                 //  scores of step j+1 were issued behind it, so their arrival says so; the last
-                //  step has o_done's first phase for it.)
-                if (!(j + 1 < n_steps ? warp_wait(&s_full[t][b ^ 1], ((j + 1) >> 1) & 1, abort_flag, status) : warp_wait(&o_done[t], 0, abort_flag, status))) {
+                //  step has a barrier for it.)
+                if (!(j + 1 < n_steps ? warp_wait(&s_full[t][b ^ 1], ((j + 1) >> 1) & 1, abort_flag, status) : warp_wait(&o_prev[t], 0, abort_flag, status))) {
                     alive = false;
                     break;
                 }
@@ -423,19 +459,18 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
                 }
             }
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;    // keeps (-inf) - (-inf) out of the exponent
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             if (edge) write_p<true>(r, s_addr, scale_log2, neg_m, c_lo, c_hi, sum4);
             else write_p<false>(r, s_addr, scale_log2, neg_m, c_lo, c_hi, sum4);
-            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            const float2 sum2 = add2(add2(sum4[0], sum4[1]), add2(sum4[2], sum4[3]));
+            l_run += sum2.x + sum2.y;
             tcgen05_wait_st();
             tcgen05_fence_before();
             mbar_arrive(&p_full[t][b]);
         }
         // ---- normalise and write this row ----
         if (t < n_act) {
-            // o_done's phases are the last two products, one after the other
-            if (alive && n_steps > 1 && !warp_wait(&o_done[t], 0, abort_flag, status)) alive = false;
-            if (alive && !warp_wait(&o_done[t], n_steps > 1 ? 1 : 0, abort_flag, status)) alive = false;
+            if (alive && !warp_wait(&o_last[t], 0, abort_flag, status)) alive = false;
             tcgen05_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const bool store = row_valid && alive;
@@ -492,7 +527,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
                 tcgen05_mma_ts(tile_addr + O_COL, tile_addr + (uint32_t)(j & 1) * PAGE + (uint32_t)k2 * 8u, dv + (uint64_t)((k2 * 2048) >> 4), idesc_pv,
                                (j > 0 || k2 > 0) ? 1u : 0u);
             }
-            if (j + 2 >= n_steps) tcgen05_commit(&o_done[t]);
+            if (j + 2 == n_steps) tcgen05_commit(&o_prev[t]);
+            if (j + 1 == n_steps) tcgen05_commit(&o_last[t]);
             tcgen05_commit(&v_empty[j % STAGES]);
         };
         // the scores of the first two pages; later ones are issued two pages ahead, behind the
