@@ -47,6 +47,11 @@ LIBRARIES: Dict[str, tuple] = {
 }
 
 _HEADERS = ["common.cuh", "page_map.cuh"]
+
+# The host library (plain C, the system compiler): the safetensors reader and the sampler.
+HOST_LIBRARY = "host"
+HOST_SOURCE, HOST_HEADERS = "host/lgml_host.c", ["host/lgml_host.h"]
+CC_FLAGS = ["-std=c11", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -62,6 +67,13 @@ def find_nvcc() -> str:
             return cand
     raise KernelBuildError("nvcc not found (looked at $LGML_NVCC, PATH, $CUDA_HOME/bin and /usr/local/cuda/bin); "
                            "the sm_100a kernels have no other implementation")
+
+
+def find_cc() -> str:
+    for cand in (os.environ.get("LGML_CC"), os.environ.get("CC"), shutil.which("cc"), shutil.which("gcc"), shutil.which("clang")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise KernelBuildError("no C compiler found (looked at $LGML_CC, $CC, cc, gcc, clang) for the host library")
 
 
 def _writable(d: Path) -> bool:
@@ -99,12 +111,16 @@ def _find_build_dir() -> Path:
 
 
 def _digest(name: str) -> str:
-    src, extra = LIBRARIES[name]
     h = hashlib.sha256()
-    for f in [src] + _HEADERS + list(LIBRARY_HEADERS.get(name, [])):
+    if name == HOST_LIBRARY:
+        files, flags = [HOST_SOURCE] + HOST_HEADERS, CC_FLAGS
+    else:
+        src, extra = LIBRARIES[name]
+        files, flags = [src] + _HEADERS + list(LIBRARY_HEADERS.get(name, [])), NVCC_FLAGS + list(extra)
+    for f in files:
         h.update(f.encode())
         h.update((HERE / f).read_bytes())
-    h.update(" ".join(NVCC_FLAGS + list(extra)).encode())
+    h.update(" ".join(flags).encode())
     return h.hexdigest()[:12]
 
 
@@ -124,17 +140,22 @@ def _say(msg: str) -> None:
 
 def compile_library(name: str, verbose: bool = True) -> Path:
     """Compile one library if its object is not there yet; returns the object's path."""
-    if name not in LIBRARIES:
+    if name not in LIBRARIES and name != HOST_LIBRARY:
         raise KernelBuildError(f"unknown kernel library '{name}'")
     out = library_path(name)
     if out.exists():
         return out
-    nvcc = find_nvcc()
-    src, extra = LIBRARIES[name]
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [nvcc] + NVCC_FLAGS + list(extra) + ["-I", str(HERE), str(HERE / src), "-o", str(tmp)]
-    if verbose:
-        _say(f"compiling {src} for sm_100a ...")
+    if name == HOST_LIBRARY:
+        src = HOST_SOURCE
+        cmd = [find_cc()] + CC_FLAGS + ["-I", str(HERE / "host"), str(HERE / src), "-o", str(tmp), "-lm"]
+        if verbose:
+            _say(f"compiling {src} ...")
+    else:
+        src, extra = LIBRARIES[name]
+        cmd = [find_nvcc()] + NVCC_FLAGS + list(extra) + ["-I", str(HERE), str(HERE / src), "-o", str(tmp)]
+        if verbose:
+            _say(f"compiling {src} for sm_100a ...")
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
@@ -155,7 +176,7 @@ def compile_library(name: str, verbose: bool = True) -> Path:
             tmp.unlink()
         except OSError:
             pass
-        raise KernelBuildError(f"nvcc failed on {src} (exit {proc.returncode}):\n{log}")
+        raise KernelBuildError(f"{cmd[0]} failed on {src} (exit {proc.returncode}):\n{log}")
     for old in out.parent.glob(f"lgml_{name}.*.so"):
         if old != tmp:
             try:
@@ -184,7 +205,7 @@ def load(name: str) -> ctypes.CDLL:
 
 def build_all(names: Optional[Iterable[str]] = None, jobs: int = 0, verbose: bool = True) -> List[Path]:
     """Compile every library (in parallel); used by the build check and before a first run."""
-    names = list(names or LIBRARIES)
+    names = list(names or list(LIBRARIES) + [HOST_LIBRARY])
     jobs = jobs or min(len(names), os.cpu_count() or 1)
     with ThreadPoolExecutor(max_workers=jobs) as ex:
         return list(ex.map(lambda n: compile_library(n, verbose), names))

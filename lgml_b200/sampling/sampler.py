@@ -11,19 +11,22 @@ draw uses one double ``(next() >> 11) * 2^-53`` (``:126-130``).
 
 When the chain is *neutral* (no bias, no penalties, top_k 0, top_p 1, min_p 0) a draw
 is exactly "softmax(logits / T), inverse CDF in id order"; the engine then samples on
-the device with the uniform number this sampler supplies, and the host chain below is
-its plain twin.  With top_k set (the default chain) the device applies bias and penalties to
+the device with the uniform number this sampler supplies, and the host chain is its plain
+twin.  The chain, the history and the generator are the host library's (C, as in mischief/lgml:
+``csrc/host/lgml_host.c``); this module holds the options and the bindings.  With top_k set (the default chain) the device applies bias and penalties to
 the rows, picks the k best in this chain's order, and ``sample_candidates`` finishes the chain
 on those k pairs; a chain without top_k that sorts the whole row stays on the host.
 """
 from __future__ import annotations
 
-import math
+import ctypes
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
+
+from .. import host
 
 MASK64 = (1 << 64) - 1
 
@@ -35,39 +38,6 @@ PRESETS = {"default": {}, "greedy": {"temperature": 0.0}}
 
 #: the chain with every filter off: what tests and the device path use
 NEUTRAL = dict(top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0, frequency_penalty=0.0, presence_penalty=0.0)
-
-
-class Xoshiro256:
-    """xoshiro256** seeded with splitmix64 (``src/sample.c:93-139``)."""
-
-    def __init__(self, seed: int):
-        x = seed & MASK64
-        self.s = []
-        for _ in range(4):
-            x = (x + 0x9E3779B97F4A7C15) & MASK64
-            z = x
-            z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & MASK64
-            z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & MASK64
-            self.s.append(z ^ (z >> 31))
-
-    @staticmethod
-    def _rotl(x: int, k: int) -> int:
-        return ((x << k) | (x >> (64 - k))) & MASK64
-
-    def next(self) -> int:
-        s = self.s
-        r = (self._rotl((s[1] * 5) & MASK64, 7) * 9) & MASK64
-        t = (s[1] << 17) & MASK64
-        s[2] ^= s[0]
-        s[3] ^= s[1]
-        s[1] ^= s[2]
-        s[0] ^= s[3]
-        s[2] ^= t
-        s[3] = self._rotl(s[3], 45)
-        return r
-
-    def double(self) -> float:
-        return (self.next() >> 11) * 2.0 ** -53
 
 
 @dataclass
@@ -130,27 +100,79 @@ class SamplingParams:
                 and self.presence_penalty == 0.0 and (self.top_k <= 0) and self.top_p >= 1.0 and self.min_p <= 0.0)
 
 
+class Xoshiro256:
+    """xoshiro256** seeded with splitmix64 (``src/sample.c:93-139``): the generator of the host
+    library's sampler, on its own."""
+
+    def __init__(self, seed: int):
+        self._lib = host.lib()
+        self._h = self._lib.lgml_sampler_new(ctypes.byref(_c_params(SamplingParams())), seed & MASK64)
+        if not self._h:
+            raise RuntimeError(host.last_error())
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.lgml_sampler_free(self._h)
+            self._h = None
+
+    @property
+    def s(self) -> List[int]:
+        out = (ctypes.c_uint64 * 4)()
+        self._lib.lgml_sampler_state(self._h, out)
+        return list(out)
+
+    def next(self) -> int:
+        return int(self._lib.lgml_sampler_next_u64(self._h))
+
+    def double(self) -> float:
+        return float(self._lib.lgml_sampler_uniform(self._h))
+
+
+def _c_params(p: "SamplingParams") -> host.SamplerParams:
+    return host.SamplerParams(p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty, p.presence_penalty,
+                              p.repeat_last_n)
+
+
 class Sampler:
+    """One request's sampler: the host library's, with its history and generator."""
+
     def __init__(self, params: Optional[SamplingParams] = None, **over):
         p = params or SamplingParams(**over)
         self.p = p
         seed = p.seed if p.seed is not None else (time.time_ns() ^ id(self))
-        self.rng = Xoshiro256(seed)
-        self.hist: List[int] = []          # ring of the last repeat_last_n ids, oldest first
+        self._lib = host.lib()
+        self._h = self._lib.lgml_sampler_new(ctypes.byref(_c_params(p)), seed & MASK64)
+        if not self._h:
+            raise ValueError(host.last_error())
+        if p.logit_bias:
+            ids = np.asarray([int(t) for t in p.logit_bias], dtype=np.int32)
+            bias = np.asarray([float(b) for b in p.logit_bias.values()], dtype=np.float32)
+            if self._lib.lgml_sampler_set_bias(self._h, ids.ctypes.data, bias.ctypes.data, len(ids)):
+                raise RuntimeError(host.last_error())
         self.last_logits: Optional[np.ndarray] = None
 
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.lgml_sampler_free(self._h)
+            self._h = None
+
     # ---- history (src/sample.c:603-650) -------------------------------------------------
+    @property
+    def hist(self) -> List[int]:
+        """The last repeat_last_n accepted ids, oldest first."""
+        n = self.p.repeat_last_n
+        if n == 0:
+            return []
+        out = np.empty(n, dtype=np.int32)
+        k = self._lib.lgml_sampler_history(self._h, out.ctypes.data, n)
+        return out[:k].tolist()
+
     def accept(self, token: int) -> None:
-        if token < 0:
+        if token < 0 or self._lib.lgml_sampler_accept(self._h, int(token)):
             raise ValueError("bad token id")
-        if self.p.repeat_last_n == 0:
-            return
-        self.hist.append(int(token))
-        if len(self.hist) > self.p.repeat_last_n:
-            self.hist.pop(0)
 
     def reset(self) -> None:
-        self.hist.clear()
+        self._lib.lgml_sampler_reset(self._h)
 
     def device_edits(self):
         """What the device needs to apply this sampler's bias and penalties to a row of logits:
@@ -166,44 +188,18 @@ class Sampler:
 
     def uniform(self) -> float:
         """The next uniform double of this request's stream (for the device draw)."""
-        return self.rng.double()
+        return float(self._lib.lgml_sampler_uniform(self._h))
 
     # ---- the chain -----------------------------------------------------------------------
-    def _penalties(self, l: np.ndarray) -> None:
-        """Each distinct id of the history once (``apply_penalties``, ``src/sample.c:652-677``)."""
-        p = self.p
-        if not self.hist or (p.repeat_penalty == 1.0 and p.frequency_penalty == 0.0 and p.presence_penalty == 0.0):
-            return
-        counts: Dict[int, int] = {}
-        for t in self.hist:
-            if t < l.shape[0]:
-                counts[t] = counts.get(t, 0) + 1
-        rep = np.float32(p.repeat_penalty)
-        for t, c in counts.items():
-            v = l[t]
-            v = v * rep if v <= 0 else v / rep
-            l[t] = np.float32(v - np.float32(np.float32(c) * np.float32(p.frequency_penalty) + np.float32(p.presence_penalty)))
-
     def sample(self, logits: Sequence[float]) -> int:
         """One id from a row of float32 logits (``sampler_sample``, ``src/sample.c:1045-1060``)."""
-        l = np.array(logits, dtype=np.float32, copy=True)
-        p = self.p
-        if p.logit_bias:
-            for t, b in p.logit_bias.items():
-                if 0 <= t < l.shape[0]:
-                    l[t] += np.float32(b)
-        self._penalties(l)
-        self.last_logits = l
-        n = l.shape[0]
-        if not p.temperature > 0.0:
-            return int(np.argmax(l))                      # first maximum: the lowest index wins a tie
-        ids = np.arange(n, dtype=np.int64)
-        vals = l
-        is_sorted = False
-        if 0 < p.top_k < n:
-            order = np.lexsort((ids, -vals.astype(np.float64)))[: p.top_k]   # logit descending, then id ascending
-            ids, vals, is_sorted = ids[order], vals[order], True
-        return self._after_top_k(ids, vals, is_sorted)
+        l = np.ascontiguousarray(logits, dtype=np.float32)
+        edited = np.empty_like(l)
+        tok = self._lib.lgml_sampler_sample(self._h, l.ctypes.data, l.shape[0], edited.ctypes.data)
+        if tok < 0:
+            raise RuntimeError(host.last_error())
+        self.last_logits = edited
+        return int(tok)
 
     def sample_candidates(self, ids: Sequence[int], vals: Sequence[float]) -> int:
         """The chain from top_p on, for candidates that top_k has already chosen on the device
@@ -211,56 +207,25 @@ class Sampler:
         ``sample`` on the whole row when no bias and no penalty is set and temperature > 0."""
         if not self.p.temperature > 0.0:
             raise ValueError("sample_candidates is for temperature > 0 (the argmax needs no candidates)")
+        i = np.ascontiguousarray(ids, dtype=np.int64)
+        v = np.ascontiguousarray(vals, dtype=np.float32)
         self.last_logits = None
-        return self._after_top_k(np.asarray(ids, dtype=np.int64), np.asarray(vals, dtype=np.float32), True)
-
-    def _after_top_k(self, ids: np.ndarray, vals: np.ndarray, is_sorted: bool) -> int:
-        p = self.p
-        if p.top_p < 1.0:
-            if not is_sorted:
-                order = np.lexsort((ids, -vals.astype(np.float64)))
-                ids, vals, is_sorted = ids[order], vals[order], True
-            w = np.exp((vals - vals[0]).astype(np.float32)).astype(np.float32)
-            # float32 running sums, as apply_top_p (:808-831); cumsum adds in order in the array's type
-            total = np.cumsum(w, dtype=np.float32)[-1]
-            cum = np.cumsum((w / total).astype(np.float32), dtype=np.float32)
-            reached = np.flatnonzero(cum >= np.float32(p.top_p))
-            keep = int(reached[0]) + 1 if reached.size else len(w)
-            ids, vals = ids[:keep], vals[:keep]
-        if p.min_p > 0.0:
-            thr = np.float32(vals.max() + np.float32(math.log(p.min_p)))   # apply_min_p (:834-852)
-            mask = vals >= thr
-            ids, vals = ids[mask], vals[mask]
-        if p.temperature != 1.0:
-            vals = (vals / np.float32(p.temperature)).astype(np.float32)
-        return self._draw(ids, vals)
-
-    def _draw(self, ids: np.ndarray, vals: np.ndarray) -> int:
-        """``draw`` (``src/sample.c:855-877``): float32 weights, float64 sums, first
-        candidate whose running sum reaches sum * u; a zero weight never wins."""
-        m = vals.max()
-        w = np.exp((vals - m).astype(np.float32)).astype(np.float32).astype(np.float64)
-        run = np.cumsum(w)                                  # sequential float64 sums
-        tgt = run[-1] * self.rng.double()
-        ok = (w > 0) & (run >= tgt)
-        hit = np.flatnonzero(ok)
-        if hit.size:
-            return int(ids[hit[0]])
-        nz = np.flatnonzero(w > 0)
-        return int(ids[nz[-1]] if nz.size else ids[0])
+        tok = self._lib.lgml_sampler_sample_candidates(self._h, i.ctypes.data, v.ctypes.data, i.shape[0])
+        if tok < 0:
+            raise RuntimeError(host.last_error())
+        return int(tok)
 
     def logprobs(self, token: int, k: int = 0):
         """Log-softmax of the last sampled row after bias and penalties, before temperature
         and truncation (``sampler_logprobs``, ``src/sample.c:1075-1110``)."""
-        l = self.last_logits
-        if l is None:
+        if self.last_logits is None:
             raise RuntimeError("no logits: sample first")
-        if not 0 <= token < l.shape[0] or not 0 <= k <= l.shape[0]:
+        n = self.last_logits.shape[0]
+        if not 0 <= token < n or not 0 <= k <= n:
             raise ValueError("bad token id or count")
-        m = float(l.max())
-        lse = m + math.log(float(np.exp(l.astype(np.float64) - m).sum()))
-        top = []
-        if k > 0:
-            order = np.lexsort((np.arange(l.shape[0]), -l.astype(np.float64)))[:k]
-            top = [(int(i), float(l[i]) - lse) for i in order]
-        return float(l[token]) - lse, top
+        lp = ctypes.c_double()
+        ids = np.empty(max(k, 1), dtype=np.int32)
+        lps = np.empty(max(k, 1), dtype=np.float64)
+        if self._lib.lgml_sampler_logprobs(self._h, int(token), int(k), ctypes.byref(lp), ids.ctypes.data, lps.ctypes.data):
+            raise RuntimeError(host.last_error())
+        return float(lp.value), [(int(ids[i]), float(lps[i])) for i in range(k)]

@@ -17,8 +17,9 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Dict, Iterable, Tuple
 
-import numpy as np
 import torch
+
+from .. import host
 
 MAX_HEADER = 100 << 20
 MAX_TENSORS = 65536
@@ -61,56 +62,22 @@ class TensorEntry:
 
 
 def read_index(path) -> Dict[str, TensorEntry]:
-    """The tensors of one file, every size and offset checked; reads no data."""
+    """The tensors of one file, every size and offset checked; reads no data.  The header is
+    read and checked by the host library (``csrc/host/lgml_host.c``)."""
     path = Path(path)
-    size = path.stat().st_size
-    with open(path, "rb") as f:
-        head = f.read(8)
-        if len(head) != 8:
-            raise SafetensorsError(f"{path}: shorter than its 8-byte header length")
-        (hlen,) = struct.unpack("<Q", head)
-        if hlen < 2 or hlen > MAX_HEADER or 8 + hlen > size:
-            raise SafetensorsError(f"{path}: bad header length {hlen} (file has {size} bytes)")
-        raw = f.read(hlen)
-    if len(raw) != hlen:
-        raise SafetensorsError(f"{path}: short read of the header")
+    lib = host.lib()
+    ix = lib.lgml_st_open(str(path).encode())
+    if not ix:
+        raise SafetensorsError(host.last_error())
     try:
-        header = json.loads(raw.decode("utf-8"))
-    except (UnicodeDecodeError, json.JSONDecodeError) as e:
-        raise SafetensorsError(f"{path}: header is not JSON: {e}") from None
-    if not isinstance(header, dict):
-        raise SafetensorsError(f"{path}: header must be an object")
-    data_start = 8 + hlen
-    data_size = size - data_start
-    out: Dict[str, TensorEntry] = {}
-    for name, ent in header.items():
-        if name == "__metadata__":
-            continue
-        nbytes = len(name.encode("utf-8"))
-        if nbytes < 1 or nbytes > MAX_NAME or "\0" in name:
-            raise SafetensorsError(f"{path}: bad tensor name {name!r} (1..{MAX_NAME} bytes, no NUL)")
-        if not isinstance(ent, dict):
-            raise SafetensorsError(f"{path}: entry of '{name}' must be an object")
-        dtype = ent.get("dtype")
-        if dtype not in _DTYPES:
-            raise SafetensorsError(f"{path}: tensor '{name}' has unsupported dtype {dtype!r}")
-        shape = ent.get("shape")
-        if not isinstance(shape, list) or len(shape) > 4 or not all(isinstance(d, int) and d >= 1 for d in shape):
-            raise SafetensorsError(f"{path}: tensor '{name}' has bad shape {shape!r} (at most 4 dimensions, each >= 1)")
-        offs = ent.get("data_offsets")
-        if not (isinstance(offs, list) and len(offs) == 2 and all(isinstance(o, int) for o in offs)):
-            raise SafetensorsError(f"{path}: tensor '{name}' has bad data_offsets {offs!r}")
-        begin, end = offs
-        numel = 1
-        for d in shape:
-            numel *= d
-        if not (0 <= begin <= end <= data_size) or end - begin != numel * _DTYPES[dtype][0]:
-            raise SafetensorsError(
-                f"{path}: tensor '{name}' offsets [{begin}, {end}) do not fit {numel} x {dtype} in {data_size} data bytes")
-        out[name] = TensorEntry(name, dtype, tuple(shape), path, data_start + begin, data_start + end)
-        if len(out) > MAX_TENSORS:
-            raise SafetensorsError(f"{path}: more than {MAX_TENSORS} tensors")
-    return out
+        out: Dict[str, TensorEntry] = {}
+        for i in range(lib.lgml_st_count(ix)):
+            e = lib.lgml_st_get(ix, i).contents
+            name = e.name.decode("utf-8")
+            out[name] = TensorEntry(name, host.ST_DTYPES[e.dtype], tuple(int(d) for d in e.shape[: e.rank]), path, int(e.begin), int(e.end))
+        return out
+    finally:
+        lib.lgml_st_close(ix)
 
 
 def index_folder(folder) -> Dict[str, TensorEntry]:
@@ -142,16 +109,15 @@ def index_folder(folder) -> Dict[str, TensorEntry]:
 
 
 def read_tensor(entry: TensorEntry) -> torch.Tensor:
-    """The tensor on the host in its stored type (a copy, so the file can close)."""
-    _, np_dtype, torch_dtype = _DTYPES[entry.dtype]
-    count = entry.numel
-    arr = np.fromfile(entry.path, dtype=np.dtype(np_dtype), count=count, offset=entry.begin)
-    if arr.size != count:
-        raise SafetensorsError(f"{entry.path}: short read of tensor '{entry.name}'")
-    t = torch.from_numpy(arr)
-    if entry.dtype == "BF16":
-        t = t.view(torch.bfloat16)
-    return t.reshape(entry.shape)
+    """The tensor on the host in its stored type, read by the host library into memory of its own."""
+    torch_dtype = _DTYPES[entry.dtype][2]
+    t = torch.empty(entry.shape, dtype=torch_dtype)
+    nbytes = entry.end - entry.begin
+    if nbytes != t.numel() * t.element_size():
+        raise SafetensorsError(f"{entry.path}: tensor '{entry.name}' holds {nbytes} bytes, its shape wants {t.numel() * t.element_size()}")
+    if nbytes and host.lib().lgml_st_read(str(entry.path).encode(), entry.begin, nbytes, t.data_ptr()):
+        raise SafetensorsError(f"{host.last_error()} (tensor '{entry.name}')")
+    return t
 
 
 def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata=None) -> None:

@@ -132,3 +132,30 @@ def test_candidates_from_top_k_give_the_same_draws_as_the_whole_row():
         s.accept(t)
     bias, hist, pen = s.device_edits()
     assert bias == [(5, 0.5)] and sorted(hist) == [(2, 1), (3, 1), (9, 2)] and pen == (1.2, 0.0, 0.0)
+
+
+def test_history_is_a_ring_of_the_last_ids():
+    s = Sampler(SamplingParams(temperature=0.0, repeat_last_n=3))
+    for t in (5, 6, 7, 8, 9):
+        s.accept(t)
+    assert s.hist == [7, 8, 9]
+    s.reset()
+    s.accept(1)
+    assert s.hist == [1]
+    with pytest.raises(ValueError):
+        s.accept(-1)
+    none = Sampler(SamplingParams(temperature=0.0, repeat_last_n=0))
+    none.accept(3)
+    assert none.hist == []
+
+
+def test_top_k_of_a_large_row_is_in_the_sampler_order():
+    """The k best, logit descending and id ascending among equals, whatever k and the row's size."""
+    rng = np.random.default_rng(3)
+    l = rng.integers(-5, 5, size=5000).astype(np.float32)          # many ties
+    s = Sampler(SamplingParams(temperature=0.0))
+    s.sample(l)
+    for k in (1, 7, 40, 5000):
+        _, top = s.logprobs(0, k)
+        want = np.lexsort((np.arange(l.size), -l.astype(np.float64)))[:k]
+        assert [t[0] for t in top] == want.tolist()

@@ -52,6 +52,35 @@ def test_malformed_files_are_refused(tmp_path, header, data, hlen, match):
         read_index(f)
 
 
+def test_header_reader_is_strict_json(tmp_path):
+    """The host library's own JSON reader: escapes in names, metadata of any shape skipped,
+    and the faults a lenient reader would let through."""
+    def raw(text: bytes, data: bytes = b"\0" * 4):
+        f = tmp_path / "h.safetensors"
+        f.write_bytes(struct.pack("<Q", len(text)) + text + data)
+        return f
+
+    ok = b'{"__metadata__": {"a": [1, 2.5e3, {"b": null}], "c": true}, "w\\u00e9\\n": {"dtype":"F32","shape":[1],"data_offsets":[0,4], "extra": -0.5}}   '
+    idx = read_index(raw(ok))
+    assert list(idx) == ["w\u00e9\n"] and idx["w\u00e9\n"].shape == (1,)
+    entry = b'{"dtype":"F32","shape":[1],"data_offsets":[0,4]}'
+    for text, match in [
+        (b'{"x": ' + entry + b', "x": ' + entry + b'}', "twice"),
+        (b'{"x": ' + entry + b'} trailing', "not JSON"),
+        (b'{"x": ' + entry + b',}', "not JSON"),
+        (b"{'x': " + entry + b'}', "not JSON"),
+        (b'{"x": {"dtype":"F32","shape":[1.0],"data_offsets":[0,4]}}', "bad shape"),
+        (b'{"x": {"dtype":"F32","shape":[1],"data_offsets":[0,"4"]}}', "bad data_offsets"),
+        (b'{"x": {"dtype":"F32","shape":[1],"data_offsets":[0,4,8]}}', "bad data_offsets"),
+        (b'{"x": {"dtype":"F32","shape":[4611686018427387904, 4],"data_offsets":[0,4]}}', "do not fit"),
+        (b'{"x": [1, 2]}', "must be an object"),
+        (b'[1]', "not JSON"),
+        (b'{"x": ' + b'[' * 64 + b']' * 64 + b'}', "not JSON"),
+    ]:
+        with pytest.raises(SafetensorsError, match=match):
+            read_index(raw(text))
+
+
 def test_truncated_and_not_json(tmp_path):
     (tmp_path / "a.safetensors").write_bytes(b"\x01\x02")
     with pytest.raises(SafetensorsError, match="shorter"):
