@@ -410,6 +410,34 @@ def test_attention_prefill_twin_kernel(H, G, D, window):
     assert torch.isfinite(got).all() and torch.allclose(got, want, atol=3e-2, rtol=2e-2)
 
 
+def test_attention_prefill_twin_many_launches_never_wait_out():
+    """A wait on an mbarrier that runs out sets the status word and costs about a second; a thread
+    that comes late to a barrier of two phases did that once in some hundred launches.  Full
+    tiles, a last page that is partly filled, and launches back to back."""
+    from lgml_b200 import ops
+    import time
+
+    H, G, D, T = 8, 2, 128, 1000
+    st = status()
+    n_pages = -(-T // 64)
+    k = torch.randn(n_pages, G, 64, D, device=DEV).to(torch.bfloat16)
+    v = torch.randn(n_pages, G, 64, D, device=DEV).to(torch.bfloat16)
+    q = torch.randn(T, H * D, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    positions = torch.arange(T, dtype=torch.int32, device=DEV)
+    table = torch.randperm(n_pages).to(torch.int32).reshape(1, n_pages).to(DEV)
+    tt = ops.prefill_twin_tile_tokens(H, G)
+    tiles = torch.tensor([(0, t0, min(tt, T - t0), 0) for t0 in reversed(range(0, T, tt))], dtype=torch.int32, device=DEV)
+    ops.prefill_attention_twin(q, positions, tiles, table, k, v, out, H, D ** -0.5, 0, st)
+    first = out.clone()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    for _ in range(1500):
+        ops.prefill_attention_twin(q, positions, tiles, table, k, v, out, H, D ** -0.5, 0, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and time.time() - t0 < 0.9 and torch.equal(out, first)
+
+
 def test_attention_finds_the_far_key():
     """The aimed query's output is that key's value, in every kernel."""
     case = make_attention_case(4, 4, 2, 64, kv_lens=[500], q_lens=[1], dtype=torch.bfloat16)
