@@ -313,8 +313,27 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tcgen05_alloc(&tmem_base_s, TMEM_COLS);
+    // The positions, tiles and block tables come from the host; everything else this kernel reads
+    // (queries, this step's keys and values) is written by the kernels ahead of it.
+    pdl_wait();
+    // queries: row r of tile t = token (t tt + r / hpc), head g0 + (r % hpc); through L2, they were just written
+    // (a thread's loads all go out before its first store: the CTA waits here for one trip to L2, not for eleven)
+    constexpr int PER_THREAD = (2 * ROWS * CHUNKS_D + THREADS - 1) / THREADS;
+    uint4 v[PER_THREAD];
+    uint32_t dst[PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int c = tid + i * THREADS;
+        const int r2 = c / CHUNKS_D, ch = c - r2 * CHUNKS_D;
+        const int t = r2 >> 7, r = r2 & (ROWS - 1);
+        const int tok_in = r / hpc, g = r - tok_in * hpc;
+        const int tok = t * tt + tok_in;
+        const bool have = c < 2 * ROWS * CHUNKS_D && tok_in < tt && tok < n_tok && g < g_count;
+        dst[i] = have ? smem_u32(Qs + t * TILE_BYTES + (ch >> 3) * (ROWS * 128)) + swz(r, ch & 7) : 0u;
+        if (have) v[i] = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
+    }
     tcgen05_fence_before();
-    __syncthreads();
+    __syncthreads();                     // the barriers and tensor memory are there; the queries are on their way
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
@@ -337,9 +356,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         for (int b = 0; b < KB; ++b) tma_load_box(smem_u32(Vs + s * PAGE_BYTES) + b * (PAGE * 128), &map_v, b * 64, z, &v_full[s]);
     };
 
-    // The positions, tiles and block tables come from the host; everything else this kernel reads
-    // (queries, this step's keys and values) is written by the kernels ahead of it.
-    pdl_wait();
     if (warp == COPY_WARP && lane == 0) {
         // in the order the products want them: K(0), K(1), then V(j), K(j + 2)
         copy_keys(0);
@@ -349,27 +365,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             if (j + 2 < n_steps) copy_keys(j + 2);
         }
     }
-    // queries: row r of tile t = token (t tt + r / hpc), head g0 + (r % hpc); through L2, they were just written
-    // (a thread's loads all go out before its first store: the CTA waits here for one trip to L2, not for eleven)
-    {
-        constexpr int PER_THREAD = (2 * ROWS * CHUNKS_D + THREADS - 1) / THREADS;
-        uint4 v[PER_THREAD];
-        uint32_t dst[PER_THREAD];
 #pragma unroll
-        for (int i = 0; i < PER_THREAD; ++i) {
-            const int c = tid + i * THREADS;
-            const int r2 = c / CHUNKS_D, ch = c - r2 * CHUNKS_D;
-            const int t = r2 >> 7, r = r2 & (ROWS - 1);
-            const int tok_in = r / hpc, g = r - tok_in * hpc;
-            const int tok = t * tt + tok_in;
-            const bool have = c < 2 * ROWS * CHUNKS_D && tok_in < tt && tok < n_tok && g < g_count;
-            dst[i] = have ? smem_u32(Qs + t * TILE_BYTES + (ch >> 3) * (ROWS * 128)) + swz(r, ch & 7) : 0u;
-            if (have) v[i] = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
-        }
-#pragma unroll
-        for (int i = 0; i < PER_THREAD; ++i)
-            if (dst[i]) st_shared_16(dst[i], v[i].x, v[i].y, v[i].z, v[i].w);
-    }
+    for (int i = 0; i < PER_THREAD; ++i)
+        if (dst[i]) st_shared_16(dst[i], v[i].x, v[i].y, v[i].z, v[i].w);
     fence_async_smem();
     __syncthreads();
 

@@ -577,12 +577,9 @@ def prefill_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
     return 16 * (8 // hpc)
 
 
-def prefill_attention(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor,
-                      k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
-                      status: torch.Tensor) -> torch.Tensor:
-    """bfloat16 tensor-core attention for prompts and portions.  ``tiles`` is int32
-    [n_tiles, 4]: (request row, first token row, tokens, 0), each tile within one request
-    and at most ``prefill_tile_tokens`` long."""
+def _prefill_attention_call(library: str, symbol: str, label: str, q, positions, tiles, block_table, k_pages, v_pages, out, n_heads, scale,
+                            window, status) -> torch.Tensor:
+    """The checks and the call that the three prefill attention kernels share (one signature)."""
     _need(q, "queries", torch.bfloat16, 2)
     _need(out, "attention output", torch.bfloat16, 2)
     ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
@@ -594,15 +591,25 @@ def prefill_attention(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Ten
     _need(tiles, "tiles", torch.int32, 2)
     _need(block_table, "block table", torch.int32, 2)
     if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4:
-        raise KernelError(f"prefill_attention: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
+        raise KernelError(f"{label}: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
     if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
-        raise KernelError("prefill_attention: pages, block table and tiles must be contiguous")
-    fn = _fn("attention_prefill", "lgml_prefill_attention", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                                             c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-    _check("attention_prefill", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
-                                   _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
-                                   int(window or 0), _ptr(status), _stream()), "prefill_attention")
+        raise KernelError(f"{label}: pages, block table and tiles must be contiguous")
+    fn = _fn(library, symbol, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                               c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(library, fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
+                       _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
+                       int(window or 0), _ptr(status), _stream()), label)
     return out
+
+
+def prefill_attention(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor,
+                      k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                      status: torch.Tensor) -> torch.Tensor:
+    """bfloat16 tensor-core attention for prompts and portions (``mma.sync``).  ``tiles`` is int32
+    [n_tiles, 4]: (request row, first token row, tokens, 0), each tile within one request
+    and at most ``prefill_tile_tokens`` long."""
+    return _prefill_attention_call("attention_prefill", "lgml_prefill_attention", "prefill_attention", q, positions, tiles, block_table,
+                                   k_pages, v_pages, out, n_heads, scale, window, status)
 
 
 def prefill_tc_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
@@ -614,28 +621,10 @@ def prefill_attention_tc(q: torch.Tensor, positions: torch.Tensor, tiles: torch.
                          k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
                          status: torch.Tensor) -> torch.Tensor:
     """bfloat16 attention for prompts and portions on tcgen05 tensor cores (S and the page's
-    output in tensor memory).  ``tiles`` as for ``prefill_attention``, each at most
-    ``prefill_tc_tile_tokens`` long."""
-    _need(q, "queries", torch.bfloat16, 2)
-    _need(out, "attention output", torch.bfloat16, 2)
-    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
-    n = q.shape[0]
-    _need(k_pages, "key pages", torch.bfloat16, 4)
-    _need(v_pages, "value pages", torch.bfloat16, 4)
-    n_pages, hkv, page, d = k_pages.shape
-    _need(positions, "positions", torch.int32, 1)
-    _need(tiles, "tiles", torch.int32, 2)
-    _need(block_table, "block table", torch.int32, 2)
-    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4:
-        raise KernelError(f"prefill_attention_tc: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
-    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
-        raise KernelError("prefill_attention_tc: pages, block table and tiles must be contiguous")
-    fn = _fn("attention_prefill_tc", "lgml_prefill_attention_tc", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                                                   c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-    _check("attention_prefill_tc", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
-                                      _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
-                                      int(window or 0), _ptr(status), _stream()), "prefill_attention_tc")
-    return out
+    output in tensor memory), one tile of 128 rows per CTA.  ``tiles`` as for
+    ``prefill_attention``, each at most ``prefill_tc_tile_tokens`` long."""
+    return _prefill_attention_call("attention_prefill_tc", "lgml_prefill_attention_tc", "prefill_attention_tc", q, positions, tiles,
+                                   block_table, k_pages, v_pages, out, n_heads, scale, window, status)
 
 
 def prefill_twin_tile_tokens(n_heads: int, n_kv_heads: int) -> int:
@@ -647,29 +636,10 @@ def prefill_attention_twin(q: torch.Tensor, positions: torch.Tensor, tiles: torc
                            k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
                            status: torch.Tensor) -> torch.Tensor:
     """bfloat16 attention for prompts and portions on tcgen05 tensor cores, two tiles of 128
-    rows per CTA and two pages per step (scores, P and the output in tensor memory), for head
-    sizes 64 and 128.  ``tiles`` as for ``prefill_attention``, each at most
-    ``prefill_twin_tile_tokens`` long."""
-    _need(q, "queries", torch.bfloat16, 2)
-    _need(out, "attention output", torch.bfloat16, 2)
-    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
-    n = q.shape[0]
-    _need(k_pages, "key pages", torch.bfloat16, 4)
-    _need(v_pages, "value pages", torch.bfloat16, 4)
-    n_pages, hkv, page, d = k_pages.shape
-    _need(positions, "positions", torch.int32, 1)
-    _need(tiles, "tiles", torch.int32, 2)
-    _need(block_table, "block table", torch.int32, 2)
-    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4:
-        raise KernelError(f"prefill_attention_twin: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
-    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
-        raise KernelError("prefill_attention_twin: pages, block table and tiles must be contiguous")
-    fn = _fn("attention_prefill_twin", "lgml_prefill_attention_twin", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                                                       c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-    _check("attention_prefill_twin", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
-                                        _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n_heads, hkv, d, float(scale),
-                                        int(window or 0), _ptr(status), _stream()), "prefill_attention_twin")
-    return out
+    rows per CTA (scores, P and the output in tensor memory), for head sizes 64 and 128.
+    ``tiles`` as for ``prefill_attention``, each at most ``prefill_twin_tile_tokens`` long."""
+    return _prefill_attention_call("attention_prefill_twin", "lgml_prefill_attention_twin", "prefill_attention_twin", q, positions, tiles,
+                                   block_table, k_pages, v_pages, out, n_heads, scale, window, status)
 
 
 def prefill_tc_supports(q: torch.Tensor, out: torch.Tensor) -> bool:
