@@ -201,6 +201,29 @@ static int json_skip(json *j, int depth) {
     return json_skip_number(j);
 }
 
+/* Is the byte range well-formed UTF-8 (no overlong forms, no surrogates, nothing past U+10FFFF)? */
+static int utf8_ok(const unsigned char *p, size_t n) {
+    size_t i = 0;
+    while (i < n) {
+        const unsigned char c = p[i];
+        size_t len;
+        uint32_t cp;
+        if (c < 0x80) { ++i; continue; }
+        else if ((c & 0xE0) == 0xC0) { len = 2; cp = c & 0x1F; }
+        else if ((c & 0xF0) == 0xE0) { len = 3; cp = c & 0x0F; }
+        else if ((c & 0xF8) == 0xF0) { len = 4; cp = c & 0x07; }
+        else return 0;
+        if (i + len > n) return 0;
+        for (size_t k = 1; k < len; ++k) {
+            if ((p[i + k] & 0xC0) != 0x80) return 0;
+            cp = (cp << 6) | (p[i + k] & 0x3F);
+        }
+        if ((len == 2 && cp < 0x80) || (len == 3 && cp < 0x800) || (len == 4 && cp < 0x10000) || cp > 0x10FFFF || (cp >= 0xD800 && cp < 0xE000)) return 0;
+        i += len;
+    }
+    return 1;
+}
+
 /* ---- safetensors ------------------------------------------------------------------------------ */
 
 static const char *const st_names[LGML_ST_N_DTYPES] = {"F64", "F32", "F16", "BF16", "I64", "I32", "I16", "I8"};
@@ -369,6 +392,10 @@ lgml_st_index *lgml_st_open(const char *path) {
     }
     const int64_t data_start = 8 + (int64_t)hlen, data_size = size - data_start;
     json j = {raw, raw + hlen, NULL};
+    if (!utf8_ok((const unsigned char *)raw, (size_t)hlen)) {
+        json_fail(&j, "the header is not UTF-8");
+        goto syntax;
+    }
     if (!json_eat(&j, '{')) {
         json_fail(&j, "the header must be an object");
         goto syntax;

@@ -75,6 +75,7 @@ def test_header_reader_is_strict_json(tmp_path):
         (b'{"x": {"dtype":"F32","shape":[4611686018427387904, 4],"data_offsets":[0,4]}}', "do not fit"),
         (b'{"x": [1, 2]}', "must be an object"),
         (b'[1]', "not JSON"),
+        (b'{"x\xff": ' + entry + b'}', "not JSON"),                                  # not UTF-8
         (b'{"x": ' + b'[' * 64 + b']' * 64 + b'}', "not JSON"),
     ]:
         with pytest.raises(SafetensorsError, match=match):
@@ -170,3 +171,42 @@ def test_random_weights_are_seeded_and_shaped(tmp_path):
     assert abs(float(norm.mean()) - 1.0) < 0.02
     assert json.loads((a / "config.json").read_text())["num_key_value_heads"] == 2
     check_index(index_folder(a), tensor_specs_for(cfg))
+
+
+def test_header_reader_agrees_with_a_json_library_and_survives_damage(tmp_path):
+    """Random well-formed headers (names with escapes and other alphabets, metadata of any shape)
+    give the index a JSON library gives; the same headers with bytes damaged either still parse
+    or are refused with SafetensorsError, never anything else."""
+    from hypothesis import given, settings, strategies as st
+
+    names = st.text(alphabet=st.characters(blacklist_categories=("Cs",), blacklist_characters="\0"), min_size=1, max_size=12).filter(
+        lambda n: len(n.encode()) <= 63 and n != "__metadata__")
+    meta = st.recursive(st.none() | st.booleans() | st.integers(-10**6, 10**6) | st.floats(allow_nan=False, allow_infinity=False) | st.text(max_size=5),
+                        lambda c: st.lists(c, max_size=3) | st.dictionaries(st.text(max_size=4), c, max_size=3), max_leaves=8)
+    f = tmp_path / "fuzz.safetensors"
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.dictionaries(names, st.lists(st.integers(1, 5), max_size=4), max_size=6), meta, st.booleans(), st.data())
+    def run(shapes, metadata, ascii_only, data):
+        header, off = {"__metadata__": {"m": metadata}}, 0
+        for name, shape in shapes.items():
+            n = 1
+            for d in shape:
+                n *= d
+            header[name] = {"dtype": "I16", "shape": shape, "data_offsets": [off, off + 2 * n]}
+            off += 2 * n
+        text = json.dumps(header, ensure_ascii=ascii_only).encode()
+        f.write_bytes(struct.pack("<Q", len(text)) + text + b"\0" * off)
+        idx = read_index(f)
+        assert {k: v.shape for k, v in idx.items()} == {k: tuple(v) for k, v in shapes.items()}
+        # damage: a few bytes of the header replaced
+        raw = bytearray(text)
+        for _ in range(data.draw(st.integers(1, 3))):
+            raw[data.draw(st.integers(0, len(raw) - 1))] = data.draw(st.integers(0, 255))
+        f.write_bytes(struct.pack("<Q", len(raw)) + bytes(raw) + b"\0" * off)
+        try:
+            read_index(f)
+        except SafetensorsError:
+            pass
+
+    run()
