@@ -115,6 +115,9 @@ class Xoshiro256:
             self._lib.lgml_sampler_free(self._h)
             self._h = None
 
+    def __reduce__(self):
+        raise TypeError(f"a {type(self).__name__} holds state of the host library and cannot be copied or pickled")
+
     @property
     def s(self) -> List[int]:
         out = (ctypes.c_uint64 * 4)()
@@ -155,6 +158,9 @@ class Sampler:
         if getattr(self, "_h", None):
             self._lib.lgml_sampler_free(self._h)
             self._h = None
+
+    def __reduce__(self):
+        raise TypeError(f"a {type(self).__name__} holds state of the host library and cannot be copied or pickled")
 
     # ---- history (src/sample.c:603-650) -------------------------------------------------
     @property
