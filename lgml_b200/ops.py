@@ -430,7 +430,9 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
     tiles = -(-N // 128)
     k_blocks = -(-K // 64)
     cover = (2 * SM_COUNT) // tiles if M <= 16 else -(-SM_COUNT // tiles)
-    return max(1, min(cover, k_blocks // 4, 16))
+    splits = max(1, min(cover, k_blocks // 4, 16))
+    # no range without K blocks: 64 blocks in 9 ranges of 8 would leave the ninth empty
+    return -(-k_blocks // -(-k_blocks // splits))
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor], status: torch.Tensor,
