@@ -328,9 +328,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         const int t = r2 >> 7, r = r2 & (ROWS - 1);
         const int tok_in = r / hpc, g = r - tok_in * hpc;
         const int tok = t * tt + tok_in;
-        const bool have = c < 2 * ROWS * CHUNKS_D && tok_in < tt && tok < n_tok && g < g_count;
-        dst[i] = have ? smem_u32(Qs + t * TILE_BYTES + (ch >> 3) * (ROWS * 128)) + swz(r, ch & 7) : 0u;
-        if (have) v[i] = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
+        // rows without a token or a head get zeros: their scores are then 0 and their sums finite,
+        // whatever the pages hold, so a page needs per-element tests only where the mask cuts it
+        const bool have = tok_in < tt && tok < n_tok && g < g_count;
+        dst[i] = c < 2 * ROWS * CHUNKS_D ? smem_u32(Qs + t * TILE_BYTES + (ch >> 3) * (ROWS * 128)) + swz(r, ch & 7) : 0u;
+        v[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (dst[i] && have) v[i] = __ldcg(reinterpret_cast<const uint4 *>(q + (size_t)(row0 + tok) * ldq + (size_t)(kvh * group + g0 + g) * D + ch * 8));
     }
     tcgen05_fence_before();
     __syncthreads();                     // the barriers and tensor memory are there; the queries are on their way
@@ -384,7 +387,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         const bool row_valid = my_tok < n_tok_t && my_g < g_count;
         const int pos_first_t = pos_first + t * tt, pos_last_t = pos_first_t + n_tok_t - 1;
         const int qpos = row_valid ? pos_first_t + my_tok : -1;
-        const bool full_rows = n_tok_t * hpc == ROWS && g_count == hpc;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)t * TILE_COLS;
         const uint32_t o_addr = lane_addr + O_COL;
         // m_ref: the maximum (base-2 units) that this row's sum l_run and its output in tensor memory
@@ -402,7 +404,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             tcgen05_fence_after();
             // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A page that lies wholly
             // inside every row's range takes the path without per-element tests.
-            const bool edge = key0 + PAGE - 1 > pos_first_t || (window > 0 && key0 < pos_last_t - window + 1) || !full_rows;
+            const bool edge = key0 + PAGE - 1 > pos_first_t || (window > 0 && key0 < pos_last_t - window + 1);
             const int c_hi = qpos - key0;                                              // qpos = -1 for a row without a token
             const int c_lo = (window > 0) ? qpos - window + 1 - key0 : -(1 << 30);
             uint32_t r[PAGE];
