@@ -385,7 +385,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             const bool have = page_id >= 0 && page_id < n_pages;
             // Columns c (keys key0 + c) this row may see: c_lo <= c <= c_hi.  A page that lies wholly
             // inside every row's range takes the path without per-element tests.
-            const bool edge = !have || key0 + PAGE - 1 > pos_first || (window > 0 && key0 < pos_last - window + 1) || n_tok * hpc < ROWS || g_count < hpc;
+            // (rows without a token or a head hold zero queries: their scores are 0, their sums finite, and they are never written)
+            const bool edge = !have || key0 + PAGE - 1 > pos_first || (window > 0 && key0 < pos_last - window + 1);
             const int c_hi = have ? qpos - key0 : -1;                                  // qpos = -1 for a row without a token
             const int c_lo = (window > 0) ? qpos - window + 1 - key0 : -(1 << 30);
             uint32_t r[PAGE];
