@@ -25,6 +25,7 @@ def main(argv=None) -> int:
     ap.add_argument("-np", "--parallel", type=int, default=4, help="slots: the most requests kept at once (default 4)")
     ap.add_argument("-ub", "--ubatch", type=int, default=512, help="prompt tokens per request per pass (default 512)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--prefix-cache", action="store_true", help="keep the full pages of ended requests findable: a prompt that begins like an earlier one computes only the rest")
     ap.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids; repeat for more requests")
     ap.add_argument("-n", "--max-tokens", type=int, default=16, help="new tokens per request")
     ap.add_argument("--temperature", type=float, default=0.8)
@@ -54,7 +55,7 @@ def main(argv=None) -> int:
         ap.error("give at least one --prompt-ids")
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt_ids]
     eng = Engine(args.model, config=cfg, random_weights=args.seed or 0, dtype=args.dtype, n_ctx=args.ctx, slots=args.parallel,
-                 ubatch=args.ubatch, repeat_stop_tokens=args.repeat_stop)
+                 ubatch=args.ubatch, repeat_stop_tokens=args.repeat_stop, prefix_cache=args.prefix_cache)
     outs = eng.generate(prompts, max_tokens=args.max_tokens, seed=args.seed, temperature=args.temperature, top_k=args.top_k,
                         top_p=args.top_p, min_p=args.min_p, repeat_penalty=args.repeat_penalty,
                         frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty,

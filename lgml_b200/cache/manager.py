@@ -16,9 +16,20 @@ Pages are taken before a step for the positions it will write
 back when the request ends (``free_seq``, ``:784-803``) or a window has passed
 them.  All of the pool exists from the start (``kv_initial = 0``,
 ``lua/lgml/engine.lua:397-399``).
+
+With ``prefix_cache`` the full pages of a request get keys when it ends or is preempted
+(a chain of hashes over the tokens, ``M.key``, ``lua/lgml/kvpool.lua:51-59``), and a new
+request whose tokens begin the same way shares those pages instead of computing them
+(``E:reuse`` ``lua/lgml/engine.lua:1775-1819``, ``E:attach_blocks`` ``:2038``); at least its
+last token is always computed, since its logits are wanted.  Shared pages are only read:
+a request writes behind its prefix, into pages of its own.  This needs every layer to keep
+all its keys (no window, no state of fixed size: those cannot be taken up in the middle,
+``check_pass`` ``lua/lgml/transformer.lua:1548-1563``).
 """
 from __future__ import annotations
 
+import hashlib
+import struct
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -86,9 +97,10 @@ class CacheManager:
     """
 
     def __init__(self, layout: Dict[int, object], n_pages: int, max_slots: int, dtype: torch.dtype, device,
-                 page_size: int = PAGE_SIZE, max_step_tokens: int = 0):
+                 page_size: int = PAGE_SIZE, max_step_tokens: int = 0, prefix_cache: bool = False):
         if max_slots <= 0:
             raise ValueError("max_slots must be positive")
+        self.prefix_cache = bool(prefix_cache)
         self.page_size = page_size
         self.max_slots = max_slots
         self.device = torch.device(device)
@@ -130,6 +142,8 @@ class CacheManager:
         for sg in self.state_groups:
             for layer in sg.layers:
                 sg.state[layer] = torch.zeros((max_slots,) + tuple(sg.spec.shape), dtype=sg.spec.dtype, device=self.device)
+        if self.prefix_cache and (self.state_groups or any(g.spec.window is not None for g in self.groups)):
+            raise ValueError("prefix_cache needs layers that keep all their keys: a window or a state of fixed size cannot be taken up in the middle")
         self._free_slots = list(range(max_slots - 1, -1, -1))
         self.live: Dict[Hashable, Request] = {}
 
@@ -157,7 +171,9 @@ class CacheManager:
         return n
 
     # ---- requests ----------------------------------------------------------------------
-    def open(self, rid: Hashable) -> Request:
+    def open(self, rid: Hashable, tokens: Optional[Sequence[int]] = None) -> Request:
+        """A slot for a new request.  With ``prefix_cache`` and the request's ``tokens`` it
+        starts with the pages that already hold its first tokens: ``n_tokens`` says how many."""
         if rid in self.live:
             raise ValueError(f"request {rid!r} is already live")
         if not self._free_slots:
@@ -168,7 +184,58 @@ class CacheManager:
             for t in sg.state.values():
                 t[slot].zero_()
         self.live[rid] = req
+        if self.prefix_cache and tokens:
+            for pages in self._cached_prefix(tokens):
+                for gi, page in enumerate(pages):
+                    self.groups[gi].pool.share(page)
+                    req.tables[gi].append(page)
+                req.n_tokens += self.page_size
         return req
+
+    # ---- prefix cache ------------------------------------------------------------------
+    def _keys(self, tokens: Sequence[int], n_blocks: int):
+        """The keys of the first ``n_blocks`` full pages of ``tokens``: each hashes the key
+        before it and its own tokens, so a key stands for the whole prefix."""
+        key = b"lgml_b200 page %d" % self.page_size
+        for b in range(n_blocks):
+            block = tokens[b * self.page_size:(b + 1) * self.page_size]
+            key = hashlib.sha256(key + struct.pack(f"<{self.page_size}q", *block)).digest()
+            yield key
+
+    def _cached_prefix(self, tokens: Sequence[int]) -> List[List[int]]:
+        """Per leading full page of ``tokens`` that every group still holds under its key: the
+        group's pages.  The last token is never part of it."""
+        out: List[List[int]] = []
+        for key in self._keys(tokens, (len(tokens) - 1) // self.page_size):
+            pages = [g.pool.lookup(key) for g in self.groups]
+            if any(p is None for p in pages):
+                break
+            out.append(pages)
+        return out
+
+    def cached_prefix_tokens(self, tokens: Sequence[int]) -> int:
+        """How many leading tokens ``open(rid, tokens)`` would find in the cache."""
+        return len(self._cached_prefix(tokens)) * self.page_size if self.prefix_cache and tokens else 0
+
+    def cached_pages_in_prefix(self, tokens: Sequence[int]) -> int:
+        """Of the pages ``open(rid, tokens)`` would share, those that nobody holds now: they
+        count among the free pages until they are shared (the tightest group's number)."""
+        if not self.prefix_cache or not tokens:
+            return 0
+        pref = self._cached_prefix(tokens)
+        return max((sum(1 for pages in pref if g.pool.refcount(pages[gi]) == 0) for gi, g in enumerate(self.groups)), default=0)
+
+    def publish(self, req: Request, tokens: Sequence[int]) -> int:
+        """Give the request's full pages their keys (``tokens[p]`` is the token at position p; only
+        positions the cache holds count).  Returns the pages that are findable afterwards."""
+        if not self.prefix_cache or req.closed:
+            return 0
+        n_blocks = min(req.n_tokens, len(tokens)) // self.page_size
+        found = 0
+        for b, key in enumerate(self._keys(tokens, n_blocks)):
+            ok = [g.pool.publish(req.tables[gi][b], key) for gi, g in enumerate(self.groups)]
+            found += all(ok)
+        return found
 
     def _first_needed_block(self, grp: PagedGroup, n_tokens: int) -> int:
         """Lowest block that a query at position >= n_tokens can still reach."""
@@ -235,7 +302,10 @@ class CacheManager:
         if req.closed:
             raise ValueError(f"request {req.id!r} closed twice")
         for gi, grp in enumerate(self.groups):
-            for page in req.tables[gi]:
+            # the deepest page first: of a chain of cached pages the pool then takes the end
+            # before the beginning, and what is left is still a prefix (the reference evicts by
+            # depth too, ``lua/lgml/kvpool.lua:139-160``)
+            for page in reversed(req.tables[gi]):
                 if page >= 0:
                     grp.pool.release(page)
             req.tables[gi] = []
@@ -254,10 +324,13 @@ class CacheManager:
         for gi, grp in enumerate(self.groups):
             grp.pool.check()
             held = [p for r in self.live.values() for p in r.tables[gi] if p >= 0]
-            if len(set(held)) != len(held):
-                raise AssertionError(f"group {gi}: a page is in two block tables")
-            if len(held) != grp.pool.n_held:
-                raise AssertionError(f"group {gi}: {grp.pool.n_held} pages held but {len(held)} in block tables (a page was lost)")
+            for p in set(held):
+                if held.count(p) != grp.pool.refcount(p):
+                    raise AssertionError(f"group {gi}: page {p} is in {held.count(p)} block tables but held {grp.pool.refcount(p)} times")
+                if held.count(p) > 1 and not self.prefix_cache:
+                    raise AssertionError(f"group {gi}: a page is in two block tables")
+            if len(set(held)) != grp.pool.n_held:
+                raise AssertionError(f"group {gi}: {grp.pool.n_held} pages held but {len(set(held))} in block tables (a page was lost)")
         slots = [r.slot for r in self.live.values()]
         if len(set(slots)) != len(slots) or len(slots) + len(self._free_slots) != self.max_slots:
             raise AssertionError("slots lost or held twice")

@@ -9,7 +9,10 @@ the pool larger than one request's context), ``slots`` (the most requests kept a
 default 512), ``max_tokens`` (default reply length: the free context),
 ``sampling`` (sampler defaults, a request's values replace them),
 ``repeat_stop_tokens``.  ``run_ahead`` (not in the reference): launch a decode step before
-the host has seen the ids of the one before, when those are chosen on the device.  ``generate.greedy`` of the reference
+the host has seen the ids of the one before, when those are chosen on the device.
+``prefix_cache`` (always on in the reference, ``E:reuse`` ``lua/lgml/engine.lua:1775-1819``; off by default
+here): the full pages of ended and preempted requests stay findable by a key of their tokens, and a
+prompt that begins like one of them computes only the rest.  ``generate.greedy`` of the reference
 (``lua/lgml/generate.lua:19-34``) is ``Engine.greedy``.
 """
 from __future__ import annotations
@@ -42,7 +45,7 @@ class Engine:
     def __init__(self, model=None, *, config=None, random_weights: Optional[int] = None, dtype="bfloat16", n_ctx: Optional[int] = None,
                  kv_tokens: Optional[int] = None, slots: int = 4, ubatch: int = UBATCH, max_batch_tokens: Optional[int] = None, max_tokens: Optional[int] = None,
                  sampling: Optional[dict] = None, repeat_stop_tokens: int = REPEAT_STOP, device="cuda:0",
-                 run_ahead: bool = True):
+                 run_ahead: bool = True, prefix_cache: bool = False):
         dt = parse_dtype(dtype)
         if model is None and config is None:
             raise ValueError("give a model folder, or a config with random_weights=seed")
@@ -58,7 +61,7 @@ class Engine:
         # the pool all slots share: n_ctx tokens as in the reference, or kv_tokens when given
         n_pages = -(-(kv_tokens or n_ctx) // 64)
         max_batch_tokens = max_batch_tokens or max(ubatch, 2048)
-        kw = dict(n_pages=n_pages, max_slots=slots, max_step_tokens=max_batch_tokens)
+        kw = dict(n_pages=n_pages, max_slots=slots, max_step_tokens=max_batch_tokens, prefix_cache=prefix_cache)
         if model is not None:
             self.runner = ModelRunner.from_folder(model, dt, device, **kw)
         else:

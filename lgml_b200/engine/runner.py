@@ -30,11 +30,12 @@ class StepError(ValueError):
 
 
 class ModelRunner:
-    def __init__(self, model, rt: Runtime, n_pages: int, max_slots: int = 4, max_step_tokens: int = 0, use_graphs: bool = True):
+    def __init__(self, model, rt: Runtime, n_pages: int, max_slots: int = 4, max_step_tokens: int = 0, use_graphs: bool = True,
+                 prefix_cache: bool = False):
         self.model = model
         self.rt = rt
         self.cache = CacheManager(model.cache_layout(), n_pages=n_pages, max_slots=max_slots, dtype=rt.dtype,
-                                  device=rt.device, max_step_tokens=max_step_tokens)
+                                  device=rt.device, max_step_tokens=max_step_tokens, prefix_cache=prefix_cache)
         # a ring of pinned staging buffers: a buffer is reused only after its copy has run
         self._pinned = [[torch.empty(1 << 16, dtype=torch.int32).pin_memory(), None] for _ in range(4)]
         self.steps = 0
@@ -91,8 +92,10 @@ class ModelRunner:
         stage[1].record()
 
     # ---- requests ----------------------------------------------------------------------
-    def open(self, rid: Hashable) -> Request:
-        return self.cache.open(rid)
+    def open(self, rid: Hashable, tokens: Optional[Sequence[int]] = None) -> Request:
+        """A slot for a new request; with the prefix cache on and its tokens given, it starts
+        behind what the cache already holds of them (``Request.n_tokens``)."""
+        return self.cache.open(rid, tokens)
 
     def close(self, req: Request) -> None:
         self.cache.close(req)

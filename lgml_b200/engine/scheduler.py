@@ -84,7 +84,7 @@ class Scheduler:
         self.finished: List[GenRequest] = []
         self._admissions = 0
         # counters, as the reference's batch_passes / batch_rows / batch_tokens (lua/lgml/engine.lua:1488-1492)
-        self.stats = dict(steps=0, rows=0, tokens=0, preemptions=0, admitted=0)
+        self.stats = dict(steps=0, rows=0, tokens=0, preemptions=0, admitted=0, prefix_tokens=0)
 
     # ---- intake --------------------------------------------------------------------------
     def add(self, req: GenRequest) -> None:
@@ -105,6 +105,9 @@ class Scheduler:
 
     # ---- planning ------------------------------------------------------------------------
     def _preempt(self, victim: GenRequest, plan: List[PlannedEntry]) -> None:
+        # (with a prefix cache its full pages stay findable: when it is admitted again it takes
+        #  up what the pool has not needed meanwhile, lua/lgml/engine.lua:1193-1243)
+        self.cache.publish(victim.cache_req, victim.tokens)
         self.cache.close(victim.cache_req)
         victim.cache_req = None
         victim.n_cached = 0
@@ -117,6 +120,7 @@ class Scheduler:
     def _finish(self, req: GenRequest, reason: str) -> None:
         req.finish_reason = reason
         if req.cache_req is not None:
+            self.cache.publish(req.cache_req, req.tokens)
             self.cache.close(req.cache_req)
             req.cache_req = None
         if req in self.running:
@@ -163,7 +167,10 @@ class Scheduler:
         while self.waiting and budget > 0 and len(self.cache.live) < self.cache.max_slots:
             req = self.waiting[0]
             total = len(req.prompt) + len(req.generated)
-            if self.cache.pages_for(total + 1) > self.cache.n_free_pages:
+            # (pages that the prefix cache already holds for its first tokens need not be free:
+            #  cached ones count as free and are not taken twice, held ones are shared)
+            shared = self.cache.cached_prefix_tokens(req.tokens) // self.cache.page_size
+            if self.cache.pages_for(total + 1) - shared > self.cache.n_free_pages - self.cache.cached_pages_in_prefix(req.tokens):
                 if not self.running and not plan:
                     # nothing will ever free a page: the request cannot run
                     self.waiting.popleft()
@@ -171,9 +178,11 @@ class Scheduler:
                     continue
                 break
             try:
-                req.cache_req = self.cache.open(req.id)
+                req.cache_req = self.cache.open(req.id, req.tokens)
             except NoSlot:
                 break
+            req.n_cached = req.cache_req.n_tokens        # what the prefix cache held of its tokens
+            self.stats["prefix_tokens"] += req.n_cached
             self.waiting.popleft()
             req.admitted_at = self._admissions
             self._admissions += 1
@@ -182,7 +191,7 @@ class Scheduler:
             n = min(req.n_pending, self.ubatch, budget)
             if not self.cache.reserve(req.cache_req, n):
                 raise AssertionError("admission checked the pool, yet the first portion found no pages")
-            plan.append(PlannedEntry(req, req.tokens[:n], sample=(n == req.n_pending)))
+            plan.append(PlannedEntry(req, req.tokens[req.n_cached:req.n_cached + n], sample=(n == req.n_pending)))
             budget -= n
         if plan:
             self.stats["steps"] += 1

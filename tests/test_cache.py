@@ -139,3 +139,96 @@ def test_random_orders_keep_the_books(seed):
         cm.close(r)
     cm.check()
     assert all(g.pool.n_held == 0 for g in cm.groups)
+
+
+# ---------------------------------------------------------------------------------------------
+# prefix cache
+# ---------------------------------------------------------------------------------------------
+
+def _prefix_manager(n_pages=12, slots=4):
+    from lgml_b200.cache import CacheManager, PagedKV
+    return CacheManager({0: PagedKV(2, 16), 1: PagedKV(2, 16)}, n_pages=n_pages, max_slots=slots, dtype=torch.float32, device="cpu",
+                        prefix_cache=True)
+
+
+def test_prefix_cache_shares_full_pages_and_never_the_last_token():
+    m = _prefix_manager()
+    toks = list(range(200))
+    a = m.open("a", toks)
+    assert a.n_tokens == 0 and m.reserve(a, 200)
+    m.commit(a, 200)
+    assert m.publish(a, toks) == 3                       # three full pages of 64
+    b = m.open("b", toks[:150] + [999] * 20)             # same first 150 tokens: two full pages in common
+    assert b.n_tokens == 128 and b.tables[0] == a.tables[0][:2]
+    assert m.groups[0].pool.refcount(a.tables[0][0]) == 2
+    c = m.open("c", toks[:128])                          # all of it is cached, but its last token must run
+    assert c.n_tokens == 64
+    m.check()
+    m.close(a)
+    m.check()
+    assert m.groups[0].pool.n_cached == 1                # the third page: keyed, nobody holds it
+    d = m.open("d", toks)                                # takes up all three again
+    assert d.n_tokens == 192 and m.groups[0].pool.n_cached == 0
+    for r in (b, c, d):
+        m.close(r)
+    m.check()
+    assert m.groups[0].pool.n_held == 0 and m.groups[0].pool.n_free == 12 and m.groups[0].pool.n_cached == 3
+
+
+def test_prefix_cache_gives_cached_pages_up_when_the_pool_needs_them():
+    m = _prefix_manager(n_pages=4, slots=2)
+    toks = list(range(1000, 1130))
+    a = m.open("a", toks)
+    assert m.reserve(a, 130)
+    m.commit(a, 130)
+    m.publish(a, toks)
+    m.close(a)
+    pool = m.groups[0].pool
+    assert pool.n_cached == 2 and pool.n_free == 4
+    b = m.open("b", list(range(5, 250)))                 # other tokens: needs all four pages
+    assert b.n_tokens == 0 and m.reserve(b, 245)
+    assert pool.n_cached == 0 and pool.evicted_total == 2
+    m.close(b)
+    c = m.open("c", toks)                                # the keys went with the pages
+    assert c.n_tokens == 0
+    m.close(c)
+    m.check()
+
+
+def test_prefix_cache_refuses_windows_and_fixed_state():
+    from lgml_b200.cache import CacheManager, FixedState, PagedKV
+    with pytest.raises(ValueError, match="prefix_cache"):
+        CacheManager({0: PagedKV(2, 16, window=100)}, n_pages=8, max_slots=2, dtype=torch.float32, device="cpu", prefix_cache=True)
+    with pytest.raises(ValueError, match="prefix_cache"):
+        CacheManager({0: PagedKV(2, 16), 1: FixedState((4,))}, n_pages=8, max_slots=2, dtype=torch.float32, device="cpu", prefix_cache=True)
+
+
+def test_prefix_cache_random_orders_keep_the_books():
+    import random
+    rng = random.Random(5)
+    m = _prefix_manager(n_pages=10, slots=3)
+    families = [[rng.randrange(50) for _ in range(400)] for _ in range(3)]
+    live = {}
+    for step in range(400):
+        if live and (len(live) == 3 or rng.random() < 0.4):
+            rid = rng.choice(list(live))
+            req, toks = live.pop(rid)
+            if rng.random() < 0.8:
+                m.publish(req, toks)
+            m.close(req)
+        else:
+            fam = rng.choice(families)
+            toks = fam[:rng.randrange(1, 300)] + [rng.randrange(50) for _ in range(rng.randrange(0, 80))]
+            req = m.open(step, toks)
+            assert req.n_tokens % 64 == 0 and req.n_tokens < len(toks)
+            n = len(toks) - req.n_tokens
+            if m.reserve(req, n):
+                m.commit(req, n)
+                live[step] = (req, toks)
+            else:
+                m.close(req)
+        m.check()
+    for req, _ in live.values():
+        m.close(req)
+    m.check()
+    assert m.groups[0].pool.n_held == 0 and m.groups[0].pool.shared_total > 0

@@ -96,6 +96,38 @@ def test_preemption_keeps_every_reply_whole(folders):
     assert tight.runner.cache.n_free_pages == 5
 
 
+@pytest.mark.skip(reason="written when the round's GPU time was spent: the prefix cache's bookkeeping is tested on the CPU "
+                         "(test_cache.py, test_scheduler.py), this comparison on a GPU has not run yet")
+def test_prefix_cache_changes_no_reply(folders):
+    """With the prefix cache on, prompts that begin like earlier ones take up the pages that hold
+    those tokens and compute only the rest: the replies equal those of an engine without it, in
+    32-bit token for token; a pool too small for everything (preemption, cached pages taken
+    away again) included."""
+    import lgml_b200
+
+    folder = folders[("B", "float32")]
+    common = H.random_ids(150, 320, 901)
+    prompts = [common + H.random_ids(n, 320, 910 + n) for n in (1, 20, 70)] + [common[:130], H.random_ids(90, 320, 950)]
+    plain = lgml_b200.Engine(str(folder), dtype="float32", slots=2, kv_tokens=64 * 16)
+    want = plain.generate(prompts, max_tokens=40, temperature=0.0)
+    for kv_pages in (16, 7):
+        eng = lgml_b200.Engine(str(folder), dtype="float32", slots=2, kv_tokens=64 * kv_pages, prefix_cache=True)
+        got = eng.generate(prompts, max_tokens=40, temperature=0.0)
+        assert got == want, kv_pages
+        again = eng.generate(prompts[:2], max_tokens=40, temperature=0.0)      # everything of these is cached by now
+        assert again == want[:2]
+        assert eng.scheduler.stats["prefix_tokens"] >= 128 * 3
+        eng.runner.cache.check()
+        assert not eng.runner.cache.live and eng.runner.cache.n_free_pages == kv_pages
+    # bfloat16: the same replies as the same engine without the cache computes for each prompt alone
+    folder = folders[("B", "bfloat16")]
+    eng = lgml_b200.Engine(str(folder), dtype="bfloat16", slots=1, kv_tokens=64 * 16, prefix_cache=True)
+    base = lgml_b200.Engine(str(folder), dtype="bfloat16", slots=1, kv_tokens=64 * 16)
+    for p in prompts[:3]:
+        assert eng.generate([p], max_tokens=8, temperature=0.0) == base.generate([p], max_tokens=8, temperature=0.0)
+    assert eng.scheduler.stats["prefix_tokens"] >= 128 * 2
+
+
 @pytest.mark.parametrize("key", [("B", "float32"), ("B", "bfloat16")])
 def test_launching_ahead_of_the_host_changes_no_reply(folders, key):
     """Decode steps launched before the host has seen the ids of the step before: replies,

@@ -286,3 +286,67 @@ def test_planning_ahead_stops_when_a_page_is_missing():
     s.complete(inflight, {"a": 3})
     assert s.plan() == [] and a.finish_reason == "length"   # alone and out of pages
     cm.check()
+
+
+# ---------------------------------------------------------------------------------------------
+# prefix cache
+# ---------------------------------------------------------------------------------------------
+
+def make_prefix(n_pages=8, slots=4, **kw):
+    cm = CacheManager({0: PagedKV(1, 8)}, n_pages=n_pages, max_slots=slots, dtype=torch.float32, device="cpu", prefix_cache=True)
+    return Scheduler(cm, max_position=4096, ubatch=kw.get("ubatch", 512), max_batch_tokens=kw.get("budget", 2048), repeat_stop_tokens=0), cm
+
+
+def test_a_prompt_that_begins_like_an_earlier_one_runs_only_the_rest():
+    s, cm = make_prefix()
+    a = req("a", 200, 2)
+    s.add(a)
+    drive(s, cm)
+    assert s.stats["prefix_tokens"] == 0 and cm.groups[0].pool.n_cached == 3      # 200 + 2 tokens: three full pages stay findable
+    b = req("b", 200, 2)                                                          # the same prompt
+    s.add(b)
+    log = []
+    drive(s, cm, log)
+    assert log[0] == [("b", 200 - 192, True)] and s.stats["prefix_tokens"] == 192
+    assert b.generated == a.generated                                             # the stub's tokens depend on the tokens alone
+    c = GenRequest(id="c", prompt=list(range(1, 101)) + [7] * 100, max_new_tokens=1, params=SamplingParams.neutral(0.0))
+    s.add(c)                                                                      # 100 tokens in common: one full page
+    log = []
+    drive(s, cm, log)
+    assert log[0] == [("c", 200 - 64, True)]
+    cm.check()
+    assert not cm.live and cm.groups[0].pool.n_held == 0
+
+
+def test_admission_counts_cached_pages_once():
+    """A pool of 4 pages whose 3 cached pages are the new prompt's prefix: the prompt needs 4 pages,
+    3 of them are the cached ones, and that fits; another prompt of the same length does not."""
+    s, cm = make_prefix(n_pages=4, slots=2)
+    a = req("a", 193, 1)
+    s.add(a)
+    drive(s, cm)
+    assert cm.groups[0].pool.n_cached == 3 and cm.n_free_pages == 4
+    b = req("b", 250, 2)                      # begins like a (192 tokens in common), needs 4 pages in all
+    s.add(b)
+    drive(s, cm)
+    assert b.finish_reason == "length" and len(b.generated) == 2 and s.stats["prefix_tokens"] == 192
+    assert cm.groups[0].pool.evicted_total == 0
+
+
+def test_a_preempted_request_takes_up_its_own_pages_again():
+    s, cm = make_prefix(n_pages=6, slots=2, ubatch=64)
+    a, b = req("a", 130, 70), GenRequest(id="b", prompt=list(range(500, 630)), max_new_tokens=70, params=SamplingParams.neutral(0.0))
+    s.add(a)
+    s.add(b)
+    drive(s, cm)
+    assert s.stats["preemptions"] >= 1 and s.stats["prefix_tokens"] >= 128       # the victim found its first pages again
+    assert a.generated == solo_prefix(130, 70, a.prompt) and b.generated == solo_prefix(130, 70, b.prompt)
+    assert not cm.live and cm.groups[0].pool.n_held == 0
+
+
+def solo_prefix(n_prompt, max_new, prompt):
+    s, cm = make_prefix(n_pages=16)
+    r = GenRequest(id="solo", prompt=list(prompt), max_new_tokens=max_new, params=SamplingParams.neutral(0.0))
+    s.add(r)
+    drive(s, cm)
+    return r.generated
