@@ -282,6 +282,32 @@ class CacheManager:
             return False
         return True
 
+    def reserve_all(self, wanted: Sequence[Tuple[Request, int]]) -> Optional[int]:
+        """``reserve`` for every (request, new tokens) of a step, or for none: when one finds
+        no page, those before it give back what this call took for them.  Returns the index
+        of the entry that found no page, or None when all have theirs."""
+        before = [[len(t) for t in req.tables] for req, _ in wanted]
+        for i, (req, n) in enumerate(wanted):
+            if not self.reserve(req, n):
+                for (r, _), lens in zip(wanted[:i], before[:i]):
+                    self.unreserve(r, lens)
+                return i
+        return None
+
+    def unreserve(self, req: Request, table_lens: Sequence[int]) -> None:
+        """Give back the pages a ``reserve`` took: cut every group's table back to the length
+        it had before (``table_lens``, one per group).  Only pages behind what the request has
+        written can go, so nothing that holds keys is lost."""
+        written = self.pages_for(req.n_tokens)
+        for gi, grp in enumerate(self.groups):
+            table = req.tables[gi]
+            if table_lens[gi] < written or table_lens[gi] > len(table):
+                raise ValueError(f"request {req.id!r}: cannot cut a table of {len(table)} pages, {written} of them written, back to {table_lens[gi]}")
+            while len(table) > table_lens[gi]:
+                page = table.pop()
+                if page >= 0:
+                    grp.pool.release(page)
+
     def commit(self, req: Request, n_new: int) -> None:
         """The step wrote ``n_new`` positions: advance, and give back what a window passed."""
         req.n_tokens += n_new

@@ -130,14 +130,22 @@ class ModelRunner:
             if max_pos is not None and req.n_tokens + len(tokens) > max_pos:
                 raise StepError(f"request {req.id!r}: context full ({req.n_tokens} + {len(tokens)} tokens > {max_pos} positions)")
 
+    def _reserve_all(self, wanted: Sequence[Tuple[Request, int]]) -> None:
+        """Pages for every entry of a step, or for none: when one entry finds no page, the
+        entries before it give back what they took in this call, so that a step that fails
+        leaves the pool and every block table as they were (the reference fails such a step
+        alone, ``lua/lgml/engine.lua:1436-1448``)."""
+        failed = self.cache.reserve_all(wanted)
+        if failed is not None:
+            req, n = wanted[failed]
+            raise PoolFull(f"kv pool full: request {req.id!r} needs pages for {n} more tokens, "
+                           f"{self.cache.n_free_pages} of {self.cache.n_pages} pages are free")
+
     def step(self, entries: Sequence[Tuple[Request, Sequence[int], Sequence[int]]]) -> torch.Tensor:
         """entries: (request, its next tokens, the places among them whose logits are
         wanted).  Returns float32 [wanted, vocab] in the order of entries and places."""
         self.validate(entries)
-        for req, tokens, _ in entries:
-            if not self.cache.reserve(req, len(tokens)):
-                raise PoolFull(f"kv pool full: request {req.id!r} needs pages for {len(tokens)} more tokens, "
-                               f"{self.cache.n_free_pages} of {self.cache.n_pages} pages are free")
+        self._reserve_all([(req, len(tokens)) for req, tokens, _ in entries])
         stage = self._pinned[self.steps % len(self._pinned)]
         if stage[1] is not None:
             stage[1].synchronize()
@@ -203,9 +211,7 @@ class ModelRunner:
             raise StepError("decode_step takes one int32 token id per request, on the device")
         entries = [(r, [0], [0]) for r in requests]
         self.validate(entries)
-        for r in requests:
-            if not self.cache.reserve(r, 1):
-                raise PoolFull(f"kv pool full: request {r.id!r} needs a page, {self.cache.n_free_pages} of {self.cache.n_pages} are free")
+        self._reserve_all([(r, 1) for r in requests])
         stage = self._pinned[self.steps % len(self._pinned)]
         if stage[1] is not None:
             stage[1].synchronize()

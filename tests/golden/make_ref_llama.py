@@ -97,6 +97,22 @@ def to_half_pairing(w):
     return out
 
 
+def write_folder(folder, dtype="float32"):
+    """The same model as a safetensors folder: rows in safetensors order (half pairing), the
+    frequency factors under ``rope_freqs.weight`` as the reference's loader takes them
+    (``lua/lgml/transformer.lua:410``).  ``dtype`` is the stored type of the matrices."""
+    from lgml_b200.weights import write_safetensors
+
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    w = to_half_pairing(build())
+    if dtype == "bfloat16":
+        w = {k: (v.to(torch.bfloat16) if v.dim() == 2 else v) for k, v in w.items()}
+    (folder / "config.json").write_text(json.dumps({**CONFIG, "model_type": "llama", "torch_dtype": dtype}, indent=1))
+    write_safetensors(folder / "model.safetensors", w, metadata={"format": "pt"})
+    return folder
+
+
 def main():
     ref = json.loads((HERE / "ref_llama.json").read_text())
     ids = [row["id"] for row in ref["rows"]]

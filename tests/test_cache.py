@@ -232,3 +232,34 @@ def test_prefix_cache_random_orders_keep_the_books():
         m.close(req)
     m.check()
     assert m.groups[0].pool.n_held == 0 and m.groups[0].pool.shared_total > 0
+
+
+def test_a_step_that_finds_no_page_leaves_the_books_as_they_were():
+    """Three entries, the third cannot fit: the first two give back what the call took for them."""
+    from lgml_b200.engine.runner import ModelRunner
+
+    cm = manager(n_pages=6, layout={0: PagedKV(2, 8), 1: PagedKV(2, 8, window=70)})
+    a, b, c = cm.open("a"), cm.open("b"), cm.open("c")
+    assert cm.reserve(a, 70)
+    cm.commit(a, 70)
+    assert cm.reserve(b, 10)
+    cm.commit(b, 10)
+    free = [g.pool.n_free for g in cm.groups]
+    lens = [[len(t) for t in r.tables] for r in (a, b, c)]
+    tables = [[list(t) for t in r.tables] for r in (a, b, c)]
+    wanted = [(a, 60), (b, 64), (c, 129)]          # a and b need a page more each, c three: one too many
+    assert cm.reserve_all(wanted) == 2
+    assert [g.pool.n_free for g in cm.groups] == free
+    assert [[len(t) for t in r.tables] for r in (a, b, c)] == lens
+    assert [[list(t) for t in r.tables] for r in (a, b, c)] == tables
+    cm.check()
+    # the step function raises and changes nothing either (no device is touched before the pages are had)
+    runner = ModelRunner.__new__(ModelRunner)
+    runner.cache = cm
+    with pytest.raises(PoolFull, match="kv pool full: request 'c'"):
+        runner._reserve_all(wanted)
+    assert [g.pool.n_free for g in cm.groups] == free and [[len(t) for t in r.tables] for r in (a, b, c)] == lens
+    assert cm.reserve_all(wanted[:2]) is None and cm.n_free_pages == free[0] - 2
+    with pytest.raises(ValueError, match="cannot cut"):
+        cm.unreserve(a, [0, 0])                     # never below what holds keys
+    cm.check()

@@ -96,8 +96,6 @@ def test_preemption_keeps_every_reply_whole(folders):
     assert tight.runner.cache.n_free_pages == 5
 
 
-@pytest.mark.skip(reason="written when the round's GPU time was spent: the prefix cache's bookkeeping is tested on the CPU "
-                         "(test_cache.py, test_scheduler.py), this comparison on a GPU has not run yet")
 def test_prefix_cache_changes_no_reply(folders):
     """With the prefix cache on, prompts that begin like earlier ones take up the pages that hold
     those tokens and compute only the rest: the replies equal those of an engine without it, in
