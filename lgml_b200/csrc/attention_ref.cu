@@ -8,7 +8,9 @@
 //
 // softmax over keys of (q . k) * scale with keys at positions <= the query's
 // (lua/lgml/transformer.lua:1805-1816, src/lgml.c:2083-2118, mask :2863-2865); head h
-// reads KV head h / (H / Hkv).  Scores, the running maximum and the sums are float32.
+// reads KV head h / (H / Hkv).  Scores, the running maximum and the sums are float32.  With
+// softcap > 0 a score s becomes softcap * tanh(s / softcap) before the softmax (the reference's
+// hp.softcap for other families, lua/lgml/transformer.lua:2097-2102; Llama has none).
 #include <math.h>
 
 #include "common.cuh"
@@ -24,7 +26,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
     const T *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const T *__restrict__ k_pages, const T *__restrict__ v_pages,
     int n_pages, int page_size, T *__restrict__ out, int ldo, int H, int Hkv, int D, float scale, int window,
-    int *__restrict__ status) {
+    float softcap, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     __shared__ float qs[MAX_D];
@@ -56,7 +58,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
         const size_t cell = (((size_t)page * Hkv + g) * page_size + (size_t)(j % page_size)) * D;
         float dot = 0.f;
         for (int d = lane; d < D; d += 32) dot = fmaf(qs[d], to_f32(act_load(k_pages + cell + d)), dot);
-        const float s = warp_sum(dot) * scale;
+        float s = warp_sum(dot) * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);   // a cap on the scores (off for Llama)
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
         const float p = expf(s - m_new);
@@ -97,22 +100,23 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_ref_kernel(
 LGML_API int lgml_paged_attention_ref(const void *q, int dtype, int ldq, const int *positions, const int *seq_of_token,
                                       const int *block_table, int max_blocks, const void *k_pages, const void *v_pages,
                                       int n_pages, int page_size, void *out, int ldo, int n_tokens, int H, int Hkv, int D,
-                                      float scale, int window, int *status, cudaStream_t stream) {
+                                      float scale, int window, float softcap, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && D > 0 && page_size > 0 && max_blocks > 0, "paged_attention_ref: bad sizes");
     LGML_REQUIRE(H % Hkv == 0, "paged_attention_ref: %d heads are no multiple of %d KV heads", H, Hkv);
     LGML_REQUIRE(D <= MAX_D, "paged_attention_ref: head_dim %d is over %d", D, MAX_D);
     LGML_REQUIRE(H <= 65535, "paged_attention_ref: too many heads");
     LGML_REQUIRE(window >= 0, "paged_attention_ref: bad window");
+    LGML_REQUIRE(softcap >= 0.f, "paged_attention_ref: a score cap must be positive (0 = none)");
     if (n_tokens == 0) return 0;
     dim3 grid(n_tokens, H);
     if (dtype == LGML_F32)
         lgml_launch(paged_attention_ref_kernel<float>, grid, WARPS * 32, 0, stream, 
             (const float *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const float *)k_pages, (const float *)v_pages,
-            n_pages, page_size, (float *)out, ldo, H, Hkv, D, scale, window, status);
+            n_pages, page_size, (float *)out, ldo, H, Hkv, D, scale, window, softcap, status);
     else if (dtype == LGML_BF16)
         lgml_launch(paged_attention_ref_kernel<__nv_bfloat16>, grid, WARPS * 32, 0, stream, 
             (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages,
-            (const __nv_bfloat16 *)v_pages, n_pages, page_size, (__nv_bfloat16 *)out, ldo, H, Hkv, D, scale, window, status);
+            (const __nv_bfloat16 *)v_pages, n_pages, page_size, (__nv_bfloat16 *)out, ldo, H, Hkv, D, scale, window, softcap, status);
     else
         LGML_FAIL("paged_attention_ref: unknown type %d", dtype);
     return lgml_launch_status("paged_attention_ref");

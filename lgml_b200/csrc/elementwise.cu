@@ -471,10 +471,38 @@ LGML_API int lgml_residual_add(float *x, const void *delta, int delta_dtype, lon
 }
 
 // ---------------------------------------------------------------------------------------
-// Seeded normal fill: value i of a tensor = mean + sd * N(0,1) from a counter-based stream
-// (splitmix64 of seed and index, then Box-Muller; mischief/lgml fills its test tensors the
-// same way, src/lgml.c:3064-3079, :3133-3137).  Used to make full-size random models on
-// the device without a host copy.
+// x *= scale, then x = cap * tanh(x / cap) when cap > 0, in place on float32: the embedding
+// scale, the logit scale and the logits' cap that other families of the reference switch on
+// (embd_scale lua/lgml/transformer.lua:2303-2306, logit_scale and softcap :2097-2102).  Llama
+// uses none of them and never launches this.
+// ---------------------------------------------------------------------------------------
+__global__ void scale_cap_kernel(float *__restrict__ x, size_t total, float scale, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = act_load(x + i) * scale;
+        if (cap > 0.f) v = cap * tanhf(v / cap);
+        x[i] = v;
+    }
+}
+
+LGML_API int lgml_scale_cap(float *x, long long total, float scale, float cap, cudaStream_t stream) {
+    LGML_REQUIRE(total >= 0 && cap >= 0.f, "scale_cap: bad size or a negative cap");
+    if (total == 0) return 0;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    lgml_launch(scale_cap_kernel, (int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream, x, (size_t)total, scale, cap);
+    return lgml_launch_status("scale_cap");
+}
+
+// ---------------------------------------------------------------------------------------
+// Seeded normal fill: value i of a tensor = mean + sd * z_i, z_i ~ N(0,1) from a counter-based
+// stream keyed by (seed, i): splitmix64 of seed and index, then Box-Muller, as mischief/lgml
+// fills its test tensors (src/lgml.c:3064-3079, :3133-3137).  The host has the same generator
+// (weights/random_init.py) and must draw the same bits, so nothing here comes from a math
+// library: the logarithm and the cosine are short polynomials of single, correctly rounded
+// float32 operations in a fixed order (the _rn intrinsics are never fused into an FMA), and
+// all range reduction is integer arithmetic on the 24-bit uniform numbers.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
     z += 0x9e3779b97f4a7c15ULL;
@@ -483,18 +511,58 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
     return z ^ (z >> 31);
 }
 
+#define FM(a, b) __fmul_rn((a), (b))
+#define FA(a, b) __fadd_rn((a), (b))
+
+// ln(k / 2^24) for an integer 1 <= k <= 2^24: k = m 2^e with m in (sqrt(1/2), sqrt(2)],
+// ln m = 2 atanh(s), s = (m - 1) / (m + 1), as an odd series up to s^11
+__device__ __forceinline__ float seeded_log_u24(uint32_t k) {
+    const uint32_t bits = __float_as_uint((float)k);         // exact: k has at most 25 bits and 2^24 is a power of two
+    int e = (int)(bits >> 23) - 127;
+    float m = __uint_as_float((bits & 0x7fffffu) | 0x3f800000u);              // [1, 2)
+    if (m > 0x1.6a09e6p+0f) { m = FM(m, 0.5f); e += 1; }
+    const float s = __fdiv_rn(FA(m, -1.0f), FA(m, 1.0f));
+    const float s2 = FM(s, s);
+    float p = FA(0x1.99999ap-3f, FM(s2, FA(0x1.24924ap-3f, FM(s2, FA(0x1.c71c72p-4f, FM(s2, 0x1.745d18p-4f))))));   // 1/5, 1/7, 1/9, 1/11
+    p = FM(s2, FA(0x1.555556p-2f, FM(s2, p)));                                                                       // 1/3
+    const float lnm = FM(2.0f, FA(s, FM(s, p)));
+    return FA(FM((float)(e - 24), 0x1.62e430p-1f), lnm);                      // + (e - 24) ln 2
+}
+
+// cos(2 pi j / 2^24) for an integer 0 <= j < 2^24: the octant and the fold to [0, pi/4] in
+// integers, then the Taylor polynomials of sine and cosine
+__device__ __forceinline__ float seeded_cos_u24(uint32_t j) {
+    const uint32_t q = j >> 21, f = j & 0x1fffffu;
+    const uint32_t g = (q & 1u) ? 0x200000u - f : f;         // odd octants run backwards
+    const float x = FM((float)g, 0x1.921fb6p-22f);           // pi / 4 / 2^21
+    const float x2 = FM(x, x);
+    float r;
+    if ((q + 1u) & 2u) {                                     // octants 1, 2, 5, 6: the sine
+        const float p = FA(-0x1.555556p-3f, FM(x2, FA(0x1.111112p-7f, FM(x2, FA(-0x1.a01a02p-13f, FM(x2, 0x1.71de3ap-19f))))));
+        r = FA(x, FM(x, FM(x2, p)));
+    } else {
+        const float p = FA(-0.5f, FM(x2, FA(0x1.555556p-5f, FM(x2, FA(-0x1.6c16c2p-10f, FM(x2, 0x1.a01a02p-16f))))));
+        r = FA(1.0f, FM(x2, p));
+    }
+    return (q >= 2u && q <= 5u) ? -r : r;
+}
+
+__device__ __forceinline__ float seeded_normal(uint64_t seed, uint64_t i) {
+    const uint64_t h = splitmix64(seed ^ splitmix64(i));
+    const float ln_u = seeded_log_u24((uint32_t)(h >> 40) + 1u);              // u1 in (0, 1]
+    const float radius = __fsqrt_rn(FM(-2.0f, ln_u));
+    return FM(radius, seeded_cos_u24((uint32_t)(h >> 8) & 0xffffffu));
+}
+
 template <typename T>
 __global__ void fill_normal_kernel(T *__restrict__ out, size_t n, float mean, float sd, uint64_t seed) {
     pdl_trigger();
     pdl_wait();
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const uint64_t h = splitmix64(seed ^ splitmix64(i));
-        const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
-        const float u2 = (float)(uint32_t)((h >> 8) & 0xffffff) * (1.0f / 16777216.0f);
-        const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
-        out[i] = from_f32<T>(mean + sd * z);
-    }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(FA(mean, FM(sd, seeded_normal(seed, i))));
 }
+#undef FM
+#undef FA
 
 LGML_API int lgml_fill_normal(void *out, int dtype, long long n, float mean, float sd, unsigned long long seed, cudaStream_t stream) {
     LGML_REQUIRE(n >= 0, "fill_normal: bad size");

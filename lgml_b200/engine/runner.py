@@ -63,12 +63,11 @@ class ModelRunner:
     @classmethod
     def from_config(cls, cfg, seed: int, dtype: torch.dtype, device="cuda:0", std: float = 0.02, on_device: bool = True,
                     **kw) -> "ModelRunner":
-        """Random weights without a folder: drawn on the device (full-size models) or on
-        the host with the same streams as ``write_random_model``."""
+        """Random weights without a folder: drawn on the device, or on the host; either way
+        the values of ``write_random_model(folder, cfg, seed)``, bit for bit (one generator)."""
         from .. import ops
-        from ..weights import MATRIX
         from ..weights.loader import target_dtype
-        import zlib
+        from ..weights.random_init import tensor_key
 
         rt = Runtime(device, dtype)
         model = build_model(cfg)
@@ -77,7 +76,7 @@ class ModelRunner:
             tensors = {}
             for s in specs:
                 t = torch.empty(s.shape, dtype=target_dtype(s.kind, dtype), device=rt.device)
-                ops.fill_normal(t, s.init[0], s.init[1] * std, (seed << 32) ^ zlib.crc32(s.name.encode()))
+                ops.fill_normal(t, s.init[0], s.init[1] * std, tensor_key(seed, s.name))
                 tensors[s.name] = t
         else:
             host = random_tensors(specs, seed, std)

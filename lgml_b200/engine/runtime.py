@@ -19,6 +19,8 @@ _STATUS_TEXT = {
     2: "a key/value write had no page in the block table",
     3: "attention met a position without a page in the block table",
     10: "a tensor-core matrix product gave up waiting for its own copies or products",
+    12: "the tensor-core prompt attention (one tile per CTA) gave up waiting for its own copies or products",
+    13: "the tensor-core prompt attention (two tiles per CTA) gave up waiting for its own copies or products",
 }
 
 
@@ -64,10 +66,12 @@ class Runtime:
         return self.dtype == torch.bfloat16 and self.gemm_backend in ("auto", "tcgen05") and ops.tcgen05_supports(x, w_pairs)
 
     # ---- attention ---------------------------------------------------------------------
-    def attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int) -> torch.Tensor:
-        if self.dtype == torch.float32 or self.attention_backend == "ref":
+    def attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, softcap: float = 0.0) -> torch.Tensor:
+        """Attention of the step's queries over the cache.  A cap on the scores (``softcap`` > 0)
+        is known to the general kernel only, so it takes that kernel in both compute types."""
+        if self.dtype == torch.float32 or self.attention_backend == "ref" or softcap:
             return ops.paged_attention_ref(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v,
-                                           out, n_heads, scale, window, self.status)
+                                           out, n_heads, scale, window, self.status, softcap=softcap)
         return ops.paged_attention(q, batch, cache, out, n_heads, scale, window, self.status)
 
     # ---- faults ------------------------------------------------------------------------

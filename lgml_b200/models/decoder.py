@@ -18,6 +18,7 @@ from typing import Dict, List, Optional
 
 import torch
 
+from .. import ops
 from ..weights import TensorSpec
 
 
@@ -29,7 +30,8 @@ class LayerCall:
 
 class DecoderModel:
     def __init__(self, config, embedding, blocks, final_norm, head, schedule: Optional[List[LayerCall]] = None,
-                 block_prefix: str = "model.layers.{}", final_norm_prefix: str = "model.norm"):
+                 block_prefix: str = "model.layers.{}", final_norm_prefix: str = "model.norm",
+                 embed_scale: Optional[float] = None, logit_scale: Optional[float] = None, logit_softcap: Optional[float] = None):
         self.config = config
         self.embedding = embedding
         self.blocks = list(blocks)
@@ -37,6 +39,10 @@ class DecoderModel:
         self.head = head
         self.block_prefix = block_prefix
         self.final_norm_prefix = final_norm_prefix
+        # scales that other families of the reference apply and Llama does not (None = no kernel):
+        # on the embedding's rows (``embd_scale``, ``lua/lgml/transformer.lua:2303-2306``), on the
+        # logits, and the logits' cap (``logit_scale``, ``softcap``, ``:2097-2102``)
+        self.embed_scale, self.logit_scale, self.logit_softcap = embed_scale, logit_scale, logit_softcap
         self.schedule = list(schedule) if schedule is not None else [LayerCall(i) for i in range(len(self.blocks))]
         for ci, call in enumerate(self.schedule):
             if not 0 <= call.block < len(self.blocks):
@@ -85,10 +91,15 @@ class DecoderModel:
     def forward(self, rt, batch) -> torch.Tensor:
         """float32 logits [len(batch.logit_rows), vocab] for the tokens of ``batch``."""
         x = self.embedding.forward(rt, batch.token_ids)
+        if self.embed_scale is not None:
+            ops.scale_cap(x, self.embed_scale)
         pending = None
         for ci, call in enumerate(self.schedule):
             owner = ci if call.cache is None else call.cache
             cache = batch.cache_view(owner, writable=call.cache is None)
             x, pending = self.blocks[call.block].forward(rt, x, pending, batch, cache)
         h = self.final_norm.forward(rt, x, rt.dtype, delta=pending, rows=batch.logit_rows)
-        return self.head.forward(rt, h)
+        logits = self.head.forward(rt, h)
+        if self.logit_scale is not None or self.logit_softcap:
+            ops.scale_cap(logits, 1.0 if self.logit_scale is None else self.logit_scale, self.logit_softcap or 0.0)
+        return logits

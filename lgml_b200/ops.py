@@ -189,6 +189,16 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
+def scale_cap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place on float32: x *= scale, then x = cap * tanh(x / cap) when cap > 0."""
+    _need(x, "tensor to scale", torch.float32)
+    if not x.is_contiguous():
+        raise KernelError("scale_cap: tensor must be contiguous")
+    fn = _fn("elementwise", "lgml_scale_cap", [c_void_p, c_longlong, c_float, c_float, c_void_p])
+    _check("elementwise", fn(_ptr(x), x.numel(), float(scale), float(cap or 0.0), _stream()), "scale_cap")
+    return x
+
+
 def fill_normal(out: torch.Tensor, mean: float, sd: float, seed: int) -> torch.Tensor:
     """Seeded N(mean, sd^2) fill on the device."""
     _need(out, "tensor to fill")
@@ -289,10 +299,10 @@ def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor, bloc
 
 def paged_attention_ref(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                         k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
-                        status: torch.Tensor) -> torch.Tensor:
+                        status: torch.Tensor, softcap: float = 0.0) -> torch.Tensor:
     """out[t, h] = attention of query (t, h) over its request's cached keys at positions
     <= its own (the last ``window`` of them if window > 0).  ``q`` may be a column slice
-    of a wider buffer."""
+    of a wider buffer.  ``softcap`` > 0 caps the scaled scores: s -> softcap * tanh(s / softcap)."""
     _need(q, "queries", ndim=2)
     _need(out, "attention output", q.dtype, 2)
     ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
@@ -308,10 +318,10 @@ def paged_attention_ref(q: torch.Tensor, positions: torch.Tensor, seq_of_token: 
     if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
         raise KernelError("paged_attention: pages and block table must be contiguous")
     fn = _fn("attention_ref", "lgml_paged_attention_ref", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                                           c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+                                                           c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p])
     _check("attention_ref", fn(_ptr(q), dtype_code(q.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
                                _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n, n_heads, hkv, d, float(scale), int(window or 0),
-                               _ptr(status), _stream()), "paged_attention_ref")
+                               float(softcap or 0.0), _ptr(status), _stream()), "paged_attention_ref")
     return out
 
 

@@ -4,7 +4,7 @@ from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .mlp import GatedMLP
 from .norm import RMSNorm
-from .rope import NoPosition, Rope, frequency_factors
+from .rope import NoPosition, Rope, RotaryPosition, frequency_factors, store_kv
 
 __all__ = ["Attention", "KINDS", "Part", "make_part", "register_part", "registered", "PreNormBlock", "LMHead",
-           "TokenEmbedding", "GatedMLP", "RMSNorm", "NoPosition", "Rope", "frequency_factors"]
+           "TokenEmbedding", "GatedMLP", "RMSNorm", "NoPosition", "Rope", "RotaryPosition", "frequency_factors", "store_kv"]

@@ -16,7 +16,11 @@ Interfaces (tensors are torch tensors on the device; ``rt`` is the ``Runtime``):
 * every part:   ``tensor_specs(prefix) -> [TensorSpec]``, ``bind(prefix, tensors, rt)``
 * norm:         ``forward(rt, x_f32, out_dtype, delta=None, rows=None) -> h``
                 (with ``delta``: x += delta first, the sum stays in x)
-* position:     attributes ``n_rot``, ``pairing``, ``inv_freq`` (device float32)
+* position:     ``apply(rt, qkv, batch, cache, n_heads, n_kv_heads, head_dim) -> q``: it owns what
+                happens to q and k between the projection and the cache write, writes this
+                step's k and v into ``cache`` and returns q for attention.  A rotation
+                (``RotaryPosition``) only gives ``n_rot``, ``pairing``, ``inv_freq`` (device
+                float32); any other part calls ``store_kv`` when its own work is done
 * mixer:        ``cache_spec() -> PagedKV | FixedState | None``,
                 ``forward(rt, h, batch, cache) -> delta``  (h, delta: [tokens, width])
 * feed-forward: ``forward(rt, h) -> delta``

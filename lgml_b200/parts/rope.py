@@ -20,6 +20,7 @@ from typing import List, Optional
 
 import torch
 
+from .. import ops
 from ..weights import VECTOR, TensorSpec
 from .base import Part, register_part
 
@@ -52,8 +53,39 @@ def frequency_factors(head_dim: int, theta: float, scaling, n_rot: Optional[int]
     return out
 
 
-class Rope(Part):
+def store_kv(rt, qkv, batch, cache, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Write the k and v of ``qkv`` ([tokens, (H + 2 Hkv) D], or ``ops.Partials`` of it) into
+    the cache as they are and return q: what a position part that has already done its own
+    work on q and k (or does none) finishes with."""
+    none = torch.zeros(1, dtype=torch.float32, device=rt.device)
+    return ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, cache.block_table, none, 0, "half", cache.k, cache.v,
+                             n_heads, n_kv_heads, head_dim, rt.status, write_kv=cache.writable)
+
+
+class RotaryPosition(Part):
+    """A position part that rotates pairs of q and k by position x frequency.  It owns what
+    happens to q and k between the projection and the cache write (``apply``); for a rotation
+    that is one fused kernel that adds up the projection's partial sums, rotates q and k by the
+    angles pos * ``inv_freq[i]`` (the first ``n_rot`` dimensions, ``pairing``) and stores k and v
+    in their cells.  A subclass only sets ``inv_freq`` (float32 on the device), ``n_rot`` and
+    ``pairing``.  A position part that is no rotation gives its own ``apply`` with the same
+    signature; ``store_kv`` does the cache write for it."""
+
     graph_safe = True
+    n_rot = 0
+    pairing = "half"
+    inv_freq = None
+
+    def apply(self, rt, qkv, batch, cache, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+        """qkv: the fused projection's output [tokens, (H + 2 Hkv) D] in the compute type, or
+        ``ops.Partials`` of it.  Writes this step's k and v into ``cache`` (unless it belongs
+        to another layer call: ``cache.writable``) and returns q [tokens, H D] in the cache's
+        type, ready for attention."""
+        return ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, cache.block_table, self.inv_freq, self.n_rot,
+                                 self.pairing, cache.k, cache.v, n_heads, n_kv_heads, head_dim, rt.status, write_kv=cache.writable)
+
+
+class Rope(RotaryPosition):
     def __init__(self, head_dim: int, theta: float, scaling=None, n_rot: Optional[int] = None, pairing: str = "half",
                  factors_tensor: Optional[str] = None):
         self.head_dim = head_dim
@@ -83,12 +115,8 @@ class Rope(Part):
         self.inv_freq = torch.tensor(inv or [0.0], dtype=torch.float64).to(torch.float32).to(rt.device)
 
 
-class NoPosition(Part):
-    graph_safe = True
-    """No position encoding: the mixer leaves q and k as they are."""
-
-    n_rot = 0
-    pairing = "half"
+class NoPosition(RotaryPosition):
+    """No position encoding: q and k stay as they are (a rotation of no dimensions)."""
 
     def __init__(self, **_):
         self.inv_freq = None

@@ -47,6 +47,26 @@ def test_greedy_generation_equals_the_plain_implementation(folders):
     assert not eng.runner.cache.live and eng.runner.cache.n_free_pages == eng.runner.cache.n_pages
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_weights_by_seed_are_the_written_folder(dtype, tmp_path):
+    """``Engine(config=C, random_weights=s)`` fills its weights on the device; ``write_random_model(dir, C, s)``
+    draws them on the host.  One generator: the same tensors bit for bit, so the same replies."""
+    import lgml_b200
+    from lgml_b200.config import config_from_dict
+    from lgml_b200.weights import write_random_model
+
+    cfg = config_from_dict(H.TINY_B)
+    folder = write_random_model(tmp_path / "m", cfg, 5, dtype=dtype)
+    by_seed = lgml_b200.Engine(config=cfg, random_weights=5, dtype=dtype, n_ctx=256)
+    by_folder = lgml_b200.Engine(str(folder), dtype=dtype, n_ctx=256)
+    a, b = by_seed.runner.model, by_folder.runner.model
+    for x, y in ((a.embedding.table, b.embedding.table), (a.blocks[2].mixer.wqkv, b.blocks[2].mixer.wqkv), (a.blocks[0].mixer.bqkv, b.blocks[0].mixer.bqkv),
+                 (a.blocks[1].ffn.wgu, b.blocks[1].ffn.wgu), (a.final_norm.weight, b.final_norm.weight), (a.head.weight, b.head.weight)):
+        assert x.dtype == y.dtype and torch.equal(x, y)
+    prompts = [H.random_ids(n, 320, 700 + n) for n in (3, 50)]
+    assert by_seed.generate(prompts, max_tokens=12, temperature=0.0) == by_folder.generate(prompts, max_tokens=12, temperature=0.0)
+
+
 def plain_sampled(cfg, w, prompt, n_new, temperature, seed):
     """Seeded sampling replayed on the plain implementation's logits with the host sampler."""
     from lgml_b200.sampling import Sampler, SamplingParams

@@ -9,8 +9,6 @@ stages over two layers): on a logit that is a standard deviation of about 2e-3 o
 range, and the largest of the 1.3 million compared logits lies five to six of those out.  The
 bounds are 2 % of the range for the largest and 0.3 % for the mean difference (measured: 1.2 %
 and 0.18 %; the logits' range is about 6.5, their standard deviation 1.3)."""
-import zlib
-
 import pytest
 import torch
 
@@ -46,6 +44,7 @@ def two_runners(n_pages=24, max_position=None, shape=SHAPE):
     from lgml_b200.engine.runtime import Runtime
     from lgml_b200.models import build_model
     from lgml_b200.weights.loader import target_dtype
+    from lgml_b200.weights.random_init import tensor_key
 
     cfg = config_from_dict({**shape, **({"max_position_embeddings": max_position} if max_position else {})})
     runners = {}
@@ -59,7 +58,7 @@ def two_runners(n_pages=24, max_position=None, shape=SHAPE):
                 continue
             if dtype == torch.bfloat16:
                 t = torch.empty(s.shape, dtype=target_dtype(s.kind, dtype), device=rt.device)
-                ops.fill_normal(t, s.init[0], s.init[1] * 0.02, (7 << 32) ^ zlib.crc32(s.name.encode()))
+                ops.fill_normal(t, s.init[0], s.init[1] * 0.02, tensor_key(7, s.name))
                 half[s.name] = t
             else:
                 t = half[s.name].to(target_dtype(s.kind, dtype))

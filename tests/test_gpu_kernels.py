@@ -129,6 +129,22 @@ def test_fill_normal_is_seeded():
     assert abs(float((z.abs() < 1).float().mean()) - 0.6827) < 5e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fill_normal_draws_the_host_generator_bit_for_bit(dtype):
+    """One generator on both sides: the device's fill equals ``fill_normal_host`` in every bit,
+    over several keys, sizes that end inside a block of threads, and both kinds of init."""
+    from lgml_b200 import ops
+    from lgml_b200.weights.random_init import fill_normal_host, tensor_key
+
+    for key, n, mean, sd in ((tensor_key(0, "model.embed_tokens.weight"), 1 << 18, 0.0, 0.02), (tensor_key(3, "x"), 100003, 1.0, 0.02),
+                             (0xFFFFFFFFFFFFFFFF, 4097, -0.5, 1.0), (1, 1, 0.0, 1.0)):
+        dev = torch.empty(n, dtype=dtype, device=DEV)
+        ops.fill_normal(dev, mean, sd, key)
+        host = fill_normal_host((n,), mean, sd, key).to(dtype)
+        assert torch.equal(dev.cpu().view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                           host.view(torch.int16 if dtype == torch.bfloat16 else torch.int32)), (key, n)
+
+
 # ---------------------------------------------------------------------------------------------
 # matrix products
 # ---------------------------------------------------------------------------------------------
