@@ -2,6 +2,8 @@
 // needs it and for its rules).  It reuses the kernels of attention_decode.cu unchanged by
 // including that file, and differs only in where the scratch for the splits' partial
 // results lives: a file-scope device array instead of memory from the caller.
+#include <atomic>
+
 #include "attention_decode.cu"
 
 #include "attention_decode_noalloc.h"
@@ -12,7 +14,8 @@ static __device__ __align__(256) float lgml_noalloc_scratch[LGML_NOALLOC_SCRATCH
 
 namespace {
 constexpr int MAX_DEVICES = 64;
-float *scratch_of_device[MAX_DEVICES];   // looked up once per device
+// looked up once per device; two threads that look it up at the same time store the same address
+std::atomic<float *> scratch_of_device[MAX_DEVICES];
 
 // The device address of the array on the current device; nullptr (and the error text) on failure.
 float *noalloc_scratch() {
@@ -23,7 +26,8 @@ float *noalloc_scratch() {
                  e != cudaSuccess ? cudaGetErrorString(e) : "index out of range");
         return nullptr;
     }
-    if (scratch_of_device[dev] == nullptr) {
+    float *known = scratch_of_device[dev].load(std::memory_order_acquire);
+    if (known == nullptr) {
         float *ptr = nullptr;
         e = cudaGetSymbolAddress((void **)&ptr, lgml_noalloc_scratch);
         if (e != cudaSuccess || ptr == nullptr) {
@@ -31,9 +35,10 @@ float *noalloc_scratch() {
                      dev, cudaGetErrorString(e));
             return nullptr;
         }
-        scratch_of_device[dev] = ptr;
+        scratch_of_device[dev].store(ptr, std::memory_order_release);
+        known = ptr;
     }
-    return scratch_of_device[dev];
+    return known;
 }
 }  // namespace
 

@@ -20,14 +20,17 @@
  *    error; nothing is launched.
  *  - The first call on a device looks up the array's device address once
  *    (cudaGetSymbolAddress, with that device current) and remembers it.  Make that first
- *    call before any stream capture begins on that device.
+ *    call before any stream capture begins on that device.  The remembered address belongs
+ *    to the context that was current then: after cudaDeviceReset, or under a second context
+ *    on the same device, it is stale, and this library must be loaded afresh.
  *  - The function calls no cudaMalloc, cudaFree or any other allocating routine.
  *  - All calls share the one array, which keeps whatever the last call left in it.  The
  *    kernels write every partial result they later read, so nothing has to be cleared
  *    between calls.  Two calls that overlap on the GPU (different streams, or a captured
  *    graph replayed next to a live call) race on it: serialise them.
  *
- * Returns 0, or a non-zero code; lgml_attention_decode_noalloc_last_error() gives the text.
+ * Returns 0, or a non-zero code; lgml_attention_decode_noalloc_last_error() gives the text,
+ * to the thread that made the failing call only (the text is kept per thread).
  */
 #pragma once
 #include <cuda_runtime.h>

@@ -526,6 +526,9 @@ uint64_t lgml_sampler_next_u64(lgml_sampler *sm) {
     s[3] = rotl64(s[3], 45);
     return r;
 }
+/* ln(min_p) as the chain computes it (float32 logf), for the device's copy of the chain. */
+float lgml_log_min_p(float min_p) { return logf(min_p); }
+
 double lgml_sampler_uniform(lgml_sampler *sm) { return (double)(lgml_sampler_next_u64(sm) >> 11) * 0x1.0p-53; }
 
 lgml_sampler *lgml_sampler_new(const lgml_sampler_params *p, uint64_t seed) {
@@ -724,7 +727,7 @@ static int64_t after_top_k(lgml_sampler *sm, cand *c, int n, int sorted) {
         float m = c[0].v;
         for (int i = 1; i < n; ++i)
             if (c[i].v > m) m = c[i].v;
-        const float thr = m + (float)log((double)p->min_p);
+        const float thr = m + logf(p->min_p);          /* float32 as the reference's (src/sample.c:841, :847) */
         int k = 0;
         for (int i = 0; i < n; ++i)
             if (c[i].v >= thr) c[k++] = c[i];

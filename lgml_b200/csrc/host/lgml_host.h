@@ -72,6 +72,8 @@ LGML_HOST_API int lgml_sampler_history(const lgml_sampler *s, int32_t *out, int 
 LGML_HOST_API void lgml_sampler_state(const lgml_sampler *s, uint64_t out[4]);
 LGML_HOST_API uint64_t lgml_sampler_next_u64(lgml_sampler *s);
 LGML_HOST_API double lgml_sampler_uniform(lgml_sampler *s);
+/* ln(min_p) in the chain's own arithmetic (float32), so that a copy of the chain elsewhere draws the same bound */
+LGML_HOST_API float lgml_log_min_p(float min_p);
 /* One id from a row of n float32 logits.  The row after bias and penalties is kept for
  * lgml_sampler_logprobs; `edited` (n floats, may be NULL) receives a copy of it. */
 LGML_HOST_API int lgml_sampler_sample(lgml_sampler *s, const float *logits, int n, float *edited);

@@ -24,7 +24,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import torch
 
 from .. import ops
-from ..sampling import Sampler, SamplingParams
+from ..sampling import Sampler, SamplingParams, log_min_p
 from .runner import ModelRunner
 from .runtime import MAX_RESULT
 from .scheduler import REPEAT_STOP, UBATCH, GenRequest, Scheduler
@@ -124,7 +124,7 @@ class Engine:
             # there for the next step, as with the argmax
             k = next(e.request.params.top_k for e in rows if not e.request.params.greedy)
             vals, ids = ops.topk_rows(logits, k)
-            params = torch.tensor([[p.top_p, math.log(p.min_p) if p.min_p > 0.0 else -math.inf, p.temperature]
+            params = torch.tensor([[p.top_p, log_min_p(p.min_p) if p.min_p > 0.0 else -math.inf, p.temperature]
                                    for p in (e.request.params for e in rows)], dtype=torch.float32).pin_memory()
             us = torch.tensor([0.0 if e.request.params.greedy else e.request.sampler.uniform() for e in rows], dtype=torch.float64).pin_memory()
             res = self.rt.result

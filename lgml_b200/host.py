@@ -45,6 +45,7 @@ def lib() -> ctypes.CDLL:
         l.lgml_sampler_state.restype, l.lgml_sampler_state.argtypes = None, [c_void_p, c_void_p]
         l.lgml_sampler_next_u64.restype, l.lgml_sampler_next_u64.argtypes = c_uint64, [c_void_p]
         l.lgml_sampler_uniform.restype, l.lgml_sampler_uniform.argtypes = c_double, [c_void_p]
+        l.lgml_log_min_p.restype, l.lgml_log_min_p.argtypes = c_float, [c_float]
         l.lgml_sampler_sample.restype, l.lgml_sampler_sample.argtypes = c_int, [c_void_p, c_void_p, c_int, c_void_p]
         l.lgml_sampler_sample_candidates.restype, l.lgml_sampler_sample_candidates.argtypes = c_int, [c_void_p, c_void_p, c_void_p, c_int]
         l.lgml_sampler_logprobs.restype, l.lgml_sampler_logprobs.argtypes = c_int, [c_void_p, c_int32, c_int, POINTER(c_double), c_void_p, c_void_p]

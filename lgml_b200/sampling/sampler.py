@@ -131,6 +131,12 @@ class Xoshiro256:
         return float(self._lib.lgml_sampler_uniform(self._h))
 
 
+def log_min_p(min_p: float) -> float:
+    """ln(min_p) as the host chain computes it (float32 ``logf``, ``src/sample.c:841``): the
+    device's copy of the chain gets its bound from here."""
+    return float(host.lib().lgml_log_min_p(float(min_p)))
+
+
 def _c_params(p: "SamplingParams") -> host.SamplerParams:
     return host.SamplerParams(p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.frequency_penalty, p.presence_penalty,
                               p.repeat_last_n)

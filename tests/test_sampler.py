@@ -21,15 +21,69 @@ def test_defaults_are_the_reference_defaults():
         SamplingParams(repeat_penalty=0.0)
 
 
+def _plain_xoshiro(seed, n):
+    """xoshiro256** seeded by four splitmix64 outputs, restated from the published algorithms
+    (``src/sample.c:93-139``): the first n outputs."""
+    M = (1 << 64) - 1
+    rotl = lambda x, k: ((x << k) | (x >> (64 - k))) & M
+    s, z = [], seed & M
+    for _ in range(4):
+        z = (z + 0x9E3779B97F4A7C15) & M
+        x = z
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & M
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & M
+        s.append(x ^ (x >> 31))
+    out = []
+    for _ in range(n):
+        out.append((rotl((s[1] * 5) & M, 7) * 9) & M)
+        t = (s[1] << 17) & M
+        s[2] ^= s[0]
+        s[3] ^= s[1]
+        s[1] ^= s[2]
+        s[0] ^= s[3]
+        s[2] ^= t
+        s[3] = rotl(s[3], 45)
+    return out
+
+
 def test_generator_is_xoshiro256_starstar_seeded_by_splitmix64():
     # splitmix64(0) gives the well-known first outputs; xoshiro256** then runs on that state
     g = Xoshiro256(0)
     assert g.s == [0xE220A8397B1DCDAF, 0x6E789E6AA1B965F4, 0x06C45D188009454F, 0xF88BB8A8724C81EC]
-    a = [Xoshiro256(42).next() for _ in range(1)]
-    b = Xoshiro256(42)
-    assert b.next() == a[0]
-    u = [Xoshiro256(7).double() for _ in range(3)]
-    assert all(0.0 <= x < 1.0 for x in u)
+    # the first output for that state, worked by hand from the definition: rotl(s1 * 5, 7) * 9
+    s1 = 0x6E789E6AA1B965F4
+    x = (s1 * 5) & ((1 << 64) - 1)
+    assert g.next() == ((((x << 7) | (x >> 57)) & ((1 << 64) - 1)) * 9) & ((1 << 64) - 1)
+    for seed in (0, 42, 7, (1 << 64) - 1, 0x5EED):
+        g = Xoshiro256(seed)
+        want = _plain_xoshiro(seed, 20)
+        assert [g.next() for _ in range(20)] == want, seed
+    # a uniform double is the top 53 bits of the next output (src/sample.c:126-130)
+    g, want = Xoshiro256(7), _plain_xoshiro(7, 3)
+    assert [g.double() for _ in range(3)] == [(w >> 11) * 2.0 ** -53 for w in want]
+    s = Sampler(SamplingParams(seed=7))
+    assert s.uniform() == (want[0] >> 11) * 2.0 ** -53
+
+
+def test_min_p_keeps_a_candidate_exactly_on_its_bound():
+    """The bound is max + logf(p) in float32 (``src/sample.c:841``, ``:847``); a logit equal to
+    it stays, the next float32 below it goes."""
+    from lgml_b200.sampling import log_min_p
+
+    for p in (0.05, 0.3, 0.123456, 1e-3):
+        ln = np.float32(log_min_p(p))
+        assert abs(float(ln) - math.log(np.float32(p))) <= 2e-7 * abs(math.log(p)) + 1e-7
+        for top in (np.float32(0.0), np.float32(3.25), np.float32(-7.5)):
+            on = np.float32(top + ln)
+            below = np.nextafter(on, np.float32(-np.inf), dtype=np.float32)
+            row = np.array([below, top, on, below], dtype=np.float32)
+            s = Sampler(SamplingParams(temperature=1.0, seed=3, top_k=0, top_p=1.0, min_p=p))
+            seen = {s.sample(row) for _ in range(300)}
+            assert seen <= {1, 2} and 1 in seen, (p, top, seen)
+            # on the bound means kept: with the top logit lowered out of the way of chance, index 2 shows
+            flat = np.array([below, on - ln, on, below], dtype=np.float32)      # the two kept ones p apart
+            s = Sampler(SamplingParams(temperature=100.0, seed=4, top_k=0, top_p=1.0, min_p=p))
+            assert {s.sample(flat) for _ in range(300)} == {1, 2}, (p, top)
 
 
 def test_greedy_and_ties():
