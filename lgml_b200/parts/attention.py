@@ -34,7 +34,6 @@ from .rope import RotaryPosition
 
 
 class Attention(Part):
-    graph_safe = True
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position, bias: bool = False,
                  out_bias: Optional[bool] = None, window: Optional[int] = None, scale: Optional[float] = None,
                  q_norm=None, k_norm=None, softcap: Optional[float] = None):
@@ -49,6 +48,12 @@ class Attention(Part):
         self.q_norm, self.k_norm = q_norm, k_norm
         self.softcap = float(softcap) if softcap else 0.0
         self.wqkv = self.bqkv = self.wo = self.bo = None
+
+    @property
+    def graph_safe(self):
+        """Its own launches are fixed by the batch's shape; whether a step through it can be
+        captured is up to the parts it is given."""
+        return all(getattr(p, "graph_safe", False) for p in (self.position, self.q_norm, self.k_norm) if p is not None)
 
     def cache_spec(self):
         return PagedKV(self.n_kv_heads, self.head_dim, self.window)

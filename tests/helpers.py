@@ -111,10 +111,13 @@ def trace_portions(seqs: Dict[str, List[int]], sizes=(7, 2, 19, 3, 64, 2, 33, 5,
     return steps
 
 
-def trace_mixed(seqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4, page: int = 64) -> List[dict]:
+def trace_mixed(seqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_live: int = 4, page: int = 64,
+                choices=(1, 1, 1, 2, 2, 5, 17, 40, 64, 90), tail: int = 0, skip: float = 0.2, first: int = 0) -> List[dict]:
     """Up to ``max_live`` requests at once: portions of some beside single tokens of others,
     a request sometimes left out of a step, and a pool of ``max_tokens`` so small that the
-    pages of finished requests are used again by later ones."""
+    pages of finished requests are used again by later ones.  ``choices``: the portion sizes
+    drawn from; the last ``tail`` tokens of a request come one by one; a request that has more
+    than ``first`` tokens before its tail starts with a portion of ``first``."""
     rng = random.Random(seed)
     waiting = list(seqs.items())
     live: Dict[str, int] = {}      # id -> tokens fed
@@ -133,10 +136,12 @@ def trace_mixed(seqs: Dict[str, List[int]], max_tokens: int, seed: int = 0, max_
         entries, end = [], []
         for rid in list(live):
             fed, ids = live[rid], seqs[rid]
-            if len(live) > 1 and rng.random() < 0.2:
+            if len(live) > 1 and rng.random() < skip:
                 continue                                            # left out of this step
             left = len(ids) - fed
-            n = min(rng.choice([1, 1, 1, 2, 2, 5, 17, 40, 64, 90]), left)
+            n = 1 if left <= tail else min(rng.choice(choices), left - tail)
+            if first and fed == 0 and left - tail > first:
+                n = first
             entries.append({"id": rid, "tokens": ids[fed:fed + n], "want": list(range(n))})
             live[rid] = fed + n
             if live[rid] == len(ids):

@@ -129,3 +129,81 @@ def test_long_context_then_decoding_across_a_page_edge():
     diff = (got - ref).abs()
     assert float(diff.max()) <= 2e-2 * scale, (float(diff.max()), scale)
     assert float(diff.mean()) <= 3e-3 * scale, (float(diff.mean()), scale)
+
+
+# ---------------------------------------------------------------------------------------------
+# the kernels of a full-size model against the plain implementation, as an engine
+# ---------------------------------------------------------------------------------------------
+
+def one_layer_model(shape, seed, n_pages):
+    """One layer at a full model's layer sizes with a small vocabulary, filled on the device by
+    seed: (config dict, bfloat16 runner, the same tensors on the host as float64 for the plain
+    implementation).  The device's fill is the host generator bit for bit
+    (``test_fill_normal_draws_the_host_generator_bit_for_bit``), so the plain implementation gets
+    exactly the model the engine runs."""
+    from lgml_b200 import ops
+    from lgml_b200.config import config_from_dict
+    from lgml_b200.engine.runner import ModelRunner
+    from lgml_b200.engine.runtime import Runtime
+    from lgml_b200.models import build_model
+    from lgml_b200.weights.loader import target_dtype
+    from lgml_b200.weights.random_init import tensor_key
+
+    d = {**shape, "num_hidden_layers": 1, "vocab_size": 4096, "max_position_embeddings": 2048}
+    cfg = config_from_dict(d)
+    rt = Runtime("cuda:0", torch.bfloat16)
+    model = build_model(cfg)
+    tensors, host = {}, {}
+    for s in model.tensor_specs():
+        if s.optional:
+            continue
+        t = torch.empty(s.shape, dtype=target_dtype(s.kind, torch.bfloat16), device=rt.device)
+        ops.fill_normal(t, s.init[0], s.init[1] * 0.02, tensor_key(seed, s.name))
+        tensors[s.name] = t
+        host[s.name] = t.cpu().double()
+    model.bind(tensors, rt)
+    return d, ModelRunner(model, rt, n_pages=n_pages, max_slots=4, max_step_tokens=1024), host
+
+
+@pytest.mark.parametrize("shape,lens", [("8b", [600, 200, 130, 90, 300, 70]), ("13b", [560, 150, 100, 70, 200])])
+def test_full_size_kernels_against_the_plain_implementation_under_the_hard_schedule(shape, lens):
+    """Four live requests, portions beside decoded tokens, a first portion of over 512 tokens
+    (pairs of CTAs in the products, the two-tile tcgen05 attention), the last tokens of every
+    request one by one (the captured decode step), and a pool so small that pages are used
+    again: bfloat16 against ``tests/plain/llama_plain.py`` in float64, not against the engine's
+    own 32-bit path.  Bounds as above: the largest difference within 2 % of the logits' range,
+    the mean within 0.3 %.  That a wrong key would show is checked on the plain side: one
+    changed token in a request's first page moves its later rows by far more than the bound."""
+    from tests import helpers as H
+    from tests.plain import llama_plain as P
+
+    total_pages = sum(-(-n // 64) for n in lens)
+    n_pages = -(-max(lens) // 64) + 7
+    assert n_pages < total_pages - 3
+    d, runner, host = one_layer_model(SHAPES[shape], 21, n_pages)
+    seqs = {f"r{i}": H.random_ids(n, 4096, 500 + i) for i, n in enumerate(lens)}
+    trace = H.trace_mixed(seqs, max_tokens=64 * n_pages, seed=3, choices=(1, 1, 2, 5, 17, 40, 90), tail=12, skip=0.1, first=530)
+    assert max(len(st["entries"]) for st in trace) == 4
+    assert any(len(e["tokens"]) >= 512 for st in trace for e in st["entries"])
+    assert any(len(st["entries"]) > 1 and min(len(e["tokens"]) for e in st["entries"]) == 1
+               and max(len(e["tokens"]) for e in st["entries"]) > 8 for st in trace)           # decoded tokens beside a portion
+    got = H.run_trace(runner, trace)
+    pool = runner.cache.groups[0].pool
+    assert pool.taken_total > pool.n_pages, "the trace never used a page twice"
+    assert runner.graph_replays > 0, "no decode step went through a captured graph"
+    worst = 0.0
+    for rid, ids in seqs.items():
+        ref = P.forward(d, host, ids)
+        rows = torch.stack([got[(rid, p)] for p in range(len(ids))]).double()
+        scale = float(ref.abs().max())
+        diff = (rows - ref).abs()
+        where = int(diff.max(dim=1).values.argmax())
+        assert float(diff.max()) <= 2e-2 * scale, f"request {rid} position {where} (page {where // 64}, cell {where % 64}): {float(diff.max()):.3g} of {scale:.3g}"
+        assert float(diff.mean()) <= 3e-3 * scale, (rid, float(diff.mean()), scale)
+        worst = max(worst, float(diff.max()) / scale)
+        if rid == "r3":
+            wrong = list(ids)
+            wrong[7] = (wrong[7] + 1) % 4096
+            moved = (P.forward(d, host, wrong)[40:] - ref[40:]).abs().max(dim=1).values
+            assert float(moved.min()) > 4e-2 * scale, "a wrong key in the first page would hide under the bound"
+    print(f"{shape}: largest difference {worst:.4f} of the logits' range")
