@@ -56,7 +56,7 @@ class ModelRunner:
         cfg = load_config(folder)
         rt = Runtime(device, dtype)
         model = build_model(cfg)
-        tensors = load_tensors(folder, model.tensor_specs(), dtype, rt.device)
+        tensors = load_tensors(folder, model.tensor_specs(), dtype, rt.device, ignore=getattr(model, "ignored_tensors", ()))
         model.bind(tensors, rt)
         return cls(model, rt, **kw)
 

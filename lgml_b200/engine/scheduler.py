@@ -83,6 +83,7 @@ class Scheduler:
         self.running: List[GenRequest] = []
         self.finished: List[GenRequest] = []
         self._admissions = 0
+        self._preempted_now: set = set()
         # counters, as the reference's batch_passes / batch_rows / batch_tokens (lua/lgml/engine.lua:1488-1492)
         self.stats = dict(steps=0, rows=0, tokens=0, preemptions=0, admitted=0, prefix_tokens=0)
 
@@ -104,7 +105,9 @@ class Scheduler:
         return not self.waiting and not self.running
 
     # ---- planning ------------------------------------------------------------------------
-    def _preempt(self, victim: GenRequest, plan: List[PlannedEntry]) -> None:
+    def _preempt(self, victim: GenRequest, plan: List[PlannedEntry]) -> int:
+        """Take ``victim`` out of the running set (and out of ``plan``, if it is in it already).
+        Returns the tokens that leave the plan with it: the caller gives them back to the step's budget."""
         # (with a prefix cache its full pages stay findable: when it is admitted again it takes
         #  up what the pool has not needed meanwhile, lua/lgml/engine.lua:1193-1243)
         self.cache.publish(victim.cache_req, victim.tokens)
@@ -114,8 +117,11 @@ class Scheduler:
         victim.preemptions += 1
         self.stats["preemptions"] += 1
         self.running.remove(victim)
+        dropped = sum(len(e.tokens) for e in plan if e.request is victim)
         plan[:] = [e for e in plan if e.request is not victim]
         self.waiting.appendleft(victim)
+        self._preempted_now.add(id(victim))
+        return dropped
 
     def _finish(self, req: GenRequest, reason: str) -> None:
         req.finish_reason = reason
@@ -127,24 +133,26 @@ class Scheduler:
             self.running.remove(req)
         self.finished.append(req)
 
-    def _reserve(self, req: GenRequest, n: int, plan: List[PlannedEntry]) -> Optional[bool]:
+    def _reserve(self, req: GenRequest, n: int, plan: List[PlannedEntry]):
         """Pages for n more tokens of a running request.  While the pool is short the most
         recently admitted running request is preempted; if that is ``req`` itself it goes
-        back to the queue (None), unless it is alone, in which case nothing can help (False)."""
+        back to the queue (None), unless it is alone, in which case nothing can help (False).
+        Returns (that outcome, the tokens that left the plan with preempted requests)."""
+        refund = 0
         while not self.cache.reserve(req.cache_req, n):
             victim = max(self.running, key=lambda r: r.admitted_at)
             if victim is req:
                 if len(self.running) == 1:
-                    return False
-                self._preempt(req, plan)
-                return None
-            self._preempt(victim, plan)
-        return True
+                    return False, refund
+                return None, refund + self._preempt(req, plan)
+            refund += self._preempt(victim, plan)
+        return True, refund
 
     def plan(self) -> List[PlannedEntry]:
         """The entries of the next step (it reserves their pages).  Empty when idle."""
         plan: List[PlannedEntry] = []
         budget = self.max_batch_tokens
+        self._preempted_now = set()     # requests this call preempts: they wait for a later turn
         # 1. running requests: single decode tokens first, then prompt portions, oldest first
         order = sorted(self.running, key=lambda r: (r.n_pending > 1, r.admitted_at))
         for req in order:
@@ -153,7 +161,12 @@ class Scheduler:
             n = min(req.n_pending, self.ubatch, budget)
             if n <= 0:
                 continue
-            got = self._reserve(req, n, plan)
+            got, refund = self._reserve(req, n, plan)
+            budget += refund                 # a preempted request's planned tokens do not run
+            if got is True and refund:
+                more = min(req.n_pending, self.ubatch, budget)
+                if more > n and self.cache.reserve(req.cache_req, more):
+                    n = more
             if got is None:
                 continue
             if got is False:
@@ -166,6 +179,10 @@ class Scheduler:
         # 2. admission, FIFO: a slot, and room for the prompt and one more token
         while self.waiting and budget > 0 and len(self.cache.live) < self.cache.max_slots:
             req = self.waiting[0]
+            if id(req) in self._preempted_now:
+                # it gave its pages up in this very call so that an older request could go on: letting
+                # it in again at once would only take them back (and prefill it from the start)
+                break
             total = len(req.prompt) + len(req.generated)
             # (pages that the prefix cache already holds for its first tokens need not be free:
             #  cached ones count as free and are not taken twice, held ones are shared)

@@ -14,7 +14,7 @@ whose logits are wanted (``:2349-2350``), the final norm and the head
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -31,7 +31,8 @@ class LayerCall:
 class DecoderModel:
     def __init__(self, config, embedding, blocks, final_norm, head, schedule: Optional[List[LayerCall]] = None,
                  block_prefix: str = "model.layers.{}", final_norm_prefix: str = "model.norm",
-                 embed_scale: Optional[float] = None, logit_scale: Optional[float] = None, logit_softcap: Optional[float] = None):
+                 embed_scale: Optional[float] = None, logit_scale: Optional[float] = None, logit_softcap: Optional[float] = None,
+                 ignored_tensors: Sequence[str] = ()):
         self.config = config
         self.embedding = embedding
         self.blocks = list(blocks)
@@ -39,6 +40,8 @@ class DecoderModel:
         self.head = head
         self.block_prefix = block_prefix
         self.final_norm_prefix = final_norm_prefix
+        # name patterns of tensors that a folder of this architecture may carry unread
+        self.ignored_tensors = tuple(ignored_tensors)
         # scales that other families of the reference apply and Llama does not (None = no kernel):
         # on the embedding's rows (``embd_scale``, ``lua/lgml/transformer.lua:2303-2306``), on the
         # logits, and the logits' cap (``logit_scale``, ``softcap``, ``:2097-2102``)

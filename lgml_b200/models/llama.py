@@ -55,7 +55,8 @@ def build_llama(cfg: LlamaConfig) -> DecoderModel:
     head = LMHead(cfg.vocab_size, cfg.hidden_size, tied_to=embedding if cfg.tie_word_embeddings else None)
     blocks = [build_block(d) for d in layer_descriptors(cfg)]
     final_norm = make_part("norm", "rmsnorm", width=cfg.hidden_size, eps=cfg.rms_norm_eps)
-    return DecoderModel(cfg, embedding, blocks, final_norm, head)
+    # older exports of this architecture still carry each layer's rotary frequencies as a buffer
+    return DecoderModel(cfg, embedding, blocks, final_norm, head, ignored_tensors=("model.layers.*.self_attn.rotary_emb.inv_freq",))
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig, build_llama)

@@ -37,10 +37,15 @@ class LMHead(Part):
         self.weight = None
 
     def tensor_specs(self, prefix=""):
-        return [] if self.tied_to is not None else [TensorSpec(self.name, (self.vocab, self.width), MATRIX)]
+        # tied: the head's own tensor is optional and wins when the folder has it, as the
+        # reference takes ``output.weight`` whenever it is there (``lua/lgml/transformer.lua:408``)
+        return [TensorSpec(self.name, (self.vocab, self.width), MATRIX, optional=self.tied_to is not None)]
 
     def bind(self, prefix, tensors, rt):
-        self.weight = self.tied_to.table if self.tied_to is not None else tensors[self.name]
+        own = tensors.get(self.name)
+        self.weight = own if own is not None or self.tied_to is None else self.tied_to.table
+        if self.weight is None:
+            raise KeyError(self.name)
 
     def forward(self, rt, h):
         """h [rows, width] in the compute type -> float32 logits [rows, vocab]."""

@@ -14,8 +14,9 @@ float32, which loses nothing (precedent: the reader's 1-D widening,
 """
 from __future__ import annotations
 
+import fnmatch
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, Iterable, List, Sequence, Tuple
 
 import torch
 
@@ -55,11 +56,14 @@ class WeightError(ValueError):
         super().__init__("weights do not fit the model; " + "; ".join(parts))
 
 
-def check_index(index: Dict[str, TensorEntry], specs: Iterable[TensorSpec]) -> None:
+def check_index(index: Dict[str, TensorEntry], specs: Iterable[TensorSpec], ignore: Sequence[str] = ()) -> None:
+    """``ignore``: patterns (``fnmatch``) of tensor names that a folder may hold although the
+    model does not read them (buffers that some exporters write); the architecture's builder
+    names them, everything else the model did not ask for is reported."""
     specs = list(specs)
     known = {s.name for s in specs}
     missing = [s.name for s in specs if not s.optional and s.name not in index]
-    unexpected = sorted(n for n in index if n not in known)
+    unexpected = sorted(n for n in index if n not in known and not any(fnmatch.fnmatchcase(n, pat) for pat in ignore))
     wrong = [(s.name, index[s.name].shape, s.shape) for s in specs
              if s.name in index and tuple(index[s.name].shape) != tuple(s.shape)]
     if missing or unexpected or wrong:
@@ -74,11 +78,11 @@ def target_dtype(kind: str, compute_dtype: torch.dtype) -> torch.dtype:
     return torch.int32
 
 
-def load_tensors(folder, specs: Iterable[TensorSpec], compute_dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+def load_tensors(folder, specs: Iterable[TensorSpec], compute_dtype: torch.dtype, device, ignore: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     """name -> device tensor for every spec present in the folder."""
     specs = list(specs)
     index = index_folder(folder)
-    check_index(index, specs)
+    check_index(index, specs, ignore)
     out: Dict[str, torch.Tensor] = {}
     for s in specs:
         ent = index.get(s.name)

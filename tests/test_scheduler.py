@@ -350,3 +350,43 @@ def solo_prefix(n_prompt, max_new, prompt):
     s.add(r)
     drive(s, cm)
     return r.generated
+
+
+def test_a_preempted_request_that_was_already_planned_gives_its_tokens_back():
+    """The latest request is decoding and is planned first; an older one, still reading its prompt
+    in portions, then finds no page and preempts it.  The victim's token leaves the plan and returns
+    to the step's budget (the portion planned after it is a token longer for it), and the victim
+    is not let in again in the same call."""
+    s, cm = make(n_pages=5, slots=4, ubatch=32, budget=2048)
+    a, c, b = req("a", 150, 4), req("c", 150, 4), req("b", 3, 200)
+    for r in (a, c, b):
+        s.add(r)
+    seen = False
+    for _ in range(400):
+        if s.idle:
+            break
+        before = s.stats["preemptions"]
+        was_running = [r.id for r in s.running]
+        plan = s.plan()
+        s.max_batch_tokens = 40              # all three are let in by the first call; from then on the budget binds
+        if s.stats["preemptions"] > before and "b" in was_running and not seen:
+            seen = True
+            ids = [e.request.id for e in plan]
+            assert "b" not in ids and b in s.waiting and b.cache_req is None      # out of the plan, not back in at once
+            assert sum(len(e.tokens) for e in plan) == 40                         # its token went to the next portion
+            assert [(e.request.id, len(e.tokens)) for e in plan] == [("a", 22), ("c", 18)]
+        for e in plan:
+            cm.commit(e.request.cache_req, len(e.tokens))
+        cm.check()
+        s.complete(plan, {e.request.id: stub_token(e.request) for e in plan if e.sample})
+    assert seen and s.idle
+    assert b.preemptions >= 1 and len(b.generated) == 200 and b.generated == solo_of(3, 200)
+    assert cm.n_free_pages == 5 and not cm.live
+
+
+def solo_of(n_prompt, max_new):
+    s, cm = make(n_pages=8)
+    r = req("b", n_prompt, max_new)
+    s.add(r)
+    drive(s, cm)
+    return r.generated

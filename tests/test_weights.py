@@ -113,13 +113,20 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del tensors["model.layers.1.mlp.up_proj.weight"]
     del tensors["model.norm.weight"]
     tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    tensors["model.layers.0.self_attn.extra.weight"] = torch.ones(3)
     tensors["model.layers.0.self_attn.q_proj.weight"] = torch.ones(64, 32)
     write_safetensors(folder / "model.safetensors", tensors)
     with pytest.raises(WeightError) as ei:
         load_tensors(folder, tensor_specs_for(cfg), torch.float32, "cpu")
     e = ei.value
     assert set(e.missing) == {"model.layers.1.mlp.up_proj.weight", "model.norm.weight"}
-    assert e.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert e.unexpected == ["model.layers.0.self_attn.extra.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    # the architecture's builder names what a folder may carry unread (old exports keep each layer's
+    # rotary frequencies as a buffer): that one is no fault, the other still is
+    from lgml_b200.models import build_model
+    with pytest.raises(WeightError) as ei2:
+        load_tensors(folder, tensor_specs_for(cfg), torch.float32, "cpu", ignore=build_model(cfg).ignored_tensors)
+    assert ei2.value.unexpected == ["model.layers.0.self_attn.extra.weight"]
     assert [w[0] for w in e.wrong_shape] == ["model.layers.0.self_attn.q_proj.weight"]
     msg = str(e)
     for name in e.missing + e.unexpected:
@@ -133,6 +140,24 @@ def test_tied_head_and_optional_tensors(tmp_path):
     names = set(index_folder(folder))
     assert "lm_head.weight" not in names and "rope_freqs.weight" not in names
     load_tensors(folder, tensor_specs_for(cfg), torch.float32, "cpu")          # optional factors may be absent
+    # a tied folder that still carries a head of its own is taken, and that head is the one used
+    # (the reference takes ``output.weight`` whenever the file has it, ``lua/lgml/transformer.lua:408``)
+    tensors = {n: read_tensor(e) for n, e in index_folder(folder).items()}
+    tensors["lm_head.weight"] = torch.full((256, 64), 0.5)
+    write_safetensors(folder / "model.safetensors", tensors)
+    got = load_tensors(folder, tensor_specs_for(cfg), torch.float32, "cpu")
+    assert torch.equal(got["lm_head.weight"], tensors["lm_head.weight"])
+    from lgml_b200.models import build_model
+    model = build_model(cfg)
+
+    class Rt:
+        device, dtype = torch.device("cpu"), torch.float32
+    model.head.bind("", got, Rt)
+    assert model.head.weight is got["lm_head.weight"]
+    del got["lm_head.weight"]
+    model.embedding.bind("", got, Rt)
+    model.head.bind("", got, Rt)
+    assert model.head.weight is model.embedding.table
     cfg_b = config_from_dict(H.TINY_B)
     names_b = set(index_folder(write_random_model(tmp_path / "b", cfg_b, seed=1, dtype="float32")))
     assert "lm_head.weight" in names_b and "model.layers.2.self_attn.k_proj.bias" in names_b
