@@ -11,7 +11,13 @@ through the Python entry point (``Engine.generate``: host token lists in, host t
 out, every step copies its inputs from pinned memory and reads the sampled tokens back).
 ``prefill`` is one 2,048-token prompt in one step; ``points`` adds decode at batch 1 and
 64; ``roofline`` is the bytes a decode step has to read (every weight once and the cache
-of the live requests) over its time, against the measured copy bandwidth.
+of the live requests, at their mean length over the timed steps) over its time, against the
+measured copy bandwidth, and ``roofline_points`` the same fraction for every batch size.
+
+``--shape llama32_3b`` runs that shape's own workload (32 prompts of 128 to 4,096 tokens in
+portions of 512 beside decodes, 512 new tokens each) through ``Engine.generate``;
+``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--cpu-baseline``
+times the plain CPU implementation at the tiny configurations.
 """
 from __future__ import annotations
 
@@ -161,7 +167,8 @@ def run_decode(runner, cfg, batch: int, steps: int, warmup: int, seed: int = 0):
         end.record()
         torch.cuda.synchronize()
         ms = start.elapsed_time(end)
-        kv_tokens = sum(r.n_tokens for r in reqs)
+        # keys a timed step reads, on average: what the requests held half-way through the timed steps
+        kv_tokens = sum(r.n_tokens for r in reqs) - batch * (steps - 1) / 2.0
         launches = ops.launch_count() - launches0 + (runner.graph_replays - replays0) * runner.graph_kernels(batch)
         runner.rt.check_status()
         return ms / steps, kv_tokens, launches
@@ -193,6 +200,105 @@ def run_prefill(runner, cfg, reps: int = 3, seed: int = 1):
     return best
 
 
+def run_mixed_workload(shape_name, shape, args, warmup: int) -> dict:
+    """The workload the 3B shape is quoted with: 32 prompts of 128 to 4,096 uniform-random tokens,
+    read in portions of 512 beside the decoding of the requests that are further on, 512 new
+    tokens each, through ``Engine.generate`` (host token lists in and out).  Rates as the
+    reference reports them per request (``prompt_per_second`` / ``predicted_per_second``,
+    ``lua/lgml/engine.lua:3225-3239``), here over the whole job, with the share of turns that
+    held portions of prompts beside decoded tokens."""
+    import torch
+
+    import lgml_b200
+    from lgml_b200.config import config_from_dict
+
+    n_req, new_tokens, ubatch, budget = 32, 512, 512, 2048
+    n_ctx = 4096 + new_tokens + 64
+    d = dict(shape)
+    full_layers = d["num_hidden_layers"]
+    if args.layers:
+        d["num_hidden_layers"] = args.layers
+    d["max_position_embeddings"] = 8192
+    cfg = config_from_dict(d)
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    g = torch.Generator().manual_seed(4)
+    lens = torch.randint(128, 4097, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    eng = lgml_b200.Engine(config=cfg, random_weights=0, dtype="bfloat16", n_ctx=n_ctx, kv_tokens=n_req * n_ctx, slots=n_req, ubatch=ubatch,
+                           max_batch_tokens=budget)
+    eng.generate([p[:600] for p in prompts[:n_req]], max_tokens=max(warmup, 3) + 2, temperature=0.0, stop=[])    # kernels loaded, decode graph captured
+    clocks = ClockSampler()
+    clocks.start()
+    out = eng.generate(prompts, max_tokens=new_tokens, temperature=0.0, stop=[])
+    clock_rec = clocks.stop()
+    wall = eng.timings["total"]
+    log = eng.turn_log
+    kinds = {"prompt": [t for t in log if t["decode"] == 0], "mixed": [t for t in log if t["decode"] > 0 and not t["pure_decode"]],
+             "decode": [t for t in log if t["pure_decode"]]}
+    n_prompt, n_new = sum(lens), sum(len(o) for o in out)
+    secs = {k: sum(t["s"] for t in v) for k, v in kinds.items()}
+    prompt_in_mixed = sum(t["tokens"] - t["decode"] for t in kinds["mixed"])
+    decode_in_mixed = sum(t["decode"] for t in kinds["mixed"])
+    mixed = {
+        "requests": n_req, "prompt_tokens": n_prompt, "new_tokens": n_new, "ubatch": ubatch, "max_batch_tokens": budget,
+        "turns": len(log), "mixed_turn_share": round(len(kinds["mixed"]) / max(len(log), 1), 4),
+        "mixed_time_share": round(secs["mixed"] / max(wall, 1e-9), 4),
+        "prompt_tok_s": round(n_prompt / max(secs["prompt"] + secs["mixed"], 1e-9), 1),
+        "decode_tok_s": round(sum(t["decode"] for t in kinds["decode"]) / max(secs["decode"], 1e-9), 1),
+        "mixed_turn_ms": round(1e3 * secs["mixed"] / max(len(kinds["mixed"]), 1), 3),
+        "mixed_turn_tokens": round((prompt_in_mixed + decode_in_mixed) / max(len(kinds["mixed"]), 1), 1),
+        "decode_turn_ms": round(1e3 * secs["decode"] / max(len(kinds["decode"]), 1), 3),
+        "preemptions": eng.scheduler.stats["preemptions"],
+    }
+    total = (n_prompt + n_new) / wall
+    h2d = sum(t["h2d"] for t in log) // max(len(log), 1)
+    d2h = sum(t["d2h"] for t in log) // max(len(log), 1)
+    return {
+        "metric": f"total tok/s (prompt + new) of the mixed workload ({shape_name}: {n_req} prompts of 128-4,096 tokens, portions of {ubatch} beside decodes, {new_tokens} new tokens each)",
+        "value": round(total, 1), "unit": "tok/s", "n_gpus": 1, "steps": len(log), "warmup": max(warmup, 3),
+        "ms_per_step": round(1e3 * wall / max(len(log), 1), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform-random token ids and prompt lengths",
+        "config": {"model": shape_name, "layers": cfg.num_hidden_layers, "layers_of_model": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": n_req, "seq_len": n_ctx, "page": 64,
+                   "parallelism": "single GPU", "l2": "inputs exceed L2 (the weights alone are %.1f GB)" % (weight_bytes(cfg) / 1e9),
+                   "peaks": peak_src, "timing": "host clock around Engine.generate (a step is a scheduler turn)"},
+        "clocks": clock_rec,
+        "e2e": {"value": round(total, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": len(log)},
+        "gpu_launches": int(lgml_b200.ops.launch_count()),
+        "mixed": mixed,
+        "kernel_libraries": lgml_b200.csrc.loaded_libraries(),
+    }
+
+
+def run_cpu_baseline() -> dict:
+    """The stated CPU baseline: the plain float64 implementation under ``tests/plain`` (whole
+    sequences, no cache) on the host, at the two tiny configurations: tokens per second of a
+    prompt of 130 tokens in one pass, and of 16 greedy tokens after it (each a pass over the
+    whole sequence so far, as that implementation works)."""
+    import tempfile
+
+    from tests import helpers as H
+    from tests.plain import llama_plain as P
+
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for name in ("A", "B"):
+            cfg_d, seed = H.TINY[name]
+            folder = H.make_folder(Path(tmp) / name, cfg_d, seed)
+            cfg, w = P.load_folder(folder)
+            n = min(130, cfg_d["max_position_embeddings"] - 17)
+            ids = H.random_ids(n, cfg_d["vocab_size"], 1)
+            P.forward(cfg, w, ids[:8])
+            t0 = time.perf_counter()
+            P.forward(cfg, w, ids)
+            t1 = time.perf_counter()
+            P.greedy(cfg, w, ids, 16)
+            t2 = time.perf_counter()
+            out[f"tiny_{name}"] = {"prompt_tokens": n, "prompt_tok_s": round(n / (t1 - t0), 1), "decode_tok_s": round(16 / (t2 - t1), 1)}
+    return {"impl": "plain-cpu", "what": "tests/plain/llama_plain.py, float64, whole sequences, host threads", "points": out}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,7 +308,12 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in the record)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--shape", default="llama31_8b", choices=list(SHAPES), help="layer sizes and workload (the default is the headline's)")
+    ap.add_argument("--decode-only", action="store_true", help="with --shape llama32_3b: plain decode steps at batch 32 instead of its mixed workload")
+    ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()
+    if args.cpu_baseline:
+        print(json.dumps(run_cpu_baseline()))
+        return 0
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "mischief/lgml is Lua on a ggml fork fetched over the network with a "
@@ -222,6 +333,9 @@ def main() -> int:
 
     global BATCH, PROMPT_LEN, CONTEXT
     shape_name, shape, BATCH, PROMPT_LEN, CONTEXT = SHAPES[args.shape]
+    if args.shape == "llama32_3b" and not args.decode_only:
+        print(json.dumps(run_mixed_workload(shape_name, shape, args, warmup)))
+        return 0
     d = dict(shape)
     full_layers = d["num_hidden_layers"]
     if args.layers:
@@ -237,15 +351,22 @@ def main() -> int:
     clocks.start()
     ms_step, kv_tokens, launches = run_decode(runner, cfg, BATCH, args.steps, warmup)
     clock_rec = clocks.stop()
+    kv_token_bytes = 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * cfg.num_hidden_layers
+
+    def hbm_frac(ms, kv):
+        """bytes a decode step has to read (every weight once, the live requests' cache) / time / the copy peak"""
+        return (weight_bytes(cfg) + kv * kv_token_bytes) / (ms * 1e-3) / 1e9 / hbm_gbs
+
     points = {}
+    roofline_points = {f"decode_b{BATCH}": round(hbm_frac(ms_step, kv_tokens), 4)}
     if points_too:
         for b, k in ((1, min(args.steps, 64)), (64, min(args.steps, 32))):
-            ms_b, _, _ = run_decode(runner, cfg, b, k, warmup)
+            ms_b, kv_b, _ = run_decode(runner, cfg, b, k, warmup)
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+            roofline_points[f"decode_b{b}"] = round(hbm_frac(ms_b, kv_b), 4)
 
     value = BATCH * 1000.0 / ms_step
-    kv_bytes = kv_tokens * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * cfg.num_hidden_layers
-    step_bytes = weight_bytes(cfg) + kv_bytes
+    step_bytes = weight_bytes(cfg) + kv_tokens * kv_token_bytes
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
     pf_flops = step_flops(cfg, PREFILL_TOKENS, [PREFILL_TOKENS])
     prefill = {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
@@ -288,6 +409,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
                      "frac": round(achieved / hbm_gbs, 4)},
         "points": points,
+        "roofline_points": roofline_points,
         "kernel_libraries": lgml_b200.csrc.loaded_libraries(),
     }
     print(json.dumps(rec))

@@ -492,9 +492,6 @@ __device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t tmem_d, uint64_t 
         : "memory");
 }
 
-// What tcgen05.alloc returned in the leader and in the other CTA of pair 0 (a check of the set-up).
-__device__ unsigned int lgml_pair_tmem_seen[2];
-
 // A TMA copy into this CTA's shared memory whose bytes are counted on a barrier of the pair's
 // leader (`bar_cluster`: a shared::cluster address from mapa).
 __device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster) {
@@ -557,7 +554,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(&tmem_base_s)), "r"(0u));
         asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(tmem_base) : "r"(ra) : "memory");
     }
-    if (threadIdx.x == 0 && pair == 0) lgml_pair_tmem_seen[rank] = tmem_base_s;
 
     if (warp == 0) {
         // ---------------- TMA producer (each CTA loads its halves) ----------------
@@ -831,24 +827,6 @@ bool pairs_enabled() {
 }
 
 }  // namespace
-
-// Pairs of CTAs of the product for many tokens that the device runs at one time.
-LGML_API int lgml_gemm_pairs_at_once(void) {
-    const size_t smem = (size_t)3 * pair_stage_bytes(256) + 1024;
-    cudaFuncSetAttribute(gemm_pair_kernel<256, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return pairs_at_once<256, 3, 2>(smem);
-}
-
-// The tensor-memory addresses that the two CTAs of pair 0 got from their allocation in the last
-// launch on pairs of CTAs (they should agree).
-LGML_API int lgml_gemm_pair_tmem_seen(unsigned int *leader, unsigned int *other) {
-    unsigned int v[2] = {0, 0};
-    cudaError_t e = cudaMemcpyFromSymbol(v, lgml_pair_tmem_seen, sizeof(v));
-    if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot read the set-up record: %s", cudaGetErrorString(e));
-    *leader = v[0];
-    *other = v[1];
-    return 0;
-}
 
 // Floats of scratch that `n_splits` > 1 needs.
 LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) {

@@ -24,6 +24,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import torch
 
 from .. import ops
+from ..cache import PAGE_SIZE
 from ..sampling import Sampler, SamplingParams, log_min_p
 from .runner import ModelRunner
 from .runtime import MAX_RESULT
@@ -55,11 +56,15 @@ class Engine:
         else:
             cfg = config
         self.config = cfg
-        max_pos = cfg.max_position_embeddings
-        n_ctx = min(n_ctx or max_pos, max_pos)
+        # a configuration that names no limit of positions is bounded by n_ctx alone
+        max_pos = getattr(cfg, "max_position_embeddings", None) or None
+        if n_ctx is None and max_pos is None:
+            raise ValueError("this configuration names no max_position_embeddings: give n_ctx")
+        n_ctx = min(n_ctx or max_pos, max_pos or n_ctx)
+        max_pos = max_pos or n_ctx
         self.n_ctx = n_ctx
         # the pool all slots share: n_ctx tokens as in the reference, or kv_tokens when given
-        n_pages = -(-(kv_tokens or n_ctx) // 64)
+        n_pages = -(-(kv_tokens or n_ctx) // PAGE_SIZE)
         max_batch_tokens = max_batch_tokens or max(ubatch, 2048)
         kw = dict(n_pages=n_pages, max_slots=slots, max_step_tokens=max_batch_tokens, prefix_cache=prefix_cache)
         if model is not None:
@@ -282,6 +287,11 @@ class Engine:
         """Greedy decode of one prompt: (new ids, timings {prefill, decode, n_decode}), as
         ``generate.greedy`` (``lua/lgml/generate.lua:19-34``)."""
         runner = self.runner
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("greedy: empty prompt")
+        if n_predict <= 0:
+            return [], {"prefill": 0.0, "decode": 0.0, "n_decode": 0}
         req = runner.open(("greedy", self._next_id))
         self._next_id += 1
         out: List[int] = []
@@ -289,7 +299,7 @@ class Engine:
         stop = set(stop or ())
         try:
             t0 = time.perf_counter()
-            ids = [int(t) for t in prompt]
+            ids = prompt
             pos = 0
             while pos < len(ids):          # the prompt in portions of ubatch
                 part = ids[pos:pos + self.scheduler.ubatch]

@@ -32,9 +32,10 @@ class DecodeBatch:
         self.widths = list(widths)
         self.seq_lens = [1] * S
         self.max_q_len = 1
+        # the longest context the captured step describes: every mixer cuts its keys into ranges
+        # for this length and its own heads, so a replay launches what the capture recorded
         self.max_kv_len = max(self.widths, default=1) * cm.page_size
-        hkv = max((g.spec.n_kv_heads for g in cm.groups), default=1)
-        self.decode_splits = ops.decode_splits(S, hkv, 1, self.max_kv_len)
+        self.decode_splits = None
         total = 3 * S + (S + 1) + 4 * S + S * sum(self.widths)
         self.total = total
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)

@@ -439,7 +439,7 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
         return 1
     tiles = -(-N // 128)
     k_blocks = -(-K // 64)
-    cover = (2 * SM_COUNT) // tiles if M <= 16 else -(-SM_COUNT // tiles)
+    cover = (2 * sm_count()) // tiles if M <= 16 else -(-sm_count() // tiles)
     splits = max(1, min(cover, k_blocks // 4, 16))
     # no range without K blocks: 64 blocks in 9 ranges of 8 would leave the ninth empty
     return -(-k_blocks // -(-k_blocks // splits))
@@ -534,7 +534,15 @@ def gemm_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, bias_pairs: Optiona
     return gemm_tcgen05(x, w_pairs, out, bias_pairs, status, swiglu=True)
 
 
-SM_COUNT = 148  # B200
+_sm_count = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (148 on a B200)."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count if torch.cuda.is_available() else 148
+    return _sm_count
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, page: int = 64) -> int:
@@ -544,7 +552,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, p
     page, 10.0 us with 12 ranges)."""
     ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
     pages = max(1, -(-max_kv_len // page))
-    return max(1, min(-(-pages // 4), (2 * SM_COUNT) // max(ctas, 1)))
+    return max(1, min(-(-pages // 4), (2 * sm_count()) // max(ctas, 1)))
 
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,

@@ -78,19 +78,75 @@ def target_dtype(kind: str, compute_dtype: torch.dtype) -> torch.dtype:
     return torch.int32
 
 
+STAGE_BYTES = 64 << 20    # the reference uploads in chunks of 64 MiB through a staging buffer (src/lgml.h:20)
+
+
+class StagedUpload:
+    """File -> pinned staging buffer -> device, in chunks, the read of one chunk beside the copy of
+    the one before (two buffers).  The host never holds a whole tensor, and the copies run at
+    pinned-memory speed (the reference: ``src/safetensors.c:396-447``)."""
+
+    def __init__(self, device, stage_bytes: int = STAGE_BYTES):
+        self.device = torch.device(device)
+        self.stage_bytes = stage_bytes
+        self.stages = [torch.empty(stage_bytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.events = [None, None]
+        self.turn = 0
+        self.bytes = 0
+
+    def upload(self, ent: TensorEntry) -> torch.Tensor:
+        """The tensor on the device in its stored type."""
+        from .. import host
+        from .safetensors import SafetensorsError, stored_dtype
+
+        dt = stored_dtype(ent)
+        out = torch.empty(ent.shape, dtype=dt, device=self.device)
+        nbytes = ent.end - ent.begin
+        if nbytes != out.numel() * out.element_size():
+            raise SafetensorsError(f"{ent.path}: tensor '{ent.name}' holds {nbytes} bytes, its shape wants {out.numel() * out.element_size()}")
+        raw = out.view(-1).view(torch.uint8) if out.numel() else out.view(torch.uint8)
+        path = str(ent.path).encode()
+        for off in range(0, nbytes, self.stage_bytes):
+            n = min(self.stage_bytes, nbytes - off)
+            i = self.turn % 2
+            self.turn += 1
+            if self.events[i] is not None:
+                self.events[i].synchronize()          # the copy out of this buffer has run
+            if host.lib().lgml_st_read(path, ent.begin + off, n, self.stages[i].data_ptr()):
+                raise SafetensorsError(f"{host.last_error()} (tensor '{ent.name}')")
+            raw[off:off + n].copy_(self.stages[i][:n], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
+        self.bytes += nbytes
+        return out
+
+    def finish(self) -> None:
+        for ev in self.events:
+            if ev is not None:
+                ev.synchronize()
+
+
 def load_tensors(folder, specs: Iterable[TensorSpec], compute_dtype: torch.dtype, device, ignore: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     """name -> device tensor for every spec present in the folder."""
     specs = list(specs)
     index = index_folder(folder)
     check_index(index, specs, ignore)
     out: Dict[str, torch.Tensor] = {}
+    staged = StagedUpload(device) if torch.device(device).type == "cuda" else None
     for s in specs:
         ent = index.get(s.name)
         if ent is None:
             continue
-        host = read_tensor(ent)
         want = target_dtype(s.kind, compute_dtype)
-        if s.kind == INT_TABLE and host.dtype.is_floating_point:
+        if s.kind == INT_TABLE and ent.dtype in ("F64", "F32", "F16", "BF16"):
             raise WeightError([], [], [(s.name + " (type " + ent.dtype + ", expected integers)", ent.shape, s.shape)])
-        out[s.name] = host.to(device=device, dtype=want, non_blocking=False).contiguous()
+        if staged is not None:
+            # to the device in the stored type through pinned chunks, converted there
+            t = staged.upload(ent)
+            out[s.name] = t if t.dtype == want else t.to(want)
+        else:
+            out[s.name] = read_tensor(ent).to(device=device, dtype=want, non_blocking=False).contiguous()
+    if staged is not None:
+        staged.finish()
     return out

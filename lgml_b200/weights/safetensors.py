@@ -108,6 +108,11 @@ def index_folder(folder) -> Dict[str, TensorEntry]:
     return out
 
 
+def stored_dtype(entry: TensorEntry) -> torch.dtype:
+    """The torch type a tensor is stored in."""
+    return _DTYPES[entry.dtype][2]
+
+
 def read_tensor(entry: TensorEntry) -> torch.Tensor:
     """The tensor on the host in its stored type, read by the host library into memory of its own."""
     torch_dtype = _DTYPES[entry.dtype][2]

@@ -152,7 +152,7 @@ def test_block_embedding_and_head(dtype):
     head = LMHead(V, E, tied_to=emb)
     wt = bind(emb, "", rt, 9, scale=0.5)
     head.bind("", {}, rt)
-    assert head.tensor_specs("") == [] and head.weight is emb.table          # tied: one tensor
+    assert [s.optional for s in head.tensor_specs("")] == [True] and head.weight is emb.table    # tied: one tensor, unless the folder has a head
     cm = CacheManager({0: block.cache_spec()}, n_pages=2, max_slots=1, dtype=dtype, device=DEV)
     r = cm.open("r")
     ids = [5, 210, 0, 77, 5, 9, 100]
