@@ -135,27 +135,8 @@ struct Params {
     int ldo;          // row stride of the output in elements
     long long split_stride;   // elements between the partial results of two splits (0: no split)
     void *out;        // y, or the float32 partial results
-    const float *bias;        // per feature, or null (only when there is no split, or with `fuse`)
+    const float *bias;        // per feature, or null (only when there is no split)
     int *status;
-    // Few tokens only (transposed).  The tokens' rows may stand for rmsnorm(x) * w with the per-token
-    // factor left undone: col_ss [n_ss, ld_ss] holds partial sums of squares of x, and the epilogue
-    // multiplies token t's column by 1 / sqrt(sum_i col_ss[i][t] * inv_width + eps) (before the bias).
-    const float *col_ss;
-    int n_ss, ld_ss;
-    float inv_width, eps;
-    // fuse = 1: the K ranges of a tile are the CTAs of one cluster; their partial sums are added
-    // through distributed shared memory in range order, then  x[t][f] += sum + bias[f]  (the residual
-    // stream, float32, row stride ld_x), xw[t][f] = bfloat16(x[t][f] * norm_w[f])  and this CTA's
-    // partial sums of squares of the new x go to ss_out[(tile * ranges + range) * ld_ss_out + t]:
-    // what the next product needs to apply the norm that follows (see col_ss).
-    int fuse;
-    float *x;
-    int ld_x;
-    const float *norm_w;
-    __nv_bfloat16 *xw;
-    int ld_xw;
-    float *ss_out;
-    int ld_ss_out;
 };
 
 // One thread's 16 consecutive features f0 .. f0 + 15 of token row a_row (tile row = token,
@@ -240,7 +221,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[NACC], acc_empty[NACC];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
-    __shared__ float col_scale_s[BN];
     volatile int *abort_flag = &abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -357,17 +337,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     } else {
         // ---------------- epilogue: 4 warps, warp w reads TMEM lanes 32 * (w % 4) .. + 31 ----------------
         pdl_wait();   // nothing is written before the earlier kernels are done (an empty K range gets here at once)
-        if (p.col_ss != nullptr) {
-            // the per-token factor of the norm that the producer of the tokens' rows left undone; the
-            // partial sums are added in their order, whoever wrote them
-            for (int t = threadIdx.x - 64; t < BN; t += 128) {
-                float ss = 0.f;
-                if (t < p.rows_b)
-                    for (int i = 0; i < p.n_ss; ++i) ss += act_load(p.col_ss + (size_t)i * p.ld_ss + t);
-                col_scale_s[t] = 1.0f / sqrtf(ss * p.inv_width + p.eps);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;                   // row of the tile = TMEM lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -388,16 +357,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                 uint32_t r[16];
                 tcgen05_ld_16(lane_addr + acc_col + (uint32_t)c0, r);
                 tcgen05_wait_ld();
-                if (p.transposed && p.col_ss != nullptr) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * col_scale_s[c0 + j]);
-                }
-                if (p.transposed && p.fuse) {
-                    // the partial sums of this K range, for the cluster to add up: [token][feature of the tile]
-                    float *red = reinterpret_cast<float *>(tiles);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) red[(size_t)(c0 + j) * BM + row] = __uint_as_float(r[j]);
-                } else if (p.transposed) {
+                if (p.transposed) {
                     // tile row = feature (a_row), tile column = token: y[token][feature]
                     const bool row_ok = a_row < p.rows_a;
                     const float b = (p.bias && row_ok) ? p.bias[a_row] : 0.f;
@@ -430,10 +390,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                     store_run(p, a_row, tile_b * BN + c0, r, out_f, out_h, f32);
                 }
             }
-        } else if (p.transposed && p.fuse) {
-            // no K range (or a wait that ran out): this range adds nothing
-            float *red = reinterpret_cast<float *>(tiles);
-            for (int c = 0; c < BN; ++c) red[(size_t)c * BM + row] = 0.f;
         } else if (ok && p.split_stride != 0) {
             // a split with no K range still owns its partial result: zeros
             for (int c = 0; c < BN; ++c) {
@@ -446,56 +402,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         tcgen05_fence_before();
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
         }
-    }
-    if (p.fuse) {
-        // Every thread of every CTA of the cluster comes here (no path above returns).  The first
-        // barrier: all ranges' partial sums lie in their CTAs' shared memory.  Then CTA `split` adds
-        // up its slice of the tile's features, 128 / ranges of them, for all tokens.
-        __syncwarp();
-        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-        if (warp >= 2) {
-            const int S = gridDim.z;
-            const int fs = BM / S;                          // features of this CTA's slice
-            const int e = threadIdx.x - 64;                 // 0 .. 127
-            const int fl = e % fs, tg = e / fs;             // feature within the slice; tokens tg, tg + S, ...
-            const int f_tile = split * fs + fl;
-            const int f = blockIdx.x * BM + f_tile;
-            const bool f_ok = f < p.rows_a;
-            const float b = (p.bias && f_ok) ? p.bias[f] : 0.f;
-            const float nw = f_ok ? p.norm_w[f] : 0.f;
-            float *red = reinterpret_cast<float *>(tiles);
-            float *sq = red + (size_t)BN * BM;              // [token][feature of the slice]
-            const uint32_t red_addr = smem_u32(red);
-            for (int t = tg; t < BN; t += S) {
-                float v = 0.f;
-                if (t < p.rows_b && f_ok) {
-                    float sum = 0.f;
-                    for (int rk = 0; rk < S; ++rk) {
-                        uint32_t ra;
-                        float part;
-                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(red_addr + (uint32_t)((t * BM + f_tile) * 4)), "r"((uint32_t)rk));
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(ra) : "memory");
-                        sum += part;
-                    }
-                    float *xp = p.x + (size_t)t * p.ld_x + f;
-                    v = act_load(xp) + (sum + b);
-                    *xp = v;
-                    p.xw[(size_t)t * p.ld_xw + f] = __float2bfloat16_rn(v * nw);
-                }
-                sq[(size_t)t * fs + fl] = v * v;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            for (int t = e; t < p.rows_b && t < BN; t += 128) {
-                float ss = 0.f;
-                for (int j = 0; j < fs; ++j) ss += sq[(size_t)t * fs + j];
-                p.ss_out[((size_t)blockIdx.x * S + split) * p.ld_ss_out + t] = ss;
-            }
-        }
-        // nobody leaves while another CTA may still read its shared memory
-        __syncwarp();
-        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -844,32 +750,7 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, dim3 g
         if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    if (p.fuse && grid.z > 1) {
-        // the K ranges of a tile form a cluster (along z)
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        int n = 0;
-        if (lgml_pdl_enabled()) {
-            attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[n].val.programmaticStreamSerializationAllowed = 1;
-            ++n;
-        }
-        attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = grid.z;
-        ++n;
-        cfg.attrs = attr;
-        cfg.numAttrs = n;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, STAGES, NACC>, ma, mb, p);
-        if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: launch of clusters of %u K ranges failed: %s", grid.z, cudaGetErrorString(e));
-    } else {
-        lgml_launch(gemm_tcgen05_kernel<BN, STAGES, NACC>, grid, THREADS, smem, stream, ma, mb, p);
-    }
+    lgml_launch(gemm_tcgen05_kernel<BN, STAGES, NACC>, grid, THREADS, smem, stream, ma, mb, p);
     return lgml_launch_status("gemm_tcgen05");
 }
 
@@ -957,98 +838,16 @@ LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) 
 // swiglu: the rows of w come in (gate, up) pairs and y[M, N / 2] = silu(gate) * up (no K split then).
 // reduce = 0 with n_splits > 1 leaves the partial sums [n_splits, M, N] in scratch for the next
 // kernel to add (bias is then not applied).
-namespace {
-// What the two fused forms of the product for few tokens need beyond the plain product's arguments.
-struct Fusion {
-    const float *col_ss = nullptr;   // [n_ss, ld_ss] partial sums of squares behind the tokens' rows (null: the rows are what they are)
-    int n_ss = 0, ld_ss = 0;
-    float inv_width = 0.f, eps = 0.f;
-    int fuse = 0;                    // add the product to the residual stream and prepare the next norm
-    float *resid = nullptr;
-    int ld_resid = 0;
-    const float *norm_w = nullptr;
-    __nv_bfloat16 *xw = nullptr;
-    int ld_xw = 0;
-    float *ss_out = nullptr;
-    int ld_ss_out = 0;
-};
-
-int gemm_impl(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx, int ldw, int ldy,
-              int n_splits, float *scratch, int swiglu, int reduce, const Fusion &fu, int *status, cudaStream_t stream);
-}  // namespace
-
 LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx,
                                int ldw, int ldy, int n_splits, float *scratch, int swiglu, int reduce, int *status,
                                cudaStream_t stream) {
-    return gemm_impl(x, w, bias, y, y_f32, M, N, K, ldx, ldw, ldy, n_splits, scratch, swiglu, reduce, Fusion(), status, stream);
-}
-
-// The product for few tokens (M <= 256) whose token rows x stand for rmsnorm(x0) * w0 with the per-token
-// factor left undone: col_ss [n_ss, ld_ss] holds partial sums of squares of x0 (width elements a row), and
-// every output of token t is multiplied by 1 / sqrt(sum_i col_ss[i][t] / width + eps) before the bias.
-// Everything else as lgml_gemm_tcgen05 (partial sums of K ranges are scaled too, so whoever adds them up
-// needs no change).
-LGML_API int lgml_gemm_tcgen05_scaled(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx,
-                                      int ldw, int ldy, int n_splits, float *scratch, int swiglu, int reduce, const float *col_ss,
-                                      int n_ss, int ld_ss, int width, float eps, int *status, cudaStream_t stream) {
-    LGML_REQUIRE(col_ss != nullptr && n_ss > 0 && ld_ss >= M && width > 0, "gemm_tcgen05_scaled: bad sums of squares");
-    LGML_REQUIRE(M <= 256, "gemm_tcgen05_scaled: for at most 256 tokens, not %d", M);
-    Fusion fu;
-    fu.col_ss = col_ss;
-    fu.n_ss = n_ss;
-    fu.ld_ss = ld_ss;
-    fu.inv_width = 1.0f / (float)width;
-    fu.eps = eps;
-    return gemm_impl(x, w, bias, y, y_f32, M, N, K, ldx, ldw, ldy, n_splits, scratch, swiglu, reduce, fu, status, stream);
-}
-
-// The product for few tokens (M <= 64) that ends a part of a layer, with what follows it done in its
-// epilogue: resid[M, N] (float32, the residual stream) += x . w^T + bias;  xw[M, N] = bfloat16(resid * norm_w)
-// (the next norm's weight applied, its per-token factor left to the next product); ss_out[i][t], i <
-// lgml_gemm_tcgen05_fused_parts(N, n_splits), partial sums of squares of the new resid row t.  n_splits is
-// 1, 2, 4 or 8: the K ranges of a tile are the CTAs of one cluster and add their sums through distributed
-// shared memory, in range order.  x may itself carry an undone norm factor (col_ss as above, or null).
-LGML_API int lgml_gemm_tcgen05_fused_parts(int N, int n_splits) { return ((N + BM - 1) / BM) * n_splits; }
-
-LGML_API int lgml_gemm_tcgen05_fused(const void *x, const void *w, const float *bias, int M, int N, int K, int ldx, int ldw, int n_splits,
-                                     const float *col_ss, int n_ss, int ld_ss, int width, float eps, float *resid, int ld_resid,
-                                     const float *norm_w, void *xw, int ld_xw, float *ss_out, int ld_ss_out, int *status,
-                                     cudaStream_t stream) {
-    LGML_REQUIRE(M <= 64, "gemm_tcgen05_fused: for at most 64 tokens, not %d", M);
-    LGML_REQUIRE(n_splits == 1 || n_splits == 2 || n_splits == 4 || n_splits == 8, "gemm_tcgen05_fused: 1, 2, 4 or 8 K ranges, not %d", n_splits);
-    LGML_REQUIRE(n_splits <= (K + BK - 1) / BK, "gemm_tcgen05_fused: %d K ranges for %d blocks of K", n_splits, (K + BK - 1) / BK);
-    LGML_REQUIRE(resid != nullptr && norm_w != nullptr && xw != nullptr && ss_out != nullptr, "gemm_tcgen05_fused: missing outputs");
-    LGML_REQUIRE(ld_resid >= N && ld_xw >= N && ld_ss_out >= M, "gemm_tcgen05_fused: a leading dimension is smaller than its row");
-    Fusion fu;
-    if (col_ss != nullptr) {
-        LGML_REQUIRE(n_ss > 0 && ld_ss >= M && width > 0, "gemm_tcgen05_fused: bad sums of squares");
-        fu.col_ss = col_ss;
-        fu.n_ss = n_ss;
-        fu.ld_ss = ld_ss;
-        fu.inv_width = 1.0f / (float)width;
-        fu.eps = eps;
-    }
-    fu.fuse = 1;
-    fu.resid = resid;
-    fu.ld_resid = ld_resid;
-    fu.norm_w = norm_w;
-    fu.xw = (__nv_bfloat16 *)xw;
-    fu.ld_xw = ld_xw;
-    fu.ss_out = ss_out;
-    fu.ld_ss_out = ld_ss_out;
-    return gemm_impl(x, w, bias, nullptr, 0, M, N, K, ldx, ldw, N, n_splits, nullptr, 0, 1, fu, status, stream);
-}
-
-namespace {
-int gemm_impl(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx, int ldw, int ldy,
-              int n_splits, float *scratch, int swiglu, int reduce, const Fusion &fu, int *status, cudaStream_t stream) {
     LGML_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: a leading dimension is smaller than its row");
     LGML_REQUIRE(!swiglu || (N % 2 == 0 && n_splits == 1), "gemm_tcgen05: the gated epilogue needs an even N and no K split");
     LGML_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: row strides (%d, %d) must be multiples of 8 elements (16 bytes) for TMA", ldx, ldw);
     LGML_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned for TMA");
     LGML_REQUIRE(n_splits >= 1 && n_splits <= 64, "gemm_tcgen05: bad split count %d", n_splits);
-    LGML_REQUIRE(n_splits == 1 || scratch != nullptr || fu.fuse, "gemm_tcgen05: %d K splits need scratch memory", n_splits);
+    LGML_REQUIRE(n_splits == 1 || scratch != nullptr, "gemm_tcgen05: %d K splits need scratch memory", n_splits);
     if (M == 0) return 0;
     const int k_blocks = (K + BK - 1) / BK;
     if (n_splits > k_blocks) n_splits = k_blocks;
@@ -1062,25 +861,6 @@ int gemm_impl(const void *x, const void *w, const float *bias, void *y, int y_f3
     p.bias = n_splits > 1 ? nullptr : bias;
     p.status = status;
     p.swiglu = swiglu;
-    p.col_ss = fu.col_ss;
-    p.n_ss = fu.n_ss;
-    p.ld_ss = fu.ld_ss;
-    p.inv_width = fu.inv_width;
-    p.eps = fu.eps;
-    p.fuse = fu.fuse;
-    p.x = fu.resid;
-    p.ld_x = fu.ld_resid;
-    p.norm_w = fu.norm_w;
-    p.xw = fu.xw;
-    p.ld_xw = fu.ld_xw;
-    p.ss_out = fu.ss_out;
-    p.ld_ss_out = fu.ld_ss_out;
-    if (fu.fuse) {
-        // the ranges' sums never leave the chip: no partial results in global memory, the bias in the epilogue
-        p.split_stride = 0;
-        p.out = nullptr;
-        p.bias = bias;
-    }
     CUtensorMap ma, mb;
     int rc;
     dim3 grid;
@@ -1137,7 +917,7 @@ int gemm_impl(const void *x, const void *w, const float *bias, void *y, int y_f3
             break;
     }
     if (rc) return rc;
-    if (n_splits > 1 && reduce && !fu.fuse) {
+    if (n_splits > 1 && reduce) {
         const long long total = (long long)M * N;
         const int threads = 256;
         const long long want = (total + threads - 1) / threads;
@@ -1150,5 +930,3 @@ int gemm_impl(const void *x, const void *w, const float *bias, void *y, int y_f3
     }
     return rc;
 }
-}  // namespace
-

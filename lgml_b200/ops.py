@@ -128,37 +128,6 @@ class Partials:
         return y if self.bias is None else y + self.bias
 
 
-class NormedRows:
-    """Token rows that stand for rmsnorm(x) * w with the per-row factor left undone: ``data``
-    bfloat16 [rows, width] = x * w, and ``ss`` float32 [parts, rows] partial sums of squares of x,
-    so that row t's factor is 1 / sqrt(sum_i ss[i, t] / width + eps).  A matrix product for few
-    tokens applies the factor in its epilogue (it is the same for a whole row, so it commutes
-    with the product); ``norm`` is the norm part these rows were prepared for.  The residual
-    stream x already holds the sum they were made from."""
-
-    def __init__(self, data: torch.Tensor, ss: torch.Tensor, eps: float, norm=None):
-        self.data, self.ss, self.eps, self.norm = data, ss, float(eps), norm
-
-    @property
-    def shape(self):
-        return self.data.shape
-
-    @property
-    def dtype(self):
-        return self.data.dtype
-
-    @property
-    def device(self):
-        return self.data.device
-
-    def factors(self) -> torch.Tensor:
-        return torch.rsqrt(self.ss.sum(dim=0) / self.data.shape[1] + self.eps)
-
-    def materialize(self, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """The normed rows themselves (for a consumer that cannot apply the factor)."""
-        return (self.data.float() * self.factors()[:, None]).to(dtype or self.data.dtype)
-
-
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
             rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = rmsnorm(x [+ delta]) * weight.  With ``delta`` (a tensor, or ``Partials``) and
@@ -483,9 +452,6 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
     accumulation, out bfloat16 or float32.  ``swiglu``: the rows of w (and bias) come in
     (gate, up) pairs and out[M, N/2] = silu(gate) * up.  ``partials_ok``: when K is cut, return
     ``Partials`` (the float32 partial sums and the bias) instead of adding them up here."""
-    rows = x if isinstance(x, NormedRows) else None
-    if rows is not None:
-        x = rows.data
     _need(x, "gemm input", torch.bfloat16, 2)
     _need(w, "gemm weight", torch.bfloat16, 2)
     ldx, ldw = _rows_contiguous(x, "gemm input"), _rows_contiguous(w, "gemm weight")
@@ -494,8 +460,6 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
     n_out = N // 2 if swiglu else N
     if w.shape[1] != K:
         raise KernelError(f"gemm_tcgen05: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
-    if rows is not None and M > 256:
-        raise KernelError(f"gemm_tcgen05: rows with an undone norm factor are for at most 256 tokens, not {M}")
     if bias is not None:
         _need(bias, "gemm bias", torch.float32, 1)
         if bias.numel() != N:
@@ -519,86 +483,14 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         if out.shape != (M, n_out) or out.dtype not in (torch.bfloat16, torch.float32):
             raise KernelError(f"gemm_tcgen05: output {tuple(out.shape)} {out.dtype} does not fit [{M}, {n_out}]")
         y_f32 = 1 if out.dtype == torch.float32 else 0
-    if rows is not None:
-        ss = _check_ss(rows, M)
-        fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05_scaled", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                              c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
-        _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(None if raw else out), y_f32, M, N, K, ldx, ldw, ldy,
-                                  n_splits, _ptr(scratch if n_splits > 1 else None), 1 if swiglu else 0, 0 if raw else 1,
-                                  _ptr(ss), ss.shape[0], ss.stride(0), K, rows.eps, _ptr(status), _stream()), "gemm_tcgen05 (scaled rows)")
-    else:
-        fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                       c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
-        _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(None if raw else out), y_f32, M, N, K, ldx, ldw, ldy,
-                                  n_splits, _ptr(scratch if n_splits > 1 else None), 1 if swiglu else 0, 0 if raw else 1, _ptr(status),
-                                  _stream()), "gemm_tcgen05")
+    fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                   c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(None if raw else out), y_f32, M, N, K, ldx, ldw, ldy,
+                              n_splits, _ptr(scratch if n_splits > 1 else None), 1 if swiglu else 0, 0 if raw else 1, _ptr(status),
+                              _stream()), "gemm_tcgen05")
     if raw:
         return Partials(scratch[: n_splits * M * N].view(n_splits, M, N), bias)
     return out
-
-
-def _check_ss(rows: NormedRows, M: int) -> torch.Tensor:
-    ss = rows.ss
-    _need(ss, "sums of squares", torch.float32, 2)
-    if ss.shape[1] != M or ss.stride(1) != 1 or ss.shape[0] < 1:
-        raise KernelError(f"sums of squares {tuple(ss.shape)} do not fit {M} rows")
-    return ss
-
-
-FUSED_MAX_TOKENS = 64
-
-
-def fused_splits(M: int, N: int, K: int) -> int:
-    """K ranges of the product that adds into the residual stream: as ``tcgen05_splits``, cut
-    down to 1, 2, 4 or 8 (the ranges of a tile are one cluster, and each adds up a whole
-    fraction of the tile's 128 features)."""
-    want = tcgen05_splits(M, N, K)
-    s = 8
-    while s > 1 and (s > want or s > -(-K // 64)):
-        s //= 2
-    return s
-
-
-def gemm_tcgen05_fused(x, w: torch.Tensor, bias: Optional[torch.Tensor], resid: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                       status: torch.Tensor, norm=None, n_splits: Optional[int] = None) -> NormedRows:
-    """For few tokens (at most ``FUSED_MAX_TOKENS``): resid[M, N] += x[M, K] . w[N, K]^T + bias in
-    float32, and the rows that the norm behind the sum (weight ``norm_weight``, ``eps``) would
-    give, with the per-row factor left to the product that reads them: ``NormedRows``.  One
-    kernel: the K ranges of a tile are the CTAs of a cluster and add their partial sums through
-    distributed shared memory in a fixed order.  ``x`` may itself be ``NormedRows``."""
-    rows = x if isinstance(x, NormedRows) else None
-    if rows is not None:
-        x = rows.data
-    _need(x, "gemm input", torch.bfloat16, 2)
-    _need(w, "gemm weight", torch.bfloat16, 2)
-    _need(resid, "residual stream", torch.float32, 2)
-    _need(norm_weight, "norm weight", torch.float32, 1)
-    ldx, ldw, ldr = _rows_contiguous(x, "gemm input"), _rows_contiguous(w, "gemm weight"), _rows_contiguous(resid, "residual stream")
-    M, K = x.shape
-    N = w.shape[0]
-    if w.shape[1] != K or tuple(resid.shape) != (M, N) or norm_weight.numel() != N:
-        raise KernelError(f"gemm_tcgen05_fused: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, residual {tuple(resid.shape)}")
-    if not 1 <= M <= FUSED_MAX_TOKENS:
-        raise KernelError(f"gemm_tcgen05_fused: for 1 to {FUSED_MAX_TOKENS} tokens, not {M}")
-    if bias is not None:
-        _need(bias, "gemm bias", torch.float32, 1)
-        if bias.numel() != N:
-            raise KernelError("gemm_tcgen05_fused: bias length is not N")
-    if n_splits is None:
-        n_splits = fused_splits(M, N, K)
-    if n_splits not in (1, 2, 4, 8) or n_splits > -(-K // 64):
-        raise KernelError(f"gemm_tcgen05_fused: {n_splits} K ranges (1, 2, 4 or 8, at most one per 64 of K)")
-    parts = -(-N // 128) * n_splits
-    xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    ss_out = torch.empty((parts, M), dtype=torch.float32, device=x.device)
-    ss_in = _check_ss(rows, M) if rows is not None else None
-    fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05_fused", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
-                                                         c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                                         c_void_p, c_void_p])
-    _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), M, N, K, ldx, ldw, n_splits, _ptr(ss_in), ss_in.shape[0] if ss_in is not None else 0,
-                              ss_in.stride(0) if ss_in is not None else 0, K, rows.eps if rows is not None else 0.0, _ptr(resid), ldr,
-                              _ptr(norm_weight), _ptr(xw), N, _ptr(ss_out), M, _ptr(status), _stream()), "gemm_tcgen05_fused")
-    return NormedRows(xw, ss_out, eps, norm)
 
 
 def gemm_cublas(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -617,16 +509,13 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Op
     y is bfloat16 or float32.  ``backend``: "tcgen05" is the hand-written tensor-core kernel,
     "cublas" the library product; "auto" takes tcgen05 whenever its operands fit TMA's
     alignment rules.  With ``partials_ok`` the result may be ``Partials``."""
-    if isinstance(x, NormedRows) and (backend == "cublas" or not tcgen05_supports(x.data, w) or x.shape[0] > 256):
-        x = x.materialize()          # only the hand-written product for few tokens applies the factor itself
-    plain = x.data if isinstance(x, NormedRows) else x
-    _need(plain, "gemm input", torch.bfloat16, 2)
+    _need(x, "gemm input", torch.bfloat16, 2)
     _need(w, "gemm weight", torch.bfloat16, 2)
     if x.shape[1] != w.shape[1]:
         raise KernelError(f"gemm_bf16: shapes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}")
     if x.shape[0] == 0:
         return torch.empty((0, w.shape[0]), dtype=out_dtype, device=x.device)
-    if backend == "cublas" or (backend == "auto" and not tcgen05_supports(plain, w)):
+    if backend == "cublas" or (backend == "auto" and not tcgen05_supports(x, w)):
         return gemm_cublas(x, w, out_dtype, bias)
     if backend not in ("auto", "tcgen05"):
         raise KernelError(f"unknown gemm backend '{backend}'")

@@ -149,59 +149,6 @@ def test_fill_normal_draws_the_host_generator_bit_for_bit(dtype):
 # matrix products
 # ---------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("M,N,K,splits", [(1, 384, 512, 8), (8, 4096, 1024, 8), (8, 200, 192, 2), (33, 384, 576, 4), (64, 256, 320, 1),
-                                          (17, 130, 64, 1), (5, 1024, 4096, None)])
-def test_product_into_the_residual_stream_with_the_next_norm_prepared(M, N, K, splits):
-    """For few tokens: x += a . w^T + bias in the product's own epilogue (the K ranges of a tile add
-    up through a cluster's shared memory), with the rows of the norm that follows and the sums of
-    squares for its factor; a second product reads those rows and applies the factor itself.
-    Against plain float64 arithmetic on the same bfloat16 inputs; N that ends inside a tile, K that
-    ends inside a block, every count of ranges, and inputs that carry an undone factor themselves."""
-    from lgml_b200 import ops
-
-    g = torch.Generator().manual_seed(M * 1000 + N)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
-    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
-    bias = torch.randn(N, generator=g) * 0.1
-    x0 = torch.randn(M, N, generator=g)
-    nw = 1.0 + 0.1 * torch.randn(N, generator=g)
-    eps = 1e-5
-    x = x0.clone().to(DEV)
-    rows = ops.gemm_tcgen05_fused(a.to(DEV), w.to(DEV), bias.to(DEV), x, nw.to(DEV), eps, status, n_splits=splits)
-    assert int(status.item()) == 0
-    want_x = x0.double() + a.double() @ w.double().t() + bias.double()
-    assert torch.allclose(x.double().cpu(), want_x, atol=2e-4, rtol=1e-5)
-    # the prepared rows: x * w as bfloat16, and partial sums of squares that add up to the row's
-    assert torch.allclose(rows.data.double().cpu(), want_x * nw.double(), atol=1e-6, rtol=2 ** -8)
-    assert rows.ss.shape[1] == M and torch.allclose(rows.ss.double().sum(0).cpu(), (want_x ** 2).sum(1), rtol=1e-5)
-    want_h = want_x / torch.sqrt((want_x ** 2).mean(1, keepdim=True) + eps) * nw.double()
-    assert torch.allclose(rows.materialize(torch.float32).double().cpu(), want_h, atol=2e-2, rtol=2e-2)
-    # a product that reads the prepared rows applies the factor: with a bias, gated, and cut along K
-    if N % 8 == 0:
-        hb = rows.data.double().cpu() / torch.sqrt((want_x ** 2).mean(1, keepdim=True) + eps)          # what the product sees, factor applied
-        w2 = (torch.randn(96, N, generator=g) * 0.05).to(torch.bfloat16)
-        b2 = torch.randn(96, generator=g) * 0.1
-        out = torch.empty(M, 96, dtype=torch.float32, device=DEV)
-        ops.gemm_tcgen05(rows, w2.to(DEV), out, b2.to(DEV), status, n_splits=1)
-        want = hb @ w2.double().t() + b2.double()
-        assert torch.allclose(out.double().cpu(), want, atol=2e-3, rtol=2e-3)
-        parts = ops.gemm_tcgen05(rows, w2.to(DEV), None, b2.to(DEV), status, n_splits=min(3, -(-N // 64)), partials_ok=True)
-        got = parts.sum() if isinstance(parts, ops.Partials) else parts
-        assert torch.allclose(got.double().cpu(), want, atol=2e-3, rtol=2e-3)
-        act = ops.gemm_bf16_swiglu(rows, w2.to(DEV), b2.to(DEV), status)
-        gu = want.reshape(M, 48, 2)
-        assert torch.allclose(act.double().cpu(), gu[..., 0] * torch.sigmoid(gu[..., 0]) * gu[..., 1], atol=1e-2, rtol=2e-2)
-        # and a second product into the stream from rows that carry a factor
-        w3 = (torch.randn(N, N, generator=g) * 0.05).to(torch.bfloat16)
-        x2 = x.clone()
-        rows2 = ops.gemm_tcgen05_fused(rows, w3.to(DEV), None, x2, nw.to(DEV), eps, status)
-        want_x2 = x.double().cpu() + hb @ w3.double().t()
-        assert torch.allclose(x2.double().cpu(), want_x2, atol=3e-3, rtol=3e-3)
-        assert torch.allclose(rows2.ss.double().sum(0).cpu(), (want_x2 ** 2).sum(1), rtol=1e-2)
-    assert int(status.item()) == 0
-
-
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 200, 120), (70, 331, 257), (3, 1000, 96)])
 def test_gemm_f32_is_exact_and_batch_invariant(M, N, K):
     from lgml_b200 import ops
