@@ -158,17 +158,32 @@ struct Args {
     int vec;      // rows, parts and vectors allow 16-byte accesses (8-byte for bfloat16)
 };
 
+// d += parts 1 .. n_parts - 1 of one quad, in order.  The loads of up to eight parts are issued
+// before the first is used: one after the other they would cost a round trip to L2 each, which
+// is most of this kernel's time when a product leaves nine partial sums.
+template <typename TD>
+__device__ __forceinline__ void add_parts(const TD *dr, int n_parts, long long part_stride, int i, int c1, int vec, float (&d)[PER]) {
+    constexpr int AHEAD = 8;
+    for (int p0 = 1; p0 < n_parts; p0 += AHEAD) {
+        float e[AHEAD][PER];
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u)
+            if (p0 + u < n_parts) load_quad(dr + (size_t)(p0 + u) * part_stride, i, c1, vec, e[u]);
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u)
+            if (p0 + u < n_parts) {
+#pragma unroll
+                for (int q = 0; q < PER; ++q) d[q] += e[u][q];
+            }
+    }
+}
+
 // x + delta of one quad: the parts in order, then the bias; written back unless rows are gathered
 template <typename TD>
 __device__ __forceinline__ void add_delta(const Args &a, float *xr, const TD *dr, int i, int c1, float (&v)[PER]) {
     float d[PER];
     load_quad(dr, i, c1, a.vec, d);
-    for (int p = 1; p < a.n_parts; ++p) {
-        float e[PER];
-        load_quad(dr + (size_t)p * a.part_stride, i, c1, a.vec, e);
-#pragma unroll
-        for (int q = 0; q < PER; ++q) d[q] += e[q];
-    }
+    add_parts(dr, a.n_parts, a.part_stride, i, c1, a.vec, d);
     if (a.delta_bias) {
         float bq[PER];
         load_quad_const(a.delta_bias, i, c1, a.vec, bq);
@@ -228,12 +243,7 @@ __global__ void __launch_bounds__(MODE == 2 ? GROUP * MAX_CS : GROUP) rmsnorm_ke
                 const int c1 = end(k), i = first(k, rd);
                 float d[PER];
                 d0[k][rd].get(d);
-                for (int p = 1; p < a.n_parts; ++p) {
-                    float e[PER];
-                    load_quad(dr + (size_t)p * a.part_stride, i, c1, vec, e);
-#pragma unroll
-                    for (int q = 0; q < PER; ++q) d[q] += e[q];
-                }
+                add_parts(dr, a.n_parts, a.part_stride, i, c1, vec, d);
                 if (a.delta_bias) {
                     float bq[PER];
                     load_quad_const(a.delta_bias, i, c1, vec, bq);

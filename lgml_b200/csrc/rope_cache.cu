@@ -52,9 +52,22 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
     const size_t col = (size_t)head * D;
     const TS *row = src + (size_t)t * lds + col;
     float a = to_f32(act_load(row + d0)), b = to_f32(act_load(row + d1));
-    for (int p = 1; p < n_parts; ++p) {
-        a += to_f32(act_load(row + (size_t)p * part_stride + d0));
-        b += to_f32(act_load(row + (size_t)p * part_stride + d1));
+    // the other parts in order; the loads of up to eight of them are issued before the first is used
+    // (one after the other they would cost a round trip to L2 each)
+    for (int p0 = 1; p0 < n_parts; p0 += 8) {
+        float ea[8], eb[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (p0 + u < n_parts) {
+                ea[u] = to_f32(act_load(row + (size_t)(p0 + u) * part_stride + d0));
+                eb[u] = to_f32(act_load(row + (size_t)(p0 + u) * part_stride + d1));
+            }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (p0 + u < n_parts) {
+                a += ea[u];
+                b += eb[u];
+            }
     }
     if (bias) {
         a += bias[col + d0];
