@@ -267,26 +267,39 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     }
 }
 
-// Merge the splits of one (token, head) in split order.
+// Merge the splits of one (token, head) in split order.  The splits' maxima and sums are fetched
+// by as many threads at once and shared; a thread then adds up its dimension, the loads of eight
+// splits' partial outputs issued before the first is used (one after the other, every load would
+// cost a round trip to L2: at batch 1 there are twelve splits).
+constexpr int MAX_SPLITS = 512;
 __global__ void decode_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                                       __nv_bfloat16 *__restrict__ out, int ldo, int n_splits, int H, int D) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float m_s[MAX_SPLITS], w_s[MAX_SPLITS];
     const int t = blockIdx.x, h = blockIdx.y;
     const float2 *ml = part_ml + ((size_t)t * H + h) * n_splits;
-    float mm = -INFINITY;
-    for (int i = 0; i < n_splits; ++i) mm = fmaxf(mm, act_load(ml + i).x);
-    float l = 0.f;
-    for (int i = 0; i < n_splits; ++i) {
+    for (int i = threadIdx.x; i < n_splits; i += blockDim.x) {
         const float2 v = act_load(ml + i);
-        l += v.x == -INFINITY ? 0.f : v.y * expf(v.x - mm);
+        m_s[i] = v.x;
+        w_s[i] = v.y;
     }
+    __syncthreads();
+    float mm = -INFINITY;
+    for (int i = 0; i < n_splits; ++i) mm = fmaxf(mm, m_s[i]);
+    float l = 0.f;
+    for (int i = 0; i < n_splits; ++i) l += m_s[i] == -INFINITY ? 0.f : w_s[i] * expf(m_s[i] - mm);
     const float *po = part_o + ((size_t)t * H + h) * n_splits * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.f;
-        for (int i = 0; i < n_splits; ++i) {
-            const float mi = act_load(ml + i).x;
-            if (mi != -INFINITY) o += act_load(po + (size_t)i * D + d) * expf(mi - mm);
+        for (int i0 = 0; i0 < n_splits; i0 += 8) {
+            float pv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + u < n_splits) pv[u] = act_load(po + (size_t)(i0 + u) * D + d);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (i0 + u < n_splits && m_s[i0 + u] != -INFINITY) o += pv[u] * expf(m_s[i0 + u] - mm);
         }
         out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
@@ -330,7 +343,7 @@ LGML_API int lgml_decode_attention(const void *q, int ldq, const int *positions,
     LGML_REQUIRE(page_size == PAGE, "decode_attention: pages of %d tokens, this kernel takes %d", page_size, PAGE);
     LGML_REQUIRE(H % Hkv == 0, "decode_attention: %d heads are no multiple of %d KV heads", H, Hkv);
     LGML_REQUIRE(D >= 16 && D <= MAX_D && D % 16 == 0, "decode_attention: head_dim %d must be a multiple of 16 up to %d", D, MAX_D);
-    LGML_REQUIRE(n_splits >= 1 && n_splits <= 65535, "decode_attention: bad split count %d", n_splits);
+    LGML_REQUIRE(n_splits >= 1 && n_splits <= MAX_SPLITS, "decode_attention: %d key ranges (1 to %d)", n_splits, MAX_SPLITS);
     LGML_REQUIRE(n_splits == 1 || scratch != nullptr, "decode_attention: %d splits need scratch memory", n_splits);
     LGML_REQUIRE(max_new_tokens >= 1, "decode_attention: max_new_tokens (the most tokens a request brings in this step) must be at least 1");
     {

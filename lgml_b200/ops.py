@@ -552,7 +552,7 @@ def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, p
     page, 10.0 us with 12 ranges)."""
     ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
     pages = max(1, -(-max_kv_len // page))
-    return max(1, min(-(-pages // 4), (2 * sm_count()) // max(ctas, 1)))
+    return max(1, min(-(-pages // 4), (2 * sm_count()) // max(ctas, 1), 512))
 
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
