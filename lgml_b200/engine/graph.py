@@ -128,7 +128,14 @@ class DecodeGraph:
         self.has_window = any(g.spec.window is not None for g in runner.cache.groups)
 
     def run(self, requests, tokens: Optional[Sequence[int]], device_tokens: Optional[torch.Tensor]) -> torch.Tensor:
+        """Replay for ``requests`` (at most S of them; the spare rows repeat the last one).  Returns
+        the logits of all S rows: the caller keeps the first ``len(requests)``."""
         b = self.batch
+        n, spare = len(requests), self.S - len(requests)
+        if spare:
+            requests = list(requests) + [requests[-1]] * spare
+            if tokens is not None:
+                tokens = list(tokens) + [tokens[-1]] * spare
         if self.has_window:
             b.invalidate()
         b.fill(requests, tokens)
@@ -142,7 +149,9 @@ class DecodeGraph:
         ev.record()
         self.events[i] = ev
         if device_tokens is not None:
-            b.token_ids.copy_(device_tokens)
+            b.token_ids[:n].copy_(device_tokens)
+            if spare:
+                b.token_ids[n:].copy_(device_tokens[n - 1:].expand(spare))
         if self.graph is None:
             # Nothing but the step's own launches may touch CUDA while the stream is capturing:
             # a finaliser that frees device or pinned memory in the middle (Python's collector

@@ -23,6 +23,18 @@ from .runtime import Runtime
 
 
 MAX_GRAPH_BATCH = 256
+# Batch sizes that decode steps are captured at.  A step of another size runs the next larger
+# graph with its last request repeated in the spare rows: those rows compute the same token at
+# the same position again (the same key and value into the same cell) and their logits are
+# dropped.  Requests that end one after the other would otherwise cost a capture per size.
+GRAPH_SIZES = [1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16, 20, 24, 28, 32, 40, 48, 56, 64, 80, 96, 112, 128, 160, 192, 224, 256]
+
+
+def graph_size(n: int) -> int:
+    for s in GRAPH_SIZES:
+        if s >= n:
+            return s
+    return n
 
 
 class StepError(ValueError):
@@ -165,8 +177,8 @@ class ModelRunner:
         return logits
 
     def graph_kernels(self, batch_size: int) -> int:
-        """Launches of this package's kernels that one replay of the graph of ``batch_size`` holds."""
-        g = self._graphs.get(batch_size)
+        """Launches of this package's kernels that one replay of the graph for ``batch_size`` requests holds."""
+        g = self._graphs.get(graph_size(batch_size))
         return g.kernels if g else 0
 
     def _graph_step(self, entries, stage, device_tokens=None) -> torch.Tensor:
@@ -175,7 +187,9 @@ class ModelRunner:
         graph computes the logits of every token; the wanted rows are picked after it."""
         from .graph import DecodeGraph
 
-        S = len(entries)
+        n = len(entries)
+        # (a mixer with state of its own would count a repeated row twice: such a model gets a graph per size)
+        S = graph_size(n) if not self.cache.state_groups else n
         reqs = [e[0] for e in entries]
         if S not in self._graph_seen:
             self._graph_seen.add(S)
@@ -190,7 +204,7 @@ class ModelRunner:
         g = self._graphs.get(S)
         if g is None:
             g = self._graphs[S] = DecodeGraph(self, S)
-        logits = g.run(reqs, None if device_tokens is not None else [e[1][0] for e in entries], device_tokens)
+        logits = g.run(reqs, None if device_tokens is not None else [e[1][0] for e in entries], device_tokens)[:n]
         self.last_batch = g.batch
         self.graph_replays += 1
         if all(len(e[2]) == 1 for e in entries):
