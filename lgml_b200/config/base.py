@@ -92,4 +92,29 @@ def load_config(folder) -> ModelConfig:
         raise ConfigError(f"{path}: not JSON: {e}") from None
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be an object")
-    return config_from_dict(d)
+    cfg = config_from_dict(d)
+    # a folder's generation_config.json may name more end tokens than config.json (chat models end a
+    # turn with another id than the text's end): a reply stops at any of them
+    ids = generation_eos_ids(folder)
+    if ids and hasattr(cfg, "eos_token_ids"):
+        cfg.eos_token_ids = list(dict.fromkeys(list(cfg.eos_token_ids) + ids))
+    return cfg
+
+
+def generation_eos_ids(folder) -> list:
+    """``eos_token_id`` of the folder's generation_config.json (an id or a list of ids); none when
+    the file is absent."""
+    path = Path(folder) / "generation_config.json"
+    if not path.exists():
+        return []
+    try:
+        g = json.loads(path.read_text())
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{path}: not JSON: {e}") from None
+    eos = g.get("eos_token_id") if isinstance(g, dict) else None
+    if eos is None:
+        return []
+    try:
+        return [int(e) for e in eos] if isinstance(eos, (list, tuple)) else [int(eos)]
+    except (TypeError, ValueError):
+        raise ConfigError(f"{path}: 'eos_token_id' must be an id or a list of ids") from None

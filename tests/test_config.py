@@ -118,3 +118,21 @@ def test_k_ranges_of_a_small_product_are_never_empty():
                 assert 1 <= s <= 16 and (s - 1) * per < k_blocks, (M, N, K, s)
                 if M > 256:
                     assert s == 1
+
+
+def test_end_tokens_of_generation_config_join_those_of_config(tmp_path):
+    import json
+
+    from lgml_b200.config import ConfigError, load_config
+    from tests import helpers as H
+
+    d = dict(H.TINY_B, eos_token_id=7)
+    (tmp_path / "config.json").write_text(json.dumps(d))
+    assert load_config(tmp_path).eos_token_ids == [7]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 7, 11], "temperature": 0.6}))
+    assert load_config(tmp_path).eos_token_ids == [7, 9, 11]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 3}))
+    assert load_config(tmp_path).eos_token_ids == [7, 3]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        load_config(tmp_path)

@@ -116,6 +116,27 @@ def test_preemption_keeps_every_reply_whole(folders):
     assert tight.runner.cache.n_free_pages == 5
 
 
+def test_preemption_keeps_seeded_draws_whole(folders):
+    """The same with temperature sampling: a preempted request keeps its sampler (history and
+    generator), so the reply it goes on with is the one it would have drawn with room to spare; and
+    against the plain implementation's logits through the host sampler."""
+    import lgml_b200
+    from lgml_b200.sampling import NEUTRAL
+
+    folder = folders[("B", "float32")]
+    cfg, w = P.load_folder(folder)
+    prompts = [H.random_ids(n, 320, 180 + n) for n in (60, 50, 40)]
+    roomy = lgml_b200.Engine(str(folder), dtype="float32", slots=3, kv_tokens=64 * 12)
+    want = roomy.generate(prompts, max_tokens=80, temperature=0.9, seed=31, **NEUTRAL)
+    tight = lgml_b200.Engine(str(folder), dtype="float32", slots=3, kv_tokens=64 * 4)
+    reqs = tight.generate(prompts, max_tokens=80, temperature=0.9, seed=31, return_details=True, **NEUTRAL)
+    assert tight.scheduler.stats["preemptions"] >= 1
+    assert [r.generated for r in reqs] == want
+    assert want[2][:20] == plain_sampled(cfg, w, prompts[2], 20, 0.9, 33)
+    tight.runner.cache.check()
+    assert tight.runner.cache.n_free_pages == 4
+
+
 def test_prefix_cache_changes_no_reply(folders):
     """With the prefix cache on, prompts that begin like earlier ones take up the pages that hold
     those tokens and compute only the rest: the replies equal those of an engine without it, in
