@@ -314,6 +314,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--shape", default="llama31_8b", choices=list(SHAPES), help="layer sizes and workload (the default is the headline's)")
     ap.add_argument("--decode-only", action="store_true", help="with --shape llama32_3b: plain decode steps at batch 32 instead of its mixed workload")
+    ap.add_argument("--no-kernel-times", action="store_true", help="leave out the per-kernel-class times of a decode step")
     ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()
     if args.cpu_baseline:
@@ -370,6 +371,28 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
             roofline_points[f"decode_b{b}"] = round(hbm_frac(ms_b, kv_b), 4)
 
+    # device time by kernel class, from events around every launch of a few eager steps (they run one after
+    # the other then: shares of a step, not its time, which the captured graph's kernels overlap)
+    kernel_us = {}
+    if not args.no_kernel_times:
+        g = torch.Generator().manual_seed(9)
+        reqs = [runner.open(("classes", i)) for i in range(BATCH)]
+        try:
+            for r in reqs:
+                ids = torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist()
+                for p0 in range(0, PROMPT_LEN, 512):
+                    runner.step([(r, ids[p0:p0 + 512], [])])
+            toks = [[int(t)] for t in torch.randint(0, cfg.vocab_size, (BATCH,), generator=g)]
+            runner.step([(r, t, [0]) for r, t in zip(reqs, toks)])
+            with ops.KernelTimes() as kt:
+                for _ in range(3):
+                    runner.step([(r, t, [0]) for r, t in zip(reqs, toks)])
+            tot = kt.totals()
+            kernel_us = {k: round(v / 3.0, 1) for k, v in tot.items() if not k.endswith(" calls")}
+        finally:
+            for r in reqs:
+                runner.close(r)
+
     value = BATCH * 1000.0 / ms_step
     step_bytes = weight_bytes(cfg) + kv_tokens * kv_token_bytes
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
@@ -415,6 +438,7 @@ def main() -> int:
                      "frac": round(achieved / hbm_gbs, 4)},
         "points": points,
         "roofline_points": roofline_points,
+        "kernel_us_per_decode_step": kernel_us,
         "kernel_libraries": lgml_b200.csrc.loaded_libraries(),
     }
     print(json.dumps(rec))

@@ -37,6 +37,8 @@ def main(argv=None) -> int:
     ap.add_argument("--presence-penalty", type=float, default=0.0)
     ap.add_argument("--repeat-last-n", type=int, default=64)
     ap.add_argument("--repeat-stop", type=int, default=256, help="equal tokens in a row that end a reply (0: off)")
+    ap.add_argument("--turn-csv", metavar="FILE", help="write one line per scheduler turn (seconds, tokens, decoded tokens, bytes copied) to FILE")
+    ap.add_argument("--kernel-times", action="store_true", help="time every kernel class with CUDA events (steps run eagerly) and print microseconds per class to standard error")
     args = ap.parse_args(argv)
 
     from . import Engine, write_random_model
@@ -56,10 +58,21 @@ def main(argv=None) -> int:
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt_ids]
     eng = Engine(args.model, config=cfg, random_weights=args.seed or 0, dtype=args.dtype, n_ctx=args.ctx, slots=args.parallel,
                  ubatch=args.ubatch, repeat_stop_tokens=args.repeat_stop, prefix_cache=args.prefix_cache)
-    outs = eng.generate(prompts, max_tokens=args.max_tokens, seed=args.seed, temperature=args.temperature, top_k=args.top_k,
-                        top_p=args.top_p, min_p=args.min_p, repeat_penalty=args.repeat_penalty,
-                        frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty,
-                        repeat_last_n=args.repeat_last_n)
+    import contextlib
+
+    from . import ops
+
+    with (ops.KernelTimes() if args.kernel_times else contextlib.nullcontext()) as kt:
+        outs = eng.generate(prompts, max_tokens=args.max_tokens, seed=args.seed, temperature=args.temperature, top_k=args.top_k,
+                            top_p=args.top_p, min_p=args.min_p, repeat_penalty=args.repeat_penalty,
+                            frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty,
+                            repeat_last_n=args.repeat_last_n)
+    if kt is not None:
+        tot = kt.totals()
+        for name in sorted((k for k in tot if not k.endswith(" calls")), key=lambda k: -tot[k]):
+            print(f"{name:28s} {tot[name]:12.1f} us in {tot[name + ' calls']} calls", file=sys.stderr)
+    if args.turn_csv:
+        eng.write_turn_csv(args.turn_csv)
     for o in outs:
         print(",".join(str(t) for t in o))
     return 0

@@ -248,6 +248,18 @@ class Engine:
         return {"tok_s": toks / secs if secs > 0 else 0.0, "steps": len(turns),
                 "h2d_bytes_per_step": sum(t["h2d"] for t in turns) // n, "d2h_bytes_per_step": sum(t["d2h"] for t in turns) // n}
 
+    def write_turn_csv(self, path) -> None:
+        """The turns of the last ``generate`` as CSV: wall seconds of the turn, tokens run, decoded tokens,
+        whether it held decoded tokens only, bytes copied each way (the reference logs the same per pass,
+        ``lua/lgml/engine.lua:1488-1492``)."""
+        import csv
+
+        with open(path, "w", newline="") as f:
+            w = csv.writer(f)
+            w.writerow(["turn", "seconds", "tokens", "decoded", "pure_decode", "h2d_bytes", "d2h_bytes"])
+            for i, t in enumerate(self.turn_log):
+                w.writerow([i, f"{t['s']:.6f}", t["tokens"], t["decode"], int(t["pure_decode"]), t["h2d"], t["d2h"]])
+
     # ---- public --------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None, stop: Optional[Sequence[int]] = None,
                  seed: Optional[int] = None, return_details: bool = False, per_prompt: Optional[Sequence[dict]] = None, **sampling):

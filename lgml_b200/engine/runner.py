@@ -161,7 +161,7 @@ class ModelRunner:
         if stage[1] is not None:
             stage[1].synchronize()
         S = len(entries)
-        if self.use_graphs and all(len(e[1]) == 1 for e in entries) and S <= MAX_GRAPH_BATCH:
+        if self._graphs_now() and all(len(e[1]) == 1 for e in entries) and S <= MAX_GRAPH_BATCH:
             logits = self._graph_step(entries, stage)
         else:
             batch = StepBatch(self.cache, [e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries],
@@ -175,6 +175,11 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += sum(len(e[1]) for e in entries)
         return logits
+
+    def _graphs_now(self) -> bool:
+        """Captured graphs, unless the kernels are being timed one by one (a replay would hide them)."""
+        from .. import ops
+        return self.use_graphs and ops.KernelTimes.active is None
 
     def graph_kernels(self, batch_size: int) -> int:
         """Launches of this package's kernels that one replay of the graph for ``batch_size`` requests holds."""
@@ -228,7 +233,7 @@ class ModelRunner:
         stage = self._pinned[self.steps % len(self._pinned)]
         if stage[1] is not None:
             stage[1].synchronize()
-        if self.use_graphs and len(requests) <= MAX_GRAPH_BATCH:
+        if self._graphs_now() and len(requests) <= MAX_GRAPH_BATCH:
             logits = self._graph_step(entries, stage, device_tokens=device_tokens)
         else:
             toks = [[int(t)] for t in device_tokens.cpu().tolist()]

@@ -59,6 +59,65 @@ def _rows_contiguous(t: torch.Tensor, what: str) -> int:
 _prototyped = set()
 
 
+class KernelTimes:
+    """Device time of every launcher of this package by kernel class, for as long as the context
+    lasts: a CUDA event before and one after each call (the launches then run one after the other
+    as usual, but a kernel that would overlap the one ahead of it through programmatic dependent
+    launch is still charged its whole length: the figures are shares, not a step's time; captured
+    graphs hide their kernels, so the runner steps eagerly meanwhile).
+
+        with ops.KernelTimes() as kt:
+            runner.step(...)
+        kt.totals()        # {"gemm_tcgen05": microseconds, ...}
+    """
+
+    active: Optional["KernelTimes"] = None
+
+    def __init__(self):
+        self.records = []          # (name, start event, end event)
+
+    def __enter__(self):
+        if KernelTimes.active is not None:
+            raise KernelError("KernelTimes does not nest")
+        KernelTimes.active = self
+        return self
+
+    def __exit__(self, *exc):
+        KernelTimes.active = None
+        torch.cuda.synchronize()
+        return False
+
+    def totals(self) -> dict:
+        """Microseconds per launcher name, and the number of calls under "<name> calls"."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.records:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b) * 1e3
+            out[name + " calls"] = out.get(name + " calls", 0) + 1
+        return out
+
+
+class _Timed:
+    """A launcher that, while a ``KernelTimes`` is open, brackets its call with two events."""
+
+    def __init__(self, fn, name: str):
+        self.fn, self.name = fn, name
+
+    def __call__(self, *args):
+        kt = KernelTimes.active
+        if kt is None:
+            return self.fn(*args)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = self.fn(*args)
+        b.record()
+        kt.records.append((self.name, a, b))
+        return rc
+
+
+_wrapped = {}
+
+
 def _fn(lib_name: str, fn_name: str, argtypes):
     lib = csrc.load(lib_name)
     fn = getattr(lib, fn_name)
@@ -69,7 +128,8 @@ def _fn(lib_name: str, fn_name: str, argtypes):
         err = getattr(lib, f"lgml_{lib_name}_last_error")
         err.restype = ctypes.c_char_p
         _prototyped.add(key)
-    return fn
+        _wrapped[key] = _Timed(fn, fn_name[len("lgml_"):] if fn_name.startswith("lgml_") else fn_name)
+    return _wrapped[key]
 
 
 _launches = 0

@@ -296,6 +296,34 @@ def test_command_line(folders):
     assert [int(t) for t in proc.stdout.strip().splitlines()[-1].split(",")] == P.greedy(cfg, w, prompt, 6)
 
 
+def test_kernel_times_and_turn_csv(folders, tmp_path):
+    """Events around every launcher give device time by kernel class (steps then run eagerly, a replayed
+    graph would hide its kernels); the command line writes them and one line per turn."""
+    import lgml_b200
+    from lgml_b200 import ops
+
+    folder = folders[("B", "bfloat16")]
+    eng = lgml_b200.Engine(str(folder), dtype="bfloat16", slots=2)
+    prompts = [H.random_ids(20, 320, 1), H.random_ids(9, 320, 2)]
+    want = eng.generate(prompts, max_tokens=6, temperature=0.0)
+    replays = eng.runner.graph_replays
+    with ops.KernelTimes() as kt:
+        got = eng.generate(prompts, max_tokens=6, temperature=0.0)
+    assert got == want and eng.runner.graph_replays == replays          # the same replies, no replay meanwhile
+    tot = kt.totals()
+    for name in ("gemm_tcgen05", "rmsnorm", "rope_kv_write", "decode_attention", "embed_rows", "argmax_rows"):
+        assert tot[name] > 0.0 and tot[name + " calls"] >= 1, name
+    assert tot["rmsnorm calls"] == (2 * 3 + 1) * len(eng.turn_log)      # two a layer and the final one, every turn
+    assert ops.KernelTimes.active is None
+    eng.write_turn_csv(tmp_path / "turns.csv")
+    lines = (tmp_path / "turns.csv").read_text().splitlines()
+    assert lines[0].startswith("turn,seconds,tokens") and len(lines) == 1 + len(eng.turn_log)
+    proc = subprocess.run([sys.executable, "-m", "lgml_b200", "-m", str(folder), "--prompt-ids", "1,2,3", "-n", "4", "--temperature", "0",
+                           "--kernel-times", "--turn-csv", str(tmp_path / "cli.csv")], cwd=ROOT, text=True, capture_output=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "gemm_tcgen05" in proc.stderr and (tmp_path / "cli.csv").read_text().count("\n") >= 2
+
+
 def test_errors_are_loud(folders, tmp_path):
     import lgml_b200
     from lgml_b200.engine.runner import ModelRunner, StepError
