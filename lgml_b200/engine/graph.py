@@ -26,7 +26,7 @@ class DecodeBatch:
     """The batch description of a captured decode step: the same attributes as ``StepBatch``,
     as views of a device buffer that stays put."""
 
-    def __init__(self, cache_manager, S: int, widths: Sequence[int], device):
+    def __init__(self, cache_manager, S: int, widths: Sequence[int], device, reach: Optional[int] = None):
         cm = self.cache_manager = cache_manager
         self.n_tokens = self.n_seqs = self.n_rows = S
         self.widths = list(widths)
@@ -35,6 +35,8 @@ class DecodeBatch:
         # the longest context the captured step describes: every mixer cuts its keys into ranges
         # for this length and its own heads, so a replay launches what the capture recorded
         self.max_kv_len = max(self.widths, default=1) * cm.page_size
+        if reach:
+            self.max_kv_len = min(self.max_kv_len, reach)       # the longest context of the steps this graph replays
         self.decode_splits = None
         total = 3 * S + (S + 1) + 4 * S + S * sum(self.widths)
         self.total = total
@@ -114,10 +116,10 @@ class DecodeGraph:
 
     RING = 4
 
-    def __init__(self, runner, S: int):
+    def __init__(self, runner, S: int, reach: Optional[int] = None):
         self.runner = runner
         self.S = S
-        self.batch = DecodeBatch(runner.cache, S, runner._graph_widths, runner.rt.device)
+        self.batch = DecodeBatch(runner.cache, S, runner._graph_widths, runner.rt.device, reach=reach)
         self.pinned = [torch.empty(self.batch.total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.pinned_np = [p.numpy() for p in self.pinned]
         self.events: List[Optional[torch.cuda.Event]] = [None] * self.RING

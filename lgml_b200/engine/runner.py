@@ -183,8 +183,8 @@ class ModelRunner:
 
     def graph_kernels(self, batch_size: int) -> int:
         """Launches of this package's kernels that one replay of the graph for ``batch_size`` requests holds."""
-        g = self._graphs.get(graph_size(batch_size))
-        return g.kernels if g else 0
+        size = graph_size(batch_size)
+        return max((g.kernels for (s, _), g in self._graphs.items() if s == size), default=0)
 
     def _graph_step(self, entries, stage, device_tokens=None) -> torch.Tensor:
         """A decode step through a captured graph.  The first step of a batch size runs
@@ -196,6 +196,14 @@ class ModelRunner:
         # (a mixer with state of its own would count a repeated row twice: such a model gets a graph per size)
         S = graph_size(n) if not self.cache.state_groups else n
         reqs = [e[0] for e in entries]
+        # A graph fixes into how many key ranges attention cuts a request's context, and that number is
+        # chosen for a context length: so a graph per power of two of the longest context in the step
+        # (from 1,024 tokens up), or a pool of 128k tokens would cut a 2k context into ranges of a page.
+        longest = max(r.n_tokens for r in reqs) + 1
+        reach = 1024
+        while reach < longest:
+            reach *= 2
+        S = (S, reach)
         if S not in self._graph_seen:
             self._graph_seen.add(S)
             toks = [e[1] for e in entries]
@@ -208,7 +216,7 @@ class ModelRunner:
             return self.model.forward(self.rt, batch)
         g = self._graphs.get(S)
         if g is None:
-            g = self._graphs[S] = DecodeGraph(self, S)
+            g = self._graphs[S] = DecodeGraph(self, S[0], reach=S[1])
         logits = g.run(reqs, None if device_tokens is not None else [e[1][0] for e in entries], device_tokens)[:n]
         self.last_batch = g.batch
         self.graph_replays += 1
