@@ -187,14 +187,14 @@ class ModelRunner:
         return max((g.kernels for (s, _), g in self._graphs.items() if s == size), default=0)
 
     def _graph_step(self, entries, stage, device_tokens=None) -> torch.Tensor:
-        """A decode step through a captured graph.  The first step of a batch size runs
-        eagerly (it also loads the kernels); the second captures; later ones replay.  The
-        graph computes the logits of every token; the wanted rows are picked after it."""
+        """A decode step through a captured graph.  The first step of a kind (batch size, reach of
+        the context) runs eagerly (it also loads the kernels); the second captures; later ones
+        replay.  The graph computes the logits of every token; the wanted rows are picked after it."""
         from .graph import DecodeGraph
 
         n = len(entries)
         # (a mixer with state of its own would count a repeated row twice: such a model gets a graph per size)
-        S = graph_size(n) if not self.cache.state_groups else n
+        size = graph_size(n) if not self.cache.state_groups else n
         reqs = [e[0] for e in entries]
         # A graph fixes into how many key ranges attention cuts a request's context, and that number is
         # chosen for a context length: so a graph per power of two of the longest context in the step
@@ -203,9 +203,9 @@ class ModelRunner:
         reach = 1024
         while reach < longest:
             reach *= 2
-        S = (S, reach)
-        if S not in self._graph_seen:
-            self._graph_seen.add(S)
+        key = (size, reach)
+        if key not in self._graph_seen:
+            self._graph_seen.add(key)
             toks = [e[1] for e in entries]
             if device_tokens is not None:
                 toks = [[int(t)] for t in device_tokens.cpu().tolist()]
@@ -214,9 +214,9 @@ class ModelRunner:
             stage[1].record()
             self.last_batch = batch
             return self.model.forward(self.rt, batch)
-        g = self._graphs.get(S)
+        g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[S] = DecodeGraph(self, S[0], reach=S[1])
+            g = self._graphs[key] = DecodeGraph(self, size, reach=reach)
         logits = g.run(reqs, None if device_tokens is not None else [e[1][0] for e in entries], device_tokens)[:n]
         self.last_batch = g.batch
         self.graph_replays += 1
