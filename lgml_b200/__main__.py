@@ -37,6 +37,7 @@ def main(argv=None) -> int:
     ap.add_argument("--presence-penalty", type=float, default=0.0)
     ap.add_argument("--repeat-last-n", type=int, default=64)
     ap.add_argument("--repeat-stop", type=int, default=256, help="equal tokens in a row that end a reply (0: off)")
+    ap.add_argument("--stream", action="store_true", help="print every new token as 'request: id' as soon as it is known")
     ap.add_argument("--turn-csv", metavar="FILE", help="write one line per scheduler turn (seconds, tokens, decoded tokens, bytes copied) to FILE")
     ap.add_argument("--kernel-times", action="store_true", help="time every kernel class with CUDA events (steps run eagerly) and print microseconds per class to standard error")
     args = ap.parse_args(argv)
@@ -66,7 +67,8 @@ def main(argv=None) -> int:
         outs = eng.generate(prompts, max_tokens=args.max_tokens, seed=args.seed, temperature=args.temperature, top_k=args.top_k,
                             top_p=args.top_p, min_p=args.min_p, repeat_penalty=args.repeat_penalty,
                             frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty,
-                            repeat_last_n=args.repeat_last_n)
+                            repeat_last_n=args.repeat_last_n,
+                            on_token=(lambda i, t: print(f"{i}: {t}", flush=True)) if args.stream else None)
     if kt is not None:
         tot = kt.totals()
         for name in sorted((k for k in tot if not k.endswith(" calls")), key=lambda k: -tot[k]):

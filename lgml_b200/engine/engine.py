@@ -84,6 +84,7 @@ class Engine:
         gc.collect()
         gc.freeze()
         self._next_id = 0
+        self._on_token = None
         self.run_ahead = run_ahead
         self._ahead: Optional[dict] = None          # the step whose ids the host has not seen yet
         self._host_ring = [torch.empty(MAX_RESULT + 1, dtype=torch.int32).pin_memory() for _ in range(3)]
@@ -211,6 +212,13 @@ class Engine:
         # a request that an earlier step ended has a token too many in this one: not counted
         n_decode = sum(1 for e in plan if len(e.tokens) == 1 and e.sample and e.request.finish_reason is None)
         done = self.scheduler.complete(plan, {e.request.id: int(t) for e, t in zip(rows, toks)})
+        if self._on_token is not None:
+            # (a token too many, run ahead of the end token that finished its request, was dropped by ``complete``)
+            for e, t in zip(rows, toks):
+                r = e.request
+                if r.generated and r.generated[-1] == int(t) and r._told < len(r.generated):
+                    r._told = len(r.generated)
+                    self._on_token(r.index, int(t))
         now = time.perf_counter()
         self.turn_log.append({"s": now - self._t_mark, "tokens": sum(len(e.tokens) for e in plan),
                               "decode": n_decode, "pure_decode": all(len(e.tokens) == 1 for e in plan),
@@ -262,16 +270,20 @@ class Engine:
 
     # ---- public --------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None, stop: Optional[Sequence[int]] = None,
-                 seed: Optional[int] = None, return_details: bool = False, per_prompt: Optional[Sequence[dict]] = None, **sampling):
+                 seed: Optional[int] = None, return_details: bool = False, per_prompt: Optional[Sequence[dict]] = None,
+                 on_token=None, **sampling):
         """Token ids in, token ids out.  ``prompts``: lists of token ids.  Sampler options
         (``temperature``, ``top_k``, ``top_p``, ``min_p``, ``repeat_penalty``,
         ``frequency_penalty``, ``presence_penalty``, ``repeat_last_n``, ``logit_bias``) and
         ``seed`` as in the sampler; request i draws from the stream of ``seed + i``.
         ``per_prompt``: one dict of sampler options per prompt that override the common ones.
+        ``on_token(i, id)`` is called for every new token of prompt i as soon as the host knows it
+        (the reference streams its replies the same way).
         Returns one list of new ids per prompt (with the stop id when one ends it)."""
         opts = {**self.sampling_defaults, **sampling}
         stop_ids = list(stop) if stop is not None else self.eos_ids
         reqs = []
+        self._on_token = on_token
         self.turn_log = []
         t0 = self._t_mark = time.perf_counter()
         for i, p in enumerate(prompts):
@@ -281,6 +293,7 @@ class Engine:
             params = SamplingParams(seed=None if seed is None else seed + i, **({**opts, **per_prompt[i]} if per_prompt else opts))
             req = GenRequest(id=("gen", self._next_id), prompt=p, max_new_tokens=max(min(limit, room), 0), params=params,
                              stop_ids=stop_ids)
+            req.index, req._told = i, 0
             self._next_id += 1
             if req.max_new_tokens == 0:
                 req.finish_reason = "length"
