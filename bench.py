@@ -189,7 +189,9 @@ def run_prefill(runner, cfg, reps: int = 3, seed: int = 1):
             torch.cuda.synchronize()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            runner.step([(r, ids, [PREFILL_TOKENS - 1])])
+            for p0 in range(0, PREFILL_TOKENS, 2048):
+                part = ids[p0:p0 + 2048]
+                runner.step([(r, part, [len(part) - 1] if p0 + 2048 >= PREFILL_TOKENS else [])])
             end.record()
             torch.cuda.synchronize()
             ms = start.elapsed_time(end)
@@ -314,6 +316,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--shape", default="llama31_8b", choices=list(SHAPES), help="layer sizes and workload (the default is the headline's)")
     ap.add_argument("--decode-only", action="store_true", help="with --shape llama32_3b: plain decode steps at batch 32 instead of its mixed workload")
+    ap.add_argument("--prompt-len", type=int, default=0, help="prompt length of the decode runs instead of the shape's own (for other context lengths)")
+    ap.add_argument("--context", type=int, default=0, help="context (tokens a request may hold) instead of the shape's own")
+    ap.add_argument("--prefill-tokens", type=int, default=0, help="tokens of the timed prompt instead of 2,048 (read in portions of 2,048)")
     ap.add_argument("--no-kernel-times", action="store_true", help="leave out the per-kernel-class times of a decode step")
     ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()
@@ -339,6 +344,14 @@ def main() -> int:
 
     global BATCH, PROMPT_LEN, CONTEXT
     shape_name, shape, BATCH, PROMPT_LEN, CONTEXT = SHAPES[args.shape]
+    global PREFILL_TOKENS
+    if args.prompt_len:
+        PROMPT_LEN = args.prompt_len
+    if args.context:
+        CONTEXT = args.context
+    if args.prefill_tokens:
+        PREFILL_TOKENS = args.prefill_tokens
+    CONTEXT = -(-max(CONTEXT, PROMPT_LEN + args.steps + 64, PREFILL_TOKENS) // 64) * 64
     if args.shape == "llama32_3b" and not args.decode_only:
         print(json.dumps(run_mixed_workload(shape_name, shape, args, warmup)))
         return 0
@@ -346,6 +359,7 @@ def main() -> int:
     full_layers = d["num_hidden_layers"]
     if args.layers:
         d["num_hidden_layers"] = args.layers
+    d["max_position_embeddings"] = max(d["max_position_embeddings"], CONTEXT)
     cfg = config_from_dict(d)
     hbm_gbs, bf16_tflops, peak_src = peaks()
     points_too = args.shape == "llama31_8b" and not args.skip_points
@@ -396,7 +410,7 @@ def main() -> int:
     value = BATCH * 1000.0 / ms_step
     step_bytes = weight_bytes(cfg) + kv_tokens * kv_token_bytes
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
-    pf_flops = step_flops(cfg, PREFILL_TOKENS, [PREFILL_TOKENS])
+    pf_flops = step_flops(cfg, PREFILL_TOKENS, [PREFILL_TOKENS])      # (read in portions: the same products and the same causal triangle)
     prefill = {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
                "frac": round(pf_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12), 4)}
 
