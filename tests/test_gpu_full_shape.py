@@ -165,7 +165,7 @@ def one_layer_model(shape, seed, n_pages):
     return d, ModelRunner(model, rt, n_pages=n_pages, max_slots=4, max_step_tokens=1024), host
 
 
-@pytest.mark.parametrize("shape,lens", [("8b", [600, 200, 130, 90, 300, 70]), ("13b", [560, 150, 100, 70, 200])])
+@pytest.mark.parametrize("shape,lens", [("8b", [600, 200, 130, 90, 300, 70]), ("13b", [560, 150, 100, 70, 200]), ("3b", [580, 170, 260, 66, 129])])
 def test_full_size_kernels_against_the_plain_implementation_under_the_hard_schedule(shape, lens):
     """Four live requests, portions beside decoded tokens, a first portion of over 512 tokens
     (pairs of CTAs in the products, the two-tile tcgen05 attention), the last tokens of every
