@@ -506,6 +506,41 @@ LGML_API int lgml_scale_cap(float *x, long long total, float scale, float cap, c
 }
 
 // ---------------------------------------------------------------------------------------
+// Asking L2 for bytes that a later kernel will read (weights): every thread requests chunks
+// with cp.async.bulk.prefetch.L2 and the kernel ends; nothing waits for the bytes.  With
+// `keep` the lines are marked to be evicted last, so that what streams through L2 before the
+// reader comes (the cache's pages) does not push them out; the reader then fetches them with a
+// plain load and they age like any other line.  Launched without programmatic serialization:
+// it runs on a stream of its own beside the step's chain.
+// ---------------------------------------------------------------------------------------
+__global__ void l2_ahead_kernel(const char *p, size_t bytes, int keep) {
+    const size_t chunk = 16384;
+    uint64_t policy = 0;
+    if (keep) asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    const size_t stride = (size_t)gridDim.x * blockDim.x * chunk;
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * chunk; i < bytes; i += stride) {
+        const size_t left = bytes - i;
+        const unsigned n = (unsigned)((left < chunk ? left : chunk) & ~(size_t)15);
+        if (n == 0) break;
+        if (keep)
+            asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(p + i), "r"(n), "l"(policy) : "memory");
+        else
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + i), "r"(n) : "memory");
+    }
+}
+
+LGML_API int lgml_l2_ahead(const void *p, long long bytes, int keep, cudaStream_t stream) {
+    LGML_REQUIRE(bytes >= 0 && ((uintptr_t)p & 15) == 0, "l2_ahead: a negative size or an address off a 16-byte boundary");
+    if (bytes < 16) return 0;
+    const long long chunks = (bytes + 16383) / 16384;
+    const int threads = 128;
+    long long blocks = (chunks + threads - 1) / threads;
+    if (blocks > 32) blocks = 32;
+    l2_ahead_kernel<<<(int)blocks, threads, 0, stream>>>((const char *)p, (size_t)bytes, keep);
+    return lgml_launch_status("l2_ahead");
+}
+
+// ---------------------------------------------------------------------------------------
 // Seeded normal fill: value i of a tensor = mean + sd * z_i, z_i ~ N(0,1) from a counter-based
 // stream keyed by (seed, i): splitmix64 of seed and index, then Box-Muller, as mischief/lgml
 // fills its test tensors (src/lgml.c:3064-3079, :3133-3137).  The host has the same generator

@@ -20,6 +20,7 @@ import torch
 
 from .. import ops
 from .batch import CacheView
+from .runtime import AHEAD_MAX_BATCH
 
 
 class DecodeBatch:
@@ -167,8 +168,15 @@ class DecodeGraph:
             try:
                 g = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
-                with torch.cuda.graph(g, capture_error_mode="relaxed"):
-                    self.logits = self.runner.model.forward(self.runner.rt, b)
+                rt = self.runner.rt
+                ahead = rt.dtype == torch.bfloat16 and self.S <= AHEAD_MAX_BATCH
+                rt.side = torch.cuda.Stream() if ahead else None
+                try:
+                    with torch.cuda.graph(g, capture_error_mode="relaxed"):
+                        self.logits = self.runner.model.forward(rt, b)
+                        rt.join()
+                finally:
+                    rt.side = None
                 self.kernels = ops.launch_count() - before
                 self.graph = g
             finally:

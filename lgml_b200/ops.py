@@ -259,6 +259,16 @@ def scale_cap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Te
     return x
 
 
+def l2_ahead(t: torch.Tensor, n_bytes: Optional[int] = None, keep: bool = True) -> None:
+    """Ask L2 for the first ``n_bytes`` of ``t`` (all of it when None); returns at once."""
+    if not t.is_contiguous():
+        raise KernelError("l2_ahead: tensor must be contiguous")
+    total = t.numel() * t.element_size()
+    n = total if n_bytes is None else min(int(n_bytes), total)
+    fn = _fn("elementwise", "lgml_l2_ahead", [c_void_p, c_longlong, c_int, c_void_p])
+    _check("elementwise", fn(_ptr(t), n, 1 if keep else 0, _stream()), "l2_ahead")
+
+
 def fill_normal(out: torch.Tensor, mean: float, sd: float, seed: int) -> torch.Tensor:
     """Seeded N(mean, sd^2) fill on the device."""
     _need(out, "tensor to fill")

@@ -23,7 +23,7 @@ Interfaces (tensors are torch tensors on the device; ``rt`` is the ``Runtime``):
                 float32); any other part calls ``store_kv`` when its own work is done
 * mixer:        ``cache_spec() -> PagedKV | FixedState | None``,
                 ``forward(rt, h, batch, cache) -> delta``  (h, delta: [tokens, width])
-* feed-forward: ``forward(rt, h) -> delta``
+* feed-forward: ``forward(rt, h) -> delta``; optionally ``first_weights() -> [tensor]``
 * block:        ``forward(rt, x, pending, batch, cache) -> (x, pending)`` where
                 ``pending`` is a delta not yet added to the residual stream x
 """
@@ -72,3 +72,8 @@ class Part:
 
     def bind(self, prefix: str, tensors: Dict[str, Any], rt) -> None:
         pass
+
+    def first_weights(self) -> List[Any]:
+        """The bound tensors this part reads first, in that order (a block may ask L2 for their
+        head while the part before it runs); none by default."""
+        return []

@@ -42,6 +42,10 @@ class PreNormBlock(Part):
     def forward(self, rt, x, pending, batch, cache):
         if self.mixer is not None:
             h = self.mixer_norm.forward(rt, x, rt.dtype, delta=pending)
+            if self.ffn is not None:
+                first = getattr(self.ffn, "first_weights", None)
+                if first is not None:
+                    rt.ahead(first())       # read after the mixer: L2 may fetch their head meanwhile
             pending = self.mixer.forward(rt, h, batch, cache)
         if self.ffn is not None:
             h = self.ffn_norm.forward(rt, x, rt.dtype, delta=pending)

@@ -45,6 +45,9 @@ class GatedMLP(Part):
             self.wgu = torch.cat([wg, wu], dim=0).contiguous()
             self.bgu = torch.cat([bg, bu], dim=0).contiguous() if self.bias else None
 
+    def first_weights(self):
+        return [self.wgu]
+
     def forward(self, rt, h):
         if self.paired and rt.fused_swiglu(h, self.wgu):
             act = ops.gemm_bf16_swiglu(h, self.wgu, self.bgu, rt.status)

@@ -114,6 +114,20 @@ def test_silu_mul(paired, dtype):
     assert torch.allclose(out.double().cpu(), want, **tol)
 
 
+def test_l2_ahead_touches_nothing_and_refuses_a_ragged_address():
+    from lgml_b200 import ops
+
+    w = torch.randn(3000, 1111, device=DEV).to(torch.bfloat16)      # a size that is no multiple of a chunk
+    before = w.clone()
+    for n in (None, 0, 15, 16, 40_000, w.numel() * 2 + 999):
+        ops.l2_ahead(w, n)
+        ops.l2_ahead(w, n, keep=False)
+    torch.cuda.synchronize()
+    assert torch.equal(w, before)
+    with pytest.raises(ops.KernelError, match="16-byte"):
+        ops.l2_ahead(w.view(-1)[1:], 64)
+
+
 def test_fill_normal_is_seeded():
     from lgml_b200 import ops
 
