@@ -167,6 +167,57 @@ def test_prefix_cache_changes_no_reply(folders):
     assert eng.scheduler.stats["prefix_tokens"] >= 128 * 2
 
 
+def test_replies_do_not_depend_on_the_schedule(folders):
+    """Seeded random workloads (prompts that share beginnings, a sampler of its own per prompt,
+    end tokens, reply limits) through engines that differ in slots, pool size, portion size, token
+    budget, prefix cache and launching ahead: in 32-bit every reply and every reason equals
+    those of one roomy engine that takes the prompts one at a time and waits for every step."""
+    import random
+
+    import lgml_b200
+
+    folder = folders[("B", "float32")]
+    V, maxpos = 320, 256
+    roomy = lgml_b200.Engine(str(folder), dtype="float32", slots=1, kv_tokens=64 * 8, run_ahead=False)
+    preemptions = from_cache = 0
+    for trial in range(8):
+        rng = random.Random(trial)
+        common = H.random_ids(rng.choice([64, 70, 128]), V, 5 + trial)
+        prompts = []
+        for i in range(rng.randint(3, 7)):
+            own = H.random_ids(rng.choice([1, 2, 30, 63, 64, 65, rng.randint(1, 120)]), V, 1000 * trial + i)
+            prompts.append((common[:rng.choice([len(common), 64, 10])] + own) if rng.random() < 0.6 else own)
+        per = []
+        for _ in prompts:
+            o = {"temperature": 0.0}
+            if rng.random() < 0.7:
+                o = {"temperature": rng.choice([0.5, 0.9, 1.3])}
+                if rng.random() < 0.5:
+                    o["top_k"] = rng.choice([1, 5, 40])
+                if rng.random() < 0.5:
+                    o["top_p"] = rng.choice([0.5, 0.9])
+                if rng.random() < 0.3:
+                    o["repeat_penalty"] = 1.2
+            per.append(o)
+        stop = [rng.randrange(V) for _ in range(rng.choice([0, 3, 20]))]
+        limit = rng.choice([5, 40, 60])
+        common_kw = dict(max_tokens=limit, stop=stop, seed=trial, per_prompt=per, return_details=True)
+        want = [(r.generated, r.finish_reason) for r in roomy.generate(prompts, **common_kw)]
+        for _ in range(2):
+            pages = -(-(max(len(p) for p in prompts) + limit) // 64) + rng.choice([0, 0, 1, 4])
+            ubatch = rng.choice([2, 7, 64, 512])
+            eng = lgml_b200.Engine(str(folder), dtype="float32", slots=rng.randint(1, 6), kv_tokens=64 * pages, ubatch=ubatch,
+                                   max_batch_tokens=max(ubatch, rng.choice([8, 64, 2048])), prefix_cache=rng.random() < 0.5,
+                                   run_ahead=rng.random() < 0.7)
+            got = [(r.generated, r.finish_reason) for r in eng.generate(prompts, **common_kw)]
+            assert got == want, (trial, pages, ubatch)
+            eng.runner.cache.check()
+            assert not eng.runner.cache.live and eng.runner.cache.n_free_pages == pages
+            preemptions += eng.scheduler.stats["preemptions"]
+            from_cache += eng.scheduler.stats.get("prefix_tokens", 0)
+    assert preemptions > 0 and from_cache > 0          # the hard paths were on the way
+
+
 @pytest.mark.parametrize("key", [("B", "float32"), ("B", "bfloat16")])
 def test_launching_ahead_of_the_host_changes_no_reply(folders, key):
     """Decode steps launched before the host has seen the ids of the step before: replies,
