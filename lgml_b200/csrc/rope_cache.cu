@@ -2,8 +2,8 @@
 // one pass over the projection's output.  q is rotated (in place, or into its own buffer);
 // k is rotated and stored; v is stored (lua/lgml/transformer.lua:1775, :1788 for the
 // rotation; :1838-1839 and :2405-2406 for set_rows into the pool; cell of position p =
-// table[p / page] * page + p % page, :1126-1133).  Angles are float32: pos * inv_freq[i],
-// then sincosf.  The input may also be the float32 partial sums of a projection that was cut
+// table[p / page] * page + p % page, :1126-1133).  Angles are formed in float32 arithmetic
+// without losing what a single float32 product would (rope_sincos).  The input may also be the float32 partial sums of a projection that was cut
 // along K: they are added in order (and the bias after them) as they are read.
 #include "common.cuh"
 
@@ -11,6 +11,23 @@ LGML_DEFINE_LAST_ERROR(lgml_rope_cache)
 
 namespace {
 constexpr int ITEMS = 256;   // work items (pairs of elements) per block
+
+// sin and cos of pos * (f + f_lo).  The product of a position in the thousands and a float32
+// frequency is thousands of radians, and rounding it to float32 would cost 1e-4 to 1e-3 of a
+// radian there.  So: the rounded product a, its exact error (one fma), the frequency's low
+// part (what float32 lost of the float64 table; 0 when the caller has none), and a taken
+// modulo 2 pi exactly (2 pi in three float32 pieces; the first difference is exact for
+// positions below 2^24) before the small terms are added.  All of it float32 operations.
+__device__ __forceinline__ void rope_sincos(int pos, float f, float f_lo, float *s, float *c) {
+    const float p = (float)pos;
+    const float a = __fmul_rn(p, f);
+    const float e = fmaf(p, f_lo, fmaf(p, f, -a));
+    const float k = rintf(a * 0x1.45f306p-3f);
+    float r = fmaf(-k, 0x1.921fb6p+2f, a);
+    r = fmaf(-k, -0x1.777a5cp-23f, r);
+    r = fmaf(-k, -0x1.ee59dap-48f, r);
+    sincosf(r + e, s, c);
+}
 
 // One work item = one pair of elements of one head of one token.
 //   heads 0 .. H-1: q, rotated, written to q_out;   H .. H+Hkv-1: k, rotated, to the cache;
@@ -22,7 +39,7 @@ template <typename TS, typename T>
 __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
     const TS *__restrict__ src, int lds, int n_parts, long long part_stride, const float *__restrict__ bias,
     T *__restrict__ q_out, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
-    const int *__restrict__ block_table, int max_blocks, const float *__restrict__ inv_freq, int n_rot, int pairing,
+    const int *__restrict__ block_table, int max_blocks, const float *__restrict__ inv_freq, const float *__restrict__ inv_freq_lo, int n_rot, int pairing,
     T *__restrict__ k_pages, T *__restrict__ v_pages, int n_pages, int page_size, int H, int Hkv, int D, int write_kv,
     int *__restrict__ status) {
     pdl_trigger();
@@ -75,7 +92,7 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
     }
     if (fi >= 0) {
         float s, c;
-        sincosf((float)pos * inv_freq[fi], &s, &c);
+        rope_sincos(pos, inv_freq[fi], inv_freq_lo ? inv_freq_lo[fi] : 0.f, &s, &c);
         const float r0 = a * c - b * s, r1 = a * s + b * c;
         a = r0;
         b = r1;
@@ -113,7 +130,7 @@ constexpr int WIDE_MAX_ROT = 512;
 __global__ void __launch_bounds__(WIDE_THREADS) rope_kv_write_wide_kernel(
     const __nv_bfloat16 *__restrict__ src, int lds, const float *__restrict__ bias, __nv_bfloat16 *__restrict__ q_out, int ldq,
     const int *__restrict__ positions, const int *__restrict__ seq_of_token, const int *__restrict__ block_table, int max_blocks,
-    const float *__restrict__ inv_freq, int n_rot, int pairing, __nv_bfloat16 *__restrict__ k_pages,
+    const float *__restrict__ inv_freq, const float *__restrict__ inv_freq_lo, int n_rot, int pairing, __nv_bfloat16 *__restrict__ k_pages,
     __nv_bfloat16 *__restrict__ v_pages, int n_pages, int page_size, int H, int Hkv, int D, int write_kv, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
@@ -123,7 +140,7 @@ __global__ void __launch_bounds__(WIDE_THREADS) rope_kv_write_wide_kernel(
     const int half_rot = n_rot / 2;
     for (int i = tid; i < half_rot; i += WIDE_THREADS) {
         float sn, c;
-        sincosf((float)pos * inv_freq[i], &sn, &c);
+        rope_sincos(pos, inv_freq[i], inv_freq_lo ? inv_freq_lo[i] : 0.f, &sn, &c);
         cs[i] = make_float2(c, sn);
     }
     // where this token's k and v go
@@ -225,12 +242,13 @@ inline bool wide_ok(const void *src, int lds, const void *q_out, int ldq, const 
 
 template <typename TS, typename T>
 int launch(const void *src, int lds, int n_parts, long long part_stride, const float *bias, void *q_out, int ldq, const int *positions,
-           const int *seq_of_token, const int *block_table, int max_blocks, const float *inv_freq, int n_rot, int pairing, void *k_pages,
-           void *v_pages, int n_pages, int page_size, int n_tokens, int H, int Hkv, int D, int write_kv, int *status, cudaStream_t stream) {
+           const int *seq_of_token, const int *block_table, int max_blocks, const float *inv_freq, const float *inv_freq_lo, int n_rot, int pairing,
+           void *k_pages, void *v_pages, int n_pages, int page_size, int n_tokens, int H, int Hkv, int D, int write_kv, int *status,
+           cudaStream_t stream) {
     const int items = (write_kv ? H + 2 * Hkv : H) * (D / 2);
     dim3 grid(n_tokens, (items + ITEMS - 1) / ITEMS);
     lgml_launch(rope_kv_write_kernel<TS, T>, grid, ITEMS, 0, stream, (const TS *)src, lds, n_parts, part_stride, bias, (T *)q_out, ldq, positions,
-                                                            seq_of_token, block_table, max_blocks, inv_freq, n_rot, pairing, (T *)k_pages,
+                                                            seq_of_token, block_table, max_blocks, inv_freq, inv_freq_lo, n_rot, pairing, (T *)k_pages,
                                                             (T *)v_pages, n_pages, page_size, H, Hkv, D, write_kv, status);
     return lgml_launch_status("rope_kv_write");
 }
@@ -239,10 +257,11 @@ int launch(const void *src, int lds, int n_parts, long long part_stride, const f
 // src: [n_parts][n_tokens][(H + 2 Hkv) D] of src_dtype (row stride lds, part_stride elements between
 // parts; n_parts > 1 only with float32).  q_out (dtype, row stride ldq) may be src itself when
 // n_parts == 1 and the types agree (rotation in place).  The cache has type `dtype`.
+// inv_freq: n_rot / 2 frequencies; inv_freq_lo: what float32 lost of each (table - (float)table), or null.
 LGML_API int lgml_rope_kv_write(const void *src, int src_dtype, int lds, int n_parts, long long part_stride, const float *bias,
                                 void *q_out, int dtype, int ldq, const int *positions, const int *seq_of_token,
-                                const int *block_table, int max_blocks, const float *inv_freq, int n_rot, int pairing,
-                                void *k_pages, void *v_pages, int n_pages, int page_size, int n_tokens, int H, int Hkv, int D,
+                                const int *block_table, int max_blocks, const float *inv_freq, const float *inv_freq_lo, int n_rot,
+                                int pairing, void *k_pages, void *v_pages, int n_pages, int page_size, int n_tokens, int H, int Hkv, int D,
                                 int write_kv, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && D > 0 && page_size > 0 && max_blocks > 0, "rope_kv_write: bad sizes");
     LGML_REQUIRE(D % 2 == 0, "rope_kv_write: head_dim %d must be even", D);
@@ -252,14 +271,14 @@ LGML_API int lgml_rope_kv_write(const void *src, int src_dtype, int lds, int n_p
     LGML_REQUIRE(pairing == 0 || pairing == 1, "rope_kv_write: unknown pairing %d", pairing);
     LGML_REQUIRE(n_parts >= 1 && (n_parts == 1 || src_dtype == LGML_F32), "rope_kv_write: partial sums are float32");
     if (n_tokens == 0) return 0;
-#define ARGS src, lds, n_parts, part_stride, bias, q_out, ldq, positions, seq_of_token, block_table, max_blocks, inv_freq, n_rot, pairing, \
+#define ARGS src, lds, n_parts, part_stride, bias, q_out, ldq, positions, seq_of_token, block_table, max_blocks, inv_freq, inv_freq_lo, n_rot, pairing, \
              k_pages, v_pages, n_pages, page_size, n_tokens, H, Hkv, D, write_kv, status, stream
     if (src_dtype == LGML_F32 && dtype == LGML_F32) return launch<float, float>(ARGS);
     if (src_dtype == LGML_F32 && dtype == LGML_BF16) return launch<float, __nv_bfloat16>(ARGS);
     if (src_dtype == LGML_BF16 && dtype == LGML_BF16) {
         if (n_parts == 1 && wide_ok(src, lds, q_out, ldq, k_pages, v_pages, n_rot, pairing, D, n_tokens)) {
             lgml_launch(rope_kv_write_wide_kernel, dim3(n_tokens), WIDE_THREADS, 0, stream, (const __nv_bfloat16 *)src, lds, bias,
-                        (__nv_bfloat16 *)q_out, ldq, positions, seq_of_token, block_table, max_blocks, inv_freq, n_rot, pairing,
+                        (__nv_bfloat16 *)q_out, ldq, positions, seq_of_token, block_table, max_blocks, inv_freq, inv_freq_lo, n_rot, pairing,
                         (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, n_pages, page_size, H, Hkv, D, write_kv, status);
             return lgml_launch_status("rope_kv_write");
         }

@@ -317,7 +317,9 @@ def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor, bloc
     their cells (``write_kv`` False: q only, for a layer that reads another layer's cache).
     ``qkv`` is [tokens, (H + 2 Hkv) D] in the cache's type (q is then rotated in place unless
     ``q_out`` is given), or ``Partials`` of a projection cut along K (``q_out`` is then made
-    if absent).  Returns the rotated q as [tokens, H D] (a view of qkv when in place)."""
+    if absent).  ``inv_freq``: float32 [n_rot / 2], or [2, n_rot / 2] with the part of each
+    frequency that float32 lost in the second row (angles at positions in the thousands are
+    then as exact as at the first ones).  Returns the rotated q as [tokens, H D] (a view of qkv when in place)."""
     _need(k_pages, "key pages", ndim=4)
     _need(v_pages, "value pages", k_pages.dtype, 4)
     cache_dt = k_pages.dtype
@@ -347,6 +349,11 @@ def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor, bloc
     _need(positions, "positions", torch.int32, 1)
     _need(seq_of_token, "request index of tokens", torch.int32, 1)
     _need(block_table, "block table", torch.int32, 2)
+    freq_lo = None
+    if inv_freq.dim() == 2:          # [2, n_rot / 2]: the frequencies, and what float32 lost of each
+        if inv_freq.shape[0] != 2 or not inv_freq.is_contiguous():
+            raise KernelError("rope_kv_write: frequencies with low parts are a contiguous [2, n_rot / 2]")
+        inv_freq, freq_lo = inv_freq[0], inv_freq[1]
     _need(inv_freq, "rotary frequencies", torch.float32, 1)
     if positions.numel() != n or seq_of_token.numel() != n or q_out.shape != (n, n_heads * head_dim):
         raise KernelError("rope_kv_write: one position, one request index and one q row per token")
@@ -358,10 +365,10 @@ def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor, bloc
     if n_rot % 2 or n_rot > head_dim or inv_freq.numel() < max(n_rot // 2, 1):
         raise KernelError(f"rope_kv_write: n_rot {n_rot} must be even, at most head_dim, and have n_rot / 2 frequencies")
     fn = _fn("rope_cache", "lgml_rope_kv_write", [c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                                   c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                    c_int, c_int, c_void_p, c_void_p])
     _check("rope_cache", fn(_ptr(src), dtype_code(src.dtype), lds, n_parts, stride, _ptr(bias), _ptr(q_out), dtype_code(cache_dt), ldq,
-                            _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), n_rot,
+                            _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(inv_freq), _ptr(freq_lo), n_rot,
                             PAIRING[pairing], _ptr(k_pages), _ptr(v_pages), n_pages, page, n, n_heads, n_kv_heads, head_dim,
                             1 if write_kv else 0, _ptr(status), _stream()), "rope_kv_write")
     return q_out

@@ -10,8 +10,9 @@ with i + n_rot/2, the order safetensors checkpoints hold; ``adjacent`` pairs 2i
 with 2i+1, the reference's "normal" mode for gguf rows (the two differ by the
 row permutation of ``lua/lgml/lora.lua:164-184``).
 
-The frequencies are computed in float64 and stored as float32; the kernel forms
-the angle in float32.
+The frequencies are computed in float64 and stored as two float32 numbers each (the
+rounded value and what the rounding lost); the kernel forms the angle from both in
+float32 arithmetic, so that a position in the thousands turns as exactly as the first.
 """
 from __future__ import annotations
 
@@ -112,7 +113,9 @@ class Rope(RotaryPosition):
         if given is not None:
             ff = [float(v) for v in given.double().cpu().tolist()]
         inv = [self.theta ** (-2.0 * i / self.n_rot) / ff[i] for i in range(half)]
-        self.inv_freq = torch.tensor(inv or [0.0], dtype=torch.float64).to(torch.float32).to(rt.device)
+        exact = torch.tensor(inv or [0.0], dtype=torch.float64)
+        hi = exact.to(torch.float32)
+        self.inv_freq = torch.stack([hi, (exact - hi.double()).to(torch.float32)]).to(rt.device)
 
 
 class NoPosition(RotaryPosition):

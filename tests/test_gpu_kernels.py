@@ -306,6 +306,42 @@ def test_rope_kv_write(dtype, pairing, n_rot, from_parts, lens):
     assert bool(torch.isnan(vc.permute(0, 2, 1, 3)[~written]).all())
 
 
+@pytest.mark.parametrize("lens", [[3, 2], [40, 2]])      # both kernels
+def test_rope_angles_at_far_positions(lens):
+    """Positions near 100,000 and near 2^24 - 1: with the float64 table's remainders beside the
+    float32 frequencies the rotation is right to a few float32 roundings; a single float32
+    product pos * frequency would be off by thousandths of a radian there (by a radian at 2^24)."""
+    from lgml_b200 import ops
+
+    torch.manual_seed(5)
+    H, G, D, page, n_rot = 3, 1, 32, 64, 32
+    pos0 = [99_990, (1 << 24) - 70]
+    n = sum(lens)
+    positions = torch.tensor([p + i for p, ln in zip(pos0, lens) for i in range(ln)], dtype=torch.int32)
+    seq_of = torch.tensor([s for s, ln in enumerate(lens) for _ in range(ln)], dtype=torch.int32)
+    width_tab = (1 << 24) // page
+    table = torch.zeros(2, width_tab, dtype=torch.int32)                # every block of both requests is page 0 or 1
+    table[1] = 1
+    exact = torch.tensor([500000.0 ** (-2.0 * i / n_rot) / (1.0 + 0.37 * i) for i in range(n_rot // 2)], dtype=torch.float64)
+    hi = exact.float()
+    both = torch.stack([hi, (exact - hi.double()).float()])
+    qkv = torch.randn(n, (H + 2 * G) * D).to(torch.bfloat16 if lens[0] > 32 else torch.float32)
+    want_q = ref_rope(qkv.double()[:, : H * D].reshape(n, H, D), positions, exact, "half", n_rot)
+    err = {}
+    for name, freq in (("with remainders", both), ("float32 alone", hi)):
+        st = status()
+        k_pages = torch.zeros((2, G, page, D), dtype=qkv.dtype, device=DEV)
+        q_out = torch.empty(n, H * D, dtype=qkv.dtype, device=DEV)
+        ops.rope_kv_write(qkv.to(DEV), positions.to(DEV), seq_of.to(DEV), table.to(DEV), freq.to(DEV), n_rot, "half", k_pages,
+                          torch.zeros_like(k_pages), H, G, D, st, q_out=q_out)
+        assert int(st.item()) == 0
+        err[name] = float((q_out.double().cpu().reshape(n, H, D) - want_q).abs().max())
+    if qkv.dtype == torch.float32:
+        assert err["with remainders"] < 5e-6 and err["float32 alone"] > 1e-3, err
+    else:
+        assert err["with remainders"] < 3e-2 and err["float32 alone"] > 1e-1, err     # bfloat16 rounds q itself to 2^-9
+
+
 # ---------------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------------

@@ -114,3 +114,46 @@ def test_long_decoding(tiny, dtype):
         steps.append({"step": p, "entries": [{"id": "x", "tokens": [ids[p]], "want": [0]}], "end": ["x"] if p == n - 1 else []})
     got = H.run_trace(runner, steps)
     H.compare_with_oracle(got, folder, {"x": ids}, **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_five_thousand_tokens_of_context(dtype, tmp_path):
+    """Positions in the thousands (rotation angles of thousands of radians in 32-bit, block
+    tables of 80 pages, key ranges cut for a long context): tiny-B with room for 16k positions,
+    one request of 5,000 tokens read in portions of up to 2,048 on pages another request
+    dirtied, its last 40 tokens one by one beside a second request's portions."""
+    cfg = dict(H.TINY_B, max_position_embeddings=16384)
+    folder = H.make_folder(tmp_path, cfg, 1, dtype=dtype, sharpen=SHARPEN[dtype])
+    n, V = 5000, cfg["vocab_size"]
+    ids, other, junk = H.random_ids(n, V, 42), H.random_ids(300, V, 43), H.random_ids(4000, V, 44)
+    from lgml_b200.engine.engine import parse_dtype
+    from lgml_b200.engine.runner import ModelRunner
+
+    runner = ModelRunner.from_folder(folder, parse_dtype(dtype), "cuda:0", n_pages=-(-n // 64) + 5, max_slots=2, max_step_tokens=2048)
+    steps = [{"step": 0, "entries": [{"id": "junk", "tokens": junk[:2048], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "junk", "tokens": junk[2048:], "want": []}], "end": ["junk"]}]
+    p = 0
+    for m in (2048, 1, 2047, 864):
+        steps.append({"step": len(steps), "entries": [{"id": "long", "tokens": ids[p:p + m], "want": sorted({0, m // 2, m - 1})}], "end": []})
+        p += m
+    q = 0
+    while p < n:
+        entries = [{"id": "long", "tokens": [ids[p]], "want": [0]}]
+        if q < len(other):
+            m = min(9, len(other) - q)
+            entries.append({"id": "other", "tokens": other[q:q + m], "want": [m - 1]})
+            q += m
+        p += 1
+        steps.append({"step": len(steps), "entries": entries, "end": ["long", "other"] if p == n else []})
+    assert q == len(other)
+    got = H.run_trace(runner, steps)
+    # only the rows that were asked for
+    for rid, seq in (("long", ids), ("other", other)):
+        ref = H.oracle_logits(folder, seq)
+        rows = [pos for (r, pos) in got if r == rid]
+        assert len(rows) >= 34
+        for pos in rows:
+            err = (got[(rid, pos)].double() - ref[pos]).abs()
+            bound = TOL[dtype]["atol"] + TOL[dtype]["rtol"] * ref[pos].abs()
+            assert bool((err <= bound).all()), (rid, pos, float(err.max()))
+    runner.cache.check()
