@@ -135,9 +135,9 @@ def test_long_context_then_decoding_across_a_page_edge():
 # the kernels of a full-size model against the plain implementation, as an engine
 # ---------------------------------------------------------------------------------------------
 
-def one_layer_model(shape, seed, n_pages):
+def one_layer_model(shape, seed, n_pages, dtype=torch.bfloat16):
     """One layer at a full model's layer sizes with a small vocabulary, filled on the device by
-    seed: (config dict, bfloat16 runner, the same tensors on the host as float64 for the plain
+    seed: (config dict, runner of ``dtype``, the same tensors on the host as float64 for the plain
     implementation).  The device's fill is the host generator bit for bit
     (``test_fill_normal_draws_the_host_generator_bit_for_bit``), so the plain implementation gets
     exactly the model the engine runs."""
@@ -151,13 +151,13 @@ def one_layer_model(shape, seed, n_pages):
 
     d = {**shape, "num_hidden_layers": 1, "vocab_size": 4096, "max_position_embeddings": 2048}
     cfg = config_from_dict(d)
-    rt = Runtime("cuda:0", torch.bfloat16)
+    rt = Runtime("cuda:0", dtype)
     model = build_model(cfg)
     tensors, host = {}, {}
     for s in model.tensor_specs():
         if s.optional:
             continue
-        t = torch.empty(s.shape, dtype=target_dtype(s.kind, torch.bfloat16), device=rt.device)
+        t = torch.empty(s.shape, dtype=target_dtype(s.kind, dtype), device=rt.device)
         ops.fill_normal(t, s.init[0], s.init[1] * 0.02, tensor_key(seed, s.name))
         tensors[s.name] = t
         host[s.name] = t.cpu().double()
@@ -165,14 +165,18 @@ def one_layer_model(shape, seed, n_pages):
     return d, ModelRunner(model, rt, n_pages=n_pages, max_slots=4, max_step_tokens=1024), host
 
 
-@pytest.mark.parametrize("shape,lens", [("8b", [600, 200, 130, 90, 300, 70]), ("13b", [560, 150, 100, 70, 200]), ("3b", [580, 170, 260, 66, 129])])
-def test_full_size_kernels_against_the_plain_implementation_under_the_hard_schedule(shape, lens):
+@pytest.mark.parametrize("shape,lens,dtype", [("8b", [600, 200, 130, 90, 300, 70], "bfloat16"), ("13b", [560, 150, 100, 70, 200], "bfloat16"),
+                                              ("3b", [580, 170, 260, 66, 129], "bfloat16"),
+                                              ("8b", [600, 200, 130, 90, 300, 70], "float32"), ("13b", [560, 150, 100, 70, 200], "float32")])
+def test_full_size_kernels_against_the_plain_implementation_under_the_hard_schedule(shape, lens, dtype):
     """Four live requests, portions beside decoded tokens, a first portion of over 512 tokens
     (pairs of CTAs in the products, the two-tile tcgen05 attention), the last tokens of every
     request one by one (the captured decode step), and a pool so small that pages are used
     again: bfloat16 against ``tests/plain/llama_plain.py`` in float64, not against the engine's
     own 32-bit path.  Bounds as above: the largest difference within 2 % of the logits' range,
-    the mean within 0.3 %.  That a wrong key would show is checked on the plain side: one
+    the mean within 0.3 %.  The 32-bit path runs the same schedule at the same sizes (sums of
+    4,096 to 14,336 float32 products in a fixed order): within 2e-5 of the range, 3e-6 in the
+    mean (measured: 6e-6 and 9e-7).  That a wrong key would show is checked on the plain side: one
     changed token in a request's first page moves its later rows by far more than the bound."""
     from tests import helpers as H
     from tests.plain import llama_plain as P
@@ -180,7 +184,8 @@ def test_full_size_kernels_against_the_plain_implementation_under_the_hard_sched
     total_pages = sum(-(-n // 64) for n in lens)
     n_pages = -(-max(lens) // 64) + 7
     assert n_pages < total_pages - 3
-    d, runner, host = one_layer_model(SHAPES[shape], 21, n_pages)
+    most, mean = (2e-2, 3e-3) if dtype == "bfloat16" else (2e-5, 3e-6)
+    d, runner, host = one_layer_model(SHAPES[shape], 21, n_pages, getattr(torch, dtype))
     seqs = {f"r{i}": H.random_ids(n, 4096, 500 + i) for i, n in enumerate(lens)}
     trace = H.trace_mixed(seqs, max_tokens=64 * n_pages, seed=3, choices=(1, 1, 2, 5, 17, 40, 90), tail=12, skip=0.1, first=530)
     assert max(len(st["entries"]) for st in trace) == 4
@@ -198,8 +203,8 @@ def test_full_size_kernels_against_the_plain_implementation_under_the_hard_sched
         scale = float(ref.abs().max())
         diff = (rows - ref).abs()
         where = int(diff.max(dim=1).values.argmax())
-        assert float(diff.max()) <= 2e-2 * scale, f"request {rid} position {where} (page {where // 64}, cell {where % 64}): {float(diff.max()):.3g} of {scale:.3g}"
-        assert float(diff.mean()) <= 3e-3 * scale, (rid, float(diff.mean()), scale)
+        assert float(diff.max()) <= most * scale, f"request {rid} position {where} (page {where // 64}, cell {where % 64}): {float(diff.max()):.3g} of {scale:.3g}"
+        assert float(diff.mean()) <= mean * scale, (rid, float(diff.mean()), scale)
         worst = max(worst, float(diff.max()) / scale)
         if rid == "r3":
             wrong = list(ids)
