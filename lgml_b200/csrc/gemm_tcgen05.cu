@@ -137,7 +137,6 @@ struct Params {
     void *out;        // y, or the float32 partial results
     const float *bias;        // per feature, or null (only when there is no split)
     int *status;
-    int skip_b;
 };
 
 // One thread's 16 consecutive features f0 .. f0 + 15 of token row a_row (tile row = token,
@@ -265,14 +264,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                 const int tile_a = first % p.tiles_a, tile_b = first / p.tiles_a;
                 for (int i = 0; i < pre; ++i) {
                     uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
-                    mbar_expect_tx(&full_bar[i], p.skip_b ? Smem<BN>::A_BYTES : Smem<BN>::STAGE_BYTES);
+                    mbar_expect_tx(&full_bar[i], Smem<BN>::STAGE_BYTES);
                     if (p.transposed) tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
                     else tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
                 }
                 pdl_wait();
                 for (int i = 0; i < pre; ++i) {
                     uint8_t *a_dst = tiles + (size_t)i * Smem<BN>::STAGE_BYTES;
-                    if (p.skip_b) continue;
                     if (p.transposed) tma_load_2d(a_dst + Smem<BN>::A_BYTES, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[i]);
                     else tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[i]);
                 }
@@ -289,9 +287,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                     }
                     uint8_t *a_dst = tiles + (size_t)s * Smem<BN>::STAGE_BYTES;
                     uint8_t *b_dst = a_dst + Smem<BN>::A_BYTES;
-                    mbar_expect_tx(&full_bar[s], p.skip_b ? Smem<BN>::A_BYTES : Smem<BN>::STAGE_BYTES);
+                    mbar_expect_tx(&full_bar[s], Smem<BN>::STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[s]);
-                    if (!p.skip_b) tma_load_2d(b_dst, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[s]);
+                    tma_load_2d(b_dst, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[s]);
                     issued = it + 1;
                 }
             }
@@ -863,7 +861,6 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
     p.bias = n_splits > 1 ? nullptr : bias;
     p.status = status;
     p.swiglu = swiglu;
-    p.skip_b = getenv("LGML_EXP_SKIPB") ? 1 : 0;
     CUtensorMap ma, mb;
     int rc;
     dim3 grid;
