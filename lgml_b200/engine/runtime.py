@@ -8,6 +8,7 @@ angles and logits stay float32.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -52,7 +53,7 @@ class Runtime:
         self.attention_backend = "auto"
         # Asking L2 for weights ahead of their reader: only inside a captured decode step of few
         # requests, which sets ``side`` (a stream beside the step's chain) for the capture.
-        self.ahead_bytes = AHEAD_BYTES
+        self.ahead_bytes = 0 if os.environ.get("LGML_L2_AHEAD") == "0" else AHEAD_BYTES
         self.side: Optional[torch.cuda.Stream] = None
         self._forked = False
 
