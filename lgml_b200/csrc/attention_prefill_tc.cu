@@ -178,7 +178,6 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int D,
     int hpc, float scale, int window, int *__restrict__ status) {
-    pdl_trigger();
     constexpr int KB = DP / 64;                       // 64-element blocks along the head dimension
     constexpr uint32_t Q_BYTES = KB * ROWS * 128;     // [KB][128 rows][128 B]
     constexpr uint32_t K_BYTES = KB * PAGE * 128;     // [KB][64 keys][128 B]      (K-major: row = key)
@@ -593,6 +592,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         }
     }
     tcgen05_fence_before();
+    pdl_trigger();      // at the end, as in the two-tile kernel: a CTA that fills its SM keeps the next kernel back until it is done
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();

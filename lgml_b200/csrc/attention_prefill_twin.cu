@@ -253,7 +253,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16 *__restrict__ q, int ldq,
     const int *__restrict__ positions, const int *__restrict__ tiles, const int *__restrict__ block_table, int max_blocks, int n_pages,
     __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int hpc, int tt, float scale, int window, int *__restrict__ status) {
-    pdl_trigger();
     constexpr int KB = D / 64;                              // 64-element blocks along the head dimension
     constexpr uint32_t TILE_BYTES = KB * ROWS * 128;        // the queries of one tile: [KB][128 rows][128 B]
     constexpr uint32_t PAGE_BYTES = KB * PAGE * 128;        // a page of keys [KB][64 keys][128 B] (K-major: row = key), or of values (N-major: 64 dims per row)
@@ -588,6 +587,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             mbar_arrive(&v_fixed);
         }
     }
+    // A CTA of this kernel fills its SM (shared and tensor memory).  It lets the next kernel's CTAs
+    // start only now, at its end: released at its start they would pile up behind it, each holding
+    // what the ones it waits for still need (see common.cuh).
+    pdl_trigger();
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {

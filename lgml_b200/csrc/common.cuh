@@ -44,6 +44,14 @@ static inline int lgml_launch_status(const char *what) {
 // earlier kernel wrote and before it writes anything at all; the wait returns when the
 // kernels before it have completed and their writes are visible.  Decoding is a chain of many
 // short kernels, and this overlaps each kernel's start-up with its predecessor's tail.
+// Where the trigger goes: a kernel whose CTAs leave room on their SM (the small kernels, the
+// products for few tokens) triggers at its start.  A kernel whose CTAs fill an SM (the products for
+// many tokens, alone or in pairs; the tcgen05 prompt attention with all of tensor memory) triggers
+// at its end.  Released at its start, the kernels behind it start too, each as soon as the one
+// ahead has started, and pile up: CTAs that hold shared and tensor memory while they wait for
+// kernels whose own CTAs are not all in yet.  Prompt steps hung that way on the GPU, rarely as the
+// kernels were and within a few hundred steps once a small kernel between two large ones did more
+// work before its wait; with the attribute off they never did.
 // LGML_PDL=0 in the environment turns the attribute off (the instructions are then no-ops).
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

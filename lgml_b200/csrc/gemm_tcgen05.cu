@@ -214,7 +214,10 @@ struct Smem {
 template <int BN, int STAGES, int NACC>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                   const __grid_constant__ CUtensorMap map_b, const Params p) {
-    pdl_trigger();   // the next kernel may start its own set-up and weight fetch
+    // Few tokens (two CTAs an SM): the next kernel may start its own set-up and weight fetch at once.
+    // A CTA that fills its SM triggers at its end instead (see common.cuh).
+    constexpr bool EARLY_TRIGGER = BN <= 64;
+    if (EARLY_TRIGGER) pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     // tiles want 1024-byte alignment for the 128-byte swizzle
     uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -403,6 +406,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
         }
     }
+    if (!EARLY_TRIGGER) pdl_trigger();
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -509,7 +513,6 @@ __device__ __forceinline__ uint32_t mapa_u32(const void *p, uint32_t rank) {
 template <int PAIR_BN, int STAGES, int PAIR_NACC>
 __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b, const Params p) {
-    pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *tiles = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[PAIR_NACC], acc_empty[PAIR_NACC];
@@ -683,6 +686,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
             else mbar_arrive_remote(&acc_empty[acc], 0);
         }
     }
+    pdl_trigger();      // at the end: a pair fills two SMs, the next kernel's CTAs start when it is done (see common.cuh)
     // nobody leaves, and no tensor memory is given back, while the other CTA may still arrive on
     // this one's barriers or the leader's products may still use this one's memory
     tcgen05_fence_before();
