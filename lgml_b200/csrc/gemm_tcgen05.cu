@@ -202,6 +202,39 @@ __device__ __forceinline__ void store_run(const Params &p, int a_row, int f0, co
     }
 }
 
+// The same for a tile whose rows are features and whose columns are tokens (the weights were the
+// tile's rows): one thread's feature a_row for the 16 tokens token0 .. token0 + 15, y[token][feature].
+// With the gated activation lanes 2i and 2i+1 hold the gate and the up row of feature a_row / 2.
+__device__ __forceinline__ void store_run_transposed(const Params &p, int a_row, int token0, const uint32_t (&r)[16], int lane, float *out_f,
+                                                     __nv_bfloat16 *out_h, bool f32) {
+    const bool row_ok = a_row < p.rows_a;
+    const float b = (p.bias && row_ok) ? p.bias[a_row] : 0.f;
+    if (p.swiglu) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float v = __uint_as_float(r[j]) + b;
+            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+            const int token = token0 + j;
+            if (row_ok && (lane & 1) == 0 && token < p.rows_b) {
+                const float act = v / (1.0f + expf(-v)) * up;
+                const size_t o = (size_t)token * p.ldo + (a_row >> 1);
+                if (f32) out_f[o] = act;
+                else out_h[o] = __float2bfloat16_rn(act);
+            }
+        }
+    } else if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int token = token0 + j;
+            if (token < p.rows_b) {
+                const float v = __uint_as_float(r[j]) + b;
+                if (f32) out_f[(size_t)token * p.ldo + a_row] = v;
+                else out_h[(size_t)token * p.ldo + a_row] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
 template <int BN>
 struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;
@@ -361,34 +394,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                 tcgen05_ld_16(lane_addr + acc_col + (uint32_t)c0, r);
                 tcgen05_wait_ld();
                 if (p.transposed) {
-                    // tile row = feature (a_row), tile column = token: y[token][feature]
-                    const bool row_ok = a_row < p.rows_a;
-                    const float b = (p.bias && row_ok) ? p.bias[a_row] : 0.f;
-                    if (p.swiglu) {
-                        // lanes 2i and 2i+1 hold the gate and the up row of feature a_row / 2
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float v = __uint_as_float(r[j]) + b;
-                            const float up = __shfl_xor_sync(0xffffffffu, v, 1);
-                            const int token = tile_b * BN + c0 + j;
-                            if (row_ok && (lane & 1) == 0 && token < p.rows_b) {
-                                const float act = v / (1.0f + expf(-v)) * up;
-                                const size_t o = (size_t)token * p.ldo + (a_row >> 1);
-                                if (f32) out_f[o] = act;
-                                else out_h[o] = __float2bfloat16_rn(act);
-                            }
-                        }
-                    } else if (row_ok) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int token = tile_b * BN + c0 + j;
-                            if (token < p.rows_b) {
-                                const float v = __uint_as_float(r[j]) + b;
-                                if (f32) out_f[(size_t)token * p.ldo + a_row] = v;
-                                else out_h[(size_t)token * p.ldo + a_row] = __float2bfloat16_rn(v);
-                            }
-                        }
-                    }
+                    store_run_transposed(p, a_row, tile_b * BN + c0, r, lane, out_f, out_h, f32);
                 } else {
                     store_run(p, a_row, tile_b * BN + c0, r, out_f, out_h, f32);
                 }
@@ -523,8 +529,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0: the leader, which issues the products
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int n_kb = (p.k_blocks + PAIR_KSUB - 1) / PAIR_KSUB;      // stages per tile
+    const int n_kb = (p.k_blocks + PAIR_KSUB - 1) / PAIR_KSUB;      // stages along all of K
     const int n_tiles = p.tiles_a * p.tiles_b;          // tiles of 256 x 256
+    // A pair's work is a list of units: unit u is tile u % n_tiles over K range u / n_tiles (stages
+    // [range * kb_per_split, ...)); one range unless the tiles alone would leave pairs idle.
+    const int per_range = p.kb_per_split;               // stages per K range
+    const int n_ranges = (n_kb + per_range - 1) / per_range;
+    const int n_units = n_tiles * n_ranges;
     constexpr int PAIR_HALF = PAIR_BN / 2, PAIR_B_BYTES = PAIR_HALF * BK * 2, PAIR_STAGE_BYTES = pair_stage_bytes(PAIR_BN);
     constexpr uint32_t ACC_COLS = PAIR_ACC_COLS;
     constexpr uint32_t TMEM_COLS = ACC_COLS * PAIR_NACC;
@@ -570,25 +581,32 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
 #pragma unroll
             for (int s = 0; s < STAGES; ++s) bar_of[s] = mapa_u32(&full_bar[s], 0);
             int q = 0;
+            int first_row[STAGES], first_kb[STAGES];     // where the activations of the first STAGES items lie
             bool waited = false, ok = true;
-            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            // the weights are B (tokens are the tile's rows), or A when the tile is y^T
+            const bool w_is_a = p.transposed != 0;
+            for (int unit = pair; unit < n_units && ok; unit += n_pairs) {
+                const int tile = unit % n_tiles, range = unit / n_tiles;
                 const int row_a = (tile % p.tiles_a) * 2 * BM + (int)rank * BM;
                 const int row_b = (tile / p.tiles_a) * PAIR_BN + (int)rank * PAIR_HALF;
-                for (int kb = 0; kb < n_kb; ++kb, ++q) {
+                const int kb_end = min(n_kb, (range + 1) * per_range);
+                for (int kb = range * per_range; kb < kb_end; ++kb, ++q) {
                     const int s = q % STAGES;
+                    if (q < STAGES) {
+                        first_row[q] = w_is_a ? row_b : row_a;
+                        first_kb[q] = kb;
+                    }
                     if (q == STAGES && !waited) {
                         // the activations of the first STAGES items, whose weights are under way
                         pdl_wait();
                         waited = true;
-                        int t2 = pair, k2 = 0;
+#pragma unroll
                         for (int q2 = 0; q2 < STAGES; ++q2) {
 #pragma unroll
-                            for (int u = 0; u < PAIR_KSUB; ++u)
-                                tma_load_2d_pair(tiles + (size_t)q2 * PAIR_STAGE_BYTES + u * PAIR_A_BYTES, &map_a, (k2 * PAIR_KSUB + u) * BK,
-                                                 (t2 % p.tiles_a) * 2 * BM + (int)rank * BM, bar_of[q2]);
-                            if (++k2 == n_kb) {
-                                k2 = 0;
-                                t2 += n_pairs;
+                            for (int u = 0; u < PAIR_KSUB; ++u) {
+                                uint8_t *st = tiles + (size_t)q2 * PAIR_STAGE_BYTES;
+                                if (w_is_a) tma_load_2d_pair(st + PAIR_KSUB * PAIR_A_BYTES + u * PAIR_B_BYTES, &map_b, (first_kb[q2] * PAIR_KSUB + u) * BK, first_row[q2], bar_of[q2]);
+                                else tma_load_2d_pair(st + u * PAIR_A_BYTES, &map_a, (first_kb[q2] * PAIR_KSUB + u) * BK, first_row[q2], bar_of[q2]);
                             }
                         }
                     }
@@ -600,23 +618,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
                     if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);
 #pragma unroll
                     for (int u = 0; u < PAIR_KSUB; ++u) {
-                        if (waited) tma_load_2d_pair(a_dst + u * PAIR_A_BYTES, &map_a, (kb * PAIR_KSUB + u) * BK, row_a, bar_of[s]);
-                        tma_load_2d_pair(a_dst + PAIR_KSUB * PAIR_A_BYTES + u * PAIR_B_BYTES, &map_b, (kb * PAIR_KSUB + u) * BK, row_b, bar_of[s]);
+                        if (waited || w_is_a) tma_load_2d_pair(a_dst + u * PAIR_A_BYTES, &map_a, (kb * PAIR_KSUB + u) * BK, row_a, bar_of[s]);
+                        if (waited || !w_is_a) tma_load_2d_pair(a_dst + PAIR_KSUB * PAIR_A_BYTES + u * PAIR_B_BYTES, &map_b, (kb * PAIR_KSUB + u) * BK, row_b, bar_of[s]);
                     }
                 }
             }
             if (!waited) {
                 // fewer items than stages: their activations are still to come
                 pdl_wait();
-                int t2 = pair, k2 = 0;
-                for (int q2 = 0; q2 < q; ++q2) {
 #pragma unroll
-                    for (int u = 0; u < PAIR_KSUB; ++u)
-                        tma_load_2d_pair(tiles + (size_t)q2 * PAIR_STAGE_BYTES + u * PAIR_A_BYTES, &map_a, (k2 * PAIR_KSUB + u) * BK,
-                                         (t2 % p.tiles_a) * 2 * BM + (int)rank * BM, bar_of[q2]);
-                    if (++k2 == n_kb) {
-                        k2 = 0;
-                        t2 += n_pairs;
+                for (int q2 = 0; q2 < STAGES; ++q2) {
+                    if (q2 < q) {
+#pragma unroll
+                        for (int u = 0; u < PAIR_KSUB; ++u) {
+                            uint8_t *st = tiles + (size_t)q2 * PAIR_STAGE_BYTES;
+                            if (w_is_a) tma_load_2d_pair(st + PAIR_KSUB * PAIR_A_BYTES + u * PAIR_B_BYTES, &map_b, (first_kb[q2] * PAIR_KSUB + u) * BK, first_row[q2], bar_of[q2]);
+                            else tma_load_2d_pair(st + u * PAIR_A_BYTES, &map_a, (first_kb[q2] * PAIR_KSUB + u) * BK, first_row[q2], bar_of[q2]);
+                        }
                     }
                 }
             }
@@ -630,12 +648,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
             constexpr uint32_t idesc = make_idesc(2 * BM, PAIR_BN);
             bool ok = true;
             int it = 0, j = 0;
-            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++j) {
+            for (int unit = pair; unit < n_units && ok; unit += n_pairs, ++j) {
                 const int acc = j % PAIR_NACC;
                 if (j >= PAIR_NACC && !mbar_wait_cluster(&acc_empty[acc], ((j / PAIR_NACC) - 1) & 1, abort_flag, p.status)) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)acc * ACC_COLS;
-                for (int i = 0; i < n_kb; ++i, ++it) {
+                const int range = unit / n_tiles;
+                const int stages_here = min(n_kb, (range + 1) * per_range) - range * per_range;
+                for (int i = 0; i < stages_here; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag, p.status);
                     if (!ok) break;
@@ -660,11 +680,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        float *out_f = (float *)p.out;
         __nv_bfloat16 *out_h = (__nv_bfloat16 *)p.out;
-        const bool f32 = p.out_f32 != 0;
+        const bool f32 = p.out_f32 != 0 || p.split_stride != 0;      // the partial sums of K ranges are float32
         int j = 0;
-        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
+        for (int unit = pair; unit < n_units; unit += n_pairs, ++j) {
+            const int tile = unit % n_tiles;
+            float *out_f = (float *)p.out + (size_t)(unit / n_tiles) * p.split_stride;
             const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
             const int acc = j % PAIR_NACC;
             const uint32_t acc_col = (uint32_t)acc * ACC_COLS;
@@ -674,10 +695,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
             if (ok) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
+                    if (p.transposed && tile_b * PAIR_BN + c0 >= p.rows_b) break;      // columns past the last token
                     uint32_t r[16];
                     tcgen05_ld_16(lane_addr + acc_col + (uint32_t)c0, r);
                     tcgen05_wait_ld();
-                    store_run(p, a_row, tile_b * PAIR_BN + c0, r, out_f, out_h, f32);
+                    if (p.transposed) store_run_transposed(p, a_row, tile_b * PAIR_BN + c0, r, lane, out_f, out_h, f32);
+                    else store_run(p, a_row, tile_b * PAIR_BN + c0, r, out_f, out_h, f32);
                 }
             }
             // this thread has read its part of the accumulator: tell the leader's MMA warp
@@ -801,6 +824,37 @@ int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, i
     return lgml_launch_status("gemm_tcgen05 pairs");
 }
 
+// From this many tokens on a product runs on pairs of CTAs.  (Up to 64 the weights are the tile's
+// rows and the tokens its columns, two CTAs an SM: gate/up product alone at 64 tokens 45 us.  Beyond,
+// that shape reads the activations again for every 128 rows of weights and needs a second round
+// for a third of its tiles: 71 us at 96 tokens, 112 at 256, where pairs take 60 to 63.)
+constexpr int PAIR_MIN_TOKENS = 65;
+// Up to this many tokens the pairs' tiles are y^T as well (256 rows of weights, the tokens as the
+// tile's 128 columns): with the tokens as rows half of a 256-row tile would be padding, and the
+// products of a tile, which bound a pair, twice what they have to be.
+constexpr int PAIR_SWAP_TOKENS = 128;
+
+// How a product of M tokens runs on pairs: y^T or not, the tile's width, and how many tiles.
+struct PairPlan {
+    bool swapped;
+    int pbn, tiles_a, tiles_b;
+};
+int pair_tile_width(int M, int N);
+inline PairPlan pair_plan(int M, int N) {
+    PairPlan pl;
+    pl.swapped = M <= PAIR_SWAP_TOKENS;
+    if (pl.swapped) {
+        pl.pbn = 128;
+        pl.tiles_a = (N + 2 * BM - 1) / (2 * BM);
+        pl.tiles_b = (M + pl.pbn - 1) / pl.pbn;
+    } else {
+        pl.pbn = pair_tile_width(M, N);
+        pl.tiles_a = (M + 2 * BM - 1) / (2 * BM);
+        pl.tiles_b = (N + pl.pbn - 1) / pl.pbn;
+    }
+    return pl;
+}
+
 // The width of the pairs' tiles for an M x N product: 256 unless a narrower tile fills the 74
 // pairs better (few tokens: 512 x 4096 is 32 tiles of 256 columns but 64 of 128).  The cost of a
 // tile is taken as its width plus a fixed part; a narrower tile must win by more than 5 %.
@@ -831,6 +885,22 @@ bool pairs_enabled() {
 }
 
 }  // namespace
+
+// K ranges that a product of M tokens should be cut into when it runs on pairs of CTAs (0: it does
+// not run on pairs): as many as fill the 74 pairs once over, each of at least four stages of 128
+// elements, at most eight (every range writes, and the next kernel reads, M x N float32 partial sums).
+LGML_API int lgml_gemm_tcgen05_pair_ranges(int M, int N, int K) {
+    if (M < PAIR_MIN_TOKENS || !pairs_enabled() || N <= 0 || K <= 0) return 0;
+    const PairPlan pl = pair_plan(M, N);
+    const long long tiles = (long long)pl.tiles_a * pl.tiles_b;
+    const int stages = ((K + BK - 1) / BK + PAIR_KSUB - 1) / PAIR_KSUB;
+    long long want = 74 / (tiles > 0 ? tiles : 1);
+    if (want > stages / 4) want = stages / 4;
+    if (want > 8) want = 8;
+    if (want < 2) return 1;
+    const int per = (int)((stages + want - 1) / want);
+    return (stages + per - 1) / per;
+}
 
 // Floats of scratch that `n_splits` > 1 needs.
 LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) {
@@ -868,7 +938,8 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
     CUtensorMap ma, mb;
     int rc;
     dim3 grid;
-    const bool swap = M <= 256;
+    const bool pair_path = M >= PAIR_MIN_TOKENS && pairs_enabled();
+    const bool swap = M <= 256 && !pair_path;
     int bn;
     if (swap) {
         bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
@@ -880,21 +951,37 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         p.tiles_a = (N + BM - 1) / BM;
         p.tiles_b = 1;
         grid = dim3(p.tiles_a, 1, n_splits);
-    } else if (n_splits == 1 && M >= 512 && pairs_enabled()) {
-        // many tokens: pairs of CTAs on 256 x 256 tiles, tile_a fastest
-        p.transposed = 0;
-        p.rows_a = M;
-        p.rows_b = N;
-        p.kb_per_split = k_blocks;
-        const int pbn = pair_tile_width(M, N);
-        if ((rc = make_map(&ma, x, M, K, ldx, BM))) return rc;
-        if ((rc = make_map(&mb, w, N, K, ldw, pbn / 2))) return rc;
-        p.tiles_a = (M + 2 * BM - 1) / (2 * BM);
-        p.tiles_b = (N + pbn - 1) / pbn;
+    } else if (pair_path) {
+        // more than 64 tokens: pairs of CTAs on 256 x 256 tiles, tile_a fastest; K in n_splits ranges of
+        // whole stages (128 elements) where the tiles alone would leave pairs idle
+        const int stages = (k_blocks + PAIR_KSUB - 1) / PAIR_KSUB;
+        p.kb_per_split = (stages + n_splits - 1) / n_splits;
+        LGML_REQUIRE((n_splits - 1) * p.kb_per_split < stages, "gemm_tcgen05: %d K ranges of %d stages leave one empty (K = %d)", n_splits,
+                     p.kb_per_split, K);
+        const PairPlan pl = pair_plan(M, N);
+        const int pbn = pl.pbn;
+        if (pl.swapped) {
+            // the tile is y^T: its rows are features (each CTA of a pair 128 of them), its columns the tokens
+            p.transposed = 1;
+            p.rows_a = N;
+            p.rows_b = M;
+            if ((rc = make_map(&ma, w, N, K, ldw, BM))) return rc;
+            if ((rc = make_map(&mb, x, M, K, ldx, pbn / 2))) return rc;
+        } else {
+            p.transposed = 0;
+            p.rows_a = M;
+            p.rows_b = N;
+            if ((rc = make_map(&ma, x, M, K, ldx, BM))) return rc;
+            if ((rc = make_map(&mb, w, N, K, ldw, pbn / 2))) return rc;
+        }
+        p.tiles_a = pl.tiles_a;
+        p.tiles_b = pl.tiles_b;
         const int n_tiles = p.tiles_a * p.tiles_b;
-        if (pbn == 128) return launch_pair<128, 4, 2>(ma, mb, p, n_tiles, stream);
-        if (pbn == 192) return launch_pair<192, 4, 2>(ma, mb, p, n_tiles, stream);
-        return launch_pair<256, 3, 2>(ma, mb, p, n_tiles, stream);
+        const int n_units = n_tiles * n_splits;
+        if (pbn == 128) rc = launch_pair<128, 4, 2>(ma, mb, p, n_units, stream);
+        else if (pbn == 192) rc = launch_pair<192, 4, 2>(ma, mb, p, n_units, stream);
+        else rc = launch_pair<256, 3, 2>(ma, mb, p, n_units, stream);
+        bn = 0;      // launched
     } else {
         bn = 256;
         p.transposed = 0;
@@ -909,8 +996,9 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         const int n_tiles = p.tiles_a * p.tiles_b;
         grid = dim3(n_tiles < 148 ? n_tiles : 148, 1, n_splits);
     }
-    LGML_REQUIRE(grid.z <= 65535, "gemm_tcgen05: grid too large");
+    LGML_REQUIRE(bn == 0 || grid.z <= 65535, "gemm_tcgen05: grid too large");
     switch (bn) {
+        case 0: break;
         case 16: rc = launch<16, 6, 1>(ma, mb, p, grid, stream); break;
         case 32: rc = launch<32, 5, 1>(ma, mb, p, grid, stream); break;
         case 64: rc = launch<64, 4, 1>(ma, mb, p, grid, stream); break;

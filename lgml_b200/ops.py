@@ -513,6 +513,12 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
     which with many tokens is no longer small beside the weights; at 64 tokens nine ranges of
     the output projection still win 0.9 us over five and cost the norm behind them 0.6), each
     with at least four 64-wide K blocks."""
+    if M > 64:
+        fn = getattr(csrc.load("gemm_tcgen05"), "lgml_gemm_tcgen05_pair_ranges")
+        fn.argtypes, fn.restype = [c_int, c_int, c_int], c_int
+        ranges = fn(M, N, K)
+        if ranges:          # on pairs of CTAs: the kernel library knows how it would cut K
+            return ranges
     if M > 256:
         return 1
     tiles = -(-N // 128)
@@ -544,6 +550,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
             raise KernelError("gemm_tcgen05: bias length is not N")
     if n_splits is None:
         n_splits = 1 if swiglu else tcgen05_splits(M, N, K)
+    elif M > 64 and n_splits > 1 and tcgen05_splits(M, N, K) and os.environ.get("LGML_GEMM_PAIR") != "0":
+        # on pairs of CTAs a K range is a whole number of 128-element stages, and none may be empty
+        stages = -(-K // 128)
+        n_splits = -(-stages // -(-stages // min(n_splits, stages)))
     n_splits = max(1, min(n_splits, -(-K // 64)))
     if swiglu and n_splits != 1:
         raise KernelError("gemm_tcgen05: the gated epilogue takes no K split")

@@ -186,6 +186,8 @@ def test_gemm_f32_is_exact_and_batch_invariant(M, N, K):
     (512, 256, 64, False, False, None), (777, 1000, 328, True, True, None), (1500, 40 * 256 + 8, 136, True, False, None),
     # narrower tiles where 256 columns would leave pairs idle: 192 (512 x 6144: 64 tiles) and 128 (512 x 4096)
     (512, 6144 - 16, 200, True, False, None), (500, 4000, 136, False, True, None),
+    # 65 to 511 rows on pairs too; few tiles: K in ranges of whole 128-element stages, summed by the reduce kernel
+    (65, 256, 2048 + 8, True, False, None), (128, 520, 3000, False, True, None), (200, 384, 1096, True, True, 3), (300, 256, 640, False, False, 5),
 ])
 def test_gemm_tcgen05(M, N, K, bias, f32, splits):
     from lgml_b200 import ops
@@ -209,7 +211,7 @@ def test_gemm_tcgen05_gated_epilogue_and_partials():
 
     torch.manual_seed(5)
     st = status()
-    for M, F, K in [(6, 100, 96), (300, 176, 120), (640, 300, 200)]:
+    for M, F, K in [(6, 100, 96), (100, 331, 264), (128, 260, 1096), (300, 176, 120), (640, 300, 200)]:
         x = torch.randn(M, K).to(torch.bfloat16)
         wg, wu = (torch.randn(F, K) * 0.1).to(torch.bfloat16), (torch.randn(F, K) * 0.1).to(torch.bfloat16)
         bg, bu = torch.randn(F), torch.randn(F)
@@ -225,6 +227,14 @@ def test_gemm_tcgen05_gated_epilogue_and_partials():
     b = torch.randn(200)
     pr = ops.gemm_tcgen05(x.to(DEV), w.to(DEV), None, b.to(DEV), st, n_splits=3, partials_ok=True)
     assert isinstance(pr, ops.Partials) and pr.data.shape == (3, 9, 200)
+    want = x.double() @ w.double().t() + b.double()
+    assert float((pr.sum().double().cpu() - want).abs().max()) <= 5e-5 * float(want.abs().max())
+    # the same from pairs of CTAs (more than 64 tokens): the K ranges the kernel library chooses
+    x = torch.randn(130, 4096 + 64).to(torch.bfloat16)
+    w = (torch.randn(300, 4096 + 64) * 0.1).to(torch.bfloat16)
+    b = torch.randn(300)
+    pr = ops.gemm_tcgen05(x.to(DEV), w.to(DEV), None, b.to(DEV), st, partials_ok=True)
+    assert isinstance(pr, ops.Partials) and pr.data.shape[0] == ops.tcgen05_splits(130, 300, 4096 + 64) > 1
     want = x.double() @ w.double().t() + b.double()
     assert float((pr.sum().double().cpu() - want).abs().max()) <= 5e-5 * float(want.abs().max())
     assert int(st.item()) == 0
