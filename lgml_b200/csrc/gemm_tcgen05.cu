@@ -516,7 +516,7 @@ __device__ __forceinline__ uint32_t mapa_u32(const void *p, uint32_t rank) {
     return ra;
 }
 
-template <int PAIR_BN, int STAGES, int PAIR_NACC>
+template <int PAIR_BN, int STAGES, int PAIR_NACC, bool YT>      // YT: the tile is y^T (the weights are its rows)
 __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b, const Params p) {
     extern __shared__ uint8_t smem_raw[];
@@ -584,7 +584,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
             int first_row[STAGES], first_kb[STAGES];     // where the activations of the first STAGES items lie
             bool waited = false, ok = true;
             // the weights are B (tokens are the tile's rows), or A when the tile is y^T
-            const bool w_is_a = p.transposed != 0;
+            constexpr bool w_is_a = YT;
             for (int unit = pair; unit < n_units && ok; unit += n_pairs) {
                 const int tile = unit % n_tiles, range = unit / n_tiles;
                 const int row_a = (tile % p.tiles_a) * 2 * BM + (int)rank * BM;
@@ -695,11 +695,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_pair_kernel(const __grid_cons
             if (ok) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < PAIR_BN; c0 += 16) {
-                    if (p.transposed && tile_b * PAIR_BN + c0 >= p.rows_b) break;      // columns past the last token
+                    if (YT && tile_b * PAIR_BN + c0 >= p.rows_b) break;      // columns past the last token
                     uint32_t r[16];
                     tcgen05_ld_16(lane_addr + acc_col + (uint32_t)c0, r);
                     tcgen05_wait_ld();
-                    if (p.transposed) store_run_transposed(p, a_row, tile_b * PAIR_BN + c0, r, lane, out_f, out_h, f32);
+                    if constexpr (YT) store_run_transposed(p, a_row, tile_b * PAIR_BN + c0, r, lane, out_f, out_h, f32);
                     else store_run(p, a_row, tile_b * PAIR_BN + c0, r, out_f, out_h, f32);
                 }
             }
@@ -784,7 +784,7 @@ int launch(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, dim3 g
 // How many pairs of CTAs the device runs at one time (pairs need both SMs of a TPC, and not
 // every TPC of a part has two): the persistent grid is this many pairs, never more, or the
 // rest would wait for a second round.  0 if the query fails.
-template <int PBN, int STAGES, int NACC>
+template <int PBN, int STAGES, int NACC, bool YT>
 int pairs_at_once(size_t smem) {
     static int n = -1;
     if (n < 0) {
@@ -800,26 +800,26 @@ int pairs_at_once(size_t smem) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<PBN, STAGES, NACC>, &cfg);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<PBN, STAGES, NACC, YT>, &cfg);
         n = (e == cudaSuccess && clusters > 0) ? clusters : 0;
         if (e != cudaSuccess) cudaGetLastError();
     }
     return n;
 }
 
-template <int PBN, int STAGES, int NACC>
+template <int PBN, int STAGES, int NACC, bool YT>
 int launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const Params &p, int n_tiles, cudaStream_t stream) {
     const size_t smem = (size_t)STAGES * pair_stage_bytes(PBN) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<PBN, STAGES, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<PBN, STAGES, NACC, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    const int at_once = pairs_at_once<PBN, STAGES, NACC>(smem);
+    const int at_once = pairs_at_once<PBN, STAGES, NACC, YT>(smem);
     if (at_once <= 0) LGML_FAIL("gemm_tcgen05: the device runs no pair of CTAs of this kernel");
     const int n_pairs = n_tiles < at_once ? n_tiles : at_once;
-    cudaError_t e = lgml_launch_cluster(gemm_pair_kernel<PBN, STAGES, NACC>, dim3(2 * n_pairs), dim3(THREADS), smem, stream, 2, ma, mb, p);
+    cudaError_t e = lgml_launch_cluster(gemm_pair_kernel<PBN, STAGES, NACC, YT>, dim3(2 * n_pairs), dim3(THREADS), smem, stream, 2, ma, mb, p);
     if (e != cudaSuccess) LGML_FAIL("gemm_tcgen05: launch of CTA pairs failed: %s", cudaGetErrorString(e));
     return lgml_launch_status("gemm_tcgen05 pairs");
 }
@@ -978,9 +978,10 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         p.tiles_b = pl.tiles_b;
         const int n_tiles = p.tiles_a * p.tiles_b;
         const int n_units = n_tiles * n_splits;
-        if (pbn == 128) rc = launch_pair<128, 4, 2>(ma, mb, p, n_units, stream);
-        else if (pbn == 192) rc = launch_pair<192, 4, 2>(ma, mb, p, n_units, stream);
-        else rc = launch_pair<256, 3, 2>(ma, mb, p, n_units, stream);
+        if (pl.swapped) rc = launch_pair<128, 4, 2, true>(ma, mb, p, n_units, stream);
+        else if (pbn == 128) rc = launch_pair<128, 4, 2, false>(ma, mb, p, n_units, stream);
+        else if (pbn == 192) rc = launch_pair<192, 4, 2, false>(ma, mb, p, n_units, stream);
+        else rc = launch_pair<256, 3, 2, false>(ma, mb, p, n_units, stream);
         bn = 0;      // launched
     } else {
         bn = 256;

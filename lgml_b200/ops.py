@@ -514,11 +514,12 @@ def tcgen05_splits(M: int, N: int, K: int) -> int:
     the output projection still win 0.9 us over five and cost the norm behind them 0.6), each
     with at least four 64-wide K blocks."""
     if M > 64:
-        fn = getattr(csrc.load("gemm_tcgen05"), "lgml_gemm_tcgen05_pair_ranges")
-        fn.argtypes, fn.restype = [c_int, c_int, c_int], c_int
-        ranges = fn(M, N, K)
-        if ranges:          # on pairs of CTAs: the kernel library knows how it would cut K
-            return ranges
+        fn = getattr(csrc.load("gemm_tcgen05"), "lgml_gemm_tcgen05_pair_ranges", None)
+        if fn is not None:
+            fn.argtypes, fn.restype = [c_int, c_int, c_int], c_int
+            ranges = fn(M, N, K)
+            if ranges:          # on pairs of CTAs: the kernel library knows how it would cut K
+                return ranges
     if M > 256:
         return 1
     tiles = -(-N // 128)
