@@ -105,18 +105,22 @@ def test_registry_takes_a_new_architecture():
 
 
 def test_k_ranges_of_a_small_product_are_never_empty():
-    """The number of K ranges a product with few tokens is cut into: every range gets at least
-    one block of 64 (9 ranges of 8 blocks would leave the ninth of 64 blocks empty)."""
+    """The number of K ranges a product is cut into: every range gets at least one block (9 ranges
+    of 8 blocks would leave the ninth of 64 blocks empty).  A block is 64 elements up to 64 tokens
+    and a stage of 128 from 65 tokens on, where the product runs on pairs of CTAs; many tokens
+    and many tiles leave K whole."""
     from lgml_b200.ops import tcgen05_splits
 
-    for M in (1, 8, 16, 17, 64, 200, 256, 300):
+    for M in (1, 8, 16, 17, 64, 65, 128, 200, 256, 300, 2048):
         for N in (1024, 3072, 4096, 5120, 6144, 9216, 14336, 28672, 128256):
             for K in (64, 512, 3072, 4096, 5120, 8192, 13824, 14336):
                 s = tcgen05_splits(M, N, K)
-                k_blocks = -(-K // 64)
-                per = -(-k_blocks // s)
-                assert 1 <= s <= 16 and (s - 1) * per < k_blocks, (M, N, K, s)
-                if M > 256:
+                blocks = -(-K // (64 if M <= 64 else 128))
+                per = -(-blocks // s)
+                assert 1 <= s <= (16 if M <= 64 else 8) and (s - 1) * per < blocks, (M, N, K, s)
+                if M > 64 and s > 1:
+                    assert per >= 4                         # no range shorter than four stages
+                if M >= 2048 and N >= 3072:
                     assert s == 1
 
 
