@@ -218,6 +218,25 @@ def test_replies_do_not_depend_on_the_schedule(folders):
     assert preemptions > 0 and from_cache > 0          # the hard paths were on the way
 
 
+@pytest.mark.parametrize("n_requests", [100, 150])
+def test_a_hundred_requests_at_once(folders, n_requests):
+    """Decode steps of 100 and 150 tokens (the products on pairs of CTAs: the y^T tile up to 128
+    tokens, tokens as rows beyond; captured steps of the next larger size on the ladder with their
+    spare rows): in 32-bit every reply equals the reply of the same prompt alone."""
+    import lgml_b200
+
+    folder = folders[("B", "float32")]
+    prompts = [H.random_ids(5 + (i * 7) % 40, 320, 100 + i) for i in range(n_requests)]
+    alone = lgml_b200.Engine(str(folder), dtype="float32", slots=1, kv_tokens=64 * 4, run_ahead=False)
+    want = alone.generate(prompts, max_tokens=10, temperature=0.0, stop=[])
+    many = lgml_b200.Engine(str(folder), dtype="float32", slots=n_requests, kv_tokens=64 * (n_requests + 8), max_batch_tokens=4096)
+    got = many.generate(prompts, max_tokens=10, temperature=0.0, stop=[])
+    assert got == want
+    assert max(t["decode"] for t in many.turn_log) == n_requests and many.runner.graph_replays > 0
+    many.runner.cache.check()
+    assert not many.runner.cache.live
+
+
 @pytest.mark.parametrize("key", [("B", "float32"), ("B", "bfloat16")])
 def test_launching_ahead_of_the_host_changes_no_reply(folders, key):
     """Decode steps launched before the host has seen the ids of the step before: replies,
