@@ -316,6 +316,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--shape", default="llama31_8b", choices=list(SHAPES), help="layer sizes and workload (the default is the headline's)")
     ap.add_argument("--decode-only", action="store_true", help="with --shape llama32_3b: plain decode steps at batch 32 instead of its mixed workload")
+    ap.add_argument("--batch", type=int, default=0, help="batch of the decode run instead of the shape's own")
     ap.add_argument("--prompt-len", type=int, default=0, help="prompt length of the decode runs instead of the shape's own (for other context lengths)")
     ap.add_argument("--context", type=int, default=0, help="context (tokens a request may hold) instead of the shape's own")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="tokens of the timed prompt instead of 2,048 (read in portions of 2,048)")
@@ -345,13 +346,18 @@ def main() -> int:
     global BATCH, PROMPT_LEN, CONTEXT
     shape_name, shape, BATCH, PROMPT_LEN, CONTEXT = SHAPES[args.shape]
     global PREFILL_TOKENS
+    if args.batch:
+        BATCH = args.batch
     if args.prompt_len:
         PROMPT_LEN = args.prompt_len
     if args.context:
         CONTEXT = args.context
     if args.prefill_tokens:
         PREFILL_TOKENS = args.prefill_tokens
-    CONTEXT = -(-max(CONTEXT, PROMPT_LEN + args.steps + 64, PREFILL_TOKENS) // 64) * 64
+    # turns in which the engine still reads prompts: a request that is done with its prompt decodes beside
+    # the others' portions, so every request gets this many new tokens more than the turns that are timed
+    prompt_turns = -(-BATCH * PROMPT_LEN // 2048)
+    CONTEXT = -(-max(CONTEXT, PROMPT_LEN + args.steps + 64 + prompt_turns, PREFILL_TOKENS) // 64) * 64
     if args.shape == "llama32_3b" and not args.decode_only:
         print(json.dumps(run_mixed_workload(shape_name, shape, args, warmup)))
         return 0
@@ -421,12 +427,12 @@ def main() -> int:
                            max_batch_tokens=2048)
     g = torch.Generator().manual_seed(2)
     prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(BATCH)]
-    eng.generate(prompts, max_tokens=warmup + 2, temperature=0.0, stop=[])      # warm-up: kernels loaded, graph captured
+    eng.generate(prompts, max_tokens=warmup + 2 + prompt_turns, temperature=0.0, stop=[])      # warm-up: kernels loaded, graph captured
     # measured twice, the better run kept: the host shares its machine with other jobs, and a
     # single stalled turn (hundreds of milliseconds) otherwise decides the figure
     e2e = None
     for _ in range(2):
-        eng.generate(prompts, max_tokens=min(args.steps, 64) + 1, temperature=0.0, stop=[])
+        eng.generate(prompts, max_tokens=min(args.steps, 64) + 1 + prompt_turns, temperature=0.0, stop=[])
         r = eng.decode_rate(skip=1, rows=BATCH)      # the turns in which all requests decode
         if r["steps"] == 0:
             r = eng.decode_rate(skip=0)              # too few steps asked for: every decode turn
