@@ -36,8 +36,19 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index = None
+
+
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream's handle.  (Asked of torch's C layer directly: a launcher is called
+    hundreds of times a step, and ``torch.cuda.current_stream()`` builds a Python object each time.)"""
+    global _device_index
+    if _raw_stream is None:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return c_void_p(_raw_stream(_device_index))
 
 
 def _need(t: torch.Tensor, what: str, dtype=None, ndim=None) -> None:
@@ -119,9 +130,12 @@ _wrapped = {}
 
 
 def _fn(lib_name: str, fn_name: str, argtypes):
+    key = (lib_name, fn_name)
+    got = _wrapped.get(key)
+    if got is not None:
+        return got
     lib = csrc.load(lib_name)
     fn = getattr(lib, fn_name)
-    key = (lib_name, fn_name)
     if key not in _prototyped:
         fn.argtypes = argtypes
         fn.restype = c_int
@@ -507,7 +521,19 @@ def tcgen05_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+_splits_memo = {}
+
+
 def tcgen05_splits(M: int, N: int, K: int) -> int:
+    """K ranges of a product (remembered per shape: a step asks for the same few shapes again and again)."""
+    key = (M, N, K)
+    got = _splits_memo.get(key)
+    if got is None:
+        got = _splits_memo[key] = _tcgen05_splits(M, N, K)
+    return got
+
+
+def _tcgen05_splits(M: int, N: int, K: int) -> int:
     """K ranges for a product with few tokens: enough CTAs to cover the SMs about twice (once
     from 65 tokens on: every range writes and the next kernel reads M x N float32 partial sums,
     which with many tokens is no longer small beside the weights; at 64 tokens nine ranges of
