@@ -37,18 +37,16 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
-_device_index = None
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream() -> c_void_p:
-    """The current stream's handle.  (Asked of torch's C layer directly: a launcher is called
-    hundreds of times a step, and ``torch.cuda.current_stream()`` builds a Python object each time.)"""
-    global _device_index
-    if _raw_stream is None:
+    """The current stream's handle on the current device.  (Asked of torch's C layer directly: a
+    launcher is called hundreds of times a step, and ``torch.cuda.current_stream()`` builds a
+    Python object each time.)"""
+    if _raw_stream is None or _raw_device is None:
         return c_void_p(torch.cuda.current_stream().cuda_stream)
-    if _device_index is None:
-        _device_index = torch.cuda.current_device()
-    return c_void_p(_raw_stream(_device_index))
+    return c_void_p(_raw_stream(_raw_device()))
 
 
 def _need(t: torch.Tensor, what: str, dtype=None, ndim=None) -> None:
