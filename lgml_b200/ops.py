@@ -659,13 +659,21 @@ def sm_count() -> int:
 
 
 def decode_splits(n_tokens: int, n_kv_heads: int, group: int, max_kv_len: int, page: int = 64) -> int:
-    """How many ranges the keys of a token are cut into, so that the grid fills the SMs about
-    twice over, with at least four pages a range: a range costs its CTA's start and its share
-    of the merge whatever its length (one request at 2,176 tokens: 15.7 us with a range per
-    page, 10.0 us with 12 ranges)."""
-    ctas = n_tokens * n_kv_heads * ((group + 7) // 8)
+    """How many ranges the keys of a token are cut into.  A range costs its CTA's start and its
+    share of the merge whatever its length, so: at least four pages a range; as many CTAs as fill
+    the SMs twice over, or once over while there are few of them to begin with and the context is
+    short (one or two requests up to 4,096 tokens: the step waits for the slowest CTA, not for
+    bandwidth); and no more than 16 ranges, or a 16th of the pages where that is more (the merge
+    reads every range of a head).  Measured with `kernel_bench decode_attention`, 32 heads on 8 KV
+    heads of 128, merge included: one request at 2,176 tokens 10.2 us with 9 ranges, 8.6 with 16,
+    9.6 with 18; at 8,192 tokens 13.8 us with 16, 15.7 with 37; at 32,768 tokens 38.3 us with 16,
+    31.7 with 37; two requests at 2,176 tokens 9.7 us with 9, 11.1 with 16, at 8,192 tokens 18.6 us
+    with 16, 21.1 with 9 or 18; eight requests 18.4 us
+    with 4 ranges, 21.8 with 3, 23.4 with 5."""
+    ctas = max(n_tokens * n_kv_heads * ((group + 7) // 8), 1)
     pages = max(1, -(-max_kv_len // page))
-    return max(1, min(-(-pages // 4), (2 * sm_count()) // max(ctas, 1), 512))
+    per_sm = 1 if ctas <= 16 and pages <= 64 else 2
+    return max(1, min(-(-pages // 4), (per_sm * sm_count()) // ctas, max(16, pages // 16), 512))
 
 
 def decode_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
