@@ -32,21 +32,22 @@ def dtype_code(dt: torch.dtype) -> int:
         raise KernelError(f"kernels take float32 or bfloat16, not {dt}") from None
 
 
-def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
-    return c_void_p(0 if t is None else t.data_ptr())
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    """The address for a ``c_void_p`` parameter (ctypes takes the integer as it is; None is NULL)."""
+    return 0 if t is None else t.data_ptr()
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
-def _stream() -> c_void_p:
+def _stream() -> int:
     """The current stream's handle on the current device.  (Asked of torch's C layer directly: a
     launcher is called hundreds of times a step, and ``torch.cuda.current_stream()`` builds a
     Python object each time.)"""
     if _raw_stream is None or _raw_device is None:
-        return c_void_p(torch.cuda.current_stream().cuda_stream)
-    return c_void_p(_raw_stream(_raw_device()))
+        return torch.cuda.current_stream().cuda_stream
+    return _raw_stream(_raw_device())
 
 
 def _need(t: torch.Tensor, what: str, dtype=None, ndim=None) -> None:
