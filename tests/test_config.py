@@ -124,6 +124,24 @@ def test_k_ranges_of_a_small_product_are_never_empty():
                     assert s == 1
 
 
+def test_key_ranges_of_the_decode_attention_stay_within_their_bounds():
+    """The rule that cuts a token's keys into ranges: at least one range, never more than the
+    merge kernel takes, no range shorter than four pages, never more CTAs than fill the SMs twice
+    (once for one or two short requests), and one range from 37 requests on 8 KV heads up."""
+    from lgml_b200.ops import decode_splits, sm_count
+
+    for n in (1, 2, 3, 4, 8, 16, 37, 64, 256):
+        for kv, group in ((8, 4), (40, 1), (1, 12), (5, 9)):
+            for ctx in (1, 64, 65, 1024, 4096, 16384, 32768, 131072, 1 << 20):
+                s = decode_splits(n, kv, group, ctx)
+                pages = -(-ctx // 64)
+                ctas = n * kv * ((group + 7) // 8)
+                assert 1 <= s <= 512
+                assert s == 1 or -(-pages // s) >= 4 or s * 4 <= pages + 3, (n, kv, group, ctx, s)
+                assert s == 1 or s * ctas <= 2 * sm_count(), (n, kv, group, ctx, s)
+    assert decode_splits(37, 8, 4, 4096) == 1 and decode_splits(1, 8, 4, 4096) == 16 and decode_splits(2, 8, 4, 4096) == 9
+
+
 def test_end_tokens_of_generation_config_join_those_of_config(tmp_path):
     import json
 
