@@ -206,6 +206,41 @@ def test_gemm_tcgen05(M, N, K, bias, f32, splits):
     assert err <= scale * (5e-5 if f32 else 6e-3), (err, scale)
 
 
+def test_gemm_tcgen05_on_single_ctas_when_pairs_are_switched_off():
+    """``LGML_GEMM_PAIR=0`` (read once per process, so a process of its own): products of more
+    than 64 tokens on single CTAs, the weights as the tile's rows up to 256 tokens and persistent
+    128 x 256 tiles beyond."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    code = """
+import torch
+from lgml_b200 import ops
+st = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+for M, N, K, gated in [(100, 320, 96, False), (129, 520, 264, False), (256, 300, 200, True), (300, 648, 200, False), (700, 1200, 520, True)]:
+    torch.manual_seed(M)
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    if gated:
+        got = ops.gemm_bf16_swiglu(x.cuda(), w.cuda(), None, st).double().cpu()
+        y = x.double() @ w.double().t()
+        want = y[:, 0::2] * torch.sigmoid(y[:, 0::2]) * y[:, 1::2]
+    else:
+        out = torch.empty(M, N, dtype=torch.float32, device="cuda:0")
+        got = ops.gemm_tcgen05(x.cuda(), w.cuda(), out, None, st).double().cpu()
+        want = x.double() @ w.double().t()
+    assert float((got - want).abs().max()) <= 6e-3 * float(want.abs().max()), (M, N, K)
+assert int(st.item()) == 0
+assert ops.tcgen05_splits(300, 256, 640) == 1          # the pairs' K ranges are off too
+print("ok")
+"""
+    root = Path(__file__).resolve().parent.parent
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, env={**os.environ, "LGML_GEMM_PAIR": "0"}, timeout=300)
+    assert p.returncode == 0 and p.stdout.strip().endswith("ok"), p.stdout + p.stderr
+
+
 def test_gemm_tcgen05_gated_epilogue_and_partials():
     from lgml_b200 import ops
 
