@@ -327,17 +327,13 @@ def test_chains_with_top_k_run_on_the_device(folders, monkeypatch):
     assert got == alone
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_as_a_process(folders, dtype, tmp_path):
-    """bin/trace_run in a separate process: a mixed trace with page reuse, logits files and
-    'done' lines, compared with the plain implementation."""
-    folder = folders[("B", dtype)]
-    seqs = {f"r{i}": H.random_ids(n, 320, 300 + i) for i, n in enumerate([25, 101, 154, 64, 130])}
-    steps = H.trace_mixed(seqs, max_tokens=64 * 7, seed=5)
+def replay_in_a_process(folder, dtype, seqs, vocab, tmp_path, extra_env=None, pool_pages=7):
+    """bin/trace_run in a separate process on a mixed trace with page reuse: (request, position) -> logits row."""
+    steps = H.trace_mixed(seqs, max_tokens=64 * pool_pages, seed=5)
     out = tmp_path / "out"
-    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), **(extra_env or {}))
     proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
-                           "--max-tokens", str(64 * 7)], input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
+                           "--max-tokens", str(64 * pool_pages)], input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
                           capture_output=True, env=env, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
@@ -345,15 +341,40 @@ def test_trace_run_as_a_process(folders, dtype, tmp_path):
     got = {}
     for st in steps:
         n_want = sum(len(e["want"]) for e in st["entries"])
-        rows = np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(n_want, 320)
+        rows = np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(n_want, vocab)
         r = 0
         for e in st["entries"]:
             for i in e["want"]:
                 got[(e["id"], fed[e["id"]] + i)] = torch.from_numpy(rows[r].copy())
                 r += 1
             fed[e["id"]] += len(e["tokens"])
+    return got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_as_a_process(folders, dtype, tmp_path):
+    """bin/trace_run in a separate process: a mixed trace with page reuse, logits files and
+    'done' lines, compared with the plain implementation."""
+    folder = folders[("B", dtype)]
+    seqs = {f"r{i}": H.random_ids(n, 320, 300 + i) for i, n in enumerate([25, 101, 154, 64, 130])}
+    got = replay_in_a_process(folder, dtype, seqs, 320, tmp_path)
     tol = dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=1.5e-2, rtol=1.5e-2)
     H.compare_with_oracle(got, folder, seqs, **tol)
+
+
+@pytest.mark.parametrize("switch", ["LGML_PDL=0", "LGML_ATTN_EARLY=0", "LGML_PREFILL_ATTENTION=single", "LGML_PREFILL_ATTENTION=mma",
+                                    "LGML_ATTN_TMA=0", "LGML_GEMM_PAIR=0", "LGML_NORM_GROUPED=0", "LGML_L2_AHEAD=0"])
+def test_every_switch_still_gives_the_plain_implementations_logits(switch, tmp_path):
+    """Each environment switch selects the older of two implementations of one thing (read once
+    per process, so a process each): the same mixed trace in bfloat16 on a tiny model with head
+    size 64 (the two-tile prompt attention's size), against the plain implementation."""
+    cfg = dict(H.TINY_B, head_dim=64, num_attention_heads=4, num_key_value_heads=2, hidden_size=128, intermediate_size=320,
+               max_position_embeddings=256)
+    folder = H.make_folder(tmp_path / "model", cfg, 3, dtype="bfloat16", sharpen=4.0)
+    seqs = {f"r{i}": H.random_ids(n, 320, 700 + i) for i, n in enumerate([25, 101, 200, 64, 130])}
+    name, value = switch.split("=")
+    got = replay_in_a_process(folder, "bfloat16", seqs, 320, tmp_path, {name: value})
+    H.compare_with_oracle(got, folder, seqs, atol=1.5e-2, rtol=1.5e-2)
 
 
 def test_command_line(folders):
