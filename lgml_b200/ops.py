@@ -557,13 +557,16 @@ def _tcgen05_splits(M: int, N: int, K: int) -> int:
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor], status: torch.Tensor,
                  n_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None, swiglu: bool = False,
-                 partials_ok: bool = False):
+                 partials_ok: bool = False, checked: bool = False):
     """out[M,N] = x[M,K] . w[N,K]^T (+ bias) on tcgen05 tensor cores; bfloat16 in, float32
     accumulation, out bfloat16 or float32.  ``swiglu``: the rows of w (and bias) come in
     (gate, up) pairs and out[M, N/2] = silu(gate) * up.  ``partials_ok``: when K is cut, return
-    ``Partials`` (the float32 partial sums and the bias) instead of adding them up here."""
-    _need(x, "gemm input", torch.bfloat16, 2)
-    _need(w, "gemm weight", torch.bfloat16, 2)
+    ``Partials`` (the float32 partial sums and the bias) instead of adding them up here.
+    ``checked``: the caller (``gemm_bf16``) has checked x and w and chosen ``n_splits`` by
+    ``tcgen05_splits``."""
+    if not checked:
+        _need(x, "gemm input", torch.bfloat16, 2)
+        _need(w, "gemm weight", torch.bfloat16, 2)
     ldx, ldw = _rows_contiguous(x, "gemm input"), _rows_contiguous(w, "gemm weight")
     M, K = x.shape
     N = w.shape[0]
@@ -576,6 +579,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
             raise KernelError("gemm_tcgen05: bias length is not N")
     if n_splits is None:
         n_splits = 1 if swiglu else tcgen05_splits(M, N, K)
+    elif checked:
+        pass
     elif M > 64 and n_splits > 1 and tcgen05_splits(M, N, K) and os.environ.get("LGML_GEMM_PAIR") != "0":
         # on pairs of CTAs a K range is a whole number of 128-element stages, and none may be empty
         stages = -(-K // 128)
@@ -635,8 +640,11 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, bias: Op
         raise KernelError(f"unknown gemm backend '{backend}'")
     if status is None:
         raise KernelError("gemm_bf16: the tcgen05 kernel needs the status word")
+    n_splits = tcgen05_splits(x.shape[0], w.shape[0], x.shape[1])
+    if partials_ok and n_splits > 1:          # the partial sums are the result: no output to make
+        return gemm_tcgen05(x, w, None, bias, status, n_splits=n_splits, partials_ok=True, checked=True)
     out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
-    return gemm_tcgen05(x, w, out, bias, status, partials_ok=partials_ok)
+    return gemm_tcgen05(x, w, out, bias, status, n_splits=n_splits, checked=True)
 
 
 def gemm_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, bias_pairs: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:
