@@ -1,4 +1,4 @@
-"""Decode steps (one token per request) as replays of a captured CUDA graph.
+"""Decode steps (one token per request), and one request's short portions, as replays of a captured CUDA graph.
 
 A graph is captured per batch size.  Its kernels were recorded with fixed addresses, so the
 step's description lives in one device buffer per batch size, laid out as ``StepBatch`` lays
@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from .batch import CacheView
+from .batch import CacheView, StepBatch
 from .runtime import AHEAD_MAX_BATCH
 
 
@@ -184,3 +184,54 @@ class DecodeGraph:
                     gc.enable()
         self.graph.replay()
         return self.logits
+
+
+class PromptGraph:
+    """One captured step for a portion of one request: ``n_tokens`` tokens (a whole number of
+    pages) that start on a page's edge, ``n_rows`` wanted logits rows (0 or 1).
+
+    A short prompt's step is bound by the host (hundreds of launches for a few milliseconds of
+    GPU work), so it is replayed like a decode step.  A portion is padded to the next page's edge
+    with token 0: the padded tokens come after the real ones, no real token looks at them (they
+    lie in the future), and the cells they write in the portion's last page, which the request
+    holds anyway, are written again by the tokens that really come there before anything reads
+    them.  The step's description lives in one device buffer as ``StepBatch`` lays it out, with
+    block tables of a fixed width; a replay refreshes it with one copy from pinned memory."""
+
+    def __init__(self, runner, n_tokens: int, n_rows: int):
+        self.runner, self.n_tokens, self.n_rows = runner, n_tokens, n_rows
+        self.widths = list(runner._graph_widths)
+        total = StepBatch.buffer_ints(n_tokens, 1, n_rows, self.widths)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=runner.rt.device)
+        self.tiles = {}                 # the attention kernels' tile lists: they depend on the shape only
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.kernels = 0
+
+    def run(self, req, tokens: Sequence[int], want: Sequence[int], pinned: torch.Tensor) -> StepBatch:
+        """Launch the step; returns the batch (``.logits`` of this object holds the result)."""
+        pad = self.n_tokens - len(tokens)
+        batch = StepBatch(self.runner.cache, [req], [list(tokens) + [0] * pad], [list(want)], self.runner.rt.device, pinned,
+                          table_widths=self.widths, device_buffer=self.dev)
+        batch._tiles = self.tiles
+        batch.after_staged_copy = None
+        if self.graph is None:
+            import gc
+
+            rt = self.runner.rt
+            self.runner.model.forward(rt, batch)            # eagerly once: kernels loaded, tile lists made (no copy inside the capture)
+            gc.collect()
+            was_on = gc.isenabled()
+            gc.disable()
+            try:
+                g = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
+                with torch.cuda.graph(g, capture_error_mode="relaxed"):
+                    self.logits = self.runner.model.forward(rt, batch)
+                self.kernels = ops.launch_count() - before
+                self.graph = g
+            finally:
+                if was_on:
+                    gc.enable()
+        self.graph.replay()
+        return batch

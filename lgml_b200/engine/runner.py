@@ -23,6 +23,7 @@ from .runtime import Runtime
 
 
 MAX_GRAPH_BATCH = 256
+PROMPT_GRAPH_TOKENS = 256      # portions of one request up to this length are replayed from captured graphs
 # Batch sizes that decode steps are captured at.  A step of another size runs the next larger
 # graph with its last request repeated in the spare rows: those rows compute the same token at
 # the same position again (the same key and value into the same cell) and their logits are
@@ -55,6 +56,7 @@ class ModelRunner:
         # decode steps (one token per request) replay a CUDA graph captured per batch size
         self.use_graphs = use_graphs and getattr(model, "graph_safe", False)
         self._graphs = {}
+        self._prompt_graphs = {}
         self._graph_seen = set()
         max_pos = model.max_position or (n_pages * self.cache.page_size)
         self._graph_widths = [min(g.pool.n_pages, -(-max_pos // self.cache.page_size)) for g in self.cache.groups]
@@ -163,6 +165,8 @@ class ModelRunner:
         S = len(entries)
         if self._graphs_now() and all(len(e[1]) == 1 for e in entries) and S <= MAX_GRAPH_BATCH:
             logits = self._graph_step(entries, stage)
+        elif self._graphs_now() and self._prompt_graph_fits(entries):
+            logits = self._prompt_graph_step(entries[0], stage)
         else:
             batch = StepBatch(self.cache, [e[0] for e in entries], [e[1] for e in entries], [e[2] for e in entries],
                               self.rt.device, stage[0])
@@ -185,6 +189,38 @@ class ModelRunner:
         """Launches of this package's kernels that one replay of the graph for ``batch_size`` requests holds."""
         size = graph_size(batch_size)
         return max((g.kernels for (s, _), g in self._graphs.items() if s == size), default=0)
+
+    def _prompt_graph_fits(self, entries) -> bool:
+        """A short portion of one request that starts on a page's edge and wants no logits or
+        those of its last token: such a step is replayed from a captured graph (a prompt of a few
+        dozen tokens is bound by the host otherwise).  Models with windows or per-request state
+        are left out: a padded token would move their window or their state."""
+        if len(entries) != 1:
+            return False
+        req, tokens, want = entries[0]
+        n, page = len(tokens), self.cache.page_size
+        if not 2 <= n <= PROMPT_GRAPH_TOKENS or req.n_tokens % page or list(want) not in ([], [n - 1]):
+            return False
+        if self.cache.state_groups or any(g.spec.window is not None for g in self.cache.groups):
+            return False
+        padded = -(-n // page) * page
+        limit = self.model.max_position or (self.cache.n_pages * page)
+        return req.n_tokens + padded <= min(limit, self._graph_widths[0] * page if self._graph_widths else limit)
+
+    def _prompt_graph_step(self, entry, stage) -> torch.Tensor:
+        from .graph import PromptGraph
+
+        req, tokens, want = entry
+        page = self.cache.page_size
+        key = (-(-len(tokens) // page) * page, len(want))
+        g = self._prompt_graphs.get(key)
+        if g is None:
+            g = self._prompt_graphs[key] = PromptGraph(self, key[0], key[1])
+        else:
+            self.graph_replays += 1
+        self.last_batch = g.run(req, tokens, want, stage[0])
+        self._mark_busy(stage)
+        return g.logits
 
     def _graph_step(self, entries, stage, device_tokens=None) -> torch.Tensor:
         """A decode step through a captured graph.  The first step of a kind (batch size, reach of

@@ -157,3 +157,47 @@ def test_five_thousand_tokens_of_context(dtype, tmp_path):
             bound = TOL[dtype]["atol"] + TOL[dtype]["rtol"] * ref[pos].abs()
             assert bool((err <= bound).all()), (rid, pos, float(err.max()))
     runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_portions_replayed_from_captured_steps(tiny, dtype):
+    """A short portion of one request that starts on a page's edge is padded to the next edge and
+    replayed from a captured graph: prompts of 70, 3 and 64 tokens, each decoded on through the
+    cells that the padding wrote, a second portion of 130 tokens behind a first of 64, and the same
+    shapes again on pages that were used before (replays, not captures).  Against the plain
+    implementation, and in 32-bit bit for bit against a runner without graphs."""
+    which, cfg, folders = tiny
+    folder, V = folders[dtype], cfg["vocab_size"]
+    n_max = min(cfg["max_position_embeddings"], 250)
+    seqs = {"a": H.random_ids(min(70 + 50, n_max), V, 11), "b": H.random_ids(3 + 40, V, 12), "c": H.random_ids(min(64 + 130 + 6, n_max), V, 13),
+            "d": H.random_ids(min(70 + 50, n_max), V, 14), "e": H.random_ids(64 + 20, V, 15)}
+    first = {"a": 70, "b": 3, "c": 64, "d": 70, "e": 64}
+    steps = []
+    for rid, ids in seqs.items():
+        p = first[rid]
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[:p], "want": [p - 1]}], "end": []})
+        if rid == "c":
+            q = min(130, len(ids) - p - 2)
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[p:p + q], "want": []}], "end": []})
+            p += q
+        while p < len(ids):
+            steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": [ids[p]], "want": [0]}], "end": [rid] if p == len(ids) - 1 else []})
+            p += 1
+    runner = make_runner(folder, dtype, n_pages=5)
+    got = H.run_trace(runner, steps)
+    assert runner._prompt_graphs and runner.graph_replays > 0
+    assert sorted(runner._prompt_graphs) == sorted({(-(-n // 64) * 64, 1) for n in (70, 3, 64)} | {(-(-min(130, len(seqs["c"]) - 66) // 64) * 64, 0)})
+    for rid, ids in seqs.items():
+        ref = H.oracle_logits(folder, ids)
+        for (r, pos), row in got.items():
+            if r == rid:
+                err = (row.double() - ref[pos]).abs()
+                assert bool((err <= TOL[dtype]["atol"] + TOL[dtype]["rtol"] * ref[pos].abs()).all()), (rid, pos, float(err.max()))
+    if dtype == "float32":
+        from lgml_b200.engine.engine import parse_dtype
+        from lgml_b200.engine.runner import ModelRunner
+
+        plain = ModelRunner.from_folder(folder, parse_dtype(dtype), "cuda:0", n_pages=5, max_slots=4, use_graphs=False)
+        want = H.run_trace(plain, steps)
+        assert not plain._prompt_graphs
+        assert all(torch.equal(got[k], want[k]) for k in want)
