@@ -187,12 +187,12 @@ class DecodeGraph:
 
 
 class PromptGraph:
-    """One captured step for a portion of one request: ``n_tokens`` tokens (a whole number of
-    pages) that start on a page's edge, ``n_rows`` wanted logits rows (0 or 1).
+    """One captured step for a portion of one request: ``n_tokens`` tokens (16, 32 or a whole
+    number of pages) that start on a page's edge, ``n_rows`` wanted logits rows (0 or 1).
 
     A short prompt's step is bound by the host (hundreds of launches for a few milliseconds of
-    GPU work), so it is replayed like a decode step.  A portion is padded to the next page's edge
-    with token 0: the padded tokens come after the real ones, no real token looks at them (they
+    GPU work), so it is replayed like a decode step.  A portion is padded with token 0 to that
+    length: the padded tokens come after the real ones, no real token looks at them (they
     lie in the future), and the cells they write in the portion's last page, which the request
     holds anyway, are written again by the tokens that really come there before anything reads
     them.  The step's description lives in one device buffer as ``StepBatch`` lays it out, with

@@ -38,6 +38,15 @@ def graph_size(n: int) -> int:
     return n
 
 
+def prompt_graph_length(n: int, page: int) -> int:
+    """The number of tokens a short portion of n tokens is padded to for its captured step: 16 or
+    32 inside the first page (the products' narrower tiles), else the next page's edge."""
+    for small in (16, 32):
+        if n <= small < page:
+            return small
+    return -(-n // page) * page
+
+
 class StepError(ValueError):
     """A step the runner refuses before anything is launched."""
 
@@ -203,7 +212,7 @@ class ModelRunner:
             return False
         if self.cache.state_groups or any(g.spec.window is not None for g in self.cache.groups):
             return False
-        padded = -(-n // page) * page
+        padded = prompt_graph_length(n, page)
         limit = self.model.max_position or (self.cache.n_pages * page)
         return req.n_tokens + padded <= min(limit, self._graph_widths[0] * page if self._graph_widths else limit)
 
@@ -212,7 +221,7 @@ class ModelRunner:
 
         req, tokens, want = entry
         page = self.cache.page_size
-        key = (-(-len(tokens) // page) * page, len(want))
+        key = (prompt_graph_length(len(tokens), page), len(want))
         g = self._prompt_graphs.get(key)
         if g is None:
             g = self._prompt_graphs[key] = PromptGraph(self, key[0], key[1])

@@ -186,7 +186,10 @@ def test_short_portions_replayed_from_captured_steps(tiny, dtype):
     runner = make_runner(folder, dtype, n_pages=5)
     got = H.run_trace(runner, steps)
     assert runner._prompt_graphs and runner.graph_replays > 0
-    assert sorted(runner._prompt_graphs) == sorted({(-(-n // 64) * 64, 1) for n in (70, 3, 64)} | {(-(-min(130, len(seqs["c"]) - 66) // 64) * 64, 0)})
+    from lgml_b200.engine.runner import prompt_graph_length as padded
+
+    assert sorted(runner._prompt_graphs) == sorted({(padded(n, 64), 1) for n in (70, 3, 64)} | {(padded(min(130, len(seqs["c"]) - 66), 64), 0)})
+    assert [padded(n, 64) for n in (2, 16, 17, 32, 33, 64, 65, 128, 129)] == [16, 16, 32, 32, 64, 64, 128, 128, 192]
     for rid, ids in seqs.items():
         ref = H.oracle_logits(folder, ids)
         for (r, pos), row in got.items():
