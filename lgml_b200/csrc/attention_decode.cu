@@ -267,19 +267,26 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(
     }
 }
 
-// Merge the splits of one (token, head) in split order.  The splits' maxima and sums are fetched
-// by as many threads at once and shared; a thread then adds up its dimension, the loads of eight
-// splits' partial outputs issued before the first is used (one after the other, every load would
-// cost a round trip to L2: at batch 1 there are twelve splits).
+// Merge the splits of one (token, head) in split order.  A thread adds up one dimension.  The
+// loads of its first sixteen splits' partial outputs go out together with those of the splits'
+// maxima and sums, before anything is computed (one after the other, every load would cost a round
+// trip to L2: at batch 1 there are sixteen splits), and a split's factor exp(m - max) is computed
+// once, by one thread, not by every thread for every split.
 constexpr int MAX_SPLITS = 512;
+constexpr int COMBINE_FIRST = 16;
 __global__ void decode_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                                       __nv_bfloat16 *__restrict__ out, int ldo, int n_splits, int H, int D) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float m_s[MAX_SPLITS], w_s[MAX_SPLITS];
-    const int t = blockIdx.x, h = blockIdx.y;
+    __shared__ float m_s[MAX_SPLITS], w_s[MAX_SPLITS], f_s[MAX_SPLITS];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const float2 *ml = part_ml + ((size_t)t * H + h) * n_splits;
-    for (int i = threadIdx.x; i < n_splits; i += blockDim.x) {
+    const float *po = part_o + ((size_t)t * H + h) * n_splits * D;
+    float first[COMBINE_FIRST];
+#pragma unroll
+    for (int u = 0; u < COMBINE_FIRST; ++u)
+        if (u < n_splits && tid < D) first[u] = act_load(po + (size_t)u * D + tid);
+    for (int i = tid; i < n_splits; i += blockDim.x) {
         const float2 v = act_load(ml + i);
         m_s[i] = v.x;
         w_s[i] = v.y;
@@ -287,19 +294,27 @@ __global__ void decode_combine_kernel(const float *__restrict__ part_o, const fl
     __syncthreads();
     float mm = -INFINITY;
     for (int i = 0; i < n_splits; ++i) mm = fmaxf(mm, m_s[i]);
+    for (int i = tid; i < n_splits; i += blockDim.x) f_s[i] = m_s[i] == -INFINITY ? 0.f : expf(m_s[i] - mm);
+    __syncthreads();
     float l = 0.f;
-    for (int i = 0; i < n_splits; ++i) l += m_s[i] == -INFINITY ? 0.f : w_s[i] * expf(m_s[i] - mm);
-    const float *po = part_o + ((size_t)t * H + h) * n_splits * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    for (int i = 0; i < n_splits; ++i) l += m_s[i] == -INFINITY ? 0.f : w_s[i] * f_s[i];
+    for (int d = tid; d < D; d += blockDim.x) {
         float o = 0.f;
-        for (int i0 = 0; i0 < n_splits; i0 += 8) {
+        int i0 = 0;
+        if (d == tid) {
+#pragma unroll
+            for (int u = 0; u < COMBINE_FIRST; ++u)
+                if (u < n_splits && m_s[u] != -INFINITY) o += first[u] * f_s[u];
+            i0 = COMBINE_FIRST;
+        }
+        for (; i0 < n_splits; i0 += 8) {
             float pv[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u)
                 if (i0 + u < n_splits) pv[u] = act_load(po + (size_t)(i0 + u) * D + d);
 #pragma unroll
             for (int u = 0; u < 8; ++u)
-                if (i0 + u < n_splits && m_s[i0 + u] != -INFINITY) o += pv[u] * expf(m_s[i0 + u] - mm);
+                if (i0 + u < n_splits && m_s[i0 + u] != -INFINITY) o += pv[u] * f_s[i0 + u];
         }
         out[(size_t)t * ldo + (size_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
     }
