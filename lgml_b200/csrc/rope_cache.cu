@@ -68,7 +68,18 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
     }
     const size_t col = (size_t)head * D;
     const TS *row = src + (size_t)t * lds + col;
+    // Every load goes out before anything waits for one: the elements and their other parts, the
+    // bias, the frequency, and the chain position -> block -> page for the cell of the cache (two
+    // trips to L2 one after the other, which used to begin only when the rotation was done).
     float a = to_f32(act_load(row + d0)), b = to_f32(act_load(row + d1));
+    const float bias0 = bias ? bias[col + d0] : 0.f, bias1 = bias ? bias[col + d1] : 0.f;
+    const float f = fi >= 0 ? inv_freq[fi] : 0.f, f_lo = (fi >= 0 && inv_freq_lo) ? inv_freq_lo[fi] : 0.f;
+    int page = -1;      // where this token's k and v go
+    if (head >= H) {
+        const int seq = seq_of_token[t];
+        const int blk = pos / page_size;
+        if (pos >= 0 && blk < max_blocks) page = block_table[(size_t)seq * max_blocks + blk];
+    }
     // the other parts in order; the loads of up to eight of them are issued before the first is used
     // (one after the other they would cost a round trip to L2 each)
     for (int p0 = 1; p0 < n_parts; p0 += 8) {
@@ -86,13 +97,11 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
                 b += eb[u];
             }
     }
-    if (bias) {
-        a += bias[col + d0];
-        b += bias[col + d1];
-    }
+    a += bias0;
+    b += bias1;
     if (fi >= 0) {
         float s, c;
-        rope_sincos(pos, inv_freq[fi], inv_freq_lo ? inv_freq_lo[fi] : 0.f, &s, &c);
+        rope_sincos(pos, f, f_lo, &s, &c);
         const float r0 = a * c - b * s, r1 = a * s + b * c;
         a = r0;
         b = r1;
@@ -103,11 +112,6 @@ __global__ void __launch_bounds__(ITEMS) rope_kv_write_kernel(
         dst[d1] = from_f32<T>(b);
         return;
     }
-    // where this token's k and v go
-    const int seq = seq_of_token[t];
-    const int blk = pos / page_size;
-    int page = -1;
-    if (pos >= 0 && blk < max_blocks) page = block_table[(size_t)seq * max_blocks + blk];
     if (page < 0 || page >= n_pages) {   // the host reserves pages first; never write outside the pool
         if (j == 0) atomicExch(status, 2);
         return;
